@@ -1,0 +1,191 @@
+/*
+ * mldfc - C ABI of the B200-native quantized FullyConnected path.
+ *
+ * ML Drift has no FFI of its own: the seam it offers is a C++ class hierarchy
+ * (GPUOperation / GpuModelBuilder).  This header is the boundary a binding for
+ * that seam calls into; every entry point names the ml-drift interface it
+ * stands in for (paths relative to ml_drift/).  All pointers are plain device
+ * or host pointers, all sizes plain integers; no C++ or torch types appear.
+ *
+ * Conventions
+ *  - every function returns an mld_status (0 = OK); nothing throws or aborts;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = default stream); work
+ *    is enqueued on it and the call returns without synchronising unless the
+ *    function says otherwise;
+ *  - the caller owns every buffer it passes; a plan owns only its workspace;
+ *  - device layouts are the reference's BUFFER layouts:
+ *      activations BHWC(1,1,M,C)  -> [ceil(C/4)][M][4]      (tensor_desc.cc:1852-1860)
+ *      weights kOSpatialIOGroupI4O4 -> [I/4][O/4][4 i][4 o], INT8 bytes hold
+ *        q+128, INT4 nibbles hold q+8 with element 2j in the low nibble
+ *        (weights_conversion.cc:46-87, 1495-1523)
+ *      scales / zero points: per-channel [O4]; block-wise [G][O4]
+ *        (tensor_desc.cc:266-311, 2245-2257), in the activation type.
+ */
+#ifndef MLDFC_H_
+#define MLDFC_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define MLD_API __attribute__((visibility("default")))
+#else
+#define MLD_API
+#endif
+
+typedef enum mld_status {
+  MLD_OK = 0,
+  MLD_INVALID_ARGUMENT = 1, /* absl::InvalidArgumentError in the reference */
+  MLD_UNIMPLEMENTED = 2,    /* absl::UnimplementedError */
+  MLD_CUDA_ERROR = 3,
+  MLD_NCCL_ERROR = 4,
+  MLD_TIMEOUT = 5,          /* a bounded device-side wait gave up */
+  MLD_OUT_OF_RANGE = 6      /* size beyond a fixed capacity */
+} mld_status;
+
+/* common/precision.h:25-36 (CalculationsPrecision). */
+typedef enum mld_precision {
+  MLD_PRECISION_F32 = 0,    /* fp32 tensors, fp32 math */
+  MLD_PRECISION_F16 = 1,    /* fp16 tensors, fp16-level math */
+  MLD_PRECISION_F32F16 = 2  /* fp16 tensors, fp32 accumulation */
+} mld_precision;
+
+/* fc::IsScalarQuantized / IsLinearQuantized / IsBlockQuantized
+ * (common/kernels/fully_connected_util.cc:499-513). */
+typedef enum mld_scale_mode {
+  MLD_SCALE_SCALAR = 0,
+  MLD_SCALE_PER_CHANNEL = 1,
+  MLD_SCALE_BLOCK = 2
+} mld_scale_mode;
+
+typedef enum mld_act_layout {
+  MLD_LAYOUT_SLICED = 0,    /* [ceil(C/4)][M][4], the reference buffer layout */
+  MLD_LAYOUT_ROW_MAJOR = 1  /* [M][C] */
+} mld_act_layout;
+
+typedef enum mld_weight_source {
+  MLD_SRC_INT8 = 0,         /* OHWI, one signed value per byte */
+  MLD_SRC_UINT4_PACKED = 1  /* OHWI (IHWO with swap_dims), two's-complement
+                               nibbles, element 2j in the low nibble */
+} mld_weight_source;
+
+MLD_API const char* mld_status_string(int status);
+/* Text of the last CUDA error seen by this thread ("" if none). */
+MLD_API const char* mld_last_error(void);
+/* Number of kernels this library has launched in the calling process. */
+MLD_API int64_t mld_kernel_launch_count(void);
+
+/* ------------------------------------------------------------------------ */
+/* Weight conversion                                                         */
+/* ------------------------------------------------------------------------ */
+
+/* WeightsDescription + source shape for the one layout the buffer FC path
+ * uses (common/task/weights_layout.h:27-93; GetFullyConnectedInt{8,4}
+ * WeightsDesc, common/kernels/fully_connected.cc:1218-1246). */
+typedef struct mld_pack_desc {
+  int32_t o, h, w, i;        /* OHWI source shape */
+  int32_t bits;              /* 8 -> kUint8, 4 -> kUint4 destination */
+  int32_t out_group_size;    /* 0 = ceil(o/4) (the FC choice) */
+  int32_t source;            /* mld_weight_source */
+  int32_t swap_dims;         /* packed source only: source is IHWO */
+  uint32_t pad_value;        /* 128 for INT8, 8 for INT4 */
+} mld_pack_desc;
+
+/* GetTotalElementsCountForLayout (common/task/weights_conversion.cc:1015-1027)
+ * times bits/8: bytes of the packed destination. */
+MLD_API size_t mld_packed_size_bytes(const mld_pack_desc* d);
+
+/* GetTensorDescriptorForWeightsLayout(int8) -> RearrangeWeightsInt8AsUint8 /
+ * AsUint4 (weights_conversion.cc:1672-1713, 1495-1523) for MLD_SRC_INT8, and
+ * RearrangeWeightsUInt4Packed (weights_conversion.cc:1604-1620, 631-708) for
+ * MLD_SRC_UINT4_PACKED, run as a CUDA kernel like the reference's own
+ * ConverterToConvWeights (common/kernels/conv_weights_converter.cc:1114-1400).
+ * src/dst are device pointers.  sum_i (device, may be NULL) receives
+ * sum_i[o] = sum of the signed weights of output o; it has sum_len >= o
+ * entries, of which the first o are cleared first and padded entries receive
+ * the (pad_value - 8) terms exactly as the reference does. */
+MLD_API int mld_pack_weights(const mld_pack_desc* d, const void* src,
+                             void* dst, int32_t* sum_i, int32_t sum_len,
+                             void* stream);
+
+/* GetWeightsAccumulatedInputChannels (weights_conversion.cc:1584-1602) from an
+ * int8 OHWI source. */
+MLD_API int mld_weights_sum_i(const int8_t* src, int32_t o, int32_t hwi,
+                              int32_t* sum_i, void* stream);
+
+/* ScaleOrZeroPointToTensorDesc (common/task/tensor_desc.cc:2245-2257):
+ * src [o][g] fp32 -> [g][o4], fp16 (IEEE RNE) when dst_f16, zero padded. */
+MLD_API int mld_pack_scales(const float* src, int32_t o, int32_t g,
+                            int32_t dst_f16, void* dst, void* stream);
+
+/* quantize_tensor_int8_sym / quantize_tensor_int4_sym with
+ * optimize_scale=False (samples/llm/extract_weights_hf.py:137-229):
+ * w [o][i] fp32 -> q [o][i] int8 and scale [o][g] fp32; bits 8 is
+ * per-channel (block ignored), bits 4 uses blocks of `block` input channels
+ * (0 = per-channel). */
+MLD_API int mld_quantize_weights(const float* w, int32_t o, int32_t i,
+                                 int32_t bits, int32_t block, int8_t* q,
+                                 float* scale, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* FullyConnected operator                                                   */
+/* ------------------------------------------------------------------------ */
+
+/* What CreateFullyConnectedExternalWeights receives
+ * (common/kernels/fully_connected.h:155-161; ExternalWeights,
+ * common/task/gpu_operation.h:354-363). */
+typedef struct mld_fc_desc {
+  int32_t n;                 /* weights.shape.o */
+  int32_t k;                 /* weights.shape.i */
+  int32_t weight_bits;       /* 4 or 8 */
+  int32_t scale_mode;        /* mld_scale_mode */
+  int32_t groups;            /* scale_zp_shape.i (1 unless block-wise) */
+  float scalar_scale;        /* ExternalWeights::scalar_scale */
+  float scalar_zero_point;   /* ExternalWeights::scalar_zero_point */
+  int32_t has_zero_point;
+  int32_t has_bias;
+  int32_t precision;         /* mld_precision */
+  int32_t src_layout;        /* mld_act_layout */
+  int32_t dst_layout;        /* mld_act_layout */
+  int32_t max_tokens;        /* largest M passed to mld_fc_run */
+  int32_t force_path;        /* 0 = IsFullyConnectedRecommended rule,
+                                1 = decode GEMV kernel, 2 = prefill GEMM */
+  int32_t device;            /* CUDA device ordinal, -1 = current */
+} mld_fc_desc;
+
+typedef struct mld_fc_plan mld_fc_plan;
+
+/* IsFullyConnectedRecommended (common/kernels/fully_connected.cc:981-1011) for
+ * a desktop GPU: 1 when `tokens` <= 16 (F16) or <= 8 (F32, F32F16). */
+MLD_API int mld_fc_is_gemv_recommended(int32_t precision, int32_t tokens);
+
+/* Builds the operator (FullyConnected constructor,
+ * common/kernels/fully_connected.cc:351-409): validates the description,
+ * picks kernels and allocates the plan's workspace.  Synchronous. */
+MLD_API int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out);
+MLD_API int mld_fc_plan_destroy(mld_fc_plan* plan);
+/* Bytes of device workspace the plan holds. */
+MLD_API size_t mld_fc_plan_workspace_bytes(const mld_fc_plan* plan);
+
+/* Dispatch of one FullyConnected node (ClOperation::AddToQueue,
+ * cl/cl_operation.cc:85-89) with the argument order of
+ * fc::AddWeightsArguments (fully_connected_util.cc:423-487):
+ * src, weights, scale, [zero_point], [bias] -> dst.  All device pointers in
+ * the layouts named at the top of this file; `tokens` = B*H*W of src.
+ * Small token counts run the decode dequant-GEMV
+ * (GetFullyConnectedKernelCode, fully_connected.cc:623-942); larger ones the
+ * prefill dequant-GEMM the reference builds from WeightsConverter + ConvGeneric
+ * (common/gpu_model_builder.cc:1110-1276). */
+MLD_API int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights,
+                       const void* scale, const void* zero_point,
+                       const void* bias, void* dst, int32_t tokens,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLDFC_H_ */

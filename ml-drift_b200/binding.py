@@ -1,0 +1,174 @@
+"""ctypes binding of libmldfc.so.  torch is used only for device memory and
+streams; every computation goes through the C ABI."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmldfc.so")
+
+OK, INVALID_ARGUMENT, UNIMPLEMENTED, CUDA_ERROR, NCCL_ERROR, TIMEOUT, OUT_OF_RANGE = range(7)
+F32, F16, F32F16 = 0, 1, 2
+SCALE_SCALAR, SCALE_PER_CHANNEL, SCALE_BLOCK = 0, 1, 2
+LAYOUT_SLICED, LAYOUT_ROW_MAJOR = 0, 1
+SRC_INT8, SRC_UINT4_PACKED = 0, 1
+PATH_AUTO, PATH_GEMV, PATH_GEMM = 0, 1, 2
+
+
+class MldError(RuntimeError):
+    def __init__(self, status, where):
+        self.status = status
+        msg = lib().mld_last_error().decode()
+        super().__init__(f"{where}: {lib().mld_status_string(status).decode()} ({msg})")
+
+
+class PackDesc(C.Structure):
+    _fields_ = [("o", C.c_int32), ("h", C.c_int32), ("w", C.c_int32), ("i", C.c_int32),
+                ("bits", C.c_int32), ("out_group_size", C.c_int32), ("source", C.c_int32),
+                ("swap_dims", C.c_int32), ("pad_value", C.c_uint32)]
+
+
+class FcDesc(C.Structure):
+    _fields_ = [("n", C.c_int32), ("k", C.c_int32), ("weight_bits", C.c_int32),
+                ("scale_mode", C.c_int32), ("groups", C.c_int32), ("scalar_scale", C.c_float),
+                ("scalar_zero_point", C.c_float), ("has_zero_point", C.c_int32),
+                ("has_bias", C.c_int32), ("precision", C.c_int32), ("src_layout", C.c_int32),
+                ("dst_layout", C.c_int32), ("max_tokens", C.c_int32), ("force_path", C.c_int32),
+                ("device", C.c_int32)]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads the CUDA library; there is no fallback when it is absent."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python ml-drift_b200/build.py`")
+        L = C.CDLL(LIB_PATH)
+        L.mld_status_string.restype = C.c_char_p
+        L.mld_last_error.restype = C.c_char_p
+        L.mld_kernel_launch_count.restype = C.c_int64
+        L.mld_packed_size_bytes.restype = C.c_size_t
+        L.mld_fc_plan_workspace_bytes.restype = C.c_size_t
+        _lib = L
+    return _lib
+
+
+def _check(rc, where):
+    if rc != OK:
+        raise MldError(rc, where)
+
+
+def _ptr(t):
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(stream=None):
+    s = torch.cuda.current_stream() if stream is None else stream
+    return C.c_void_p(s.cuda_stream)
+
+
+def kernel_launch_count() -> int:
+    return int(lib().mld_kernel_launch_count())
+
+
+def div_up(a, b):
+    return (a + b - 1) // b
+
+
+# ------------------------------------------------------------ weight conversion
+def packed_size_bytes(o, i, bits, h=1, w=1, group=0) -> int:
+    d = PackDesc(o, h, w, i, bits, group, SRC_INT8, 0, 128 if bits == 8 else 8)
+    return int(lib().mld_packed_size_bytes(C.byref(d)))
+
+
+def pack_weights(src: torch.Tensor, shape, bits, source=SRC_INT8, group=0, swap_dims=False,
+                 pad_value=None, want_sum=False, sum_len=None, sum_init=None, stream=None):
+    """src: device int8 OHWI tensor (SRC_INT8) or dense nibble bytes (SRC_UINT4_PACKED).
+    Returns (packed uint8 tensor, sum_i int32 tensor or None)."""
+    o, h, w, i = shape
+    if pad_value is None:
+        pad_value = 128 if bits == 8 else 8
+    d = PackDesc(o, h, w, i, bits, group, source, int(swap_dims), pad_value)
+    nbytes = int(lib().mld_packed_size_bytes(C.byref(d)))
+    dst = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=src.device)[:nbytes]
+    sums = None
+    n_sum = 0
+    if want_sum:
+        n_sum = o if sum_len is None else sum_len
+        sums = torch.zeros(n_sum, dtype=torch.int32, device=src.device)
+        if sum_init is not None:
+            sums.copy_(torch.as_tensor(sum_init, dtype=torch.int32))
+    _check(lib().mld_pack_weights(C.byref(d), _ptr(src), _ptr(dst), _ptr(sums), n_sum, _stream(stream)),
+           "mld_pack_weights")
+    return dst, sums
+
+
+def weights_sum_i(q: torch.Tensor, stream=None):
+    o = q.shape[0]
+    hwi = q.numel() // max(o, 1)
+    out = torch.empty(o, dtype=torch.int32, device=q.device)
+    _check(lib().mld_weights_sum_i(_ptr(q), o, hwi, _ptr(out), _stream(stream)), "mld_weights_sum_i")
+    return out
+
+
+def pack_scales(scale: torch.Tensor, f16: bool, stream=None):
+    """[O] or [O][G] fp32 device tensor -> [G][O4] in fp16 or fp32."""
+    s = scale.reshape(scale.shape[0], -1).contiguous()
+    o, g = s.shape
+    o4 = div_up(o, 4) * 4
+    dst = torch.empty((g, o4), dtype=torch.float16 if f16 else torch.float32, device=s.device)
+    _check(lib().mld_pack_scales(_ptr(s), o, g, int(f16), _ptr(dst), _stream(stream)), "mld_pack_scales")
+    return dst
+
+
+def quantize_weights(w: torch.Tensor, bits: int, block: int = 0, stream=None):
+    o, i = w.shape
+    g = i // block if (bits == 4 and block > 0) else 1
+    q = torch.empty((o, i), dtype=torch.int8, device=w.device)
+    s = torch.empty((o, g), dtype=torch.float32, device=w.device)
+    _check(lib().mld_quantize_weights(_ptr(w), o, i, bits, block, _ptr(q), _ptr(s), _stream(stream)),
+           "mld_quantize_weights")
+    return q, s
+
+
+# --------------------------------------------------------------------- operator
+def is_gemv_recommended(precision, tokens) -> bool:
+    return bool(lib().mld_fc_is_gemv_recommended(precision, tokens))
+
+
+class FullyConnectedPlan:
+    """Owns one mld_fc_plan (the operator object of the C ABI)."""
+
+    def __init__(self, n, k, weight_bits, scale_mode=SCALE_PER_CHANNEL, groups=1, scalar_scale=0.0,
+                 scalar_zero_point=0.0, has_zero_point=False, has_bias=False, precision=F32F16,
+                 src_layout=LAYOUT_SLICED, dst_layout=LAYOUT_SLICED, max_tokens=1, force_path=PATH_AUTO,
+                 device=-1):
+        self.desc = FcDesc(n, k, weight_bits, scale_mode, groups, scalar_scale, scalar_zero_point,
+                           int(has_zero_point), int(has_bias), precision, src_layout, dst_layout,
+                           max_tokens, force_path, device)
+        self._h = C.c_void_p()
+        _check(lib().mld_fc_plan_create(C.byref(self.desc), C.byref(self._h)), "mld_fc_plan_create")
+
+    def workspace_bytes(self) -> int:
+        return int(lib().mld_fc_plan_workspace_bytes(self._h))
+
+    def run(self, src, weights, scale, dst, tokens, zero_point=None, bias=None, stream=None):
+        _check(lib().mld_fc_run(self._h, _ptr(src), _ptr(weights), _ptr(scale), _ptr(zero_point), _ptr(bias),
+                                _ptr(dst), tokens, _stream(stream)), "mld_fc_run")
+
+    def close(self):
+        if self._h:
+            lib().mld_fc_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

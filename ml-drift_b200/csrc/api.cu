@@ -1,0 +1,375 @@
+// C ABI of libmldfc: argument checking, plan objects and dispatch.  There is
+// no CPU fallback anywhere in this file: a call either enqueues CUDA work or
+// returns an error status.
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mld {
+
+namespace {
+thread_local std::string g_last_error;
+std::atomic<int64_t> g_launches{0};
+}  // namespace
+
+void set_last_error(const char* what, cudaError_t err) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(err);
+}
+void set_last_error_text(const char* what) { g_last_error = what; }
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int sm_count(int device) {
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+  return n;
+}
+
+encode_tiled_fn get_encode_tiled() {
+  static encode_tiled_fn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<encode_tiled_fn>(p);
+  });
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t pitch_bytes,
+                 uint32_t box_bytes, uint32_t box_rows, int elem_bytes, CUtensorMapSwizzle swizzle,
+                 CUtensorMapDataType dtype_override, bool use_override) {
+  encode_tiled_fn enc = get_encode_tiled();
+  if (enc == nullptr) {
+    set_last_error_text("cuTensorMapEncodeTiled is not available from this driver");
+    return MLD_CUDA_ERROR;
+  }
+  CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  if (use_override)
+    dt = dtype_override;
+  else if (elem_bytes == 2)
+    dt = CU_TENSOR_MAP_DATA_TYPE_UINT16;
+  else if (elem_bytes == 4)
+    dt = CU_TENSOR_MAP_DATA_TYPE_UINT32;
+  const cuuint64_t dims[2] = {row_bytes / elem_bytes, rows};
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {box_bytes / elem_bytes, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[160];
+    snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (%d): row_bytes=%llu rows=%llu pitch=%llu box=%ux%u",
+             static_cast<int>(r), (unsigned long long)row_bytes, (unsigned long long)rows,
+             (unsigned long long)pitch_bytes, box_bytes, box_rows);
+    set_last_error_text(buf);
+    return MLD_CUDA_ERROR;
+  }
+  return MLD_OK;
+}
+
+}  // namespace mld
+
+using namespace mld;
+
+// ------------------------------------------------------------------ plan type
+struct TmapEntry {
+  const void* w;
+  const void* s;
+  CUtensorMap tw, ts;
+};
+
+struct mld_fc_plan {
+  mld_fc_desc d;
+  int device;
+  int sms;
+  bool stream_ok;        // the streaming GEMV can serve this operator
+  bool subnormal;        // operand encoding of the streaming GEMV
+  int group_slices;
+  StreamGeometry gm[2];  // [0]: up to 8 tokens, [1]: 9..16 tokens
+  float* partials;
+  int* tickets;
+  int* error;
+  size_t ws_bytes;
+  std::vector<TmapEntry> tmaps;  // tensor maps keyed by the (weights, scale) pointers last seen
+  std::mutex mu;
+};
+
+extern "C" {
+
+const char* mld_status_string(int status) {
+  switch (status) {
+    case MLD_OK: return "OK";
+    case MLD_INVALID_ARGUMENT: return "INVALID_ARGUMENT";
+    case MLD_UNIMPLEMENTED: return "UNIMPLEMENTED";
+    case MLD_CUDA_ERROR: return "CUDA_ERROR";
+    case MLD_NCCL_ERROR: return "NCCL_ERROR";
+    case MLD_TIMEOUT: return "TIMEOUT";
+    case MLD_OUT_OF_RANGE: return "OUT_OF_RANGE";
+  }
+  return "UNKNOWN";
+}
+
+const char* mld_last_error(void) { return g_last_error.c_str(); }
+int64_t mld_kernel_launch_count(void) { return g_launches.load(); }
+
+// ----------------------------------------------------------- weight conversion
+static int check_pack_desc(const mld_pack_desc* d) {
+  MLD_REQUIRE(d != nullptr, "null pack descriptor");
+  MLD_REQUIRE(d->o >= 0 && d->h >= 1 && d->w >= 1 && d->i >= 0, "bad OHWI shape");
+  MLD_REQUIRE(d->bits == 8 || d->bits == 4, "bits must be 4 or 8");
+  MLD_REQUIRE(d->out_group_size >= 0, "bad out_group_size");
+  MLD_REQUIRE(d->source == MLD_SRC_INT8 || d->source == MLD_SRC_UINT4_PACKED, "bad source kind");
+  if (d->source == MLD_SRC_UINT4_PACKED) {
+    MLD_REQUIRE(d->bits == 4, "a nibble-packed source converts to kUint4 only");
+    MLD_REQUIRE(d->pad_value < 16, "pad_value must fit a nibble");
+  } else {
+    MLD_REQUIRE(d->swap_dims == 0, "swap_dims applies to the nibble-packed source only");
+  }
+  return MLD_OK;
+}
+
+size_t mld_packed_size_bytes(const mld_pack_desc* d) {
+  if (check_pack_desc(d) != MLD_OK) return 0;
+  const int ds = div_up(d->o, 4);
+  const int group = d->out_group_size > 0 ? d->out_group_size : (ds > 0 ? ds : 1);
+  const size_t elems =
+      static_cast<size_t>(align_n(d->i, 4)) * static_cast<size_t>(align_n(d->o, 4 * group)) * d->h * d->w;
+  return d->bits == 8 ? elems : elems / 2;
+}
+
+int mld_pack_weights(const mld_pack_desc* d, const void* src, void* dst, int32_t* sum_i, int32_t sum_len,
+                     void* stream) {
+  int rc = check_pack_desc(d);
+  if (rc != MLD_OK) return rc;
+  if (d->o == 0 || d->i == 0) return MLD_OK;
+  MLD_REQUIRE(src != nullptr && dst != nullptr, "null buffer");
+  MLD_REQUIRE((reinterpret_cast<uintptr_t>(dst) & 15) == 0, "dst must be 16-byte aligned");
+  MLD_REQUIRE(sum_i == nullptr || sum_len >= d->o, "sum_i needs at least o entries");
+  return pack_weights_impl(d, src, dst, sum_i, sum_len, static_cast<cudaStream_t>(stream));
+}
+
+int mld_weights_sum_i(const int8_t* src, int32_t o, int32_t hwi, int32_t* sum_i, void* stream) {
+  MLD_REQUIRE(o >= 0 && hwi >= 0, "bad shape");
+  MLD_REQUIRE(o == 0 || (src != nullptr && sum_i != nullptr), "null buffer");
+  return weights_sum_i_impl(src, o, hwi, sum_i, static_cast<cudaStream_t>(stream));
+}
+
+int mld_pack_scales(const float* src, int32_t o, int32_t g, int32_t dst_f16, void* dst, void* stream) {
+  MLD_REQUIRE(o >= 0 && g >= 0, "bad shape");
+  MLD_REQUIRE(o * g == 0 || (src != nullptr && dst != nullptr), "null buffer");
+  return pack_scales_impl(src, o, g, dst_f16, dst, static_cast<cudaStream_t>(stream));
+}
+
+int mld_quantize_weights(const float* w, int32_t o, int32_t i, int32_t bits, int32_t block, int8_t* q,
+                         float* scale, void* stream) {
+  MLD_REQUIRE(bits == 8 || bits == 4, "bits must be 4 or 8");
+  MLD_REQUIRE(o >= 0 && i >= 0 && block >= 0, "bad shape");
+  if (bits == 4 && block > 0) MLD_REQUIRE(i % block == 0, "input channels not divisible by block size");
+  MLD_REQUIRE(o * i == 0 || (w != nullptr && q != nullptr && scale != nullptr), "null buffer");
+  return quantize_weights_impl(w, o, i, bits, block, q, scale, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------------ operator
+int mld_fc_is_gemv_recommended(int32_t precision, int32_t tokens) {
+  // GetRecommendedMaxTotalSpatialSize: 4, x2 for kF16, x2 for non-Mali, capped at 16
+  const int limit = precision == MLD_PRECISION_F16 ? 16 : 8;
+  return tokens <= limit ? 1 : 0;
+}
+
+int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
+  MLD_REQUIRE(d != nullptr && out != nullptr, "null argument");
+  *out = nullptr;
+  MLD_REQUIRE(d->n > 0 && d->k > 0, "weights shape must be positive");
+  MLD_REQUIRE(d->weight_bits == 4 || d->weight_bits == 8, "Unsupported WeightsDescription type.");
+  MLD_REQUIRE(d->precision >= MLD_PRECISION_F32 && d->precision <= MLD_PRECISION_F32F16, "bad precision");
+  MLD_REQUIRE(d->scale_mode >= MLD_SCALE_SCALAR && d->scale_mode <= MLD_SCALE_BLOCK, "bad scale mode");
+  MLD_REQUIRE(d->src_layout == MLD_LAYOUT_SLICED || d->src_layout == MLD_LAYOUT_ROW_MAJOR, "bad src layout");
+  MLD_REQUIRE(d->dst_layout == MLD_LAYOUT_SLICED || d->dst_layout == MLD_LAYOUT_ROW_MAJOR, "bad dst layout");
+  MLD_REQUIRE(d->max_tokens >= 1, "max_tokens must be at least 1");
+  const int src_slices = div_up(d->k, 4);
+  int group_slices = src_slices;
+  if (d->scale_mode == MLD_SCALE_BLOCK) {
+    MLD_REQUIRE(d->groups >= 1, "block-wise scales need groups >= 1");
+    group_slices = src_slices / d->groups;  // fully_connected.cc:365-370
+    MLD_REQUIRE(group_slices >= 1, "more scale groups than input slices");
+  }
+  int device = d->device;
+  if (device < 0) MLD_CUDA_CHECK(cudaGetDevice(&device));
+
+  mld_fc_plan* p = new mld_fc_plan();
+  p->d = *d;
+  p->device = device;
+  p->sms = sm_count(device);
+  p->group_slices = group_slices;
+  p->partials = nullptr;
+  p->tickets = nullptr;
+  p->error = nullptr;
+  p->ws_bytes = 0;
+  const char* enc = getenv("MLD_GEMV_OPERANDS");  // "exact" or "subnormal"
+  p->subnormal = !(enc != nullptr && strcmp(enc, "exact") == 0);
+
+  const int N4 = align_n(d->n, 4);
+  bool ok = d->precision != MLD_PRECISION_F32 && !d->has_zero_point && (N4 % 8 == 0) && (d->k % 8 == 0) &&
+            p->sms > 0 && get_encode_tiled() != nullptr;
+  if (d->scale_mode == MLD_SCALE_BLOCK) {
+    const bool pow2_small = group_slices >= 8 && group_slices <= 128 && (group_slices & (group_slices - 1)) == 0;
+    const bool large = group_slices > 128 && group_slices % 128 == 0;
+    ok = ok && (pow2_small || large) && (group_slices * d->groups == src_slices);
+  }
+  p->stream_ok = ok;
+  if (ok) {
+    const int max_m = d->max_tokens < 16 ? d->max_tokens : 16;
+    p->gm[0] = stream_geometry(d->weight_bits, d->n, d->k, max_m < 8 ? max_m : 8, group_slices, d->scale_mode, p->sms);
+    p->gm[1] = stream_geometry(d->weight_bits, d->n, d->k, 16, group_slices, d->scale_mode, p->sms);
+    size_t floats = p->gm[0].partial_floats;
+    if (max_m > 8 && p->gm[1].partial_floats > floats) floats = p->gm[1].partial_floats;
+    const int n_tiles = p->gm[0].n_tiles;
+    cudaError_t e = cudaSetDevice(device);
+    if (e == cudaSuccess) e = cudaMalloc(&p->partials, floats * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&p->tickets, (n_tiles + 1) * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(p->tickets, 0, (n_tiles + 1) * sizeof(int));
+    if (e != cudaSuccess) {
+      set_last_error("plan workspace", e);
+      if (p->partials) cudaFree(p->partials);
+      if (p->tickets) cudaFree(p->tickets);
+      delete p;
+      return MLD_CUDA_ERROR;
+    }
+    p->error = p->tickets + n_tiles;
+    p->ws_bytes = floats * sizeof(float) + (n_tiles + 1) * sizeof(int);
+  }
+  *out = p;
+  return MLD_OK;
+}
+
+int mld_fc_plan_destroy(mld_fc_plan* plan) {
+  if (plan == nullptr) return MLD_OK;
+  if (plan->partials) cudaFree(plan->partials);
+  if (plan->tickets) cudaFree(plan->tickets);
+  delete plan;
+  return MLD_OK;
+}
+
+size_t mld_fc_plan_workspace_bytes(const mld_fc_plan* plan) { return plan ? plan->ws_bytes : 0; }
+
+static int run_generic(mld_fc_plan* p, const void* src, const void* weights, const void* scale, const void* zp,
+                       const void* bias, void* dst, int tokens, cudaStream_t stream) {
+  const mld_fc_desc& d = p->d;
+  GenericArgs a;
+  a.x = src;
+  a.weights = weights;
+  a.scale = scale;
+  a.zp = zp;
+  a.bias = bias;
+  a.y = dst;
+  a.M = tokens;
+  a.K = d.k;
+  a.N = d.n;
+  a.src_slices = div_up(d.k, 4);
+  a.dst_slices = div_up(d.n, 4);
+  a.scale_mode = d.scale_mode;
+  a.groups = d.scale_mode == MLD_SCALE_BLOCK ? d.groups : 1;
+  a.group_slices = p->group_slices;
+  a.scalar_scale = d.scalar_scale;
+  a.scalar_zp = d.scalar_zero_point;
+  a.has_zp = d.has_zero_point;
+  a.src_layout = d.src_layout;
+  a.dst_layout = d.dst_layout;
+  return launch_fc_generic(a, d.weight_bits, d.precision == MLD_PRECISION_F32, stream);
+}
+
+static int run_stream(mld_fc_plan* p, const void* src, const void* weights, const void* scale, const void* bias,
+                      void* dst, int tokens, cudaStream_t stream) {
+  const mld_fc_desc& d = p->d;
+  const StreamGeometry& gm = p->gm[tokens > 8 ? 1 : 0];
+  const int N4 = align_n(d.n, 4), SS = div_up(d.k, 4), DS = N4 / 4;
+  const TmapEntry* te = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(p->mu);
+    for (const TmapEntry& e : p->tmaps)
+      if (e.w == weights && e.s == scale) te = &e;
+    if (te == nullptr) {
+      TmapEntry e;
+      e.w = weights;
+      e.s = scale;
+      const uint64_t blk = d.weight_bits == 4 ? 8 : 16;
+      int rc = make_tmap_2d(&e.tw, weights, (uint64_t)DS * blk, SS, (uint64_t)DS * blk, 128, 128, 1,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc != MLD_OK) return rc;
+      if (gm.scale_rows > 0) {
+        const int G = d.scale_mode == MLD_SCALE_BLOCK ? d.groups : 1;
+        rc = make_tmap_2d(&e.ts, scale, (uint64_t)N4 * 2, G, (uint64_t)N4 * 2, gm.tile_n * 2, gm.scale_rows, 1,
+                          CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != MLD_OK) return rc;
+      } else {
+        memset(&e.ts, 0, sizeof e.ts);
+      }
+      if (p->tmaps.size() >= 64) p->tmaps.erase(p->tmaps.begin());
+      p->tmaps.push_back(e);
+      te = &p->tmaps.back();
+    }
+  }
+  StreamArgs a;
+  a.x = src;
+  a.bias = bias;
+  a.y = dst;
+  a.partials = p->partials;
+  a.tickets = p->tickets;
+  a.error = p->error;
+  a.M = tokens;
+  a.N = d.n;
+  a.N4 = N4;
+  a.src_slices = SS;
+  a.n_tiles = gm.n_tiles;
+  a.n_chunks = gm.n_chunks;
+  a.stages = gm.stages;
+  a.stage_bytes = gm.stage_bytes;
+  a.scale_stage_bytes = gm.scale_stage_bytes;
+  a.scale_rows = gm.scale_rows;
+  a.group_slices = gm.group_slices;
+  a.gs_shift = gm.gs_shift;
+  a.max_pieces = gm.max_pieces;
+  a.dst_layout = d.dst_layout;
+  a.scalar_scale = d.scalar_scale;
+  const CUtensorMap tw = te->tw, ts = te->ts;
+  return launch_fc_stream(d.weight_bits, p->subnormal, tw, ts, a, gm, stream);
+}
+
+int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const void* scale, const void* zero_point,
+               const void* bias, void* dst, int32_t tokens, void* stream_v) {
+  MLD_REQUIRE(plan != nullptr, "null plan");
+  const mld_fc_desc& d = plan->d;
+  MLD_REQUIRE(tokens >= 0 && tokens <= d.max_tokens, "tokens exceeds the plan's max_tokens");
+  if (tokens == 0) return MLD_OK;
+  MLD_REQUIRE(src != nullptr && weights != nullptr && dst != nullptr, "null tensor");
+  MLD_REQUIRE(d.scale_mode == MLD_SCALE_SCALAR || scale != nullptr, "weights_scale tensor missing");
+  MLD_REQUIRE(!d.has_bias || bias != nullptr, "biases tensor missing");
+  MLD_REQUIRE((reinterpret_cast<uintptr_t>(weights) & 15) == 0, "weights must be 16-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const void* b = d.has_bias ? bias : nullptr;
+  const void* zp = d.has_zero_point ? zero_point : nullptr;
+
+  int path = d.force_path;
+  if (path == 0) path = mld_fc_is_gemv_recommended(d.precision, tokens) ? 1 : 2;
+  if (path == 2) {
+    set_last_error_text("prefill GEMM path is not built into this library yet");
+    return MLD_UNIMPLEMENTED;
+  }
+  const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+                       (scale == nullptr || (reinterpret_cast<uintptr_t>(scale) & 15) == 0);
+  const bool layout_ok = d.src_layout == MLD_LAYOUT_SLICED || tokens == 1;
+  if (plan->stream_ok && tokens <= 16 && aligned && layout_ok)
+    return run_stream(plan, src, weights, scale, b, dst, tokens, stream);
+  return run_generic(plan, src, weights, scale, zp, b, dst, tokens, stream);
+}
+
+}  // extern "C"

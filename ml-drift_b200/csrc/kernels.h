@@ -1,0 +1,69 @@
+// Internal launch interfaces shared by the mldfc CUDA translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "mldfc.h"
+
+namespace mld {
+
+// ------------------------------------------------------------ weight conversion
+int pack_weights_impl(const mld_pack_desc* d, const void* src, void* dst, int32_t* sum_i, int32_t sum_len,
+                      cudaStream_t stream);
+int weights_sum_i_impl(const int8_t* src, int32_t o, int32_t hwi, int32_t* sum_i, cudaStream_t stream);
+int pack_scales_impl(const float* src, int32_t o, int32_t g, int32_t dst_f16, void* dst, cudaStream_t stream);
+int quantize_weights_impl(const float* w, int32_t o, int32_t i, int32_t bits, int32_t block, int8_t* q,
+                          float* scale, cudaStream_t stream);
+
+// ------------------------------------------------------------------ decode GEMV
+struct GenericArgs {
+  const void* x;
+  const void* weights;
+  const void* scale;
+  const void* zp;
+  const void* bias;
+  void* y;
+  int M, K, N;
+  int src_slices, dst_slices;
+  int scale_mode, groups, group_slices;
+  float scalar_scale, scalar_zp;
+  int has_zp;
+  int src_layout, dst_layout;
+};
+int launch_fc_generic(const GenericArgs& a, int bits, bool f32, cudaStream_t stream);
+
+struct StreamArgs {
+  const void* x;      // fp16, sliced [K/4][M][4] (for M == 1 a plain vector)
+  const void* bias;   // fp16 [N4] or null
+  void* y;            // fp16
+  float* partials;    // split-K workspace
+  int* tickets;       // one per output tile, zero between launches
+  int* error;         // device error word (0 = ok)
+  int M, N, N4;
+  int src_slices;
+  int n_tiles, n_chunks;
+  int stages, stage_bytes, scale_stage_bytes;
+  int scale_rows;     // rows of the per-stage scale box (0 = scalar scale)
+  int group_slices;   // k-slices per scale group
+  int gs_shift;       // log2(group_slices) when it is a power of two <= 128, else -1
+  int max_pieces;
+  int dst_layout;
+  float scalar_scale;
+};
+
+struct StreamGeometry {
+  int nb, tile_n, n_tiles, n_chunks;
+  int scale_rows, group_slices, gs_shift;
+  int scale_stage_bytes, stage_bytes, stages;
+  size_t smem_bytes;
+  int grid, max_pieces;
+  size_t partial_floats;
+};
+StreamGeometry stream_geometry(int bits, int N, int K, int M, int group_slices, int scale_mode, int sms);
+int launch_fc_stream(int bits, bool subnormal, const CUtensorMap& tw, const CUtensorMap& ts, const StreamArgs& a,
+                     const StreamGeometry& gm, cudaStream_t stream);
+
+}  // namespace mld

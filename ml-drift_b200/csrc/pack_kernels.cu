@@ -1,0 +1,287 @@
+// Weight conversion kernels: quantisation, rearrangement into the reference's
+// kOSpatialIOGroupI4O4 buffer layout, scale layout.  All integer/byte work is
+// bit-exact with the CPU rearrangers of ml-drift
+// (common/task/weights_conversion.cc); these kernels are HBM-bound, so they
+// read rows coalesced, transpose through shared memory and write whole 4x4
+// blocks with vector stores.
+#include "common.cuh"
+
+namespace mld {
+
+namespace {
+
+constexpr int kTileSlices = 32;                  // 32 x 32 blocks of 4x4 per CTA
+constexpr int kTileCh = kTileSlices * 4;         // 128 channels each way
+constexpr int kRowPitch = kTileSlices * 16 + 4;  // bytes per src-slice row of the staged tile (+4: bank spread)
+
+// Position of element (o_local, i_local) inside the staged tile, which is kept
+// in destination order: [src slice][dst slice][4 i][4 o], one byte per element.
+__device__ __forceinline__ int tile_pos(int o_local, int i_local) {
+  return (i_local >> 2) * kRowPitch + (o_local >> 2) * 16 + (i_local & 3) * 4 + (o_local & 3);
+}
+
+struct PackArgs {
+  const uint8_t* src;
+  uint8_t* dst;
+  int32_t* sum_i;
+  int O, HW, I;
+  int group;       // out_group_size
+  int dst_slices;  // ceil(O/4)
+  int src_slices;  // ceil(I/4)
+  int total_ds;    // dst_groups * group (>= dst_slices)
+  int sum_len;
+  int shift;       // added to int8 sources (128 / 8)
+  uint32_t pad;    // pad value as the reference passes it
+  int swap_dims;
+};
+
+// Writes the staged tile to global memory.  BITS == 8: 16 bytes per block;
+// BITS == 4: consecutive element pairs share a byte, first in the low nibble
+// (RearrangeWeightsInt8AsUint4, weights_conversion.cc:1510-1523).
+template <int BITS>
+__device__ __forceinline__ void store_tile(const uint8_t* tile, const PackArgs& a, int hw, int s0, int d0) {
+  for (int blk = threadIdx.x; blk < kTileSlices * kTileSlices; blk += blockDim.x) {
+    const int ss = blk / kTileSlices, dsl = blk % kTileSlices;
+    const int s = s0 + ss, ds = d0 + dsl;
+    if (s >= a.src_slices || ds >= a.total_ds) continue;
+    const int d = ds / a.group, dg = ds % a.group;
+    // [dst_groups][HW][src_slices][group] blocks
+    const int64_t block_index = (((int64_t)d * a.HW + hw) * a.src_slices + s) * a.group + dg;
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(tile + ss * kRowPitch + dsl * 16);
+    const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3];
+    if (BITS == 8) {
+      *reinterpret_cast<uint4*>(a.dst + block_index * 16) = make_uint4(w0, w1, w2, w3);
+    } else {
+      // bytes v0 v1 v2 v3 of a word -> (v1<<4|v0), (v3<<4|v2), truncated to 8 bits
+      auto squeeze = [](uint32_t x) -> uint32_t {
+        const uint32_t b0 = x & 0xFF, b1 = (x >> 8) & 0xFF, b2 = (x >> 16) & 0xFF, b3 = x >> 24;
+        return (((b1 << 4) | b0) & 0xFF) | ((((b3 << 4) | b2) & 0xFF) << 8);
+      };
+      const uint32_t lo = squeeze(w0) | (squeeze(w1) << 16);
+      const uint32_t hi = squeeze(w2) | (squeeze(w3) << 16);
+      *reinterpret_cast<uint2*>(a.dst + block_index * 8) = make_uint2(lo, hi);
+    }
+  }
+}
+
+// int8 OHWI source -> staged tile of (q + shift) bytes.  One warp reads 128
+// consecutive input channels of one output row per step (coalesced).
+template <int BITS>
+__global__ void __launch_bounds__(256) pack_from_int8_kernel(PackArgs a) {
+  __shared__ __align__(16) uint8_t tile[kTileSlices * kRowPitch];
+  const int s0 = blockIdx.x * kTileSlices, d0 = blockIdx.y * kTileSlices, hw = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int8_t* src = reinterpret_cast<const int8_t*>(a.src);
+  const uint8_t padv = static_cast<uint8_t>(a.pad);
+  const bool vec = (a.I % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 3) == 0);
+  for (int r = warp; r < kTileCh; r += 8) {
+    const int o = d0 * 4 + r;
+    const int i = s0 * 4 + lane * 4;
+    uint8_t v[4];
+    int32_t rowsum = 0;
+    if (o < a.O) {
+      const int64_t base = ((int64_t)o * a.HW + hw) * a.I + i;
+      if (vec && i + 3 < a.I) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(src + base);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int8_t q = static_cast<int8_t>((w >> (8 * j)) & 0xFF);
+          v[j] = static_cast<uint8_t>(q + a.shift);
+          rowsum += q;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (i + j < a.I) {
+            const int8_t q = src[base + j];
+            v[j] = static_cast<uint8_t>(q + a.shift);
+            rowsum += q;
+          } else {
+            v[j] = padv;
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = padv;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) tile[tile_pos(r, lane * 4 + j)] = v[j];
+    if (a.sum_i != nullptr) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) rowsum += __shfl_xor_sync(0xffffffffu, rowsum, off);
+      if (lane == 0 && o < a.O && o < a.sum_len && rowsum != 0) atomicAdd(a.sum_i + o, rowsum);
+    }
+  }
+  __syncthreads();
+  store_tile<BITS>(tile, a, hw, s0, d0);
+}
+
+// Dense two's-complement nibble source (Uint4PackedkOSpatialIOGroupI4O4,
+// weights_conversion.cc:631-708).  The staged byte is the *destination nibble*
+// (source nibble ^ 8, or the pad rules of the reference), the store step packs
+// pairs.  sum_i receives (nibble ^ 8) - 8 per element, and pad - 8 for padded
+// output channels of valid input channels, as the reference does.
+__global__ void __launch_bounds__(256) pack_from_u4_kernel(PackArgs a) {
+  __shared__ __align__(16) uint8_t tile[kTileSlices * kRowPitch];
+  const int s0 = blockIdx.x * kTileSlices, d0 = blockIdx.y * kTileSlices, hw = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint8_t pad_nib = static_cast<uint8_t>(a.pad & 0xFF);              // "double_pad" nibble (s_ch >= I)
+  const uint8_t pad_dst = static_cast<uint8_t>(((a.pad ^ 0x8) ^ 0x8) & 0xF);  // padded output channel
+  for (int r = warp; r < kTileCh; r += 8) {
+    const int o = d0 * 4 + r;
+    const int i = s0 * 4 + lane * 4;
+    int32_t rowsum = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint8_t out;
+      if (i + j >= a.I) {
+        // both nibbles of the byte are the raw pad value (weights_conversion.cc:660-664)
+        out = pad_nib & 0xF;
+      } else if (o >= a.O) {
+        out = pad_dst;
+        rowsum += static_cast<int32_t>(static_cast<uint8_t>((a.pad ^ 0x8) & 0xFF) ^ 0x8) - 8;
+      } else {
+        const int64_t f = a.swap_dims ? (((int64_t)(i + j) * a.HW + hw) * a.O + o)
+                                      : (((int64_t)o * a.HW + hw) * a.I + (i + j));
+        const uint8_t b = a.src[f >> 1];
+        const uint8_t nib = (f & 1) ? (b >> 4) : (b & 0xF);
+        out = nib ^ 0x8;
+        rowsum += static_cast<int32_t>(nib ^ 0x8) - 8;
+      }
+      tile[tile_pos(r, lane * 4 + j)] = out;
+    }
+    if (a.sum_i != nullptr) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) rowsum += __shfl_xor_sync(0xffffffffu, rowsum, off);
+      // padded channels exist only inside the last, partly filled slice
+      if (lane == 0 && o < a.dst_slices * 4 && o < a.sum_len && rowsum != 0) atomicAdd(a.sum_i + o, rowsum);
+    }
+  }
+  __syncthreads();
+  store_tile<4>(tile, a, hw, s0, d0);
+}
+
+__global__ void sum_i_kernel(const int8_t* src, int O, int64_t hwi, int32_t* sum_i) {
+  const int o = blockIdx.x;
+  if (o >= O) return;
+  const int8_t* row = src + (int64_t)o * hwi;
+  int32_t s = 0;
+  for (int64_t k = threadIdx.x; k < hwi; k += blockDim.x) s += row[k];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  __shared__ int32_t part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t t = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += part[w];
+    sum_i[o] = t;
+  }
+}
+
+// [O][G] fp32 -> [G][O4] fp16/fp32, zero padded (OHIToHOIO4 in buffer storage).
+__global__ void pack_scales_kernel(const float* src, int O, int G, int O4, int dst_f16, void* dst) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)G * O4) return;
+  const int g = static_cast<int>(idx / O4), o = static_cast<int>(idx % O4);
+  const float v = o < O ? src[(int64_t)o * G + g] : 0.0f;
+  if (dst_f16)
+    reinterpret_cast<__half*>(dst)[idx] = __float2half_rn(v);
+  else
+    reinterpret_cast<float*>(dst)[idx] = v;
+}
+
+// One warp per (row, block): absmax -> scale -> round-half-even -> clip.
+// IEEE division (__fdiv_rn) and rintf reproduce numpy's float32 results.
+__global__ void __launch_bounds__(128) quantize_kernel(const float* w, int O, int I, int block, int G,
+                                                       float qmax, float qlo, float qhi, int8_t* q,
+                                                       float* scale) {
+  const int o = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int g = warp + blockIdx.y * nwarps; g < G; g += nwarps * gridDim.y) {
+    const float* blk = w + (int64_t)o * I + (int64_t)g * block;
+    float bound = 0.0f;
+    for (int i = lane; i < block; i += 32) bound = fmaxf(bound, fabsf(blk[i]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, off));
+    float s = __fdiv_rn(bound, qmax);
+    if (s == 0.0f) s = 1.0f;
+    int8_t* qb = q + (int64_t)o * I + (int64_t)g * block;
+    for (int i = lane; i < block; i += 32) {
+      float v = rintf(__fdiv_rn(blk[i], s));
+      v = fminf(fmaxf(v, qlo), qhi);
+      qb[i] = static_cast<int8_t>(v);
+    }
+    if (lane == 0) scale[(int64_t)o * G + g] = s;
+  }
+}
+
+}  // namespace
+
+int pack_weights_impl(const mld_pack_desc* d, const void* src, void* dst, int32_t* sum_i, int32_t sum_len,
+                      cudaStream_t stream) {
+  PackArgs a;
+  a.src = static_cast<const uint8_t*>(src);
+  a.dst = static_cast<uint8_t*>(dst);
+  a.sum_i = sum_i;
+  a.O = d->o;
+  a.HW = d->h * d->w;
+  a.I = d->i;
+  a.dst_slices = div_up(d->o, 4);
+  a.src_slices = div_up(d->i, 4);
+  a.group = d->out_group_size > 0 ? d->out_group_size : a.dst_slices;
+  a.total_ds = div_up(a.dst_slices, a.group) * a.group;
+  a.sum_len = sum_len;
+  a.shift = d->bits == 8 ? 128 : 8;
+  a.pad = d->pad_value;
+  a.swap_dims = d->swap_dims;
+  if (sum_i != nullptr) {
+    const int n = sum_len < d->o ? sum_len : d->o;
+    if (n > 0) MLD_CUDA_CHECK(cudaMemsetAsync(sum_i, 0, sizeof(int32_t) * n, stream));
+  }
+  dim3 grid(div_up(a.src_slices, kTileSlices), div_up(a.total_ds, kTileSlices), a.HW);
+  if (grid.x == 0 || grid.y == 0 || grid.z == 0) return MLD_OK;
+  if (d->source == MLD_SRC_INT8) {
+    if (d->bits == 8)
+      pack_from_int8_kernel<8><<<grid, 256, 0, stream>>>(a);
+    else
+      pack_from_int8_kernel<4><<<grid, 256, 0, stream>>>(a);
+  } else {
+    pack_from_u4_kernel<<<grid, 256, 0, stream>>>(a);
+  }
+  MLD_LAUNCH_CHECK();
+  return MLD_OK;
+}
+
+int weights_sum_i_impl(const int8_t* src, int32_t o, int32_t hwi, int32_t* sum_i, cudaStream_t stream) {
+  if (o == 0) return MLD_OK;
+  sum_i_kernel<<<o, 256, 0, stream>>>(src, o, hwi, sum_i);
+  MLD_LAUNCH_CHECK();
+  return MLD_OK;
+}
+
+int pack_scales_impl(const float* src, int32_t o, int32_t g, int32_t dst_f16, void* dst, cudaStream_t stream) {
+  const int O4 = align_n(o, 4);
+  const int64_t n = (int64_t)g * O4;
+  if (n == 0) return MLD_OK;
+  pack_scales_kernel<<<static_cast<unsigned>(div_up64(n, 256)), 256, 0, stream>>>(src, o, g, O4, dst_f16, dst);
+  MLD_LAUNCH_CHECK();
+  return MLD_OK;
+}
+
+int quantize_weights_impl(const float* w, int32_t o, int32_t i, int32_t bits, int32_t block, int8_t* q,
+                          float* scale, cudaStream_t stream) {
+  if (o == 0 || i == 0) return MLD_OK;
+  if (bits == 8 || block <= 0) block = i;
+  const int G = i / block;
+  const float qmax = bits == 8 ? 127.0f : 7.0f;
+  const float qlo = bits == 8 ? -128.0f : -8.0f;
+  const float qhi = bits == 8 ? 127.0f : 7.0f;
+  dim3 grid(o, G >= 64 ? 4 : 1);
+  quantize_kernel<<<grid, 128, 0, stream>>>(w, o, i, block, G, qmax, qlo, qhi, q, scale);
+  MLD_LAUNCH_CHECK();
+  return MLD_OK;
+}
+
+}  // namespace mld
