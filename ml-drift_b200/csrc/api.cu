@@ -84,6 +84,7 @@ using namespace mld;
 struct TmapEntry {
   const void* w;
   const void* s;
+  int geom;
   CUtensorMap tw, ts;
 };
 
@@ -93,11 +94,10 @@ struct mld_fc_plan {
   int sms;
   bool stream_ok;        // the streaming GEMV can serve this operator
   bool subnormal;        // operand encoding of the streaming GEMV
+  bool pdl;              // launch GEMVs with programmatic stream serialization
   int group_slices;
-  StreamGeometry gm[2];  // [0]: up to 8 tokens, [1]: 9..16 tokens
-  float* partials;
-  int* tickets;
-  int* error;
+  StripGeometry gm;
+  int* error;            // device error word written by kernels whose bounded waits ran out
   size_t ws_bytes;
   std::vector<TmapEntry> tmaps;  // tensor maps keyed by the (weights, scale) pointers last seen
   std::mutex mu;
@@ -210,42 +210,38 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   p->device = device;
   p->sms = sm_count(device);
   p->group_slices = group_slices;
-  p->partials = nullptr;
-  p->tickets = nullptr;
   p->error = nullptr;
   p->ws_bytes = 0;
   const char* enc = getenv("MLD_GEMV_OPERANDS");  // "exact" or "subnormal"
   p->subnormal = !(enc != nullptr && strcmp(enc, "exact") == 0);
+  const char* pdl = getenv("MLD_GEMV_PDL");        // "0" disables programmatic dependent launch
+  p->pdl = !(pdl != nullptr && strcmp(pdl, "0") == 0);
 
   const int N4 = align_n(d->n, 4);
   bool ok = d->precision != MLD_PRECISION_F32 && !d->has_zero_point && (N4 % 8 == 0) && (d->k % 8 == 0) &&
             p->sms > 0 && get_encode_tiled() != nullptr;
   if (d->scale_mode == MLD_SCALE_BLOCK) {
-    const bool pow2_small = group_slices >= 8 && group_slices <= 128 && (group_slices & (group_slices - 1)) == 0;
-    const bool large = group_slices > 128 && group_slices % 128 == 0;
-    ok = ok && (pow2_small || large) && (group_slices * d->groups == src_slices);
+    const bool small = group_slices == 8 || group_slices == 16 || group_slices == 32;
+    const bool large = group_slices >= 64 && group_slices % 64 == 0;
+    ok = ok && (small || large) && (group_slices * d->groups == src_slices);
   }
   p->stream_ok = ok;
   if (ok) {
     const int max_m = d->max_tokens < 16 ? d->max_tokens : 16;
-    p->gm[0] = stream_geometry(d->weight_bits, d->n, d->k, max_m < 8 ? max_m : 8, group_slices, d->scale_mode, p->sms);
-    p->gm[1] = stream_geometry(d->weight_bits, d->n, d->k, 16, group_slices, d->scale_mode, p->sms);
-    size_t floats = p->gm[0].partial_floats;
-    if (max_m > 8 && p->gm[1].partial_floats > floats) floats = p->gm[1].partial_floats;
-    const int n_tiles = p->gm[0].n_tiles;
+    p->gm = strip_geometry(d->weight_bits, d->n, d->k, max_m, group_slices, d->scale_mode, p->sms, p->pdl);
+    if (p->gm.stages < 2) p->stream_ok = false;
+  }
+  {
     cudaError_t e = cudaSetDevice(device);
-    if (e == cudaSuccess) e = cudaMalloc(&p->partials, floats * sizeof(float));
-    if (e == cudaSuccess) e = cudaMalloc(&p->tickets, (n_tiles + 1) * sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(p->tickets, 0, (n_tiles + 1) * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&p->error, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(p->error, 0, sizeof(int));
     if (e != cudaSuccess) {
       set_last_error("plan workspace", e);
-      if (p->partials) cudaFree(p->partials);
-      if (p->tickets) cudaFree(p->tickets);
+      if (p->error) cudaFree(p->error);
       delete p;
       return MLD_CUDA_ERROR;
     }
-    p->error = p->tickets + n_tiles;
-    p->ws_bytes = floats * sizeof(float) + (n_tiles + 1) * sizeof(int);
+    p->ws_bytes = sizeof(int);
   }
   *out = p;
   return MLD_OK;
@@ -253,8 +249,7 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
 
 int mld_fc_plan_destroy(mld_fc_plan* plan) {
   if (plan == nullptr) return MLD_OK;
-  if (plan->partials) cudaFree(plan->partials);
-  if (plan->tickets) cudaFree(plan->tickets);
+  if (plan->error) cudaFree(plan->error);
   delete plan;
   return MLD_OK;
 }
@@ -290,24 +285,27 @@ static int run_generic(mld_fc_plan* p, const void* src, const void* weights, con
 static int run_stream(mld_fc_plan* p, const void* src, const void* weights, const void* scale, const void* bias,
                       void* dst, int tokens, cudaStream_t stream) {
   const mld_fc_desc& d = p->d;
-  const StreamGeometry& gm = p->gm[tokens > 8 ? 1 : 0];
+  const StripGeometry& gm = p->gm;
   const int N4 = align_n(d.n, 4), SS = div_up(d.k, 4), DS = N4 / 4;
-  const TmapEntry* te = nullptr;
+  CUtensorMap tw, ts;
   {
     std::lock_guard<std::mutex> lock(p->mu);
+    const TmapEntry* te = nullptr;
     for (const TmapEntry& e : p->tmaps)
       if (e.w == weights && e.s == scale) te = &e;
     if (te == nullptr) {
       TmapEntry e;
       e.w = weights;
       e.s = scale;
+      e.geom = 0;
       const uint64_t blk = d.weight_bits == 4 ? 8 : 16;
-      int rc = make_tmap_2d(&e.tw, weights, (uint64_t)DS * blk, SS, (uint64_t)DS * blk, 128, 128, 1,
+      int rc = make_tmap_2d(&e.tw, weights, (uint64_t)DS * blk, SS, (uint64_t)DS * blk, 128, 64, 1,
                             CU_TENSOR_MAP_SWIZZLE_128B);
       if (rc != MLD_OK) return rc;
       if (gm.scale_rows > 0) {
         const int G = d.scale_mode == MLD_SCALE_BLOCK ? d.groups : 1;
-        rc = make_tmap_2d(&e.ts, scale, (uint64_t)N4 * 2, G, (uint64_t)N4 * 2, gm.tile_n * 2, gm.scale_rows, 1,
+        const int wt = gm.w * (d.weight_bits == 4 ? 64 : 32);
+        rc = make_tmap_2d(&e.ts, scale, (uint64_t)N4 * 2, G, (uint64_t)N4 * 2, wt * 2, gm.scale_rows, 2,
                           CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc != MLD_OK) return rc;
       } else {
@@ -317,31 +315,40 @@ static int run_stream(mld_fc_plan* p, const void* src, const void* weights, cons
       p->tmaps.push_back(e);
       te = &p->tmaps.back();
     }
+    tw = te->tw;
+    ts = te->ts;
   }
-  StreamArgs a;
+  StripArgs a;
   a.x = src;
   a.bias = bias;
   a.y = dst;
-  a.partials = p->partials;
-  a.tickets = p->tickets;
   a.error = p->error;
-  a.M = tokens;
+  a.M_total = tokens;
   a.N = d.n;
   a.N4 = N4;
   a.src_slices = SS;
-  a.n_tiles = gm.n_tiles;
-  a.n_chunks = gm.n_chunks;
+  a.units = gm.units;
+  a.gran = gm.gran;
+  a.strips = gm.strips;
+  a.ksplit = gm.ksplit;
+  a.rows_per_split = gm.rows_per_split;
   a.stages = gm.stages;
   a.stage_bytes = gm.stage_bytes;
   a.scale_stage_bytes = gm.scale_stage_bytes;
   a.scale_rows = gm.scale_rows;
   a.group_slices = gm.group_slices;
   a.gs_shift = gm.gs_shift;
-  a.max_pieces = gm.max_pieces;
+  a.red_m = gm.red_m;
   a.dst_layout = d.dst_layout;
   a.scalar_scale = d.scalar_scale;
-  const CUtensorMap tw = te->tw, ts = te->ts;
-  return launch_fc_stream(d.weight_bits, p->subnormal, tw, ts, a, gm, stream);
+  a.pdl = p->pdl ? 1 : 0;
+  for (int tok0 = 0; tok0 < tokens; tok0 += 8) {
+    a.tok0 = tok0;
+    a.M = tokens - tok0 < 8 ? tokens - tok0 : 8;
+    const int rc = launch_fc_strip(d.weight_bits, p->subnormal, tw, ts, a, gm, stream);
+    if (rc != MLD_OK) return rc;
+  }
+  return MLD_OK;
 }
 
 int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const void* scale, const void* zero_point,

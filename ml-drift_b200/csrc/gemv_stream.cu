@@ -1,0 +1,572 @@
+// Decode-stage dequant-GEMV, streaming form (1..8 tokens per launch) over the
+// reference's packed weight layout [K/4][N/4][4 k][4 n].
+//
+// The kernel is HBM-bound, so it is organised around keeping the memory system
+// busy and the exit path short:
+//  * the grid is one CTA per SM; each CTA owns a contiguous strip of output
+//    columns (16-byte granularity, so the strips balance to within one chunk)
+//    and streams every K row of that strip - no split-K traffic through global
+//    memory.  When the matrix is too narrow for 148 useful strips, two CTAs of
+//    a thread-block cluster share a strip, take half of K each and combine
+//    through distributed shared memory;
+//  * packed weights (128-byte-swizzled boxes), block scales and activations are
+//    staged by TMA / bulk copies into a ring of shared-memory stages, all
+//    completing on one mbarrier per stage;
+//  * eight consumer warps dequantise in registers and feed m16n8k16 tensor-core
+//    MMAs (weights as the 16-row operand, tokens as columns), fp32 accumulate;
+//  * with programmatic dependent launch the next GEMV starts streaming its
+//    weights while this one drains; only the activation loads wait for the
+//    predecessor.
+//
+// Arithmetic restated from GetFullyConnectedKernelCode
+// (ml_drift/common/kernels/fully_connected.cc:623-942) and fc:: helpers
+// (fully_connected_util.cc:80-229, 356-407); accumulation is fp32 for both
+// fp16 precision modes.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mld {
+
+namespace {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kStageRows = 64;                 // k-slices per stage (256 input channels)
+constexpr int kBoxBytes = kStageRows * 128;    // one weight box: 64 rows x 128 bytes
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t x, uint32_t mask, uint32_t orv) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(x), "r"(mask), "r"(orv));  // (x & mask) | orv
+  return r;
+}
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+
+// Fragment geometry.  Lane = 4*g + t.  One warp step covers four k-slice rows
+// (row of lane = base + 2*t + parity) of one 128-byte box row; lane g owns 16
+// bytes (one "chunk") of it.
+//   BITS 4: a chunk = two 4x4 blocks (8 outputs) -> 4 MMAs, 64 outputs per box
+//   BITS 8: a chunk = one 4x4 block  (4 outputs) -> 2 MMAs, 32 outputs per box
+// MMA f of a lane: rows g / g+8 are outputs NPL*g + 2*f + {0,1} of the box; the
+// sixteen k columns are (row t: k0 k1) at 2t,2t+1 and (row t: k2 k3) at 2t+8,9.
+template <int BITS>
+struct Frag {
+  static constexpr int NF = BITS == 4 ? 4 : 2;   // MMAs (accumulator fragments) per lane and box
+  static constexpr int NPL = BITS == 4 ? 8 : 4;  // outputs per chunk
+  static constexpr int BOX_N = NPL * 8;          // outputs per box (64 / 32)
+};
+
+// EXACT operands: (1024 + u) with the offset removed by one packed half
+// subtract, giving the signed weight exactly (x16 for high nibbles).
+// SUBNORMAL operands: the raw masked bits, i.e. fp16 subnormals u * 2^-24 (x16
+// for high nibbles); the "- shift * sum(x)" term comes from one extra MMA per
+// step against a constant operand, and results carry a 2^-24 factor.
+template <int BITS, bool SUBNORMAL>
+__device__ __forceinline__ void unpack(const uint4& q, uint32_t (&a)[Frag<BITS>::NF][4]) {
+  if constexpr (BITS == 4) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};  // blockA.lo(k0k1) blockA.hi(k2k3) blockB.lo blockB.hi
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      const uint32_t lo = w[2 * b], hi = w[2 * b + 1];
+      const uint32_t lo8 = lo >> 8, hi8 = hi >> 8;
+      if constexpr (SUBNORMAL) {
+        a[2 * b][0] = lo & 0x000F000Fu;
+        a[2 * b][1] = lo & 0x00F000F0u;
+        a[2 * b][2] = hi & 0x000F000Fu;
+        a[2 * b][3] = hi & 0x00F000F0u;
+        a[2 * b + 1][0] = lo8 & 0x000F000Fu;
+        a[2 * b + 1][1] = lo8 & 0x00F000F0u;
+        a[2 * b + 1][2] = hi8 & 0x000F000Fu;
+        a[2 * b + 1][3] = hi8 & 0x00F000F0u;
+      } else {
+        const uint32_t kLo = 0x64086408u;  // half2(1032): 1024 + 8
+        const uint32_t kHi = 0x64806480u;  // half2(1152): 1024 + 16*8
+        a[2 * b][0] = hsub2_u32(lop3_and_or(lo, 0x000F000Fu, 0x64006400u), kLo);
+        a[2 * b][1] = hsub2_u32(lop3_and_or(lo, 0x00F000F0u, 0x64006400u), kHi);
+        a[2 * b][2] = hsub2_u32(lop3_and_or(hi, 0x000F000Fu, 0x64006400u), kLo);
+        a[2 * b][3] = hsub2_u32(lop3_and_or(hi, 0x00F000F0u, 0x64006400u), kHi);
+        a[2 * b + 1][0] = hsub2_u32(lop3_and_or(lo8, 0x000F000Fu, 0x64006400u), kLo);
+        a[2 * b + 1][1] = hsub2_u32(lop3_and_or(lo8, 0x00F000F0u, 0x64006400u), kHi);
+        a[2 * b + 1][2] = hsub2_u32(lop3_and_or(hi8, 0x000F000Fu, 0x64006400u), kLo);
+        a[2 * b + 1][3] = hsub2_u32(lop3_and_or(hi8, 0x00F000F0u, 0x64006400u), kHi);
+      }
+    }
+  } else {
+    // bytes: q.x = k0:(n0..n3), q.y = k1, q.z = k2, q.w = k3
+    const uint32_t p01 = prmt(q.x, q.y, 0x5140u);  // [k0n0 k1n0 k0n1 k1n1]
+    const uint32_t p23 = prmt(q.z, q.w, 0x5140u);
+    const uint32_t r01 = prmt(q.x, q.y, 0x7362u);  // [k0n2 k1n2 k0n3 k1n3]
+    const uint32_t r23 = prmt(q.z, q.w, 0x7362u);
+    if constexpr (SUBNORMAL) {
+      a[0][0] = prmt(p01, 0u, 0x4140u);
+      a[0][1] = prmt(p01, 0u, 0x4342u);
+      a[0][2] = prmt(p23, 0u, 0x4140u);
+      a[0][3] = prmt(p23, 0u, 0x4342u);
+      a[1][0] = prmt(r01, 0u, 0x4140u);
+      a[1][1] = prmt(r01, 0u, 0x4342u);
+      a[1][2] = prmt(r23, 0u, 0x4140u);
+      a[1][3] = prmt(r23, 0u, 0x4342u);
+    } else {
+      const uint32_t kM = 0x64646464u;
+      const uint32_t kOff = 0x64806480u;  // half2(1152) = 1024 + 128
+      a[0][0] = hsub2_u32(prmt(p01, kM, 0x4140u), kOff);
+      a[0][1] = hsub2_u32(prmt(p01, kM, 0x4342u), kOff);
+      a[0][2] = hsub2_u32(prmt(p23, kM, 0x4140u), kOff);
+      a[0][3] = hsub2_u32(prmt(p23, kM, 0x4342u), kOff);
+      a[1][0] = hsub2_u32(prmt(r01, kM, 0x4140u), kOff);
+      a[1][1] = hsub2_u32(prmt(r01, kM, 0x4342u), kOff);
+      a[1][2] = hsub2_u32(prmt(r23, kM, 0x4140u), kOff);
+      a[1][3] = hsub2_u32(prmt(r23, kM, 0x4342u), kOff);
+    }
+  }
+}
+
+// --------------------------------------------------------- cluster primitives
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+  }
+}
+
+#define MLD_CONSUMER_BARRIER() asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory")
+
+// W: weight boxes per stage (strip width up to W * 128 bytes per pass).
+// MONE: single-token launch (only token column 0 is kept).
+template <int BITS, int W, bool SUBNORMAL, bool MONE>
+__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
+    fc_strip_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
+                    StripArgs a) {
+  using F = Frag<BITS>;
+  constexpr int WT = W * F::BOX_N;       // outputs per pass
+  constexpr int NJ = MONE ? 2 : 4;       // accumulator values kept per fragment
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* red = reinterpret_cast<float*>(smem + (size_t)a.stages * a.stage_bytes);  // [warps][WT][red_m]
+  float* peer = red + kConsumerWarps * WT * a.red_m;                                // [WT][red_m]
+  uint64_t* full = reinterpret_cast<uint64_t*>(peer + ((WT * a.red_m + 1) & ~1));
+  uint64_t* empty = full + a.stages;
+  uint64_t* peer_bar = empty + a.stages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kr = a.ksplit > 1 ? static_cast<int>(cluster_ctarank()) : 0;
+  const int strip = blockIdx.x / a.ksplit;
+
+  // strip -> chunk range (16-byte chunks of a weight row), balanced to one unit
+  const int64_t u_lo = (int64_t)strip * a.units / a.strips, u_hi = (int64_t)(strip + 1) * a.units / a.strips;
+  const int cs = static_cast<int>(u_lo) * a.gran, ce = static_cast<int>(u_hi) * a.gran;
+  const int passes = (ce - cs + W * 8 - 1) / (W * 8);
+  const int r_lo = kr * a.rows_per_split;
+  const int r_hi = min(a.src_slices, r_lo + a.rows_per_split);
+  const int n_st = (r_hi - r_lo + kStageRows - 1) / kStageRows;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kConsumerWarps);
+    }
+    mbar_init(peer_bar, kConsumerWarps * 32);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (a.ksplit > 1) cluster_sync_all();  // the partner's barriers exist before anyone signals them
+  if (a.pdl) pdl_launch_dependents();
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0 && n_st > 0) {
+      prefetch_tmap(&tmap_w);
+      if (a.scale_rows > 0) prefetch_tmap(&tmap_s);
+      const uint64_t pol = policy_evict_first();
+      const int total = passes * n_st;
+      const uint32_t s_bytes = a.scale_rows > 0 ? static_cast<uint32_t>(a.scale_rows) * WT * 2u : 0u;
+      auto issue_weights = [&](int item, int stage) {
+        const int pass = item / n_st, si = item % n_st;
+        uint8_t* st = smem + (size_t)stage * a.stage_bytes;
+        const int row0 = r_lo + si * kStageRows;
+        const int rows = min(kStageRows, r_hi - row0);
+        const int chunk0 = cs + pass * W * 8;
+        mbar_arrive_expect_tx(&full[stage], W * kBoxBytes + s_bytes + static_cast<uint32_t>(rows) * a.M_total * 8u);
+#pragma unroll
+        for (int b = 0; b < W; ++b)
+          tma_load_2d_hint(st + b * kBoxBytes, &tmap_w, &full[stage], (chunk0 + b * 8) * 16, row0, pol);
+        if (a.scale_rows > 0)
+          tma_load_2d(st + W * kBoxBytes, &tmap_s, &full[stage], chunk0 * F::NPL, row0 / a.group_slices);
+      };
+      auto issue_x = [&](int item, int stage) {
+        const int si = item % n_st;
+        uint8_t* st = smem + (size_t)stage * a.stage_bytes;
+        const int row0 = r_lo + si * kStageRows;
+        const int rows = min(kStageRows, r_hi - row0);
+        bulk_load_1d(st + W * kBoxBytes + a.scale_stage_bytes,
+                     static_cast<const uint8_t*>(a.x) + (size_t)row0 * a.M_total * 8,
+                     static_cast<uint32_t>(rows) * a.M_total * 8u, &full[stage]);
+      };
+      // weights and scales are constants: the first ring-full of them is
+      // requested before waiting for the preceding kernel; activations after.
+      const int head = total < a.stages ? total : a.stages;
+      for (int it = 0; it < head; ++it) issue_weights(it, it);
+      if (a.pdl) pdl_wait();
+      for (int it = 0; it < head; ++it) issue_x(it, it);
+      int stage = head == a.stages ? 0 : head;
+      uint32_t phase = head == a.stages ? 1 : 0;
+      for (int it = head; it < total; ++it) {
+        if (!mbar_wait(&empty[stage], phase ^ 1)) {
+          atomicExch(a.error, 1);
+          break;
+        }
+        issue_weights(it, stage);
+        issue_x(it, stage);
+        if (++stage == a.stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int g = lane >> 2, t = lane & 3;
+  constexpr uint32_t kOnesA = BITS == 4 ? 0x00080008u : 0x00800080u;  // subnormal 8 / 128
+  constexpr float kOdd = BITS == 4 ? 0.0625f : 1.0f;                  // high nibbles are carried x16
+  constexpr float kOutScale = SUBNORMAL ? 16777216.0f : 1.0f;
+  const int rbase = warp * 8;
+  int stage = 0;
+  uint32_t phase = 0;
+  bool failed = false;
+
+  for (int pass = 0; pass < passes && !failed; ++pass) {
+    float tot[W][F::NF][NJ];
+#pragma unroll
+    for (int b = 0; b < W; ++b)
+#pragma unroll
+      for (int f = 0; f < F::NF; ++f)
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) tot[b][f][j] = 0.0f;
+
+    for (int si = 0; si < n_st; ++si) {
+      if (!mbar_wait(&full[stage], phase)) {
+        atomicExch(a.error, 2);
+        failed = true;
+        break;
+      }
+      const uint8_t* st = smem + (size_t)stage * a.stage_bytes;
+      const uint8_t* xs = st + W * kBoxBytes + a.scale_stage_bytes;
+      const int row0 = r_lo + si * kStageRows;
+      // activation fragments of this warp's eight rows (two steps)
+      uint32_t bx[2][2];
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        const int r = rbase + 2 * t + p;
+        bx[p][0] = bx[p][1] = 0u;
+        if (row0 + r < r_hi && g < a.M) {
+          const uint2 xv = *reinterpret_cast<const uint2*>(xs + ((size_t)r * a.M_total + a.tok0 + g) * 8);
+          bx[p][0] = xv.x;
+          bx[p][1] = xv.y;
+        }
+      }
+      float ones[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      if constexpr (SUBNORMAL) {
+        const uint32_t oa[4] = {kOnesA, kOnesA, kOnesA, kOnesA};
+        mma_f16(ones, oa, bx[0][0], bx[0][1]);
+        mma_f16(ones, oa, bx[1][0], bx[1][1]);
+      }
+      const int gidx = a.gs_shift >= 0 ? (rbase >> a.gs_shift) : 0;
+#pragma unroll
+      for (int b = 0; b < W; ++b) {
+        float grp[F::NF][4];
+#pragma unroll
+        for (int f = 0; f < F::NF; ++f) grp[f][0] = grp[f][1] = grp[f][2] = grp[f][3] = 0.0f;
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          const int r = rbase + 2 * t + p;
+          const uint4 q = *reinterpret_cast<const uint4*>(st + b * kBoxBytes + r * 128 + ((g ^ (r & 7)) << 4));
+          uint32_t av[F::NF][4];
+          unpack<BITS, SUBNORMAL>(q, av);
+#pragma unroll
+          for (int f = 0; f < F::NF; ++f) mma_f16(grp[f], av[f], bx[p][0], bx[p][1]);
+        }
+        // scales of this lane's outputs for the group these eight rows are in
+        float sc[F::NPL];
+        if (a.scale_rows > 0) {
+          const __half* sp = reinterpret_cast<const __half*>(st + W * kBoxBytes) + gidx * WT + b * F::BOX_N + F::NPL * g;
+          if constexpr (BITS == 4) {
+            const uint4 sv = *reinterpret_cast<const uint4*>(sp);
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&sv.z));
+            const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&sv.w));
+            sc[0] = f0.x; sc[1] = f0.y; sc[2] = f1.x; sc[3] = f1.y;
+            sc[4] = f2.x; sc[5] = f2.y; sc[6] = f3.x; sc[7] = f3.y;
+          } else {
+            const uint2 sv = *reinterpret_cast<const uint2*>(sp);
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
+            sc[0] = f0.x; sc[1] = f0.y; sc[2] = f1.x; sc[3] = f1.y;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < F::NPL; ++i) sc[i] = a.scalar_scale;
+        }
+        // row g of MMA f is output 2f, row g+8 is output 2f+1
+#pragma unroll
+        for (int f = 0; f < F::NF; ++f)
+#pragma unroll
+          for (int jj = 0; jj < NJ; ++jj) {
+            const int j = MONE ? 2 * jj : jj;  // MONE keeps (row g, token 2t) and (row g+8, token 2t)
+            const bool odd = (j & 2) != 0;
+            float v = grp[f][j];
+            if constexpr (SUBNORMAL) {
+              v = odd ? fmaf(v, kOdd, -ones[j & 1]) : (v - ones[j & 1]);
+            } else {
+              if (odd) v *= kOdd;
+            }
+            tot[b][f][jj] = fmaf(sc[2 * f + (odd ? 1 : 0)], v, tot[b][f][jj]);
+          }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[stage]);
+      if (++stage == a.stages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+    if (failed) break;
+
+    // ------------------------------------------------ pass epilogue
+#pragma unroll
+    for (int b = 0; b < W; ++b)
+#pragma unroll
+      for (int f = 0; f < F::NF; ++f)
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) {
+          const int j = MONE ? 2 * jj : jj;
+          const int n_local = b * F::BOX_N + F::NPL * g + 2 * f + ((j >> 1) & 1);
+          const int tok = 2 * t + (j & 1);
+          if (tok < a.M) red[(warp * WT + n_local) * a.red_m + tok] = tot[b][f][jj];
+        }
+    MLD_CONSUMER_BARRIER();
+    const int chunk0 = cs + pass * W * 8;
+    const int n0 = chunk0 * F::NPL;               // first output of this pass
+    const int n_end = min(ce * F::NPL, a.N4);      // one past the last output this CTA owns
+    const int nvals = WT * a.M;
+    uint32_t peer_remote = 0, bar_remote = 0;
+    if (a.ksplit > 1 && kr == 1) {
+      peer_remote = map_to_rank(smem_u32(peer), 0);
+      bar_remote = map_to_rank(smem_u32(peer_bar), 0);
+    }
+    if (a.ksplit > 1 && kr == 0) {
+      if (!mbar_wait_cluster(peer_bar, pass & 1)) {
+        atomicExch(a.error, 3);
+        failed = true;
+      }
+    }
+    for (int idx = threadIdx.x; idx < nvals && !failed; idx += kConsumerWarps * 32) {
+      const int n_local = idx / a.M, tok = idx - n_local * a.M;
+      float s = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) s += red[(w * WT + n_local) * a.red_m + tok];
+      if (a.ksplit > 1 && kr == 1) {
+        st_cluster_f32(peer_remote + (n_local * a.red_m + tok) * 4, s);
+        continue;
+      }
+      if (a.ksplit > 1) s += peer[n_local * a.red_m + tok];  // fixed order: lower half of K first
+      const int n = n0 + n_local;
+      if (n < n_end) {
+        __half r = __float2half_rn(s * kOutScale);
+        if (a.bias != nullptr) r = __hadd(r, static_cast<const __half*>(a.bias)[n]);
+        const int tk = a.tok0 + tok;
+        if (a.dst_layout == MLD_LAYOUT_SLICED)
+          static_cast<__half*>(a.y)[((int64_t)(n >> 2) * a.M_total + tk) * 4 + (n & 3)] = r;
+        else if (n < a.N)
+          static_cast<__half*>(a.y)[(int64_t)tk * a.N + n] = r;
+      }
+    }
+    if (a.ksplit > 1 && kr == 1) mbar_arrive_cluster(bar_remote);  // release: the stores above are visible
+    MLD_CONSUMER_BARRIER();
+  }
+}
+
+template <int BITS, int W, bool SUBNORMAL, bool MONE>
+int launch_strip_t(const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a, const StripGeometry& gm,
+                   cudaStream_t stream) {
+  auto kern = fc_strip_kernel<BITS, W, SUBNORMAL, MONE>;
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    MLD_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(gm.grid, 1, 1);
+  cfg.blockDim = dim3((kConsumerWarps + 1) * 32, 1, 1);
+  cfg.dynamicSmemBytes = gm.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  if (gm.ksplit > 1) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = gm.ksplit;
+    attrs[na].val.clusterDim.y = 1;
+    attrs[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (a.pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  MLD_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tw, ts, a));
+  count_launch();
+  return MLD_OK;
+}
+
+template <int BITS, int W>
+int launch_strip_w(bool subnormal, bool mone, const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a,
+                   const StripGeometry& gm, cudaStream_t stream) {
+  if (subnormal) {
+    if (mone) return launch_strip_t<BITS, W, true, true>(tw, ts, a, gm, stream);
+    return launch_strip_t<BITS, W, true, false>(tw, ts, a, gm, stream);
+  }
+  if (mone) return launch_strip_t<BITS, W, false, true>(tw, ts, a, gm, stream);
+  return launch_strip_t<BITS, W, false, false>(tw, ts, a, gm, stream);
+}
+
+}  // namespace
+
+StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slices, int scale_mode, int sms,
+                             bool pdl) {
+  StripGeometry gm;
+  memset(&gm, 0, sizeof gm);
+  const int N4 = align_n(N, 4), SS = div_up(K, 4);
+  const int box_n = bits == 4 ? 64 : 32;
+  const int row_bytes = (N4 / 4) * (bits == 4 ? 8 : 16);
+  gm.gran = bits == 4 ? 1 : 2;
+  const int C = row_bytes / 16;
+  gm.units = C / gm.gran;
+  // Two CTAs per strip (a cluster splitting K) when single strips would be
+  // narrower than 128 bytes and K is long enough to halve.
+  gm.ksplit = (C < 8 * sms && SS >= 4 * kStageRows && sms >= 2) ? 2 : 1;
+  int strips = sms / gm.ksplit;
+  if (strips > gm.units) strips = gm.units;
+  if (strips < 1) strips = 1;
+  gm.strips = strips;
+  gm.grid = strips * gm.ksplit;
+  const int max_width = div_up(gm.units, strips) * gm.gran;  // chunks
+  int w = div_up(max_width, 8);
+  if (gm.ksplit > 1 && w > 4) {  // a cluster pair runs a single pass
+    gm.ksplit = 1;
+    strips = sms < gm.units ? sms : gm.units;
+    gm.strips = strips;
+    gm.grid = strips;
+    w = div_up(div_up(gm.units, strips) * gm.gran, 8);
+  }
+  gm.w = w > 4 ? 4 : w;
+  gm.rows_per_split = gm.ksplit == 1 ? align_n(SS, kStageRows) : align_n(div_up(SS, 2), kStageRows);
+  if (scale_mode == MLD_SCALE_SCALAR) {
+    gm.scale_rows = 0;
+    gm.group_slices = 1;
+    gm.gs_shift = -1;
+  } else {
+    gm.group_slices = scale_mode == MLD_SCALE_PER_CHANNEL ? align_n(SS, kStageRows) : group_slices;
+    gm.scale_rows = gm.group_slices >= kStageRows ? 1 : kStageRows / gm.group_slices;
+    gm.gs_shift = -1;
+    if (gm.group_slices < kStageRows)
+      for (int sh = 3; sh < 6; ++sh)
+        if ((1 << sh) == gm.group_slices) gm.gs_shift = sh;
+  }
+  const int wt = gm.w * box_n;
+  gm.scale_stage_bytes = align_n(gm.scale_rows * wt * 2, 128);
+  const int x_bytes = align_n(kStageRows * m_total * 8, 128);
+  gm.stage_bytes = align_n(gm.w * kBoxBytes + gm.scale_stage_bytes + x_bytes, 1024);
+  gm.red_m = m_total < 8 ? m_total : 8;
+  const int fixed = (kConsumerWarps + 1) * wt * gm.red_m * 4 + 8 + (2 * 16 + 1) * 8 + 1024 + 64;
+  const int budget = pdl ? 112 * 1024 : 224 * 1024;
+  int stages = (budget - fixed) / gm.stage_bytes;
+  if (stages > 16) stages = 16;
+  if (stages < 2) stages = (227 * 1024 - fixed) / gm.stage_bytes;
+  gm.stages = stages;
+  gm.smem_bytes = (size_t)stages * gm.stage_bytes + fixed;
+  return gm;
+}
+
+int launch_fc_strip(int bits, bool subnormal, const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a,
+                    const StripGeometry& gm, cudaStream_t stream) {
+  if (a.M == 0 || gm.grid == 0) return MLD_OK;
+  const bool mone = a.M == 1;
+#define MLD_W(B, WV) \
+  case WV:           \
+    return launch_strip_w<B, WV>(subnormal, mone, tw, ts, a, gm, stream)
+  if (bits == 4) {
+    switch (gm.w) {
+      MLD_W(4, 1);
+      MLD_W(4, 2);
+      MLD_W(4, 3);
+      MLD_W(4, 4);
+    }
+  } else {
+    switch (gm.w) {
+      MLD_W(8, 1);
+      MLD_W(8, 2);
+      MLD_W(8, 3);
+      MLD_W(8, 4);
+    }
+  }
+#undef MLD_W
+  set_last_error_text("bad strip geometry");
+  return MLD_INVALID_ARGUMENT;
+}
+
+}  // namespace mld

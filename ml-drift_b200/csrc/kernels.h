@@ -35,35 +35,39 @@ struct GenericArgs {
 };
 int launch_fc_generic(const GenericArgs& a, int bits, bool f32, cudaStream_t stream);
 
-struct StreamArgs {
-  const void* x;      // fp16, sliced [K/4][M][4] (for M == 1 a plain vector)
+struct StripArgs {
+  const void* x;      // fp16, sliced [K/4][M_total][4] (for one token a plain vector)
   const void* bias;   // fp16 [N4] or null
   void* y;            // fp16
-  float* partials;    // split-K workspace
-  int* tickets;       // one per output tile, zero between launches
   int* error;         // device error word (0 = ok)
-  int M, N, N4;
+  int M;              // tokens handled by this launch (1..8)
+  int M_total;        // tokens in the x / y tensors
+  int tok0;           // first token handled by this launch
+  int N, N4;
   int src_slices;
-  int n_tiles, n_chunks;
+  int units, gran;    // strip granularity: `units` units of `gran` 16-byte chunks per weight row
+  int strips, ksplit;
+  int rows_per_split;
   int stages, stage_bytes, scale_stage_bytes;
   int scale_rows;     // rows of the per-stage scale box (0 = scalar scale)
   int group_slices;   // k-slices per scale group
-  int gs_shift;       // log2(group_slices) when it is a power of two <= 128, else -1
-  int max_pieces;
+  int gs_shift;       // log2(group_slices) when it is 8, 16 or 32, else -1
+  int red_m;          // token stride of the reduction buffers
   int dst_layout;
   float scalar_scale;
+  int pdl;            // launched with programmatic stream serialization
 };
 
-struct StreamGeometry {
-  int nb, tile_n, n_tiles, n_chunks;
+struct StripGeometry {
+  int gran, units, strips, ksplit, grid, w;
+  int rows_per_split;
   int scale_rows, group_slices, gs_shift;
-  int scale_stage_bytes, stage_bytes, stages;
+  int scale_stage_bytes, stage_bytes, stages, red_m;
   size_t smem_bytes;
-  int grid, max_pieces;
-  size_t partial_floats;
 };
-StreamGeometry stream_geometry(int bits, int N, int K, int M, int group_slices, int scale_mode, int sms);
-int launch_fc_stream(int bits, bool subnormal, const CUtensorMap& tw, const CUtensorMap& ts, const StreamArgs& a,
-                     const StreamGeometry& gm, cudaStream_t stream);
+StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slices, int scale_mode, int sms,
+                             bool pdl);
+int launch_fc_strip(int bits, bool subnormal, const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a,
+                    const StripGeometry& gm, cudaStream_t stream);
 
 }  // namespace mld

@@ -168,6 +168,11 @@ STREAM_CASES = [
     (4, 2048, 1024, 1024, 1), (4, 2048, 1024, 0, 1),
     (8, 2048, 2048, 0, 1),       # config-1 geometry with fp16 tensors
     (8, 4096, 1000, 0, 4), (8, 1024, 3584, 0, 16),
+    (4, 512, 65536, 32, 1),      # strips wider than four boxes: several column passes per CTA
+    (4, 1024, 40000, 128, 2),    # multi-pass with ragged last strip
+    (8, 8192, 3584, 0, 1),       # config-5 shard geometry, one token
+    (4, 256, 4096, 32, 1),       # K too short to split: narrow strips, one CTA each
+    (4, 1024, 8, 32, 1), (4, 1024, 16, 32, 3), (8, 1024, 8, 0, 1),   # a single chunk / unit
 ]
 
 
