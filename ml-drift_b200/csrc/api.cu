@@ -80,6 +80,8 @@ int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_
 
 using namespace mld;
 
+static int gm_stage_rows() { return strip_geometry(4, 64, 64, 1, 8, MLD_SCALE_BLOCK, 1, false).stage_rows; }
+
 // ------------------------------------------------------------------ plan type
 struct TmapEntry {
   const void* w;
@@ -222,7 +224,7 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
             p->sms > 0 && get_encode_tiled() != nullptr;
   if (d->scale_mode == MLD_SCALE_BLOCK) {
     const bool small = group_slices == 8 || group_slices == 16 || group_slices == 32;
-    const bool large = group_slices >= 64 && group_slices % 64 == 0;
+    const bool large = group_slices >= gm_stage_rows() && group_slices % gm_stage_rows() == 0;
     ok = ok && (small || large) && (group_slices * d->groups == src_slices);
   }
   p->stream_ok = ok;
@@ -299,7 +301,7 @@ static int run_stream(mld_fc_plan* p, const void* src, const void* weights, cons
       e.s = scale;
       e.geom = 0;
       const uint64_t blk = d.weight_bits == 4 ? 8 : 16;
-      int rc = make_tmap_2d(&e.tw, weights, (uint64_t)DS * blk, SS, (uint64_t)DS * blk, 128, 64, 1,
+      int rc = make_tmap_2d(&e.tw, weights, (uint64_t)DS * blk, SS, (uint64_t)DS * blk, 128, gm.stage_rows, 1,
                             CU_TENSOR_MAP_SWIZZLE_128B);
       if (rc != MLD_OK) return rc;
       if (gm.scale_rows > 0) {

@@ -32,8 +32,8 @@ namespace mld {
 namespace {
 
 constexpr int kConsumerWarps = 8;
-constexpr int kStageRows = 64;                 // k-slices per stage (256 input channels)
-constexpr int kBoxBytes = kStageRows * 128;    // one weight box: 64 rows x 128 bytes
+constexpr int kStageRows = kConsumerWarps * 8;  // k-slices per stage (256 input channels)
+constexpr int kBoxBytes = kStageRows * 128;     // one weight box: 64 rows x 128 bytes
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -524,7 +524,7 @@ StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slic
     gm.scale_rows = gm.group_slices >= kStageRows ? 1 : kStageRows / gm.group_slices;
     gm.gs_shift = -1;
     if (gm.group_slices < kStageRows)
-      for (int sh = 3; sh < 6; ++sh)
+      for (int sh = 3; sh < 7; ++sh)
         if ((1 << sh) == gm.group_slices) gm.gs_shift = sh;
   }
   const int wt = gm.w * box_n;
@@ -533,6 +533,9 @@ StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slic
   gm.stage_bytes = align_n(gm.w * kBoxBytes + gm.scale_stage_bytes + x_bytes, 1024);
   gm.red_m = m_total < 8 ? m_total : 8;
   const int fixed = (kConsumerWarps + 1) * wt * gm.red_m * 4 + 8 + (2 * 16 + 1) * 8 + 1024 + 64;
+  gm.stage_rows = kStageRows;
+  // With programmatic dependent launch two consecutive GEMVs share an SM while
+  // one drains and the next prefetches, so each takes at most half of it.
   const int budget = pdl ? 112 * 1024 : 224 * 1024;
   int stages = (budget - fixed) / gm.stage_bytes;
   if (stages > 16) stages = 16;

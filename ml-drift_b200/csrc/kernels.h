@@ -51,7 +51,7 @@ struct StripArgs {
   int stages, stage_bytes, scale_stage_bytes;
   int scale_rows;     // rows of the per-stage scale box (0 = scalar scale)
   int group_slices;   // k-slices per scale group
-  int gs_shift;       // log2(group_slices) when it is 8, 16 or 32, else -1
+  int gs_shift;       // log2(group_slices) when it is a power of two below a stage, else -1
   int red_m;          // token stride of the reduction buffers
   int dst_layout;
   float scalar_scale;
@@ -62,7 +62,7 @@ struct StripGeometry {
   int gran, units, strips, ksplit, grid, w;
   int rows_per_split;
   int scale_rows, group_slices, gs_shift;
-  int scale_stage_bytes, stage_bytes, stages, red_m;
+  int scale_stage_bytes, stage_bytes, stages, red_m, stage_rows;
   size_t smem_bytes;
 };
 StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slices, int scale_mode, int sms,
