@@ -185,6 +185,58 @@ MLD_API int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights,
                        const void* bias, void* dst, int32_t tokens,
                        void* stream);
 
+/* ------------------------------------------------------------------------ */
+/* Decode step: the callers of the FullyConnected path                       */
+/* ------------------------------------------------------------------------ */
+
+/* Geometry of a Llama-style decoder whose projections are INT4 block-quantized
+ * FullyConnected nodes - what samples/llm/qwen3_model_builder.cc:947-1038
+ * (SelfAttention, FFLayer, TransformerLayer) builds per layer, for one token.
+ * rank/world select the column shard this process holds (world == 1: all). */
+typedef struct mld_decoder_desc {
+  int32_t layers, d_model, heads, head_dim, ffn, max_seq;
+  int32_t block;                 /* INT4 scale block along K (32) */
+  float rms_eps;                 /* 1e-6 in the reference builder */
+  float rope_min_timescale;      /* 1 */
+  float rope_max_timescale;      /* 1e6 */
+  int32_t rank, world;
+  int32_t device;                /* -1 = current */
+} mld_decoder_desc;
+
+/* Device tensors of one layer, in the layouts named at the top of this file.
+ * Shard-local: wqkv packs the rows [q heads | k heads | v heads] of this rank
+ * (N = 3*d_model/world, K = d_model); wo N = d_model/world, K = d_model;
+ * wgu packs [gate rows | up rows] of this rank (N = 2*ffn/world, K = d_model);
+ * wdown N = d_model/world, K = ffn.  s* are the fp16 block scales [K/block][N].
+ * norm1/norm2: fp16 RMSNorm weights [d_model].  kcache/vcache: fp16
+ * [max_seq][heads/world * head_dim], updated in place at `pos`. */
+typedef struct mld_layer_weights {
+  const void *wqkv, *sqkv, *wo, *so, *wgu, *sgu, *wdown, *sdown;
+  const void *norm1, *norm2;
+  void *kcache, *vcache;
+} mld_layer_weights;
+
+typedef struct mld_decoder mld_decoder;
+
+/* 128-byte id shared by all ranks of a sharded decoder (rank 0 creates it and
+ * the caller distributes it).  No counterpart in the reference, which is
+ * single-device. */
+MLD_API int mld_comm_unique_id(void* id128);
+/* nccl_id128 may be NULL when world == 1.  Collective when world > 1. */
+MLD_API int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_decoder** out);
+MLD_API int mld_decoder_destroy(mld_decoder* dec);
+MLD_API size_t mld_decoder_scratch_bytes(const mld_decoder* dec);
+MLD_API int mld_decoder_set_layer(mld_decoder* dec, int32_t layer, const mld_layer_weights* w);
+/* One token through all layers (OpenCLLlmModelRunner::Decode,
+ * samples/llm/llm_opencl.cc:503-596, minus embedding lookup and sampling):
+ * x_in, x_out fp16 [d_model] device vectors; pos = index of the new token in
+ * the KV cache.  Enqueues on `stream` and returns. */
+MLD_API int mld_decoder_step(mld_decoder* dec, const void* x_in, void* x_out, int32_t pos, void* stream);
+/* The same step with host vectors: copies x_host to the device, runs the step,
+ * copies the result back and synchronises `stream` (the shape of the
+ * reference runner's per-token host round trip, llm_opencl.cc:503-596). */
+MLD_API int mld_decoder_step_host(mld_decoder* dec, const void* x_host, void* y_host, int32_t pos, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

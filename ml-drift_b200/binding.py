@@ -40,6 +40,18 @@ class FcDesc(C.Structure):
                 ("device", C.c_int32)]
 
 
+class DecoderDesc(C.Structure):
+    _fields_ = [("layers", C.c_int32), ("d_model", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+                ("ffn", C.c_int32), ("max_seq", C.c_int32), ("block", C.c_int32), ("rms_eps", C.c_float),
+                ("rope_min_timescale", C.c_float), ("rope_max_timescale", C.c_float), ("rank", C.c_int32),
+                ("world", C.c_int32), ("device", C.c_int32)]
+
+
+class LayerWeights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("wqkv", "sqkv", "wo", "so", "wgu", "sgu", "wdown", "sdown",
+                                          "norm1", "norm2", "kcache", "vcache")]
+
+
 _lib = None
 
 
@@ -55,6 +67,7 @@ def lib() -> C.CDLL:
         L.mld_kernel_launch_count.restype = C.c_int64
         L.mld_packed_size_bytes.restype = C.c_size_t
         L.mld_fc_plan_workspace_bytes.restype = C.c_size_t
+        L.mld_decoder_scratch_bytes.restype = C.c_size_t
         _lib = L
     return _lib
 
@@ -165,6 +178,54 @@ class FullyConnectedPlan:
     def close(self):
         if self._h:
             lib().mld_fc_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---------------------------------------------------------------- decode step
+def comm_unique_id() -> bytes:
+    buf = C.create_string_buffer(128)
+    _check(lib().mld_comm_unique_id(buf), "mld_comm_unique_id")
+    return buf.raw
+
+
+class Decoder:
+    """Owns one mld_decoder: a stack of decoder layers whose projections are INT4
+    FullyConnected nodes.  Layer tensors are torch tensors kept alive here."""
+
+    def __init__(self, layers, d_model, heads, ffn, max_seq, block=32, head_dim=128, rms_eps=1e-6,
+                 rope_min_timescale=1.0, rope_max_timescale=1.0e6, rank=0, world=1, nccl_id=None, device=-1):
+        self.desc = DecoderDesc(layers, d_model, heads, head_dim, ffn, max_seq, block, rms_eps,
+                                rope_min_timescale, rope_max_timescale, rank, world, device)
+        self._h = C.c_void_p()
+        self._keep = []
+        idbuf = None if nccl_id is None else C.create_string_buffer(nccl_id, 128)
+        _check(lib().mld_decoder_create(C.byref(self.desc), idbuf, C.byref(self._h)), "mld_decoder_create")
+
+    def set_layer(self, layer, **tensors):
+        lw = LayerWeights(*[tensors[n].data_ptr() for n, _ in LayerWeights._fields_])
+        self._keep.append(tensors)
+        _check(lib().mld_decoder_set_layer(self._h, layer, C.byref(lw)), "mld_decoder_set_layer")
+
+    def step(self, x_in, x_out, pos, stream=None):
+        _check(lib().mld_decoder_step(self._h, _ptr(x_in), _ptr(x_out), pos, _stream(stream)), "mld_decoder_step")
+
+    def step_host(self, x_host, y_host, pos, stream=None):
+        """x_host / y_host: pinned CPU fp16 tensors; includes both copies and a stream sync."""
+        _check(lib().mld_decoder_step_host(self._h, _ptr(x_host), _ptr(y_host), pos, _stream(stream)),
+               "mld_decoder_step_host")
+
+    def scratch_bytes(self):
+        return int(lib().mld_decoder_scratch_bytes(self._h))
+
+    def close(self):
+        if self._h:
+            lib().mld_decoder_destroy(self._h)
             self._h = C.c_void_p()
 
     def __del__(self):

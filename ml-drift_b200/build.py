@@ -9,7 +9,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libmldfc.so")
 
-SOURCES = ["api.cu", "pack_kernels.cu", "gemv_generic.cu", "gemv_stream.cu"]
+SOURCES = ["api.cu", "pack_kernels.cu", "gemv_generic.cu", "gemv_stream.cu", "decode_step.cu"]
 HEADERS = ["common.cuh", "kernels.h", os.path.join(ROOT, "include", "mldfc.h")]
 
 NVCC_FLAGS = [
@@ -58,6 +58,7 @@ def build(force=False, verbose=False):
     if failed:
         raise RuntimeError("nvcc failed")
     cmd = [_nvcc(), "-shared", "-o", OUT, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    cmd += ["-ldl"]
     subprocess.check_call(cmd)
     return OUT
 

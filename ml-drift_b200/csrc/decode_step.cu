@@ -1,0 +1,487 @@
+// One decode step of a Llama-style decoder whose seven projections per layer
+// are quantized FullyConnected nodes (the callers of the FC hot path in
+// ml_drift/samples/llm/qwen3_model_builder.cc:907-1038: Linear, FFLayer,
+// SelfAttention, TransformerLayer).  The FullyConnected nodes run through the
+// same plans mld_fc_run uses; the glue around them (RMSNorm, RoPE + KV-cache
+// update, decode attention, SiLU*mul, residual adds) is plain CUDA.
+//
+// Column sharding: with world > 1 every projection holds the rows of its own
+// output shard; shard outputs are concatenated by an all-gather before the next
+// full-width consumer (after attention, o_proj, SiLU*mul and down_proj).
+#include <cuda_fp16.h>
+#include <dlfcn.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mld {
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+// h = x (+ r); y = h * rsqrt(mean(h^2) + eps) * gamma.  One CTA.
+// RMSNormalization with epsilon 1e-6 and a gamma vector
+// (qwen3_model_builder.cc:890-902).  gamma == null: only h is written.
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ r,
+                                                          const __half* __restrict__ gamma, __half* __restrict__ h_out,
+                                                          __half* __restrict__ y, int d, float eps) {
+  __shared__ float part[32];
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = __half2float(x[i]);
+    if (r != nullptr) v = __half2float(__float2half_rn(v + __half2float(r[i])));
+    if (h_out != nullptr) h_out[i] = __float2half_rn(v);
+    ss += v * v;
+  }
+  if (gamma == nullptr) return;
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.0f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) part[0] = rsqrtf(t / static_cast<float>(d) + eps);
+  }
+  __syncthreads();
+  const float inv = part[0];
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v;
+    if (h_out != nullptr) {
+      v = __half2float(h_out[i]);  // written above by this same thread (h_out may alias x)
+    } else {
+      v = __half2float(x[i]);
+      if (r != nullptr) v = __half2float(__float2half_rn(v + __half2float(r[i])));
+    }
+    y[i] = __float2half_rn(v * inv * __half2float(gamma[i]));
+  }
+}
+
+// Split-half rotary embedding on q and k (common/kernels/rope.cc:70-89:
+// timescale = min * (max/min)^(2i/d), angle = pos / timescale,
+// out0 = v0 cos - v1 sin, out1 = v1 cos + v0 sin with (v0, v1) = (x[i], x[i+d/2]))
+// and the KV-cache write of the new token.  qkv = [q | k | v] of the local heads.
+__global__ void rope_kv_kernel(__half* __restrict__ qkv, __half* __restrict__ kcache, __half* __restrict__ vcache,
+                               int heads, int head_dim, int pos, float min_ts, float max_ts, float q_scale) {
+  const int head = blockIdx.x;           // 0 .. 2*heads-1 : q heads then k heads
+  const int half = head_dim / 2;
+  const int i = threadIdx.x;             // pair index
+  const int width = heads * head_dim;
+  if (i < half) {
+    const float fraction = 2.0f * i / static_cast<float>(head_dim);
+    const float timescale = min_ts * powf(max_ts / min_ts, fraction);
+    float s, c;
+    sincosf(static_cast<float>(pos) / timescale, &s, &c);
+    __half* p = qkv + (size_t)head * head_dim;
+    const float v0 = __half2float(p[i]), v1 = __half2float(p[i + half]);
+    const float o0 = v0 * c - v1 * s, o1 = v1 * c + v0 * s;
+    if (head < heads) {
+      p[i] = __float2half_rn(o0 * q_scale);
+      p[i + half] = __float2half_rn(o1 * q_scale);
+    } else {
+      const int kh = head - heads;
+      __half* kc = kcache + (size_t)pos * width + kh * head_dim;
+      kc[i] = __float2half_rn(o0);
+      kc[i + half] = __float2half_rn(o1);
+    }
+  }
+  if (head >= heads) {  // the matching v head
+    const int kh = head - heads;
+    const __half* v = qkv + (size_t)(2 * heads + kh) * head_dim;
+    __half* vc = vcache + (size_t)pos * width + kh * head_dim;
+    for (int j = threadIdx.x; j < head_dim; j += blockDim.x) vc[j] = v[j];
+  }
+}
+
+// Decode attention for one query token, split over the cached tokens.
+// grid (heads, splits), 128 threads.  Eight lanes share a token (16 dims each);
+// every 8-lane group keeps its own running max / sum / output and the groups
+// are merged at the end.  head_dim is fixed at 128.  Partial results:
+// part_o [heads][splits][128] fp32, part_ml [heads][splits][2] (max, sum).
+constexpr int kHeadDim = 128;
+__global__ void __launch_bounds__(128) attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ kcache,
+                                                          const __half* __restrict__ vcache, float* __restrict__ part_o,
+                                                          float* __restrict__ part_ml, int heads, int n_tokens,
+                                                          int splits) {
+  const int head = blockIdx.x, split = blockIdx.y;
+  const int per = (n_tokens + splits - 1) / splits;
+  const int t0 = split * per, t1 = min(n_tokens, t0 + per);
+  const int grp = threadIdx.x >> 3, sub = threadIdx.x & 7;  // 16 groups of 8 lanes
+  const int width = heads * kHeadDim;
+  float qv[16];
+  {
+    const __half* qp = q + (size_t)head * kHeadDim + sub * 16;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) qv[j] = __half2float(qp[j]);
+  }
+  float m = -INFINITY, l = 0.0f, acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+  for (int t = t0 + grp; t < t1; t += 16) {
+    const uint4* kp = reinterpret_cast<const uint4*>(kcache + (size_t)t * width + head * kHeadDim + sub * 16);
+    const uint4 k0 = kp[0], k1 = kp[1];
+    const __half2* kh = reinterpret_cast<const __half2*>(&k0);
+    const __half2* kh2 = reinterpret_cast<const __half2*>(&k1);
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = __half22float2(kh[j]), b = __half22float2(kh2[j]);
+      s += qv[2 * j] * a.x + qv[2 * j + 1] * a.y + qv[8 + 2 * j] * b.x + qv[8 + 2 * j + 1] * b.y;
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    const float m_new = fmaxf(m, s);
+    const float corr = __expf(m - m_new), p = __expf(s - m_new);
+    const uint4* vp = reinterpret_cast<const uint4*>(vcache + (size_t)t * width + head * kHeadDim + sub * 16);
+    const uint4 v0 = vp[0], v1 = vp[1];
+    const __half2* vh = reinterpret_cast<const __half2*>(&v0);
+    const __half2* vh2 = reinterpret_cast<const __half2*>(&v1);
+    l = l * corr + p;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = __half22float2(vh[j]), b = __half22float2(vh2[j]);
+      acc[2 * j] = acc[2 * j] * corr + p * a.x;
+      acc[2 * j + 1] = acc[2 * j + 1] * corr + p * a.y;
+      acc[8 + 2 * j] = acc[8 + 2 * j] * corr + p * b.x;
+      acc[8 + 2 * j + 1] = acc[8 + 2 * j + 1] * corr + p * b.y;
+    }
+    m = m_new;
+  }
+  // merge the 16 groups
+  __shared__ float sm_m[16], sm_l[16], sm_o[16][kHeadDim];
+  if (sub == 0) {
+    sm_m[grp] = m;
+    sm_l[grp] = l;
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) sm_o[grp][sub * 16 + j] = acc[j];
+  __syncthreads();
+  float gm = -INFINITY;
+#pragma unroll
+  for (int g = 0; g < 16; ++g) gm = fmaxf(gm, sm_m[g]);
+  const int dim = threadIdx.x;  // 128 threads, one output dim each
+  float o = 0.0f, lsum = 0.0f;
+#pragma unroll
+  for (int g = 0; g < 16; ++g) {
+    const float w = sm_m[g] == -INFINITY ? 0.0f : __expf(sm_m[g] - gm);
+    o += w * sm_o[g][dim];
+    lsum += w * sm_l[g];
+  }
+  part_o[((size_t)head * splits + split) * kHeadDim + dim] = o;
+  if (dim == 0) {
+    part_ml[((size_t)head * splits + split) * 2 + 0] = gm;
+    part_ml[((size_t)head * splits + split) * 2 + 1] = lsum;
+  }
+}
+
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part_o,
+                                                           const float* __restrict__ part_ml, __half* __restrict__ out,
+                                                           int splits) {
+  const int head = blockIdx.x, dim = threadIdx.x;
+  float gm = -INFINITY;
+  for (int s = 0; s < splits; ++s) gm = fmaxf(gm, part_ml[((size_t)head * splits + s) * 2]);
+  float o = 0.0f, l = 0.0f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[((size_t)head * splits + s) * 2];
+    const float w = ms == -INFINITY ? 0.0f : __expf(ms - gm);
+    o += w * part_o[((size_t)head * splits + s) * kHeadDim + dim];
+    l += w * part_ml[((size_t)head * splits + s) * 2 + 1];
+  }
+  out[(size_t)head * kHeadDim + dim] = __float2half_rn(o / l);
+}
+
+// act = silu(gate) * up over the local hidden slice (SiluMul,
+// qwen3_model_builder.cc:918-932); gu = [gate | up].
+__global__ void swiglu_kernel(const __half* __restrict__ gu, __half* __restrict__ act, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float g = __half2float(gu[i]), u = __half2float(gu[n + i]);
+  act[i] = __float2half_rn(g / (1.0f + __expf(-g)) * u);
+}
+
+// ---------------------------------------------------------------- NCCL (lazy)
+typedef struct ncclComm* ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+struct Nccl {
+  void* lib = nullptr;
+  int (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  int (*CommDestroy)(ncclComm_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  bool load() {
+    if (lib != nullptr) return true;
+    lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (lib == nullptr) return false;
+    GetUniqueId = reinterpret_cast<decltype(GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
+    CommInitRank = reinterpret_cast<decltype(CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
+    CommDestroy = reinterpret_cast<decltype(CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
+    AllGather = reinterpret_cast<decltype(AllGather)>(dlsym(lib, "ncclAllGather"));
+    GetErrorString = reinterpret_cast<decltype(GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
+    return GetUniqueId && CommInitRank && CommDestroy && AllGather;
+  }
+};
+Nccl g_nccl;
+constexpr int kNcclHalf = 6;  // ncclFloat16
+
+}  // namespace
+}  // namespace mld
+
+using namespace mld;
+
+struct mld_decoder {
+  mld_decoder_desc d;
+  int heads_local, d_local, ffn_local;
+  mld_fc_plan *p_qkv, *p_o, *p_gu, *p_down;
+  std::vector<mld_layer_weights> layers;
+  // scratch (owned)
+  __half *xn, *qkv, *attn_local, *attn_full, *o_local, *o_full, *h, *hn, *gu, *act_local, *act_full, *d_full, *x_stage, *y_stage;
+  float *part_o, *part_ml;
+  uint8_t* scratch;
+  int splits;
+  ncclComm_t comm;
+  size_t scratch_bytes;
+};
+
+namespace {
+
+int make_plan(int n, int k, int block, int device, mld_fc_plan** out) {
+  mld_fc_desc fd;
+  memset(&fd, 0, sizeof fd);
+  fd.n = n;
+  fd.k = k;
+  fd.weight_bits = 4;
+  fd.scale_mode = MLD_SCALE_BLOCK;
+  fd.groups = k / block;
+  fd.precision = MLD_PRECISION_F32F16;
+  fd.src_layout = MLD_LAYOUT_SLICED;
+  fd.dst_layout = MLD_LAYOUT_SLICED;
+  fd.max_tokens = 1;
+  fd.force_path = 1;
+  fd.device = device;
+  return mld_fc_plan_create(&fd, out);
+}
+
+int gather(mld_decoder* dec, const __half* send, __half* recv, int count, cudaStream_t stream) {
+  if (dec->d.world == 1) return MLD_OK;  // callers alias send == recv
+  const int rc = g_nccl.AllGather(send, recv, static_cast<size_t>(count), kNcclHalf, dec->comm, stream);
+  if (rc != 0) {
+    set_last_error_text(g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "ncclAllGather failed");
+    return MLD_NCCL_ERROR;
+  }
+  return MLD_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int mld_comm_unique_id(void* id128) {
+  MLD_REQUIRE(id128 != nullptr, "null id buffer");
+  if (!g_nccl.load()) {
+    set_last_error_text("libnccl.so.2 could not be loaded");
+    return MLD_NCCL_ERROR;
+  }
+  ncclUniqueId id;
+  if (g_nccl.GetUniqueId(&id) != 0) return MLD_NCCL_ERROR;
+  memcpy(id128, &id, sizeof id);
+  return MLD_OK;
+}
+
+int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_decoder** out) {
+  MLD_REQUIRE(d != nullptr && out != nullptr, "null argument");
+  *out = nullptr;
+  MLD_REQUIRE(d->layers > 0 && d->d_model > 0 && d->heads > 0 && d->ffn > 0 && d->max_seq > 0, "bad decoder shape");
+  MLD_REQUIRE(d->head_dim == kHeadDim, "head_dim must be 128");
+  MLD_REQUIRE(d->heads * d->head_dim == d->d_model, "heads * head_dim must equal d_model");
+  MLD_REQUIRE(d->world >= 1 && d->rank >= 0 && d->rank < d->world, "bad rank/world");
+  MLD_REQUIRE(d->heads % d->world == 0 && d->ffn % d->world == 0, "heads and ffn must divide by world");
+  MLD_REQUIRE(d->block > 0 && d->d_model % d->block == 0 && d->ffn % d->block == 0, "block must divide K");
+  MLD_REQUIRE(d->world == 1 || nccl_id128 != nullptr, "a multi-rank decoder needs the shared NCCL id");
+  int device = d->device;
+  if (device < 0) MLD_CUDA_CHECK(cudaGetDevice(&device));
+  MLD_CUDA_CHECK(cudaSetDevice(device));
+
+  mld_decoder* dec = new mld_decoder();
+  dec->d = *d;
+  dec->d.device = device;
+  dec->heads_local = d->heads / d->world;
+  dec->d_local = d->d_model / d->world;
+  dec->ffn_local = d->ffn / d->world;
+  dec->layers.resize(d->layers);
+  memset(dec->layers.data(), 0, sizeof(mld_layer_weights) * d->layers);
+  dec->comm = nullptr;
+  dec->scratch = nullptr;
+  dec->p_qkv = dec->p_o = dec->p_gu = dec->p_down = nullptr;
+  int rc = make_plan(3 * dec->d_local, d->d_model, d->block, device, &dec->p_qkv);
+  if (rc == MLD_OK) rc = make_plan(dec->d_local, d->d_model, d->block, device, &dec->p_o);
+  if (rc == MLD_OK) rc = make_plan(2 * dec->ffn_local, d->d_model, d->block, device, &dec->p_gu);
+  if (rc == MLD_OK) rc = make_plan(dec->d_local, d->ffn, d->block, device, &dec->p_down);
+  // split count: fill the GPU about four CTAs deep
+  int sms = sm_count(device);
+  int splits = (4 * sms) / dec->heads_local;
+  if (splits < 1) splits = 1;
+  if (splits > 64) splits = 64;
+  dec->splits = splits;
+  const size_t dm = d->d_model, ff = d->ffn;
+  auto pad = [](size_t bytes) { return (bytes + 255) & ~size_t(255); };  // bulk copies need 16-byte alignment
+  const size_t sizes_h[11] = {dm, 3 * (size_t)dec->d_local, dm, dm, dm, dm, 2 * (size_t)dec->ffn_local, ff, dm, dm, dm};
+  size_t total = 0;
+  for (size_t n : sizes_h) total += pad(n * 2);
+  total += pad((size_t)dec->heads_local * splits * kHeadDim * 4) + pad((size_t)dec->heads_local * splits * 2 * 4);
+  dec->scratch_bytes = total;
+  dec->scratch = nullptr;
+  if (rc == MLD_OK && cudaMalloc(&dec->scratch, total) != cudaSuccess) {
+    set_last_error_text("decoder scratch allocation failed");
+    rc = MLD_CUDA_ERROR;
+  }
+  if (rc != MLD_OK) {
+    mld_decoder_destroy(dec);
+    return rc;
+  }
+  cudaMemset(dec->scratch, 0, total);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    uint8_t* p = dec->scratch + off;
+    off += pad(bytes);
+    return p;
+  };
+  dec->xn = reinterpret_cast<__half*>(take(sizes_h[0] * 2));
+  dec->qkv = reinterpret_cast<__half*>(take(sizes_h[1] * 2));
+  dec->attn_full = reinterpret_cast<__half*>(take(sizes_h[2] * 2));
+  dec->o_full = reinterpret_cast<__half*>(take(sizes_h[3] * 2));
+  dec->h = reinterpret_cast<__half*>(take(sizes_h[4] * 2));
+  dec->hn = reinterpret_cast<__half*>(take(sizes_h[5] * 2));
+  dec->gu = reinterpret_cast<__half*>(take(sizes_h[6] * 2));
+  dec->act_full = reinterpret_cast<__half*>(take(sizes_h[7] * 2));
+  dec->d_full = reinterpret_cast<__half*>(take(sizes_h[8] * 2));
+  dec->x_stage = reinterpret_cast<__half*>(take(sizes_h[9] * 2));
+  dec->y_stage = reinterpret_cast<__half*>(take(sizes_h[10] * 2));
+  dec->part_o = reinterpret_cast<float*>(take((size_t)dec->heads_local * splits * kHeadDim * 4));
+  dec->part_ml = reinterpret_cast<float*>(take((size_t)dec->heads_local * splits * 2 * 4));
+  // a rank's shard of a gathered vector is written in place
+  dec->attn_local = dec->attn_full + (size_t)d->rank * dec->d_local;
+  dec->o_local = dec->o_full + (size_t)d->rank * dec->d_local;
+  dec->act_local = dec->act_full + (size_t)d->rank * dec->ffn_local;
+  if (d->world > 1) {
+    if (!g_nccl.load()) {
+      set_last_error_text("libnccl.so.2 could not be loaded");
+      mld_decoder_destroy(dec);
+      return MLD_NCCL_ERROR;
+    }
+    ncclUniqueId id;
+    memcpy(&id, nccl_id128, sizeof id);
+    const int nrc = g_nccl.CommInitRank(&dec->comm, d->world, id, d->rank);
+    if (nrc != 0) {
+      set_last_error_text(g_nccl.GetErrorString ? g_nccl.GetErrorString(nrc) : "ncclCommInitRank failed");
+      dec->comm = nullptr;
+      mld_decoder_destroy(dec);
+      return MLD_NCCL_ERROR;
+    }
+  }
+  *out = dec;
+  return MLD_OK;
+}
+
+int mld_decoder_destroy(mld_decoder* dec) {
+  if (dec == nullptr) return MLD_OK;
+  if (dec->comm != nullptr && g_nccl.CommDestroy) g_nccl.CommDestroy(dec->comm);
+  mld_fc_plan_destroy(dec->p_qkv);
+  mld_fc_plan_destroy(dec->p_o);
+  mld_fc_plan_destroy(dec->p_gu);
+  mld_fc_plan_destroy(dec->p_down);
+  if (dec->scratch != nullptr) cudaFree(dec->scratch);
+  delete dec;
+  return MLD_OK;
+}
+
+size_t mld_decoder_scratch_bytes(const mld_decoder* dec) { return dec ? dec->scratch_bytes : 0; }
+
+int mld_decoder_set_layer(mld_decoder* dec, int32_t layer, const mld_layer_weights* w) {
+  MLD_REQUIRE(dec != nullptr && w != nullptr, "null argument");
+  MLD_REQUIRE(layer >= 0 && layer < dec->d.layers, "layer index out of range");
+  MLD_REQUIRE(w->wqkv && w->sqkv && w->wo && w->so && w->wgu && w->sgu && w->wdown && w->sdown && w->norm1 &&
+                  w->norm2 && w->kcache && w->vcache,
+              "missing layer tensor");
+  dec->layers[layer] = *w;
+  return MLD_OK;
+}
+
+int mld_decoder_step(mld_decoder* dec, const void* x_in, void* x_out, int32_t pos, void* stream_v) {
+  MLD_REQUIRE(dec != nullptr && x_in != nullptr && x_out != nullptr, "null argument");
+  MLD_REQUIRE(pos >= 0 && pos < dec->d.max_seq, "position beyond the KV cache");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const mld_decoder_desc& d = dec->d;
+  const int dm = d.d_model, Hl = dec->heads_local, dl = dm / d.world, fl = dec->ffn_local;
+  const float q_scale = 1.0f / sqrtf(static_cast<float>(d.head_dim));
+  const __half* x = static_cast<const __half*>(x_in);
+  const __half* resid = nullptr;  // pending residual (the previous layer's down_proj output)
+  __half* d_local_ptr = dec->d_full + (size_t)d.rank * dl;
+  int rc;
+  for (int l = 0; l < d.layers; ++l) {
+    const mld_layer_weights& w = dec->layers[l];
+    MLD_REQUIRE(w.wqkv != nullptr, "layer weights not set");
+    // x_l = x_{l-1} + down_{l-1}; xn = rmsnorm(x_l)
+    __half* xl = l == 0 ? nullptr : dec->h;  // layer 0 reads x_in directly
+    add_rmsnorm_kernel<<<1, 1024, 0, stream>>>(x, resid, static_cast<const __half*>(w.norm1), xl, dec->xn, dm,
+                                               d.rms_eps);
+    MLD_LAUNCH_CHECK();
+    const __half* xcur = l == 0 ? x : dec->h;
+    rc = mld_fc_run(dec->p_qkv, dec->xn, w.wqkv, w.sqkv, nullptr, nullptr, dec->qkv, 1, stream);
+    if (rc != MLD_OK) return rc;
+    rope_kv_kernel<<<2 * Hl, 64, 0, stream>>>(dec->qkv, static_cast<__half*>(w.kcache), static_cast<__half*>(w.vcache),
+                                              Hl, d.head_dim, pos, d.rope_min_timescale, d.rope_max_timescale, q_scale);
+    MLD_LAUNCH_CHECK();
+    attn_decode_kernel<<<dim3(Hl, dec->splits), 128, 0, stream>>>(dec->qkv, static_cast<const __half*>(w.kcache),
+                                                                  static_cast<const __half*>(w.vcache), dec->part_o,
+                                                                  dec->part_ml, Hl, pos + 1, dec->splits);
+    MLD_LAUNCH_CHECK();
+    attn_combine_kernel<<<Hl, 128, 0, stream>>>(dec->part_o, dec->part_ml, dec->attn_local, dec->splits);
+    MLD_LAUNCH_CHECK();
+    if ((rc = gather(dec, dec->attn_local, dec->attn_full, dl, stream)) != MLD_OK) return rc;
+    rc = mld_fc_run(dec->p_o, dec->attn_full, w.wo, w.so, nullptr, nullptr, dec->o_local, 1, stream);
+    if (rc != MLD_OK) return rc;
+    if ((rc = gather(dec, dec->o_local, dec->o_full, dl, stream)) != MLD_OK) return rc;
+    // h = x_l + o; hn = rmsnorm(h)
+    add_rmsnorm_kernel<<<1, 1024, 0, stream>>>(xcur, dec->o_full, static_cast<const __half*>(w.norm2), dec->h,
+                                               dec->hn, dm, d.rms_eps);
+    MLD_LAUNCH_CHECK();
+    rc = mld_fc_run(dec->p_gu, dec->hn, w.wgu, w.sgu, nullptr, nullptr, dec->gu, 1, stream);
+    if (rc != MLD_OK) return rc;
+    swiglu_kernel<<<div_up(fl, 256), 256, 0, stream>>>(dec->gu, dec->act_local, fl);
+    MLD_LAUNCH_CHECK();
+    if ((rc = gather(dec, dec->act_local, dec->act_full, fl, stream)) != MLD_OK) return rc;
+    rc = mld_fc_run(dec->p_down, dec->act_full, w.wdown, w.sdown, nullptr, nullptr, d_local_ptr, 1, stream);
+    if (rc != MLD_OK) return rc;
+    if ((rc = gather(dec, d_local_ptr, dec->d_full, dl, stream)) != MLD_OK) return rc;
+    x = dec->h;
+    resid = dec->d_full;
+  }
+  // x_out = h + down of the last layer
+  add_rmsnorm_kernel<<<1, 1024, 0, stream>>>(x, resid, nullptr, static_cast<__half*>(x_out), nullptr, dm, d.rms_eps);
+  MLD_LAUNCH_CHECK();
+  return MLD_OK;
+}
+
+int mld_decoder_step_host(mld_decoder* dec, const void* x_host, void* y_host, int32_t pos, void* stream_v) {
+  MLD_REQUIRE(dec != nullptr && x_host != nullptr && y_host != nullptr, "null argument");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const size_t bytes = static_cast<size_t>(dec->d.d_model) * 2;
+  MLD_CUDA_CHECK(cudaMemcpyAsync(dec->x_stage, x_host, bytes, cudaMemcpyHostToDevice, stream));
+  const int rc = mld_decoder_step(dec, dec->x_stage, dec->y_stage, pos, stream);
+  if (rc != MLD_OK) return rc;
+  MLD_CUDA_CHECK(cudaMemcpyAsync(y_host, dec->y_stage, bytes, cudaMemcpyDeviceToHost, stream));
+  MLD_CUDA_CHECK(cudaStreamSynchronize(stream));
+  return MLD_OK;
+}
+
+}  // extern "C"

@@ -446,8 +446,7 @@ int launch_strip_t(const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs
     MLD_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     configured = true;
   }
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof cfg);
+  cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(gm.grid, 1, 1);
   cfg.blockDim = dim3((kConsumerWarps + 1) * 32, 1, 1);
   cfg.dynamicSmemBytes = gm.smem_bytes;
