@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __half* __restri
   float m = -INFINITY, l = 0.0f, acc[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+  const unsigned gmask = 0xFFu << (threadIdx.x & 24);
   for (int t = t0 + grp; t < t1; t += 16) {
     const uint4* kp = reinterpret_cast<const uint4*>(kcache + (size_t)t * width + head * kHeadDim + sub * 16);
     const uint4 k0 = kp[0], k1 = kp[1];
@@ -136,9 +137,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __half* __restri
       const float2 a = __half22float2(kh[j]), b = __half22float2(kh2[j]);
       s += qv[2 * j] * a.x + qv[2 * j + 1] * a.y + qv[8 + 2 * j] * b.x + qv[8 + 2 * j + 1] * b.y;
     }
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    // the eight lanes of a token group run this loop together; other groups of
+    // the warp may have a different trip count, so the shuffle names only them
+    s += __shfl_xor_sync(gmask, s, 1);
+    s += __shfl_xor_sync(gmask, s, 2);
+    s += __shfl_xor_sync(gmask, s, 4);
     const float m_new = fmaxf(m, s);
     const float corr = __expf(m - m_new), p = __expf(s - m_new);
     const uint4* vp = reinterpret_cast<const uint4*>(vcache + (size_t)t * width + head * kHeadDim + sub * 16);
