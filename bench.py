@@ -257,6 +257,69 @@ def gemv_roofline(mld, torch, layers, world, peaks):
             "algorithmic_bytes_per_launch": algo / launches}
 
 
+def side_benchmarks(mld, torch, peaks):
+    """The two kernel-level figures the metric also names: decode GEMV bandwidth on BASELINE
+    config 2 and prefill GEMM throughput on config 3, each timed alone with CUDA events."""
+    out = {}
+    # config 2: N=16384, K=2048, INT4 block 32, one token; 16 weight sets (303 MB) rotate to defeat L2
+    N, K, blk, sets = 16384, 2048, 32, 16
+    plan = mld.FullyConnectedPlan(N, K, 4, scale_mode=mld.SCALE_BLOCK, groups=K // blk, precision=mld.F32F16)
+    nbytes = mld.packed_size_bytes(N, K, 4)
+    ws = [torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device="cuda") for _ in range(sets)]
+    ss = [(torch.rand((K // blk, N), device="cuda") * 0.01).half() for _ in range(sets)]
+    x = torch.randn(K, device="cuda").half()
+    y = torch.empty(N, dtype=torch.float16, device="cuda")
+    for i in range(2 * sets):
+        plan.run(x, ws[i % sets], ss[i % sets], y, 1)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters = 20 * sets
+    e0.record()
+    for i in range(iters):
+        plan.run(x, ws[i % sets], ss[i % sets], y, 1)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / iters
+    algo = nbytes + (K // blk) * N * 2 + K * 2 + N * 2
+    peak = peaks.get("hbm_gbs") or 6650.0
+    out["fc_gemv_config2"] = {"workload": "INT4 block-32 GEMV N=16384 K=2048, 1 token, 16 rotating weight sets",
+                              "us_per_launch": us, "GBps": algo / us / 1e3, "frac_of_hbm_peak": algo / us / 1e3 / peak,
+                              "algorithmic_bytes": algo}
+    plan.close()
+    del ws, ss
+    # config 3: M=1024, K=4096, N=14336
+    M, K, N = 1024, 4096, 14336
+    g = torch.Generator(device="cuda").manual_seed(0)
+    w = torch.randn((N, K), generator=g, device="cuda") * 0.02
+    q, s = mld.quantize_weights(w, 4, blk)
+    packed, _ = mld.pack_weights(q, (N, 1, 1, K), 4)
+    sc = mld.pack_scales(s, True)
+    del w, q, s
+    xs = torch.randn((K // 4, M, 4), generator=g, device="cuda").half()
+    yy = torch.empty((N // 4, M, 4), dtype=torch.float16, device="cuda")
+    flops = 2.0 * M * K * N
+    res = {}
+    for label, cache in (("with_weight_conversion", False), ("weights_prepared_once", True)):
+        plan = mld.FullyConnectedPlan(N, K, 4, scale_mode=mld.SCALE_BLOCK, groups=K // blk, precision=mld.F32F16,
+                                      max_tokens=M, force_path=mld.PATH_GEMM, cache_prepared_weights=cache)
+        for _ in range(3):
+            plan.run(xs, packed, sc, yy, M)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(20):
+            plan.run(xs, packed, sc, yy, M)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / 20
+        res[label] = {"us": us, "TFLOPs": flops / us / 1e6}
+        plan.close()
+    pk = peaks.get("bf16_tflops") or 1590.0
+    out["prefill_config3"] = {"workload": "INT4 block-32 GEMM M=1024 K=4096 N=14336, fp16 in, fp32 accumulate", **res,
+                              "frac_of_bf16_burst_peak": res["weights_prepared_once"]["TFLOPs"] / pk,
+                              "frac_with_conversion": res["with_weight_conversion"]["TFLOPs"] / pk, "peak_TFLOPs": pk}
+    return out
+
+
 def run_ours(args):
     import torch
     import __graft_entry__ as g
@@ -361,6 +424,15 @@ def run_ours(args):
     e2e_tok_s = args.steps / (e2e_ms * 1e-3)
 
     roof = gemv_roofline(mld, torch, layers, world, peaks) if rank == 0 or world > 1 else None
+    side = None
+    if rank == 0 and world == 1:
+        dec.close()
+        del layers
+        torch.cuda.empty_cache()
+        try:
+            side = side_benchmarks(mld, torch, peaks)
+        except Exception as exc:  # noqa: BLE001
+            side = {"error": str(exc)}
     cpu = None
     if rank == 0 and world == 1:
         tok_cpu, cores, _ = time_cpu(2, reps=3, warm=1)
@@ -380,7 +452,7 @@ def run_ours(args):
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": d * 2, "d2h_bytes_per_step": d * 2},
             "gpu_launches": int(launches_per_step) * args.steps,
             "launches_per_step": int(launches_per_step),
-            "roofline": roof, "cpu_baseline": cpu, "clocks": clocks,
+            "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "kernels": side,
         }
         print(json.dumps(line), flush=True)
     dec.close()

@@ -155,6 +155,17 @@ typedef struct mld_fc_desc {
   int32_t force_path;        /* 0 = IsFullyConnectedRecommended rule,
                                 1 = decode GEMV kernel, 2 = prefill GEMM */
   int32_t device;            /* CUDA device ordinal, -1 = current */
+  int32_t prefill_act_quant; /* prefill GEMM only: 0 = float activations
+                                (WeightsConverter + float conv route,
+                                gpu_model_builder.cc:1110-1276); 1 = per-token
+                                symmetric int8 activations x int8 weights
+                                (FullyConnectedInt8QuantizedWithSrcQuantization,
+                                gpu_model_builder.cc:1325-1431; per-channel
+                                INT8 weights only) */
+  int32_t cache_prepared_weights; /* prefill GEMM only: keep the K-major copy of
+                                the weights between calls while the weights and
+                                scale pointers stay the same (the caller
+                                promises not to modify them in between) */
 } mld_fc_desc;
 
 typedef struct mld_fc_plan mld_fc_plan;
@@ -215,6 +226,17 @@ typedef struct mld_layer_weights {
   const void *norm1, *norm2;
   void *kcache, *vcache;
 } mld_layer_weights;
+
+/* Decode attention of one query token over an fp16 KV cache: what the
+ * reference assembles from FullyConnected(q, K-cache) -> mask -> SoftmaxReduce
+ * -> FullyConnected(p, V-cache) (samples/llm/qwen3_model_builder.cc:983-1017),
+ * as one split-KV pass.  q: fp16 [heads][128], already scaled and rotated;
+ * kcache/vcache: fp16 [n_tokens][heads*128]; out: fp16 [heads][128].  Partial
+ * results live in a per-device scratch buffer the library allocates on first
+ * use and grows when a larger shape arrives (calls on one device must not
+ * overlap on different streams). */
+MLD_API int mld_attn_decode(const void* q, const void* kcache, const void* vcache, void* out, int32_t heads,
+                            int32_t head_dim, int32_t n_tokens, void* stream);
 
 typedef struct mld_decoder mld_decoder;
 

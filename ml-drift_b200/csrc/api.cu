@@ -101,6 +101,12 @@ struct mld_fc_plan {
   StripGeometry gm;
   int* error;            // device error word written by kernels whose bounded waits ran out
   size_t ws_bytes;
+  // prefill GEMM workspace (allocated on first use)
+  void* w_kmajor;        // dequantised fp16 / re-biased s8 weights, [N4][kp]
+  void* x_kmajor;        // activations, [max_tokens][kp]
+  float* a_params;       // per-token {inv_scale, offset, sum}
+  const void* prepared_w;
+  const void* prepared_s;
   std::vector<TmapEntry> tmaps;  // tensor maps keyed by the (weights, scale) pointers last seen
   std::mutex mu;
 };
@@ -197,6 +203,10 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   MLD_REQUIRE(d->src_layout == MLD_LAYOUT_SLICED || d->src_layout == MLD_LAYOUT_ROW_MAJOR, "bad src layout");
   MLD_REQUIRE(d->dst_layout == MLD_LAYOUT_SLICED || d->dst_layout == MLD_LAYOUT_ROW_MAJOR, "bad dst layout");
   MLD_REQUIRE(d->max_tokens >= 1, "max_tokens must be at least 1");
+  MLD_REQUIRE(d->prefill_act_quant == 0 || d->prefill_act_quant == 1, "bad prefill_act_quant");
+  if (d->prefill_act_quant == 1)
+    MLD_REQUIRE(d->weight_bits == 8 && d->scale_mode == MLD_SCALE_PER_CHANNEL && !d->has_zero_point,
+                "int8-activation prefill needs per-channel INT8 weights without zero points");
   const int src_slices = div_up(d->k, 4);
   int group_slices = src_slices;
   if (d->scale_mode == MLD_SCALE_BLOCK) {
@@ -214,6 +224,9 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   p->group_slices = group_slices;
   p->error = nullptr;
   p->ws_bytes = 0;
+  p->w_kmajor = p->x_kmajor = nullptr;
+  p->a_params = nullptr;
+  p->prepared_w = p->prepared_s = nullptr;
   const char* enc = getenv("MLD_GEMV_OPERANDS");  // "exact" or "subnormal"
   p->subnormal = !(enc != nullptr && strcmp(enc, "exact") == 0);
   const char* pdl = getenv("MLD_GEMV_PDL");        // "0" disables programmatic dependent launch
@@ -252,6 +265,9 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
 int mld_fc_plan_destroy(mld_fc_plan* plan) {
   if (plan == nullptr) return MLD_OK;
   if (plan->error) cudaFree(plan->error);
+  if (plan->w_kmajor) cudaFree(plan->w_kmajor);
+  if (plan->x_kmajor) cudaFree(plan->x_kmajor);
+  if (plan->a_params) cudaFree(plan->a_params);
   delete plan;
   return MLD_OK;
 }
@@ -353,6 +369,40 @@ static int run_stream(mld_fc_plan* p, const void* src, const void* weights, cons
   return MLD_OK;
 }
 
+// Prefill: operand preparation + tcgen05 GEMM.
+static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const void* scale, const void* bias,
+                    void* dst, int tokens, cudaStream_t stream) {
+  const mld_fc_desc& d = p->d;
+  const bool i8 = d.prefill_act_quant == 1;
+  const GemmGeometry g = gemm_geometry(tokens, d.n, d.k, i8, p->sms);
+  const int N4 = align_n(d.n, 4);
+  const size_t esz = i8 ? 1 : 2;
+  if (p->w_kmajor == nullptr) {
+    const GemmGeometry gmax = gemm_geometry(d.max_tokens, d.n, d.k, i8, p->sms);
+    MLD_CUDA_CHECK(cudaMalloc(&p->w_kmajor, (size_t)N4 * gmax.kp * esz));
+    MLD_CUDA_CHECK(cudaMalloc(&p->x_kmajor, (size_t)d.max_tokens * gmax.kp * esz));
+    MLD_CUDA_CHECK(cudaMalloc(&p->a_params, (size_t)d.max_tokens * 3 * sizeof(float)));
+    p->ws_bytes += (size_t)N4 * gmax.kp * esz + (size_t)d.max_tokens * gmax.kp * esz + (size_t)d.max_tokens * 12;
+  }
+  int rc;
+  const bool reuse = d.cache_prepared_weights && p->prepared_w == weights && p->prepared_s == scale;
+  if (!reuse) {
+    rc = launch_dequant_weights(d.weight_bits, i8, weights, scale, d.scale_mode,
+                                d.scale_mode == MLD_SCALE_BLOCK ? d.groups : 1, p->group_slices, d.scalar_scale, d.n,
+                                d.k, g.kp, p->w_kmajor, stream);
+    if (rc != MLD_OK) return rc;
+    p->prepared_w = weights;
+    p->prepared_s = scale;
+  }
+  if (i8)
+    rc = launch_quantize_act(src, d.src_layout, tokens, d.k, g.kp, p->x_kmajor, p->a_params, stream);
+  else
+    rc = launch_transpose_x(src, d.src_layout, tokens, d.k, g.kp, p->x_kmajor, stream);
+  if (rc != MLD_OK) return rc;
+  return launch_gemm_umma(i8, p->x_kmajor, p->w_kmajor, g, tokens, d.n, d.k, bias, scale, p->a_params, dst,
+                          d.dst_layout, p->error, stream);
+}
+
 int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const void* scale, const void* zero_point,
                const void* bias, void* dst, int32_t tokens, void* stream_v) {
   MLD_REQUIRE(plan != nullptr, "null plan");
@@ -370,8 +420,16 @@ int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const vo
   int path = d.force_path;
   if (path == 0) path = mld_fc_is_gemv_recommended(d.precision, tokens) ? 1 : 2;
   if (path == 2) {
-    set_last_error_text("prefill GEMM path is not built into this library yet");
-    return MLD_UNIMPLEMENTED;
+    // the tensor-core route takes fp16 tensors without zero points; anything
+    // else is served, correctly but slowly, by the general kernel below
+    const bool gemm_ok = d.precision != MLD_PRECISION_F32 && !d.has_zero_point && get_encode_tiled() != nullptr &&
+                         (reinterpret_cast<uintptr_t>(src) & 7) == 0;
+    if (gemm_ok) return run_gemm(plan, src, weights, scale, b, dst, tokens, stream);
+    if (d.prefill_act_quant != 0) {
+      set_last_error_text("quantised-activation prefill needs fp16 tensors and no zero points");
+      return MLD_UNIMPLEMENTED;
+    }
+    return run_generic(plan, src, weights, scale, zp, b, dst, tokens, stream);
   }
   const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
                        (scale == nullptr || (reinterpret_cast<uintptr_t>(scale) & 15) == 0);

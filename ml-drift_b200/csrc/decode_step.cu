@@ -13,7 +13,9 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -35,6 +37,8 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __half* __restr
                                                           const __half* __restrict__ gamma, __half* __restrict__ h_out,
                                                           __half* __restrict__ y, int d, float eps) {
   __shared__ float part[32];
+  pdl_wait();
+  pdl_launch_dependents();
   float ss = 0.0f;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = __half2float(x[i]);
@@ -71,6 +75,8 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __half* __restr
 // and the KV-cache write of the new token.  qkv = [q | k | v] of the local heads.
 __global__ void rope_kv_kernel(__half* __restrict__ qkv, __half* __restrict__ kcache, __half* __restrict__ vcache,
                                int heads, int head_dim, int pos, float min_ts, float max_ts, float q_scale) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int head = blockIdx.x;           // 0 .. 2*heads-1 : q heads then k heads
   const int half = head_dim / 2;
   const int i = threadIdx.x;             // pair index
@@ -111,6 +117,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __half* __restri
                                                           const __half* __restrict__ vcache, float* __restrict__ part_o,
                                                           float* __restrict__ part_ml, int heads, int n_tokens,
                                                           int splits) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int head = blockIdx.x, split = blockIdx.y;
   const int per = (n_tokens + splits - 1) / splits;
   const int t0 = split * per, t1 = min(n_tokens, t0 + per);
@@ -189,6 +197,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __half* __restri
 __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part_o,
                                                            const float* __restrict__ part_ml, __half* __restrict__ out,
                                                            int splits) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int head = blockIdx.x, dim = threadIdx.x;
   float gm = -INFINITY;
   for (int s = 0; s < splits; ++s) gm = fmaxf(gm, part_ml[((size_t)head * splits + s) * 2]);
@@ -205,11 +215,59 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
 // act = silu(gate) * up over the local hidden slice (SiluMul,
 // qwen3_model_builder.cc:918-932); gu = [gate | up].
 __global__ void swiglu_kernel(const __half* __restrict__ gu, __half* __restrict__ act, int n) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float g = __half2float(gu[i]), u = __half2float(gu[n + i]);
   act[i] = __float2half_rn(g / (1.0f + __expf(-g)) * u);
 }
+
+// Launches a glue kernel so that it may be scheduled while its predecessor in
+// the stream drains (programmatic dependent launch); every glue kernel starts
+// with griddepcontrol.wait, so it touches memory only after the predecessor
+// has completed.
+bool g_glue_pdl = true;
+template <typename... KArgs, typename... Args>
+int launch_glue(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_glue_pdl ? 1 : 0;
+  MLD_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...));
+  count_launch();
+  return MLD_OK;
+}
+
+// Split count that fills the GPU about four CTAs deep.
+int attn_splits(int heads, int sms) {
+  int splits = (4 * sms) / (heads > 0 ? heads : 1);
+  if (splits < 1) splits = 1;
+  if (splits > 64) splits = 64;
+  return splits;
+}
+
+int launch_attn_decode(const __half* q, const __half* kcache, const __half* vcache, float* part_o, float* part_ml,
+                       __half* out, int heads, int n_tokens, int splits, cudaStream_t stream) {
+  int rc = launch_glue(attn_decode_kernel, dim3(heads, splits), dim3(128), stream, q, kcache, vcache, part_o, part_ml,
+                       heads, n_tokens, splits);
+  if (rc != MLD_OK) return rc;
+  return launch_glue(attn_combine_kernel, dim3(heads), dim3(128), stream, part_o, part_ml, out, splits);
+}
+
+// Grow-only per-device scratch of mld_attn_decode.
+struct AttnScratch {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+AttnScratch g_attn_scratch[64];
+std::mutex g_attn_mu;
 
 // ---------------------------------------------------------------- NCCL (lazy)
 typedef struct ncclComm* ncclComm_t;
@@ -300,6 +358,34 @@ int mld_comm_unique_id(void* id128) {
   return MLD_OK;
 }
 
+int mld_attn_decode(const void* q, const void* kcache, const void* vcache, void* out, int32_t heads,
+                    int32_t head_dim, int32_t n_tokens, void* stream) {
+  MLD_REQUIRE(q != nullptr && kcache != nullptr && vcache != nullptr && out != nullptr, "null tensor");
+  MLD_REQUIRE(head_dim == kHeadDim, "head_dim must be 128");
+  MLD_REQUIRE(heads > 0 && n_tokens > 0, "bad shape");
+  int device = 0;
+  MLD_CUDA_CHECK(cudaGetDevice(&device));
+  MLD_REQUIRE(device < 64, "device ordinal too large");
+  const int splits = attn_splits(heads, sm_count(device));
+  const size_t need = (size_t)heads * splits * (kHeadDim + 2) * sizeof(float);
+  float* base;
+  {
+    std::lock_guard<std::mutex> lock(g_attn_mu);
+    AttnScratch& sc = g_attn_scratch[device];
+    if (sc.bytes < need) {
+      if (sc.ptr != nullptr) MLD_CUDA_CHECK(cudaFree(sc.ptr));
+      sc.ptr = nullptr;
+      sc.bytes = 0;
+      MLD_CUDA_CHECK(cudaMalloc(&sc.ptr, need));
+      sc.bytes = need;
+    }
+    base = static_cast<float*>(sc.ptr);
+  }
+  return launch_attn_decode(static_cast<const __half*>(q), static_cast<const __half*>(kcache),
+                            static_cast<const __half*>(vcache), base, base + (size_t)heads * splits * kHeadDim,
+                            static_cast<__half*>(out), heads, n_tokens, splits, static_cast<cudaStream_t>(stream));
+}
+
 int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_decoder** out) {
   MLD_REQUIRE(d != nullptr && out != nullptr, "null argument");
   *out = nullptr;
@@ -314,6 +400,10 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   if (device < 0) MLD_CUDA_CHECK(cudaGetDevice(&device));
   MLD_CUDA_CHECK(cudaSetDevice(device));
 
+  {
+    const char* pdl = getenv("MLD_GEMV_PDL");  // "0" disables programmatic dependent launch everywhere
+    g_glue_pdl = !(pdl != nullptr && strcmp(pdl, "0") == 0);
+  }
   mld_decoder* dec = new mld_decoder();
   dec->d = *d;
   dec->d.device = device;
@@ -331,9 +421,7 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   if (rc == MLD_OK) rc = make_plan(dec->d_local, d->ffn, d->block, device, &dec->p_down);
   // split count: fill the GPU about four CTAs deep
   int sms = sm_count(device);
-  int splits = (4 * sms) / dec->heads_local;
-  if (splits < 1) splits = 1;
-  if (splits > 64) splits = 64;
+  const int splits = attn_splits(dec->heads_local, sms);
   dec->splits = splits;
   const size_t dm = d->d_model, ff = d->ffn;
   auto pad = [](size_t bytes) { return (bytes + 255) & ~size_t(255); };  // bulk copies need 16-byte alignment
@@ -435,33 +523,32 @@ int mld_decoder_step(mld_decoder* dec, const void* x_in, void* x_out, int32_t po
     MLD_REQUIRE(w.wqkv != nullptr, "layer weights not set");
     // x_l = x_{l-1} + down_{l-1}; xn = rmsnorm(x_l)
     __half* xl = l == 0 ? nullptr : dec->h;  // layer 0 reads x_in directly
-    add_rmsnorm_kernel<<<1, 1024, 0, stream>>>(x, resid, static_cast<const __half*>(w.norm1), xl, dec->xn, dm,
-                                               d.rms_eps);
-    MLD_LAUNCH_CHECK();
+    rc = launch_glue(add_rmsnorm_kernel, dim3(1), dim3(1024), stream, x, resid, static_cast<const __half*>(w.norm1), xl,
+                     dec->xn, dm, d.rms_eps);
+    if (rc != MLD_OK) return rc;
     const __half* xcur = l == 0 ? x : dec->h;
     rc = mld_fc_run(dec->p_qkv, dec->xn, w.wqkv, w.sqkv, nullptr, nullptr, dec->qkv, 1, stream);
     if (rc != MLD_OK) return rc;
-    rope_kv_kernel<<<2 * Hl, 64, 0, stream>>>(dec->qkv, static_cast<__half*>(w.kcache), static_cast<__half*>(w.vcache),
-                                              Hl, d.head_dim, pos, d.rope_min_timescale, d.rope_max_timescale, q_scale);
-    MLD_LAUNCH_CHECK();
-    attn_decode_kernel<<<dim3(Hl, dec->splits), 128, 0, stream>>>(dec->qkv, static_cast<const __half*>(w.kcache),
-                                                                  static_cast<const __half*>(w.vcache), dec->part_o,
-                                                                  dec->part_ml, Hl, pos + 1, dec->splits);
-    MLD_LAUNCH_CHECK();
-    attn_combine_kernel<<<Hl, 128, 0, stream>>>(dec->part_o, dec->part_ml, dec->attn_local, dec->splits);
-    MLD_LAUNCH_CHECK();
+    rc = launch_glue(rope_kv_kernel, dim3(2 * Hl), dim3(64), stream, dec->qkv, static_cast<__half*>(w.kcache),
+                     static_cast<__half*>(w.vcache), Hl, d.head_dim, pos, d.rope_min_timescale, d.rope_max_timescale,
+                     q_scale);
+    if (rc != MLD_OK) return rc;
+    rc = launch_attn_decode(dec->qkv, static_cast<const __half*>(w.kcache), static_cast<const __half*>(w.vcache),
+                            dec->part_o, dec->part_ml, dec->attn_local, Hl, pos + 1, dec->splits, stream);
+    if (rc != MLD_OK) return rc;
     if ((rc = gather(dec, dec->attn_local, dec->attn_full, dl, stream)) != MLD_OK) return rc;
     rc = mld_fc_run(dec->p_o, dec->attn_full, w.wo, w.so, nullptr, nullptr, dec->o_local, 1, stream);
     if (rc != MLD_OK) return rc;
     if ((rc = gather(dec, dec->o_local, dec->o_full, dl, stream)) != MLD_OK) return rc;
     // h = x_l + o; hn = rmsnorm(h)
-    add_rmsnorm_kernel<<<1, 1024, 0, stream>>>(xcur, dec->o_full, static_cast<const __half*>(w.norm2), dec->h,
-                                               dec->hn, dm, d.rms_eps);
-    MLD_LAUNCH_CHECK();
+    rc = launch_glue(add_rmsnorm_kernel, dim3(1), dim3(1024), stream, xcur, static_cast<const __half*>(dec->o_full),
+                     static_cast<const __half*>(w.norm2), dec->h, dec->hn, dm, d.rms_eps);
+    if (rc != MLD_OK) return rc;
     rc = mld_fc_run(dec->p_gu, dec->hn, w.wgu, w.sgu, nullptr, nullptr, dec->gu, 1, stream);
     if (rc != MLD_OK) return rc;
-    swiglu_kernel<<<div_up(fl, 256), 256, 0, stream>>>(dec->gu, dec->act_local, fl);
-    MLD_LAUNCH_CHECK();
+    rc = launch_glue(swiglu_kernel, dim3(div_up(fl, 256)), dim3(256), stream, static_cast<const __half*>(dec->gu),
+                     dec->act_local, fl);
+    if (rc != MLD_OK) return rc;
     if ((rc = gather(dec, dec->act_local, dec->act_full, fl, stream)) != MLD_OK) return rc;
     rc = mld_fc_run(dec->p_down, dec->act_full, w.wdown, w.sdown, nullptr, nullptr, d_local_ptr, 1, stream);
     if (rc != MLD_OK) return rc;
@@ -470,9 +557,8 @@ int mld_decoder_step(mld_decoder* dec, const void* x_in, void* x_out, int32_t po
     resid = dec->d_full;
   }
   // x_out = h + down of the last layer
-  add_rmsnorm_kernel<<<1, 1024, 0, stream>>>(x, resid, nullptr, static_cast<__half*>(x_out), nullptr, dm, d.rms_eps);
-  MLD_LAUNCH_CHECK();
-  return MLD_OK;
+  return launch_glue(add_rmsnorm_kernel, dim3(1), dim3(1024), stream, x, resid, static_cast<const __half*>(nullptr),
+                     static_cast<__half*>(x_out), static_cast<__half*>(nullptr), dm, d.rms_eps);
 }
 
 int mld_decoder_step_host(mld_decoder* dec, const void* x_host, void* y_host, int32_t pos, void* stream_v) {

@@ -70,4 +70,22 @@ StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slic
 int launch_fc_strip(int bits, bool subnormal, const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a,
                     const StripGeometry& gm, cudaStream_t stream);
 
+// ----------------------------------------------------------------- prefill GEMM
+struct GemmGeometry {
+  int kp;              // K rounded up so that a K-major row is a multiple of 16 bytes
+  int tile_n;          // UMMA N
+  int m_tiles, n_tiles, k_blocks;
+  int stages, a_stage_bytes, b_stage_bytes;
+  size_t smem_bytes;
+  int grid;
+};
+GemmGeometry gemm_geometry(int M, int N, int K, bool i8, int sms);
+int launch_dequant_weights(int bits, bool to_s8, const void* packed, const void* scale, int scale_mode, int G,
+                           int group_slices, float scalar_scale, int N, int K, int Kp, void* out, cudaStream_t stream);
+int launch_transpose_x(const void* x, int layout, int M, int K, int Kp, void* out, cudaStream_t stream);
+int launch_quantize_act(const void* x, int layout, int M, int K, int Kp, void* xq, float* params, cudaStream_t stream);
+int launch_gemm_umma(bool i8, const void* a_mat, const void* b_mat, const GemmGeometry& g, int M, int N, int K,
+                     const void* bias, const void* w_scale, const float* a_params, void* y, int dst_layout, int* error,
+                     cudaStream_t stream);
+
 }  // namespace mld

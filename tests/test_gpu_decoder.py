@@ -75,3 +75,20 @@ def test_decode_step_matches_oracle(mld, oracle):
     torch.cuda.synchronize()
     assert torch.equal(y2, y3)
     dec.close()
+
+
+@pytest.mark.parametrize("heads,n_tokens", [(2, 1), (2, 70), (32, 2049), (4, 515), (64, 33)])
+def test_attention_decode_matches_softmax(mld, heads, n_tokens):
+    rng = np.random.default_rng(heads * 1000 + n_tokens)
+    q = (rng.standard_normal((heads, 128)) / np.sqrt(128)).astype(np.float16)
+    k = rng.standard_normal((n_tokens, heads, 128)).astype(np.float16)
+    v = rng.standard_normal((n_tokens, heads, 128)).astype(np.float16)
+    out = torch.empty((heads, 128), dtype=torch.float16, device="cuda")
+    mld.attn_decode(_dev(q), _dev(k), _dev(v), out, heads, n_tokens)
+    torch.cuda.synchronize()
+    s = np.einsum("hd,thd->ht", q.astype(np.float64), k.astype(np.float64))
+    p = np.exp(s - s.max(axis=1, keepdims=True))
+    p /= p.sum(axis=1, keepdims=True)
+    ref = np.einsum("ht,thd->hd", p, v.astype(np.float64))
+    got = out.float().cpu().numpy()
+    assert np.max(np.abs(got - ref)) <= 2e-3 * max(1.0, np.max(np.abs(ref)))
