@@ -63,5 +63,23 @@ def build(force=False, verbose=False):
     return OUT
 
 
+HOST_TEST = os.path.join(HERE, "build", "host_test")
+
+
+def build_host_test(force=False):
+    """Compiles the C++ host mirror and its test program against libmldfc.so (g++ only)."""
+    build()
+    srcs = [os.path.join(HERE, "host", "tests", "host_test.cc"), os.path.join(HERE, "host", "mld_host.cc")]
+    deps = srcs + [os.path.join(HERE, "host", "mld_host.h"), OUT]
+    if not force and os.path.exists(HOST_TEST) and all(os.path.getmtime(d) <= os.path.getmtime(HOST_TEST) for d in deps):
+        return HOST_TEST
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = ["g++", "-O2", "-std=c++17", "-Wall", "-o", HOST_TEST, *srcs, "-I", os.path.join(ROOT, "include"),
+           "-I", os.path.join(cuda, "include"), "-L", HERE, "-lmldfc", "-L", os.path.join(cuda, "lib64"), "-lcudart",
+           "-Wl,-rpath," + HERE, "-Wl,-rpath," + os.path.join(cuda, "lib64")]
+    subprocess.check_call(cmd)
+    return HOST_TEST
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -450,13 +450,19 @@ GemmGeometry gemm_geometry(int M, int N, int K, bool i8, int sms) {
   const int N4 = align_n(N, 4);
   g.kp = align_n(K, i8 ? 16 : 8);  // K-major row pitch must be a multiple of 16 bytes
   g.m_tiles = div_up(M, kTileM);
-  // choose the UMMA N that minimises (waves x tile width) for this grid
+  // Choose the UMMA N.  A tile costs 2*N tensor-pipe cycles per 64-wide K block
+  // and pulls (128 + N) * 128 bytes of operands through L2 for it; with one CTA
+  // per tile the L2 -> SM traffic, not the tensor pipe, bounds narrow tiles, so
+  // the estimate is the larger of the two over all waves (L2 feed taken as
+  // 6.5 KB per cycle across the GPU, the rate this kernel was measured to draw).
   int best_n = 256;
-  long best_cost = -1;
+  double best_cost = -1.0;
   for (int tn = 256; tn >= 64; tn -= 16) {
-    const long tiles = (long)g.m_tiles * div_up(N4, tn);
-    const long waves = (tiles + sms - 1) / sms;
-    const long cost = waves * tn;
+    const double tiles = (double)g.m_tiles * div_up(N4, tn);
+    const double waves = (double)(((long)tiles + sms - 1) / sms);
+    const double mma = waves * 2.0 * tn;
+    const double l2 = tiles * (128.0 + tn) * 128.0 / 6500.0;
+    const double cost = mma > l2 ? mma : l2;
     if (best_cost < 0 || cost < best_cost) {
       best_cost = cost;
       best_n = tn;
