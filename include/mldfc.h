@@ -238,6 +238,22 @@ typedef struct mld_layer_weights {
 MLD_API int mld_attn_decode(const void* q, const void* kcache, const void* vcache, void* out, int32_t heads,
                             int32_t head_dim, int32_t n_tokens, void* stream);
 
+/* The same attention for callers that must not trigger a device allocation:
+ * a host that has handed the whole GPU to its own memory pool, or one that
+ * froze its memory plan before the first dispatch, cannot afford a cudaMalloc
+ * hidden inside a library call (it may fail, and it stalls the device).  This
+ * entry point has no counterpart in the reference.  It allocates nothing: the
+ * partial results go to a 2.03 MB array that is part of the library image on
+ * every GPU, sized for heads x splits <= 4096 - the split count shrinks to fit,
+ * and more than 4096 heads are refused with MLD_OUT_OF_RANGE.  The first call
+ * on a device looks up the array's device address (make that call with the
+ * device current and before starting any stream capture).  All calls share the
+ * one array: two calls that overlap on the GPU, on any streams, corrupt each
+ * other; calls ordered on one stream are safe, and no call depends on what an
+ * earlier one left behind. */
+MLD_API int mld_attn_decode_static(const void* q, const void* kcache, const void* vcache, void* out,
+                                   int32_t heads, int32_t head_dim, int32_t n_tokens, void* stream);
+
 typedef struct mld_decoder mld_decoder;
 
 /* 128-byte id shared by all ranks of a sharded decoder (rank 0 creates it and

@@ -188,6 +188,12 @@ class FullyConnectedPlan:
 
 
 # ---------------------------------------------------------------- decode step
+def attn_decode_static(q, kcache, vcache, out, heads, n_tokens, head_dim=128, stream=None):
+    """Decode attention without any device allocation (fixed scratch array inside the library)."""
+    _check(lib().mld_attn_decode_static(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(out), heads, head_dim, n_tokens,
+                                        _stream(stream)), "mld_attn_decode_static")
+
+
 def attn_decode(q, kcache, vcache, out, heads, n_tokens, head_dim=128, stream=None):
     _check(lib().mld_attn_decode(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(out), heads, head_dim, n_tokens,
                                  _stream(stream)), "mld_attn_decode")

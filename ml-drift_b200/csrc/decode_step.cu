@@ -386,6 +386,58 @@ int mld_attn_decode(const void* q, const void* kcache, const void* vcache, void*
                             static_cast<__half*>(out), heads, n_tokens, splits, static_cast<cudaStream_t>(stream));
 }
 
+// ------------------------------------------------------------------------
+// Allocation-free decode attention.
+//
+// Some hosts cannot let a library allocate device memory on their behalf: a
+// serving process whose own pool already owns the whole GPU (a late cudaMalloc
+// then fails, and it stalls every stream while the driver looks), or an
+// embedded runtime that fixes its memory plan before the first dispatch, the
+// way ML Drift's InferenceContext does.  For them the split-KV partial results
+// live in this fixed array, which every GPU that loads the library carries
+// until the process exits (2.03 MB).
+constexpr int kStaticPairs = 4096;  // (head, split) pairs the array can hold
+static __device__ __align__(256) float g_attn_static_scratch[kStaticPairs * (kHeadDim + 2)];
+
+namespace {
+// Device address of the array, looked up once per device.  In host code the
+// symbol's name is only a handle, never a pointer a kernel could use.
+float* g_attn_static_ptr[64] = {nullptr};
+std::mutex g_attn_static_mu;
+}  // namespace
+
+int mld_attn_decode_static(const void* q, const void* kcache, const void* vcache, void* out, int32_t heads,
+                           int32_t head_dim, int32_t n_tokens, void* stream) {
+  MLD_REQUIRE(q != nullptr && kcache != nullptr && vcache != nullptr && out != nullptr, "null tensor");
+  MLD_REQUIRE(head_dim == kHeadDim, "head_dim must be 128");
+  MLD_REQUIRE(heads > 0 && n_tokens > 0, "bad shape");
+  if (heads > kStaticPairs) {
+    set_last_error_text("mld_attn_decode_static: more than 4096 heads do not fit the fixed scratch array");
+    return MLD_OUT_OF_RANGE;
+  }
+  int device = 0;
+  MLD_CUDA_CHECK(cudaGetDevice(&device));
+  MLD_REQUIRE(device < 64, "device ordinal too large");
+  float* base;
+  {
+    std::lock_guard<std::mutex> lock(g_attn_static_mu);
+    if (g_attn_static_ptr[device] == nullptr) {
+      // first call on this device (which is current): resolve the symbol
+      void* p = nullptr;
+      MLD_CUDA_CHECK(cudaGetSymbolAddress(&p, g_attn_static_scratch));
+      g_attn_static_ptr[device] = static_cast<float*>(p);
+    }
+    base = g_attn_static_ptr[device];
+  }
+  int splits = attn_splits(heads, sm_count(device));
+  if (heads * splits > kStaticPairs) splits = kStaticPairs / heads;
+  // every (head, split) slot used below is rewritten by this call, so nothing
+  // left from an earlier call can leak into the result
+  return launch_attn_decode(static_cast<const __half*>(q), static_cast<const __half*>(kcache),
+                            static_cast<const __half*>(vcache), base, base + (size_t)heads * splits * kHeadDim,
+                            static_cast<__half*>(out), heads, n_tokens, splits, static_cast<cudaStream_t>(stream));
+}
+
 int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_decoder** out) {
   MLD_REQUIRE(d != nullptr && out != nullptr, "null argument");
   *out = nullptr;
