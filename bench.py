@@ -178,34 +178,41 @@ class ClockSampler:
 
 
 def build_model(mld, torch, rank, world, n_layers, dev):
-    """Random-init 7B-geometry shard, quantised and packed on the GPU by the library."""
-    d, ffn, blk, heads = CFG["d_model"], CFG["ffn"], CFG["block"], CFG["heads"]
-    dl, fl = d // world, ffn // world
+    """Random-init 7B-geometry model, quantised and packed on the GPU by the library.  The model is
+    defined globally (one seed per projection); a rank keeps the rows of its column shard, so every
+    world size runs the same model."""
+    d, ffn, blk, heads, hd = CFG["d_model"], CFG["ffn"], CFG["block"], CFG["heads"], CFG["head_dim"]
+    dl = d // world
     T = CFG["kv_len"] + 1
+    shd = mld.sharding
     layers = []
     gen = torch.Generator(device=dev)
 
-    def qpack(rows, K, seed):
+    def qpack(n_full, K, seed, rows):
         gen.manual_seed(seed)
-        w = torch.randn((rows, K), generator=gen, device=dev, dtype=torch.float32) * 0.02
+        w = torch.randn((n_full, K), generator=gen, device=dev, dtype=torch.float32) * 0.02
+        if world > 1:
+            w = w.index_select(0, torch.from_numpy(rows).to(dev))
         q, s = mld.quantize_weights(w, 4, blk)
-        packed, _ = mld.pack_weights(q, (rows, 1, 1, K), 4)
+        packed, _ = mld.pack_weights(q, (w.shape[0], 1, 1, K), 4)
         sc = mld.pack_scales(s, True)
         del w, q, s
         return packed, sc
 
+    head_cols = torch.from_numpy(shd.column_shard_rows(d, rank, world)).to(dev)
     for l in range(n_layers):
-        base = 1000 * l + 10 * rank
+        base = 1000 * l
         t = {}
-        t["wqkv"], t["sqkv"] = qpack(3 * dl, d, base + 1)
-        t["wo"], t["so"] = qpack(dl, d, base + 2)
-        t["wgu"], t["sgu"] = qpack(2 * fl, d, base + 3)
-        t["wdown"], t["sdown"] = qpack(dl, ffn, base + 4)
+        t["wqkv"], t["sqkv"] = qpack(3 * d, d, base + 1, shd.qkv_shard_rows(heads, hd, rank, world))
+        t["wo"], t["so"] = qpack(d, d, base + 2, shd.column_shard_rows(d, rank, world))
+        t["wgu"], t["sgu"] = qpack(2 * ffn, d, base + 3, shd.gate_up_shard_rows(ffn, rank, world))
+        t["wdown"], t["sdown"] = qpack(d, ffn, base + 4, shd.column_shard_rows(d, rank, world))
         t["norm1"] = torch.ones(d, dtype=torch.float16, device=dev)
         t["norm2"] = torch.ones(d, dtype=torch.float16, device=dev)
-        gen.manual_seed(base + 5)
-        t["kcache"] = torch.randn((T, dl), generator=gen, device=dev, dtype=torch.float32).half()
-        t["vcache"] = torch.randn((T, dl), generator=gen, device=dev, dtype=torch.float32).half()
+        for name, seed in (("kcache", base + 5), ("vcache", base + 6)):
+            gen.manual_seed(seed)
+            full = torch.randn((T, d), generator=gen, device=dev, dtype=torch.float32).half()
+            t[name] = full.index_select(1, head_cols).contiguous() if world > 1 else full
         layers.append(t)
     torch.cuda.synchronize()
     return layers

@@ -6,5 +6,5 @@ The product is the CUDA library ``libmldfc.so`` (sources in ``csrc/``, C ABI in
 tests and the benchmark; it holds no compute of its own and has no CPU
 fallback: importing :mod:`binding` fails loudly when the library is missing.
 """
-from . import binding  # noqa: F401
+from . import binding, sharding  # noqa: F401
 from .binding import *  # noqa: F401,F403

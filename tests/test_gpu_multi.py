@@ -1,0 +1,98 @@
+"""Column-sharded decode step on two GPUs vs the same model on one GPU (skipped with fewer than
+two devices).  Ranks are child processes; the shards come from one global model definition."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _model(rng, L, heads, ffn, T):
+    d = heads * 128
+    layers = []
+    for _ in range(L):
+        layer = {n: (rng.standard_normal(shape) * 0.02).astype(np.float32)
+                 for n, shape in (("qkv", (3 * d, d)), ("o", (d, d)), ("gu", (2 * ffn, d)), ("down", (d, ffn)))}
+        layer["norm1"] = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float16)
+        layer["norm2"] = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float16)
+        layers.append(layer)
+    kc = rng.standard_normal((L, T, d)).astype(np.float16)
+    vc = rng.standard_normal((L, T, d)).astype(np.float16)
+    return layers, kc, vc
+
+
+def _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id):
+    shd = mld.sharding
+    d = heads * 128
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dec = mld.Decoder(len(layers), d, heads, ffn, T, rank=rank, world=world, nccl_id=nccl_id)
+    rows = {"qkv": shd.qkv_shard_rows(heads, 128, rank, world), "o": shd.column_shard_rows(d, rank, world),
+            "gu": shd.gate_up_shard_rows(ffn, rank, world), "down": shd.column_shard_rows(d, rank, world)}
+    cols = shd.column_shard_rows(d, rank, world)
+    keep = []
+    for l, layer in enumerate(layers):
+        t = {}
+        for n in ("qkv", "o", "gu", "down"):
+            w = torch.from_numpy(np.ascontiguousarray(layer[n][rows[n]])).to(dev)
+            q, s = mld.quantize_weights(w, 4, 32)
+            t["w" + n], _ = mld.pack_weights(q, (w.shape[0], 1, 1, w.shape[1]), 4)
+            t["s" + n] = mld.pack_scales(s, True)
+        t["norm1"] = torch.from_numpy(layer["norm1"]).to(dev)
+        t["norm2"] = torch.from_numpy(layer["norm2"]).to(dev)
+        t["kcache"] = torch.from_numpy(np.ascontiguousarray(kc[l][:, cols])).to(dev)
+        t["vcache"] = torch.from_numpy(np.ascontiguousarray(vc[l][:, cols])).to(dev)
+        dec.set_layer(l, **t)
+        keep.append(t)
+    return dec, keep
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    import __graft_entry__ as g
+    mld = g.import_package()
+    torch.cuda.set_device(rank)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    idt = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        idt = torch.frombuffer(bytearray(mld.comm_unique_id()), dtype=torch.uint8).clone()
+    dist.broadcast(idt, 0)
+    L, heads, ffn, T, pos = 2, 4, 512, 64, 40
+    d = heads * 128
+    layers, kc, vc = _model(np.random.default_rng(0), L, heads, ffn, T)
+    x = torch.from_numpy(np.random.default_rng(1).standard_normal(d).astype(np.float16)).cuda()
+    dec, keep = _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, idt.numpy().tobytes())
+    y = torch.empty(d, dtype=torch.float16, device="cuda")
+    for _ in range(3):                       # repeated steps reuse the gather buffers
+        dec.step(x, y, pos)
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 0:
+        single, keep1 = _make_decoder(mld, layers, kc, vc, heads, ffn, T, 0, 1, None)
+        y1 = torch.empty_like(y)
+        single.step(x, y1, pos)
+        torch.cuda.synchronize()
+        err = (y.float() - y1.float()).abs().max().item() / y1.float().abs().max().item()
+        with open(os.path.join(out_dir, "result.txt"), "w") as f:
+            f.write(f"{err}\n{int(torch.isfinite(y).all())}")
+        single.close()
+    dist.barrier()
+    dec.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_sharded_decode_equals_single_gpu(tmp_path):
+    import torch.multiprocessing as mp
+    port = 29700 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    err, finite = open(tmp_path / "result.txt").read().split()
+    assert int(finite) == 1
+    assert float(err) < 1e-2
