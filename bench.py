@@ -191,7 +191,7 @@ def build_model(mld, torch, rank, world, n_layers, dev):
     def qpack(n_full, K, seed, rows):
         gen.manual_seed(seed)
         w = torch.randn((n_full, K), generator=gen, device=dev, dtype=torch.float32) * 0.02
-        if world > 1:
+        if len(rows) != n_full or (rows[:-1] > rows[1:]).any():     # a shard, or the interleaved gate/up order
             w = w.index_select(0, torch.from_numpy(rows).to(dev))
         q, s = mld.quantize_weights(w, 4, blk)
         packed, _ = mld.pack_weights(q, (w.shape[0], 1, 1, K), 4)
@@ -462,9 +462,17 @@ def run_ours(args):
             "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "kernels": side,
         }
         print(json.dumps(line), flush=True)
-    dec.close()
+    # Tear down without collective destructors: every rank has printed / finished its work, and a
+    # hard exit cannot hang on a peer that is already gone.
+    sys.stdout.flush()
+    sys.stderr.flush()
     if world > 1:
-        dist.destroy_process_group()
+        try:
+            dist.barrier()
+        except Exception:  # noqa: BLE001
+            pass
+        os._exit(0)
+    dec.close()
 
 
 def main():

@@ -67,6 +67,17 @@ typedef enum mld_act_layout {
   MLD_LAYOUT_ROW_MAJOR = 1  /* [M][C] */
 } mld_act_layout;
 
+/* Elementwise operation fused into the destination write (the reference links
+ * elementwise nodes into the FC's dst write, fully_connected_util.cc:356-407,
+ * common/task/gpu_operation.cc:1182-1256). */
+typedef enum mld_epilogue {
+  MLD_EPILOGUE_NONE = 0,
+  /* Weight rows alternate gate_i, up_i (N rows -> N/2 outputs):
+   * dst[i] = silu(row 2i) * (row 2i+1), the SiluMul of the FFN
+   * (samples/llm/qwen3_model_builder.cc:918-932).  Decode kernel only. */
+  MLD_EPILOGUE_SWIGLU_PAIRS = 1
+} mld_epilogue;
+
 typedef enum mld_weight_source {
   MLD_SRC_INT8 = 0,         /* OHWI, one signed value per byte */
   MLD_SRC_UINT4_PACKED = 1  /* OHWI (IHWO with swap_dims), two's-complement
@@ -166,6 +177,7 @@ typedef struct mld_fc_desc {
                                 the weights between calls while the weights and
                                 scale pointers stay the same (the caller
                                 promises not to modify them in between) */
+  int32_t epilogue;          /* mld_epilogue */
 } mld_fc_desc;
 
 typedef struct mld_fc_plan mld_fc_plan;
@@ -217,7 +229,8 @@ typedef struct mld_decoder_desc {
 /* Device tensors of one layer, in the layouts named at the top of this file.
  * Shard-local: wqkv packs the rows [q heads | k heads | v heads] of this rank
  * (N = 3*d_model/world, K = d_model); wo N = d_model/world, K = d_model;
- * wgu packs [gate rows | up rows] of this rank (N = 2*ffn/world, K = d_model);
+ * wgu packs this rank's FFN rows interleaved gate_i, up_i, gate_i+1, ...
+ * (N = 2*ffn/world, K = d_model) for the fused SiLU*mul write;
  * wdown N = d_model/world, K = ffn.  s* are the fp16 block scales [K/block][N].
  * norm1/norm2: fp16 RMSNorm weights [d_model].  kcache/vcache: fp16
  * [max_seq][heads/world * head_dim], updated in place at `pos`. */

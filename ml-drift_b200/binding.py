@@ -16,6 +16,7 @@ SCALE_SCALAR, SCALE_PER_CHANNEL, SCALE_BLOCK = 0, 1, 2
 LAYOUT_SLICED, LAYOUT_ROW_MAJOR = 0, 1
 SRC_INT8, SRC_UINT4_PACKED = 0, 1
 PATH_AUTO, PATH_GEMV, PATH_GEMM = 0, 1, 2
+EPILOGUE_NONE, EPILOGUE_SWIGLU_PAIRS = 0, 1
 
 
 class MldError(RuntimeError):
@@ -37,7 +38,7 @@ class FcDesc(C.Structure):
                 ("scalar_zero_point", C.c_float), ("has_zero_point", C.c_int32),
                 ("has_bias", C.c_int32), ("precision", C.c_int32), ("src_layout", C.c_int32),
                 ("dst_layout", C.c_int32), ("max_tokens", C.c_int32), ("force_path", C.c_int32),
-                ("device", C.c_int32), ("prefill_act_quant", C.c_int32), ("cache_prepared_weights", C.c_int32)]
+                ("device", C.c_int32), ("prefill_act_quant", C.c_int32), ("cache_prepared_weights", C.c_int32), ("epilogue", C.c_int32)]
 
 
 class DecoderDesc(C.Structure):
@@ -161,10 +162,10 @@ class FullyConnectedPlan:
     def __init__(self, n, k, weight_bits, scale_mode=SCALE_PER_CHANNEL, groups=1, scalar_scale=0.0,
                  scalar_zero_point=0.0, has_zero_point=False, has_bias=False, precision=F32F16,
                  src_layout=LAYOUT_SLICED, dst_layout=LAYOUT_SLICED, max_tokens=1, force_path=PATH_AUTO,
-                 device=-1, prefill_act_quant=0, cache_prepared_weights=False):
+                 device=-1, prefill_act_quant=0, cache_prepared_weights=False, epilogue=0):
         self.desc = FcDesc(n, k, weight_bits, scale_mode, groups, scalar_scale, scalar_zero_point,
                            int(has_zero_point), int(has_bias), precision, src_layout, dst_layout,
-                           max_tokens, force_path, device, prefill_act_quant, int(cache_prepared_weights))
+                           max_tokens, force_path, device, prefill_act_quant, int(cache_prepared_weights), epilogue)
         self._h = C.c_void_p()
         _check(lib().mld_fc_plan_create(C.byref(self.desc), C.byref(self._h)), "mld_fc_plan_create")
 

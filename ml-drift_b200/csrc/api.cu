@@ -111,7 +111,14 @@ struct mld_fc_plan {
   std::mutex mu;
 };
 
+// Tuning aid: when set (mld_debug_set_trace), the streaming GEMV records per-CTA timestamps.
+static unsigned long long* g_trace_buffer = nullptr;
+
 extern "C" {
+
+__attribute__((visibility("default"))) void mld_debug_set_trace(void* dev_buffer) {
+  g_trace_buffer = static_cast<unsigned long long*>(dev_buffer);
+}
 
 const char* mld_status_string(int status) {
   switch (status) {
@@ -204,6 +211,9 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   MLD_REQUIRE(d->dst_layout == MLD_LAYOUT_SLICED || d->dst_layout == MLD_LAYOUT_ROW_MAJOR, "bad dst layout");
   MLD_REQUIRE(d->max_tokens >= 1, "max_tokens must be at least 1");
   MLD_REQUIRE(d->prefill_act_quant == 0 || d->prefill_act_quant == 1, "bad prefill_act_quant");
+  MLD_REQUIRE(d->epilogue == MLD_EPILOGUE_NONE || d->epilogue == MLD_EPILOGUE_SWIGLU_PAIRS, "bad epilogue");
+  if (d->epilogue == MLD_EPILOGUE_SWIGLU_PAIRS)
+    MLD_REQUIRE(d->n % 8 == 0 && !d->has_bias, "the SiLU*mul write needs an even row count (n % 8 == 0) and no bias");
   if (d->prefill_act_quant == 1)
     MLD_REQUIRE(d->weight_bits == 8 && d->scale_mode == MLD_SCALE_PER_CHANNEL && !d->has_zero_point,
                 "int8-activation prefill needs per-channel INT8 weights without zero points");
@@ -358,8 +368,10 @@ static int run_stream(mld_fc_plan* p, const void* src, const void* weights, cons
   a.gs_shift = gm.gs_shift;
   a.red_m = gm.red_m;
   a.dst_layout = d.dst_layout;
+  a.epilogue = d.epilogue;
   a.scalar_scale = d.scalar_scale;
   a.pdl = p->pdl ? 1 : 0;
+  a.trace = g_trace_buffer;
   for (int tok0 = 0; tok0 < tokens; tok0 += 8) {
     a.tok0 = tok0;
     a.M = tokens - tok0 < 8 ? tokens - tok0 : 8;
@@ -431,11 +443,19 @@ int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const vo
     }
     return run_generic(plan, src, weights, scale, zp, b, dst, tokens, stream);
   }
+  if (d.epilogue != MLD_EPILOGUE_NONE && !(path == 1 && plan->stream_ok && tokens <= 16)) {
+    set_last_error_text("the fused SiLU*mul write is available on the streaming decode kernel only");
+    return MLD_UNIMPLEMENTED;
+  }
   const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
                        (scale == nullptr || (reinterpret_cast<uintptr_t>(scale) & 15) == 0);
   const bool layout_ok = d.src_layout == MLD_LAYOUT_SLICED || tokens == 1;
   if (plan->stream_ok && tokens <= 16 && aligned && layout_ok)
     return run_stream(plan, src, weights, scale, b, dst, tokens, stream);
+  if (d.epilogue != MLD_EPILOGUE_NONE) {
+    set_last_error_text("the fused SiLU*mul write needs 16-byte aligned fp16 tensors in the sliced layout");
+    return MLD_UNIMPLEMENTED;
+  }
   return run_generic(plan, src, weights, scale, zp, b, dst, tokens, stream);
 }
 

@@ -2,8 +2,9 @@
 // are quantized FullyConnected nodes (the callers of the FC hot path in
 // ml_drift/samples/llm/qwen3_model_builder.cc:907-1038: Linear, FFLayer,
 // SelfAttention, TransformerLayer).  The FullyConnected nodes run through the
-// same plans mld_fc_run uses; the glue around them (RMSNorm, RoPE + KV-cache
-// update, decode attention, SiLU*mul, residual adds) is plain CUDA.
+// same plans mld_fc_run uses, with the residual adds and SiLU*mul fused into the
+// projections' dst writes; the glue around them (RMSNorm, one attention kernel
+// doing RoPE + KV-cache update + decode attention) is plain CUDA.
 //
 // Column sharding: with world > 1 every projection holds the rows of its own
 // output shard; shard outputs are concatenated by an all-gather before the next
@@ -66,44 +67,6 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __half* __restr
       if (r != nullptr) v = __half2float(__float2half_rn(v + __half2float(r[i])));
     }
     y[i] = __float2half_rn(v * inv * __half2float(gamma[i]));
-  }
-}
-
-// Split-half rotary embedding on q and k (common/kernels/rope.cc:70-89:
-// timescale = min * (max/min)^(2i/d), angle = pos / timescale,
-// out0 = v0 cos - v1 sin, out1 = v1 cos + v0 sin with (v0, v1) = (x[i], x[i+d/2]))
-// and the KV-cache write of the new token.  qkv = [q | k | v] of the local heads.
-__global__ void rope_kv_kernel(__half* __restrict__ qkv, __half* __restrict__ kcache, __half* __restrict__ vcache,
-                               int heads, int head_dim, int pos, float min_ts, float max_ts, float q_scale) {
-  pdl_wait();
-  pdl_launch_dependents();
-  const int head = blockIdx.x;           // 0 .. 2*heads-1 : q heads then k heads
-  const int half = head_dim / 2;
-  const int i = threadIdx.x;             // pair index
-  const int width = heads * head_dim;
-  if (i < half) {
-    const float fraction = 2.0f * i / static_cast<float>(head_dim);
-    const float timescale = min_ts * powf(max_ts / min_ts, fraction);
-    float s, c;
-    sincosf(static_cast<float>(pos) / timescale, &s, &c);
-    __half* p = qkv + (size_t)head * head_dim;
-    const float v0 = __half2float(p[i]), v1 = __half2float(p[i + half]);
-    const float o0 = v0 * c - v1 * s, o1 = v1 * c + v0 * s;
-    if (head < heads) {
-      p[i] = __float2half_rn(o0 * q_scale);
-      p[i + half] = __float2half_rn(o1 * q_scale);
-    } else {
-      const int kh = head - heads;
-      __half* kc = kcache + (size_t)pos * width + kh * head_dim;
-      kc[i] = __float2half_rn(o0);
-      kc[i + half] = __float2half_rn(o1);
-    }
-  }
-  if (head >= heads) {  // the matching v head
-    const int kh = head - heads;
-    const __half* v = qkv + (size_t)(2 * heads + kh) * head_dim;
-    __half* vc = vcache + (size_t)pos * width + kh * head_dim;
-    for (int j = threadIdx.x; j < head_dim; j += blockDim.x) vc[j] = v[j];
   }
 }
 
@@ -212,15 +175,140 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
   out[(size_t)head * kHeadDim + dim] = __float2half_rn(o / l);
 }
 
-// act = silu(gate) * up over the local hidden slice (SiluMul,
-// qwen3_model_builder.cc:918-932); gu = [gate | up].
-__global__ void swiglu_kernel(const __half* __restrict__ gu, __half* __restrict__ act, int n) {
+// The decoder's attention node in one launch: rotary embedding of q and of the
+// new token's k (rope.cc:70-89), KV-cache write of the new token, split-KV
+// attention, and the merge of the splits by whichever CTA of a head finishes
+// last (a ticket per head; nothing waits).  qkv = raw [q | k | v] of the local
+// heads as the projection wrote them.
+struct AttnStepArgs {
+  const __half* qkv;
+  __half* kcache;
+  __half* vcache;
+  float* part_o;
+  float* part_ml;
+  int* tickets;   // one per head, zero between launches
+  __half* out;
+  int heads, pos, splits;
+  float min_ts, max_ts, q_scale;
+};
+__global__ void __launch_bounds__(128) attn_step_kernel(AttnStepArgs a) {
   pdl_wait();
   pdl_launch_dependents();
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  const float g = __half2float(gu[i]), u = __half2float(gu[n + i]);
-  act[i] = __float2half_rn(g / (1.0f + __expf(-g)) * u);
+  const int head = blockIdx.x, split = blockIdx.y;
+  const int n_tokens = a.pos + 1;
+  const int per = (n_tokens + a.splits - 1) / a.splits;
+  const int t0 = split * per, t1 = min(n_tokens, t0 + per);
+  const int grp = threadIdx.x >> 3, sub = threadIdx.x & 7;
+  const int width = a.heads * kHeadDim;
+  __shared__ float sq[kHeadDim];
+  __shared__ float sm_m[16], sm_l[16], sm_o[16][kHeadDim];
+  __shared__ int s_last;
+  const bool owns_new = a.pos >= t0 && a.pos < t1;
+  if (threadIdx.x < kHeadDim / 2) {
+    const int i = threadIdx.x, half = kHeadDim / 2;
+    const float fraction = 2.0f * i / static_cast<float>(kHeadDim);
+    const float timescale = a.min_ts * powf(a.max_ts / a.min_ts, fraction);
+    float sn, cs;
+    sincosf(static_cast<float>(a.pos) / timescale, &sn, &cs);
+    const __half* qp = a.qkv + (size_t)head * kHeadDim;
+    const float q0 = __half2float(qp[i]), q1 = __half2float(qp[i + half]);
+    // rounded to fp16 exactly where the unfused graph stores the rotated q
+    sq[i] = __half2float(__float2half_rn((q0 * cs - q1 * sn) * a.q_scale));
+    sq[i + half] = __half2float(__float2half_rn((q1 * cs + q0 * sn) * a.q_scale));
+    if (owns_new) {
+      const __half* kp = a.qkv + (size_t)(a.heads + head) * kHeadDim;
+      const float k0 = __half2float(kp[i]), k1 = __half2float(kp[i + half]);
+      __half* kc = a.kcache + (size_t)a.pos * width + head * kHeadDim;
+      kc[i] = __float2half_rn(k0 * cs - k1 * sn);
+      kc[i + half] = __float2half_rn(k1 * cs + k0 * sn);
+    }
+  } else if (owns_new) {
+    const int j = threadIdx.x - kHeadDim / 2;  // 64 threads copy the 128 v values
+    const __half* vp = a.qkv + (size_t)(2 * a.heads + head) * kHeadDim;
+    __half* vc = a.vcache + (size_t)a.pos * width + head * kHeadDim;
+    vc[j] = vp[j];
+    vc[j + kHeadDim / 2] = vp[j + kHeadDim / 2];
+  }
+  __syncthreads();  // the new token's cache rows are visible to this CTA, which is the only reader of them
+  float qv[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) qv[j] = sq[sub * 16 + j];
+  float m = -INFINITY, l = 0.0f, acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+  const unsigned gmask = 0xFFu << (threadIdx.x & 24);
+  for (int t = t0 + grp; t < t1; t += 16) {
+    const uint4* kp = reinterpret_cast<const uint4*>(a.kcache + (size_t)t * width + head * kHeadDim + sub * 16);
+    const uint4 k0 = kp[0], k1 = kp[1];
+    const __half2* kh = reinterpret_cast<const __half2*>(&k0);
+    const __half2* kh2 = reinterpret_cast<const __half2*>(&k1);
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x0 = __half22float2(kh[j]), x1 = __half22float2(kh2[j]);
+      s += qv[2 * j] * x0.x + qv[2 * j + 1] * x0.y + qv[8 + 2 * j] * x1.x + qv[8 + 2 * j + 1] * x1.y;
+    }
+    s += __shfl_xor_sync(gmask, s, 1);
+    s += __shfl_xor_sync(gmask, s, 2);
+    s += __shfl_xor_sync(gmask, s, 4);
+    const float m_new = fmaxf(m, s);
+    const float corr = __expf(m - m_new), p = __expf(s - m_new);
+    const uint4* vp = reinterpret_cast<const uint4*>(a.vcache + (size_t)t * width + head * kHeadDim + sub * 16);
+    const uint4 v0 = vp[0], v1 = vp[1];
+    const __half2* vh = reinterpret_cast<const __half2*>(&v0);
+    const __half2* vh2 = reinterpret_cast<const __half2*>(&v1);
+    l = l * corr + p;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x0 = __half22float2(vh[j]), x1 = __half22float2(vh2[j]);
+      acc[2 * j] = acc[2 * j] * corr + p * x0.x;
+      acc[2 * j + 1] = acc[2 * j + 1] * corr + p * x0.y;
+      acc[8 + 2 * j] = acc[8 + 2 * j] * corr + p * x1.x;
+      acc[8 + 2 * j + 1] = acc[8 + 2 * j + 1] * corr + p * x1.y;
+    }
+    m = m_new;
+  }
+  if (sub == 0) {
+    sm_m[grp] = m;
+    sm_l[grp] = l;
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) sm_o[grp][sub * 16 + j] = acc[j];
+  __syncthreads();
+  float gm = -INFINITY;
+#pragma unroll
+  for (int g = 0; g < 16; ++g) gm = fmaxf(gm, sm_m[g]);
+  const int dim = threadIdx.x;
+  float o = 0.0f, lsum = 0.0f;
+#pragma unroll
+  for (int g = 0; g < 16; ++g) {
+    const float w = sm_m[g] == -INFINITY ? 0.0f : __expf(sm_m[g] - gm);
+    o += w * sm_o[g][dim];
+    lsum += w * sm_l[g];
+  }
+  a.part_o[((size_t)head * a.splits + split) * kHeadDim + dim] = o;
+  if (dim == 0) {
+    a.part_ml[((size_t)head * a.splits + split) * 2 + 0] = gm;
+    a.part_ml[((size_t)head * a.splits + split) * 2 + 1] = lsum;
+  }
+  // the last CTA of this head to get here merges the splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(a.tickets + head, 1) == a.splits - 1 ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float tm = -INFINITY;
+  for (int s = 0; s < a.splits; ++s) tm = fmaxf(tm, __ldcg(a.part_ml + ((size_t)head * a.splits + s) * 2));
+  float to = 0.0f, tl = 0.0f;
+  for (int s = 0; s < a.splits; ++s) {
+    const float ms = __ldcg(a.part_ml + ((size_t)head * a.splits + s) * 2);
+    const float w = ms == -INFINITY ? 0.0f : __expf(ms - tm);
+    to += w * __ldcg(a.part_o + ((size_t)head * a.splits + s) * kHeadDim + dim);
+    tl += w * __ldcg(a.part_ml + ((size_t)head * a.splits + s) * 2 + 1);
+  }
+  a.out[(size_t)head * kHeadDim + dim] = __float2half_rn(to / tl);
+  if (threadIdx.x == 0) a.tickets[head] = 0;
 }
 
 // Launches a glue kernel so that it may be scheduled while its predecessor in
@@ -307,6 +395,7 @@ struct mld_decoder {
   // scratch (owned)
   __half *xn, *qkv, *attn_local, *attn_full, *o_local, *o_full, *h, *hn, *gu, *act_local, *act_full, *d_full, *x_stage, *y_stage;
   float *part_o, *part_ml;
+  int* tickets;
   uint8_t* scratch;
   int splits;
   ncclComm_t comm;
@@ -315,7 +404,7 @@ struct mld_decoder {
 
 namespace {
 
-int make_plan(int n, int k, int block, int device, mld_fc_plan** out) {
+int make_plan(int n, int k, int block, int device, bool residual, int epilogue, mld_fc_plan** out) {
   mld_fc_desc fd;
   memset(&fd, 0, sizeof fd);
   fd.n = n;
@@ -329,6 +418,8 @@ int make_plan(int n, int k, int block, int device, mld_fc_plan** out) {
   fd.max_tokens = 1;
   fd.force_path = 1;
   fd.device = device;
+  fd.has_bias = residual ? 1 : 0;  // the residual vector rides in the bias slot of the dst write
+  fd.epilogue = epilogue;
   return mld_fc_plan_create(&fd, out);
 }
 
@@ -467,10 +558,11 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   dec->comm = nullptr;
   dec->scratch = nullptr;
   dec->p_qkv = dec->p_o = dec->p_gu = dec->p_down = nullptr;
-  int rc = make_plan(3 * dec->d_local, d->d_model, d->block, device, &dec->p_qkv);
-  if (rc == MLD_OK) rc = make_plan(dec->d_local, d->d_model, d->block, device, &dec->p_o);
-  if (rc == MLD_OK) rc = make_plan(2 * dec->ffn_local, d->d_model, d->block, device, &dec->p_gu);
-  if (rc == MLD_OK) rc = make_plan(dec->d_local, d->ffn, d->block, device, &dec->p_down);
+  int rc = make_plan(3 * dec->d_local, d->d_model, d->block, device, false, MLD_EPILOGUE_NONE, &dec->p_qkv);
+  if (rc == MLD_OK) rc = make_plan(dec->d_local, d->d_model, d->block, device, true, MLD_EPILOGUE_NONE, &dec->p_o);
+  if (rc == MLD_OK)
+    rc = make_plan(2 * dec->ffn_local, d->d_model, d->block, device, false, MLD_EPILOGUE_SWIGLU_PAIRS, &dec->p_gu);
+  if (rc == MLD_OK) rc = make_plan(dec->d_local, d->ffn, d->block, device, true, MLD_EPILOGUE_NONE, &dec->p_down);
   // split count: fill the GPU about four CTAs deep
   int sms = sm_count(device);
   const int splits = attn_splits(dec->heads_local, sms);
@@ -480,7 +572,8 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   const size_t sizes_h[11] = {dm, 3 * (size_t)dec->d_local, dm, dm, dm, dm, 2 * (size_t)dec->ffn_local, ff, dm, dm, dm};
   size_t total = 0;
   for (size_t n : sizes_h) total += pad(n * 2);
-  total += pad((size_t)dec->heads_local * splits * kHeadDim * 4) + pad((size_t)dec->heads_local * splits * 2 * 4);
+  total += pad((size_t)dec->heads_local * splits * kHeadDim * 4) + pad((size_t)dec->heads_local * splits * 2 * 4) +
+           pad((size_t)dec->heads_local * 4);
   dec->scratch_bytes = total;
   dec->scratch = nullptr;
   if (rc == MLD_OK && cudaMalloc(&dec->scratch, total) != cudaSuccess) {
@@ -511,6 +604,7 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   dec->y_stage = reinterpret_cast<__half*>(take(sizes_h[10] * 2));
   dec->part_o = reinterpret_cast<float*>(take((size_t)dec->heads_local * splits * kHeadDim * 4));
   dec->part_ml = reinterpret_cast<float*>(take((size_t)dec->heads_local * splits * 2 * 4));
+  dec->tickets = reinterpret_cast<int*>(take((size_t)dec->heads_local * 4));  // zeroed above
   // a rank's shard of a gathered vector is written in place
   dec->attn_local = dec->attn_full + (size_t)d->rank * dec->d_local;
   dec->o_local = dec->o_full + (size_t)d->rank * dec->d_local;
@@ -566,51 +660,63 @@ int mld_decoder_step(mld_decoder* dec, const void* x_in, void* x_out, int32_t po
   const mld_decoder_desc& d = dec->d;
   const int dm = d.d_model, Hl = dec->heads_local, dl = dm / d.world, fl = dec->ffn_local;
   const float q_scale = 1.0f / sqrtf(static_cast<float>(d.head_dim));
+  // Per layer (x = layer input, all vectors fp16):
+  //   xn = rmsnorm(x) g1;  qkv = Wqkv xn;  attn = attention(rope(q), cache + rope(k), v)
+  //   h  = x + Wo attn            (residual added in the projection's dst write)
+  //   hn = rmsnorm(h) g2;  act = silu(Wg hn) * (Wu hn)   (fused into the projection's dst write)
+  //   x' = h + Wdown act
   const __half* x = static_cast<const __half*>(x_in);
-  const __half* resid = nullptr;  // pending residual (the previous layer's down_proj output)
-  __half* d_local_ptr = dec->d_full + (size_t)d.rank * dl;
   int rc;
   for (int l = 0; l < d.layers; ++l) {
     const mld_layer_weights& w = dec->layers[l];
     MLD_REQUIRE(w.wqkv != nullptr, "layer weights not set");
-    // x_l = x_{l-1} + down_{l-1}; xn = rmsnorm(x_l)
-    __half* xl = l == 0 ? nullptr : dec->h;  // layer 0 reads x_in directly
-    rc = launch_glue(add_rmsnorm_kernel, dim3(1), dim3(1024), stream, x, resid, static_cast<const __half*>(w.norm1), xl,
-                     dec->xn, dm, d.rms_eps);
+    const bool last = l + 1 == d.layers;
+    // the layer's output vector: the caller's buffer for the last layer, else a ping-pong pair
+    __half* x_next = last ? static_cast<__half*>(x_out) : ((l & 1) ? dec->d_full : dec->o_full);
+    rc = launch_glue(add_rmsnorm_kernel, dim3(1), dim3(1024), stream, x, static_cast<const __half*>(nullptr),
+                     static_cast<const __half*>(w.norm1), static_cast<__half*>(nullptr), dec->xn, dm, d.rms_eps);
     if (rc != MLD_OK) return rc;
-    const __half* xcur = l == 0 ? x : dec->h;
     rc = mld_fc_run(dec->p_qkv, dec->xn, w.wqkv, w.sqkv, nullptr, nullptr, dec->qkv, 1, stream);
     if (rc != MLD_OK) return rc;
-    rc = launch_glue(rope_kv_kernel, dim3(2 * Hl), dim3(64), stream, dec->qkv, static_cast<__half*>(w.kcache),
-                     static_cast<__half*>(w.vcache), Hl, d.head_dim, pos, d.rope_min_timescale, d.rope_max_timescale,
-                     q_scale);
-    if (rc != MLD_OK) return rc;
-    rc = launch_attn_decode(dec->qkv, static_cast<const __half*>(w.kcache), static_cast<const __half*>(w.vcache),
-                            dec->part_o, dec->part_ml, dec->attn_local, Hl, pos + 1, dec->splits, stream);
-    if (rc != MLD_OK) return rc;
+    {
+      AttnStepArgs aa;
+      aa.qkv = dec->qkv;
+      aa.kcache = static_cast<__half*>(w.kcache);
+      aa.vcache = static_cast<__half*>(w.vcache);
+      aa.part_o = dec->part_o;
+      aa.part_ml = dec->part_ml;
+      aa.tickets = dec->tickets;
+      aa.out = dec->attn_local;
+      aa.heads = Hl;
+      aa.pos = pos;
+      aa.splits = dec->splits;
+      aa.min_ts = d.rope_min_timescale;
+      aa.max_ts = d.rope_max_timescale;
+      aa.q_scale = q_scale;
+      rc = launch_glue(attn_step_kernel, dim3(Hl, dec->splits), dim3(128), stream, aa);
+      if (rc != MLD_OK) return rc;
+    }
     if ((rc = gather(dec, dec->attn_local, dec->attn_full, dl, stream)) != MLD_OK) return rc;
-    rc = mld_fc_run(dec->p_o, dec->attn_full, w.wo, w.so, nullptr, nullptr, dec->o_local, 1, stream);
+    // h shard = x shard + Wo attn
+    __half* h_local = dec->h + (size_t)d.rank * dl;
+    rc = mld_fc_run(dec->p_o, dec->attn_full, w.wo, w.so, nullptr, x + (size_t)d.rank * dl, h_local, 1, stream);
     if (rc != MLD_OK) return rc;
-    if ((rc = gather(dec, dec->o_local, dec->o_full, dl, stream)) != MLD_OK) return rc;
-    // h = x_l + o; hn = rmsnorm(h)
-    rc = launch_glue(add_rmsnorm_kernel, dim3(1), dim3(1024), stream, xcur, static_cast<const __half*>(dec->o_full),
-                     static_cast<const __half*>(w.norm2), dec->h, dec->hn, dm, d.rms_eps);
+    if ((rc = gather(dec, h_local, dec->h, dl, stream)) != MLD_OK) return rc;
+    rc = launch_glue(add_rmsnorm_kernel, dim3(1), dim3(1024), stream, static_cast<const __half*>(dec->h),
+                     static_cast<const __half*>(nullptr), static_cast<const __half*>(w.norm2),
+                     static_cast<__half*>(nullptr), dec->hn, dm, d.rms_eps);
     if (rc != MLD_OK) return rc;
-    rc = mld_fc_run(dec->p_gu, dec->hn, w.wgu, w.sgu, nullptr, nullptr, dec->gu, 1, stream);
-    if (rc != MLD_OK) return rc;
-    rc = launch_glue(swiglu_kernel, dim3(div_up(fl, 256)), dim3(256), stream, static_cast<const __half*>(dec->gu),
-                     dec->act_local, fl);
+    rc = mld_fc_run(dec->p_gu, dec->hn, w.wgu, w.sgu, nullptr, nullptr, dec->act_local, 1, stream);
     if (rc != MLD_OK) return rc;
     if ((rc = gather(dec, dec->act_local, dec->act_full, fl, stream)) != MLD_OK) return rc;
-    rc = mld_fc_run(dec->p_down, dec->act_full, w.wdown, w.sdown, nullptr, nullptr, d_local_ptr, 1, stream);
+    __half* xn_local = x_next + (size_t)d.rank * dl;
+    rc = mld_fc_run(dec->p_down, dec->act_full, w.wdown, w.sdown, nullptr, dec->h + (size_t)d.rank * dl, xn_local, 1,
+                    stream);
     if (rc != MLD_OK) return rc;
-    if ((rc = gather(dec, d_local_ptr, dec->d_full, dl, stream)) != MLD_OK) return rc;
-    x = dec->h;
-    resid = dec->d_full;
+    if ((rc = gather(dec, xn_local, x_next, dl, stream)) != MLD_OK) return rc;
+    x = x_next;
   }
-  // x_out = h + down of the last layer
-  return launch_glue(add_rmsnorm_kernel, dim3(1), dim3(1024), stream, x, resid, static_cast<const __half*>(nullptr),
-                     static_cast<__half*>(x_out), static_cast<__half*>(nullptr), dm, d.rms_eps);
+  return MLD_OK;
 }
 
 int mld_decoder_step_host(mld_decoder* dec, const void* x_host, void* y_host, int32_t pos, void* stream_v) {

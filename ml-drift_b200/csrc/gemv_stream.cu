@@ -24,6 +24,8 @@
 // fp16 precision modes.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -142,9 +144,6 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
@@ -209,16 +208,27 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
   const int r_hi = min(a.src_slices, r_lo + a.rows_per_split);
   const int n_st = (r_hi - r_lo + kStageRows - 1) / kStageRows;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < a.stages; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kConsumerWarps);
+  unsigned long long* tr = a.trace != nullptr ? a.trace + (size_t)blockIdx.x * 8 : nullptr;
+  // The producer thread initialises the barriers and goes straight on to issue
+  // its first loads; the consumers wait for the initialisation on a named
+  // barrier the producer warp only arrives at.
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      if (tr) tr[0] = globaltimer_ns();
+      for (int s = 0; s < a.stages; ++s) {
+        mbar_init(&full[s], 1);
+        mbar_init(&empty[s], kConsumerWarps);
+      }
+      mbar_init(peer_bar, kConsumerWarps * 32);
+      fence_barrier_init();
     }
-    mbar_init(peer_bar, kConsumerWarps * 32);
-    fence_barrier_init();
+    __syncwarp();
+    asm volatile("bar.arrive 2, %0;" ::"n"((kConsumerWarps + 1) * 32) : "memory");
+  } else {
+    asm volatile("bar.sync 2, %0;" ::"n"((kConsumerWarps + 1) * 32) : "memory");
   }
-  __syncthreads();
-  if (a.ksplit > 1) cluster_sync_all();  // the partner's barriers exist before anyone signals them
+  // cluster partners: arrive now, wait only before the first remote access
+  if (a.ksplit > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   if (a.pdl) pdl_launch_dependents();
 
   if (warp == kConsumerWarps) {
@@ -255,7 +265,9 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
       // requested before waiting for the preceding kernel; activations after.
       const int head = total < a.stages ? total : a.stages;
       for (int it = 0; it < head; ++it) issue_weights(it, it);
+      if (tr) tr[1] = globaltimer_ns();
       if (a.pdl) pdl_wait();
+      if (tr) tr[2] = globaltimer_ns();
       for (int it = 0; it < head; ++it) issue_x(it, it);
       int stage = head == a.stages ? 0 : head;
       uint32_t phase = head == a.stages ? 1 : 0;
@@ -300,6 +312,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
         failed = true;
         break;
       }
+      if (tr && threadIdx.x == 0 && pass == 0 && si == 0) tr[3] = globaltimer_ns();
       const uint8_t* st = smem + (size_t)stage * a.stage_bytes;
       const uint8_t* xs = st + W * kBoxBytes + a.scale_stage_bytes;
       const int row0 = r_lo + si * kStageRows;
@@ -384,6 +397,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
     if (failed) break;
 
     // ------------------------------------------------ pass epilogue
+    if (tr && threadIdx.x == 0) tr[4] = globaltimer_ns();
 #pragma unroll
     for (int b = 0; b < W; ++b)
 #pragma unroll
@@ -401,6 +415,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
     const int n_end = min(ce * F::NPL, a.N4);      // one past the last output this CTA owns
     const int nvals = WT * a.M;
     uint32_t peer_remote = 0, bar_remote = 0;
+    if (a.ksplit > 1 && pass == 0) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (a.ksplit > 1 && kr == 1) {
       peer_remote = map_to_rank(smem_u32(peer), 0);
       bar_remote = map_to_rank(smem_u32(peer_bar), 0);
@@ -411,29 +426,65 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
         failed = true;
       }
     }
-    for (int idx = threadIdx.x; idx < nvals && !failed; idx += kConsumerWarps * 32) {
-      const int n_local = idx / a.M, tok = idx - n_local * a.M;
-      float s = 0.0f;
+    if (a.ksplit > 1 && kr == 1) {
+      // upper half of K: hand the sums to the partner
+      for (int idx = threadIdx.x; idx < nvals && !failed; idx += kConsumerWarps * 32) {
+        const int n_local = idx / a.M, tok = idx - n_local * a.M;
+        float s = 0.0f;
 #pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) s += red[(w * WT + n_local) * a.red_m + tok];
-      if (a.ksplit > 1 && kr == 1) {
+        for (int w = 0; w < kConsumerWarps; ++w) s += red[(w * WT + n_local) * a.red_m + tok];
         st_cluster_f32(peer_remote + (n_local * a.red_m + tok) * 4, s);
-        continue;
       }
-      if (a.ksplit > 1) s += peer[n_local * a.red_m + tok];  // fixed order: lower half of K first
-      const int n = n0 + n_local;
-      if (n < n_end) {
-        __half r = __float2half_rn(s * kOutScale);
-        if (a.bias != nullptr) r = __hadd(r, static_cast<const __half*>(a.bias)[n]);
-        const int tk = a.tok0 + tok;
-        if (a.dst_layout == MLD_LAYOUT_SLICED)
-          static_cast<__half*>(a.y)[((int64_t)(n >> 2) * a.M_total + tk) * 4 + (n & 3)] = r;
-        else if (n < a.N)
-          static_cast<__half*>(a.y)[(int64_t)tk * a.N + n] = r;
+    } else if (a.epilogue == MLD_EPILOGUE_SWIGLU_PAIRS) {
+      // rows alternate gate_i, up_i: out[i] = silu(gate_i) * up_i, each rounded to
+      // fp16 where the unfused graph would store it
+      const int npairs = (WT / 2) * a.M;
+      for (int idx = threadIdx.x; idx < npairs && !failed; idx += kConsumerWarps * 32) {
+        const int p_local = idx / a.M, tok = idx - p_local * a.M;
+        float sg = 0.0f, su = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+          sg += red[(w * WT + 2 * p_local) * a.red_m + tok];
+          su += red[(w * WT + 2 * p_local + 1) * a.red_m + tok];
+        }
+        if (a.ksplit > 1) {
+          sg += peer[(2 * p_local) * a.red_m + tok];
+          su += peer[(2 * p_local + 1) * a.red_m + tok];
+        }
+        const int n = n0 + 2 * p_local;
+        if (n + 1 < n_end) {
+          const float g = __half2float(__float2half_rn(sg * kOutScale));
+          const float u = __half2float(__float2half_rn(su * kOutScale));
+          const __half r = __float2half_rn(g / (1.0f + __expf(-g)) * u);
+          const int i = n >> 1, tk = a.tok0 + tok;
+          if (a.dst_layout == MLD_LAYOUT_SLICED)
+            static_cast<__half*>(a.y)[((int64_t)(i >> 2) * a.M_total + tk) * 4 + (i & 3)] = r;
+          else
+            static_cast<__half*>(a.y)[(int64_t)tk * (a.N / 2) + i] = r;
+        }
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < nvals && !failed; idx += kConsumerWarps * 32) {
+        const int n_local = idx / a.M, tok = idx - n_local * a.M;
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) s += red[(w * WT + n_local) * a.red_m + tok];
+        if (a.ksplit > 1) s += peer[n_local * a.red_m + tok];  // fixed order: lower half of K first
+        const int n = n0 + n_local;
+        if (n < n_end) {
+          __half r = __float2half_rn(s * kOutScale);
+          if (a.bias != nullptr) r = __hadd(r, static_cast<const __half*>(a.bias)[n]);
+          const int tk = a.tok0 + tok;
+          if (a.dst_layout == MLD_LAYOUT_SLICED)
+            static_cast<__half*>(a.y)[((int64_t)(n >> 2) * a.M_total + tk) * 4 + (n & 3)] = r;
+          else if (n < a.N)
+            static_cast<__half*>(a.y)[(int64_t)tk * a.N + n] = r;
+        }
       }
     }
     if (a.ksplit > 1 && kr == 1) mbar_arrive_cluster(bar_remote);  // release: the stores above are visible
     MLD_CONSUMER_BARRIER();
+    if (tr && threadIdx.x == 0) tr[5] = globaltimer_ns();
   }
 }
 
@@ -535,7 +586,11 @@ StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slic
   gm.stage_rows = kStageRows;
   // With programmatic dependent launch two consecutive GEMVs share an SM while
   // one drains and the next prefetches, so each takes at most half of it.
-  const int budget = pdl ? 112 * 1024 : 224 * 1024;
+  int budget = pdl ? 112 * 1024 : 224 * 1024;
+  if (const char* kb = getenv("MLD_GEMV_SMEM_KB")) {  // tuning override
+    const int v = atoi(kb);
+    if (v >= 32 && v <= 224) budget = v * 1024;
+  }
   int stages = (budget - fixed) / gm.stage_bytes;
   if (stages > 16) stages = 16;
   if (stages < 2) stages = (227 * 1024 - fixed) / gm.stage_bytes;

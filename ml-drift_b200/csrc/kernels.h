@@ -54,8 +54,10 @@ struct StripArgs {
   int gs_shift;       // log2(group_slices) when it is a power of two below a stage, else -1
   int red_m;          // token stride of the reduction buffers
   int dst_layout;
+  int epilogue;       // mld_epilogue
   float scalar_scale;
   int pdl;            // launched with programmatic stream serialization
+  unsigned long long* trace;  // optional [grid][8] timestamps (ns) for tuning; null in normal use
 };
 
 struct StripGeometry {

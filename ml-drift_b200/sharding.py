@@ -5,7 +5,8 @@ quantises / packs that sub-matrix on its own (per-row and per-block scales do no
 concatenating the shard outputs in rank order reproduces the unsharded output.  The fused matrices
 are split so that the concatenation of shard outputs is again a plain vector:
   q|k|v   : each rank takes the rows of its own heads from q, from k and from v;
-  gate|up : each rank takes its slice of the hidden dimension from gate and from up.
+  gate|up : each rank takes its slice of the hidden dimension, rows interleaved gate_i, up_i, so
+            that the projection's fused SiLU*mul write sees both halves of a pair.
 The reference has no counterpart (it is single-device); the rule follows from the FC definition
 (ml_drift/common/task/testing_ref_ops.cc:961-988: every output channel is its own dot product).
 """
@@ -35,9 +36,10 @@ def qkv_shard_rows(heads: int, head_dim: int, rank: int, world: int) -> np.ndarr
 
 
 def gate_up_shard_rows(ffn: int, rank: int, world: int) -> np.ndarray:
-    """Rows of the fused [2*ffn][k] gate|up matrix held by `rank`."""
+    """Rows of the logical [gate ; up] matrix ([2*ffn][k]) held by `rank`, in the interleaved order
+    gate_i, up_i, gate_i+1, up_i+1, ... the decoder's fused gate/up projection expects."""
     own = _block(ffn, rank, world)
-    return np.concatenate([own, ffn + own])
+    return np.stack([own, ffn + own], axis=1).reshape(-1)
 
 
 def gathered_order(kind: str, rank_outputs):
@@ -45,6 +47,8 @@ def gathered_order(kind: str, rank_outputs):
     kind: 'column' (plain concatenation), 'qkv' or 'gate_up' (fused matrices: per-part concatenation)."""
     if kind == "column":
         return np.concatenate(rank_outputs)
-    parts = 3 if kind == "qkv" else 2
-    split = [np.split(np.asarray(o), parts) for o in rank_outputs]
-    return np.concatenate([np.concatenate([s[p] for s in split]) for p in range(parts)])
+    if kind == "gate_up":      # per rank: gate_i, up_i interleaved -> [all gates | all ups]
+        outs = [np.asarray(o) for o in rank_outputs]
+        return np.concatenate([np.concatenate([o[0::2] for o in outs]), np.concatenate([o[1::2] for o in outs])])
+    split = [np.split(np.asarray(o), 3) for o in rank_outputs]
+    return np.concatenate([np.concatenate([s[p] for s in split]) for p in range(3)])

@@ -28,7 +28,10 @@ def build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos, world=1, rank=0
             w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
             q, s = oracle.quantize_int4_sym(w, 32)
             layer[name] = {"packed": oracle.rearrange_int8_as_uint4(q), "scale": s}
-            dev["w" + name] = _dev(layer[name]["packed"])
+            if name == "gu":   # the device matrix interleaves gate_i, up_i rows for the fused SiLU*mul write
+                order = mld.sharding.gate_up_shard_rows(ffn, 0, 1)
+                q, s = q[order], s[order]
+            dev["w" + name] = _dev(oracle.rearrange_int8_as_uint4(q))
             dev["s" + name] = _dev(oracle.scale_layout(s, True).view(np.float16))
         for n in ("norm1", "norm2"):
             g = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float16)

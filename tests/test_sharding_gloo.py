@@ -63,7 +63,7 @@ def test_shard_row_helpers():
     shd = g.import_package().sharding
     assert shd.column_shard_rows(8, 1, 2).tolist() == [4, 5, 6, 7]
     assert shd.qkv_shard_rows(2, 2, 1, 2).tolist() == [2, 3, 6, 7, 10, 11]
-    assert shd.gate_up_shard_rows(4, 0, 2).tolist() == [0, 1, 4, 5]
+    assert shd.gate_up_shard_rows(4, 0, 2).tolist() == [0, 4, 1, 5]
     allrows = np.sort(np.concatenate([shd.qkv_shard_rows(32, 128, r, 8) for r in range(8)]))
     assert np.array_equal(allrows, np.arange(3 * 4096))
     import pytest
