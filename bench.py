@@ -338,14 +338,18 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     nccl_id = None
+    # how the ranks assemble sharded vectors: "peer" = the producing kernels store their shards into
+    # every rank's memory over NVLink; "nccl" = an all-gather after each producing kernel
+    exchange = os.environ.get("MLD_SHARD_EXCHANGE", "peer") if world > 1 else "none"
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-        idt = torch.zeros(128, dtype=torch.uint8, device=dev)
-        if rank == 0:
-            idt.copy_(torch.frombuffer(bytearray(mld.comm_unique_id()), dtype=torch.uint8))
-        dist.broadcast(idt, 0)
-        nccl_id = bytes(idt.cpu().numpy().tobytes())
+        if exchange == "nccl":
+            idt = torch.zeros(128, dtype=torch.uint8, device=dev)
+            if rank == 0:
+                idt.copy_(torch.frombuffer(bytearray(mld.comm_unique_id()), dtype=torch.uint8))
+            dist.broadcast(idt, 0)
+            nccl_id = bytes(idt.cpu().numpy().tobytes())
 
     def barrier():
         if world > 1:
@@ -365,6 +369,12 @@ def run_ours(args):
                       world=world, nccl_id=nccl_id)
     for l, t in enumerate(layers):
         dec.set_layer(l, **t)
+    if exchange == "peer":
+        mine = torch.frombuffer(bytearray(dec.ipc_export()), dtype=torch.uint8).to(dev)
+        table = [torch.zeros(64, dtype=torch.uint8, device=dev) for _ in range(world)]
+        dist.all_gather(table, mine)
+        dec.ipc_import(b"".join(t.cpu().numpy().tobytes() for t in table))
+        barrier()
     pos = CFG["kv_len"]
     gen = torch.Generator(device=dev).manual_seed(7)
     x = torch.randn(CFG["d_model"], generator=gen, device=dev, dtype=torch.float32).half()
@@ -453,7 +463,7 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"7B INT4 decode step ({n_layers}L, d{d}, 32h x128, ffn{ffn}, KV 2048, batch 1)",
                        "weights": "INT4 block-32, fp16 scales, random init ~N(0,0.02)",
-                       "parallelism": f"column-sharded x{world}" if world > 1 else "single GPU",
+                       "parallelism": f"column-sharded x{world}, shard exchange: {exchange}" if world > 1 else "single GPU",
                        "l2": "inputs larger than L2 (3.6 GB of weights per step / world)",
                        "timed_with": "cuda graph replay" if graph is not None else "direct launches"},
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": d * 2, "d2h_bytes_per_step": d * 2},

@@ -194,6 +194,13 @@ MLD_API int mld_fc_plan_destroy(mld_fc_plan* plan);
 /* Bytes of device workspace the plan holds. */
 MLD_API size_t mld_fc_plan_workspace_bytes(const mld_fc_plan* plan);
 
+/* Optional hint for the next mld_fc_run on this plan: once that call's decode
+ * kernel has requested all of its own data it also asks for `bytes` of
+ * `next_weights` (the packed weights of whichever projection runs after it) to
+ * be brought into L2, so the bytes travel while the memory system would be
+ * idle.  One-shot; has no effect on results.  No counterpart in the reference. */
+MLD_API int mld_fc_plan_prefetch_next(mld_fc_plan* plan, const void* next_weights, size_t bytes);
+
 /* Dispatch of one FullyConnected node (ClOperation::AddToQueue,
  * cl/cl_operation.cc:85-89) with the argument order of
  * fc::AddWeightsArguments (fully_connected_util.cc:423-487):
@@ -273,9 +280,22 @@ typedef struct mld_decoder mld_decoder;
  * the caller distributes it).  No counterpart in the reference, which is
  * single-device. */
 MLD_API int mld_comm_unique_id(void* id128);
-/* nccl_id128 may be NULL when world == 1.  Collective when world > 1. */
+/* nccl_id128 may be NULL when world == 1, or when the ranks will exchange
+ * shards directly (mld_decoder_ipc_export / _import below).  Collective when
+ * an id is given. */
 MLD_API int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_decoder** out);
 MLD_API int mld_decoder_destroy(mld_decoder* dec);
+/* Direct shard exchange between the ranks of one node, without a collective
+ * library: every kernel that produces a shard stores it straight into each
+ * rank's copy of the gathered vector (peer stores over NVLink) and raises a
+ * completion flag there; the consuming kernel waits for all flags (bounded).
+ * Each rank exports a 64-byte handle of its exchange block, the caller
+ * distributes them (rank order, world x 64 bytes) and every rank imports the
+ * table; all ranks must have imported before any of them steps.  Without this
+ * the sharded decoder all-gathers through NCCL.  No counterpart in the
+ * reference. */
+MLD_API int mld_decoder_ipc_export(mld_decoder* dec, void* handle64);
+MLD_API int mld_decoder_ipc_import(mld_decoder* dec, const void* handles);
 MLD_API size_t mld_decoder_scratch_bytes(const mld_decoder* dec);
 MLD_API int mld_decoder_set_layer(mld_decoder* dec, int32_t layer, const mld_layer_weights* w);
 /* One token through all layers (OpenCLLlmModelRunner::Decode,

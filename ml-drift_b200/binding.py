@@ -224,6 +224,16 @@ class Decoder:
         self._keep.append(tensors)
         _check(lib().mld_decoder_set_layer(self._h, layer, C.byref(lw)), "mld_decoder_set_layer")
 
+    def ipc_export(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        _check(lib().mld_decoder_ipc_export(self._h, buf), "mld_decoder_ipc_export")
+        return buf.raw
+
+    def ipc_import(self, handles: bytes):
+        """handles: the 64-byte exports of all ranks, concatenated in rank order."""
+        _check(lib().mld_decoder_ipc_import(self._h, C.create_string_buffer(handles, len(handles))),
+               "mld_decoder_ipc_import")
+
     def step(self, x_in, x_out, pos, stream=None):
         _check(lib().mld_decoder_step(self._h, _ptr(x_in), _ptr(x_out), pos, _stream(stream)), "mld_decoder_step")
 

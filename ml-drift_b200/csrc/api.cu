@@ -107,6 +107,8 @@ struct mld_fc_plan {
   float* a_params;       // per-token {inv_scale, offset, sum}
   const void* prepared_w;
   const void* prepared_s;
+  const void* next_w;    // one-shot L2 prefetch hint for the next mld_fc_run on this plan
+  size_t next_w_bytes;
   std::vector<TmapEntry> tmaps;  // tensor maps keyed by the (weights, scale) pointers last seen
   std::mutex mu;
 };
@@ -237,6 +239,8 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   p->w_kmajor = p->x_kmajor = nullptr;
   p->a_params = nullptr;
   p->prepared_w = p->prepared_s = nullptr;
+  p->next_w = nullptr;
+  p->next_w_bytes = 0;
   const char* enc = getenv("MLD_GEMV_OPERANDS");  // "exact" or "subnormal"
   p->subnormal = !(enc != nullptr && strcmp(enc, "exact") == 0);
   const char* pdl = getenv("MLD_GEMV_PDL");        // "0" disables programmatic dependent launch
@@ -284,6 +288,14 @@ int mld_fc_plan_destroy(mld_fc_plan* plan) {
 
 size_t mld_fc_plan_workspace_bytes(const mld_fc_plan* plan) { return plan ? plan->ws_bytes : 0; }
 
+int mld_fc_plan_prefetch_next(mld_fc_plan* plan, const void* next_weights, size_t bytes) {
+  MLD_REQUIRE(plan != nullptr, "null plan");
+  MLD_REQUIRE((reinterpret_cast<uintptr_t>(next_weights) & 15) == 0, "prefetch address must be 16-byte aligned");
+  plan->next_w = bytes > 0 ? next_weights : nullptr;
+  plan->next_w_bytes = bytes;
+  return MLD_OK;
+}
+
 static int run_generic(mld_fc_plan* p, const void* src, const void* weights, const void* scale, const void* zp,
                        const void* bias, void* dst, int tokens, cudaStream_t stream) {
   const mld_fc_desc& d = p->d;
@@ -311,7 +323,7 @@ static int run_generic(mld_fc_plan* p, const void* src, const void* weights, con
 }
 
 static int run_stream(mld_fc_plan* p, const void* src, const void* weights, const void* scale, const void* bias,
-                      void* dst, int tokens, cudaStream_t stream) {
+                      void* dst, int tokens, cudaStream_t stream, const PeerScatter* scatter, const PeerWait* wait) {
   const mld_fc_desc& d = p->d;
   const StripGeometry& gm = p->gm;
   const int N4 = align_n(d.n, 4), SS = div_up(d.k, 4), DS = N4 / 4;
@@ -372,6 +384,13 @@ static int run_stream(mld_fc_plan* p, const void* src, const void* weights, cons
   a.scalar_scale = d.scalar_scale;
   a.pdl = p->pdl ? 1 : 0;
   a.trace = g_trace_buffer;
+  memset(&a.scatter, 0, sizeof a.scatter);
+  memset(&a.wait, 0, sizeof a.wait);
+  if (scatter != nullptr) a.scatter = *scatter;
+  if (wait != nullptr) a.wait = *wait;
+  a.next_w = p->next_w;
+  a.next_w_bytes = p->next_w_bytes;
+  p->next_w = nullptr;  // the hint is consumed by this call
   for (int tok0 = 0; tok0 < tokens; tok0 += 8) {
     a.tok0 = tok0;
     a.M = tokens - tok0 < 8 ? tokens - tok0 : 8;
@@ -417,6 +436,14 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
 
 int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const void* scale, const void* zero_point,
                const void* bias, void* dst, int32_t tokens, void* stream_v) {
+  return mld::fc_run_internal(plan, src, weights, scale, zero_point, bias, dst, tokens, stream_v, nullptr, nullptr);
+}
+
+}  // extern "C"
+
+int mld::fc_run_internal(mld_fc_plan* plan, const void* src, const void* weights, const void* scale,
+                         const void* zero_point, const void* bias, void* dst, int32_t tokens, void* stream_v,
+                         const PeerScatter* scatter, const PeerWait* wait) {
   MLD_REQUIRE(plan != nullptr, "null plan");
   const mld_fc_desc& d = plan->d;
   MLD_REQUIRE(tokens >= 0 && tokens <= d.max_tokens, "tokens exceeds the plan's max_tokens");
@@ -451,7 +478,7 @@ int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const vo
                        (scale == nullptr || (reinterpret_cast<uintptr_t>(scale) & 15) == 0);
   const bool layout_ok = d.src_layout == MLD_LAYOUT_SLICED || tokens == 1;
   if (plan->stream_ok && tokens <= 16 && aligned && layout_ok)
-    return run_stream(plan, src, weights, scale, b, dst, tokens, stream);
+    return run_stream(plan, src, weights, scale, b, dst, tokens, stream, scatter, wait);
   if (d.epilogue != MLD_EPILOGUE_NONE) {
     set_last_error_text("the fused SiLU*mul write needs 16-byte aligned fp16 tensors in the sliced layout");
     return MLD_UNIMPLEMENTED;
@@ -459,4 +486,4 @@ int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const vo
   return run_generic(plan, src, weights, scale, zp, b, dst, tokens, stream);
 }
 
-}  // extern "C"
+

@@ -158,6 +158,10 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
                ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+// Fire-and-forget request to bring [gsrc, gsrc + bytes) into L2 (16-byte aligned, size % 16 == 0).
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -170,6 +174,25 @@ __device__ __forceinline__ bool elect_one() {
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(pred));
   return pred != 0;
+}
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Waits until every rank's flag has reached `seq`; false when the time limit ran out.
+__device__ __forceinline__ bool wait_peer_flags(const unsigned* flags, int world, unsigned seq) {
+  const unsigned long long t0 = globaltimer_ns();
+  for (int r = 0; r < world; ++r) {
+    while (static_cast<int>(ld_acquire_sys(flags + r) - seq) < 0) {
+      if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    }
+  }
+  return true;
 }
 
 // Programmatic dependent launch: wait for the preceding kernel's memory, and

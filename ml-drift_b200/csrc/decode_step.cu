@@ -36,10 +36,15 @@ __device__ __forceinline__ float warp_sum(float v) {
 // (qwen3_model_builder.cc:890-902).  gamma == null: only h is written.
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ r,
                                                           const __half* __restrict__ gamma, __half* __restrict__ h_out,
-                                                          __half* __restrict__ y, int d, float eps) {
+                                                          __half* __restrict__ y, int d, float eps, PeerWait wait) {
   __shared__ float part[32];
   pdl_wait();
   pdl_launch_dependents();
+  if (wait.world > 1) {  // x is a vector other ranks contribute to: wait for all of its shards
+    if (threadIdx.x == 0)
+      wait_peer_flags(wait.flags, wait.world, static_cast<unsigned>(*wait.step * wait.seq_per_step + wait.seq_off));
+    __syncthreads();
+  }
   float ss = 0.0f;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = __half2float(x[i]);
@@ -190,6 +195,7 @@ struct AttnStepArgs {
   __half* out;
   int heads, pos, splits;
   float min_ts, max_ts, q_scale;
+  PeerScatter scatter;  // world > 1: the merged head outputs go to every rank's attention vector
 };
 __global__ void __launch_bounds__(128) attn_step_kernel(AttnStepArgs a) {
   pdl_wait();
@@ -307,8 +313,47 @@ __global__ void __launch_bounds__(128) attn_step_kernel(AttnStepArgs a) {
     to += w * __ldcg(a.part_o + ((size_t)head * a.splits + s) * kHeadDim + dim);
     tl += w * __ldcg(a.part_ml + ((size_t)head * a.splits + s) * 2 + 1);
   }
-  a.out[(size_t)head * kHeadDim + dim] = __float2half_rn(to / tl);
+  const __half res = __float2half_rn(to / tl);
+  if (a.scatter.world > 1) {
+    for (int pr = 0; pr < a.scatter.world; ++pr)
+      static_cast<__half*>(a.scatter.y_peers[pr])[(size_t)head * kHeadDim + dim] = res;
+    // second-level ticket over the heads of this rank: the last head raises the flag everywhere
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      a.tickets[head] = 0;
+      if (atomicAdd(a.scatter.ticket, 1) == a.heads - 1) {
+        *a.scatter.ticket = 0;
+        __threadfence_system();
+        const unsigned seq = static_cast<unsigned>(*a.scatter.step * a.scatter.seq_per_step + a.scatter.seq_off);
+        for (int pr = 0; pr < a.scatter.world; ++pr) st_release_sys(a.scatter.flag_peers[pr], seq);
+      }
+    }
+    return;
+  }
+  a.out[(size_t)head * kHeadDim + dim] = res;
   if (threadIdx.x == 0) a.tickets[head] = 0;
+}
+
+// Step bookkeeping of the peer exchange: bumps the device-side step counter
+// (flag values are derived from it, so CUDA-graph replays produce fresh values).
+__global__ void bump_step_kernel(int* step) {
+  pdl_wait();
+  pdl_launch_dependents();
+  *step += 1;
+}
+
+// Final copy of a gathered vector out of the exchange block, after all shards arrived.
+__global__ void __launch_bounds__(256) copy_after_wait_kernel(const __half* __restrict__ src, __half* __restrict__ dst,
+                                                              int n, PeerWait wait) {
+  pdl_wait();
+  pdl_launch_dependents();
+  if (wait.world > 1) {
+    if (threadIdx.x == 0)
+      wait_peer_flags(wait.flags, wait.world, static_cast<unsigned>(*wait.step * wait.seq_per_step + wait.seq_off));
+    __syncthreads();
+  }
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = src[i];
 }
 
 // Launches a glue kernel so that it may be scheduled while its predecessor in
@@ -396,10 +441,19 @@ struct mld_decoder {
   __half *xn, *qkv, *attn_local, *attn_full, *o_local, *o_full, *h, *hn, *gu, *act_local, *act_full, *d_full, *x_stage, *y_stage;
   float *part_o, *part_ml;
   int* tickets;
+  bool prefetch;
+  size_t bytes_qkv, bytes_o, bytes_gu, bytes_down;
   uint8_t* scratch;
   int splits;
   ncclComm_t comm;
   size_t scratch_bytes;
+  // peer exchange (world > 1, after mld_decoder_ipc_import): gathered vectors and flags live in one
+  // IPC-shared block with the same layout on every rank
+  uint8_t* xchg;                 // this rank's block
+  uint8_t* xchg_peers[8];        // every rank's block as mapped here (index = rank; own entry = xchg)
+  bool peer_mode;
+  size_t off_attn, off_h, off_act, off_xa, off_xb, off_flags, xchg_bytes;
+  int* peer_tickets;             // local: [4] CTA counters + [1] step counter
 };
 
 namespace {
@@ -538,7 +592,7 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   MLD_REQUIRE(d->world >= 1 && d->rank >= 0 && d->rank < d->world, "bad rank/world");
   MLD_REQUIRE(d->heads % d->world == 0 && d->ffn % d->world == 0, "heads and ffn must divide by world");
   MLD_REQUIRE(d->block > 0 && d->d_model % d->block == 0 && d->ffn % d->block == 0, "block must divide K");
-  MLD_REQUIRE(d->world == 1 || nccl_id128 != nullptr, "a multi-rank decoder needs the shared NCCL id");
+  MLD_REQUIRE(d->world <= 8, "at most 8 ranks");
   int device = d->device;
   if (device < 0) MLD_CUDA_CHECK(cudaGetDevice(&device));
   MLD_CUDA_CHECK(cudaSetDevice(device));
@@ -557,6 +611,10 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   memset(dec->layers.data(), 0, sizeof(mld_layer_weights) * d->layers);
   dec->comm = nullptr;
   dec->scratch = nullptr;
+  dec->xchg = nullptr;
+  dec->peer_tickets = nullptr;
+  dec->peer_mode = false;
+  for (int r = 0; r < 8; ++r) dec->xchg_peers[r] = nullptr;
   dec->p_qkv = dec->p_o = dec->p_gu = dec->p_down = nullptr;
   int rc = make_plan(3 * dec->d_local, d->d_model, d->block, device, false, MLD_EPILOGUE_NONE, &dec->p_qkv);
   if (rc == MLD_OK) rc = make_plan(dec->d_local, d->d_model, d->block, device, true, MLD_EPILOGUE_NONE, &dec->p_o);
@@ -565,6 +623,14 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   if (rc == MLD_OK) rc = make_plan(dec->d_local, d->ffn, d->block, device, true, MLD_EPILOGUE_NONE, &dec->p_down);
   // split count: fill the GPU about four CTAs deep
   int sms = sm_count(device);
+  {
+    const char* pf = getenv("MLD_DECODER_PREFETCH");  // "0" disables the next-projection L2 prefetch
+    dec->prefetch = !(pf != nullptr && strcmp(pf, "0") == 0);
+    dec->bytes_qkv = (size_t)3 * dec->d_local * d->d_model / 2;
+    dec->bytes_o = (size_t)dec->d_local * d->d_model / 2;
+    dec->bytes_gu = (size_t)2 * dec->ffn_local * d->d_model / 2;
+    dec->bytes_down = (size_t)dec->d_local * d->ffn / 2;
+  }
   const int splits = attn_splits(dec->heads_local, sms);
   dec->splits = splits;
   const size_t dm = d->d_model, ff = d->ffn;
@@ -605,11 +671,41 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   dec->part_o = reinterpret_cast<float*>(take((size_t)dec->heads_local * splits * kHeadDim * 4));
   dec->part_ml = reinterpret_cast<float*>(take((size_t)dec->heads_local * splits * 2 * 4));
   dec->tickets = reinterpret_cast<int*>(take((size_t)dec->heads_local * 4));  // zeroed above
+  if (d->world > 1) {
+    // Vectors that every rank contributes a shard to live in one block with the same layout on all
+    // ranks, so that it can be shared between the processes (IPC) and written by peers.
+    size_t xo = 0;
+    auto xtake = [&](size_t bytes) {
+      const size_t o = xo;
+      xo += pad(bytes);
+      return o;
+    };
+    dec->off_attn = xtake(dm * 2);
+    dec->off_h = xtake(dm * 2);
+    dec->off_act = xtake(ff * 2);
+    dec->off_xa = xtake(dm * 2);
+    dec->off_xb = xtake(dm * 2);
+    dec->off_flags = xtake(4 * 8 * sizeof(unsigned));
+    dec->xchg_bytes = xo;
+    if (cudaMalloc(&dec->xchg, xo) != cudaSuccess || cudaMalloc(&dec->peer_tickets, 256) != cudaSuccess) {
+      set_last_error_text("decoder exchange allocation failed");
+      mld_decoder_destroy(dec);
+      return MLD_CUDA_ERROR;
+    }
+    cudaMemset(dec->xchg, 0, xo);
+    cudaMemset(dec->peer_tickets, 0, 256);
+    dec->xchg_peers[d->rank] = dec->xchg;
+    dec->attn_full = reinterpret_cast<__half*>(dec->xchg + dec->off_attn);
+    dec->h = reinterpret_cast<__half*>(dec->xchg + dec->off_h);
+    dec->act_full = reinterpret_cast<__half*>(dec->xchg + dec->off_act);
+    dec->o_full = reinterpret_cast<__half*>(dec->xchg + dec->off_xa);   // layer outputs ping-pong between
+    dec->d_full = reinterpret_cast<__half*>(dec->xchg + dec->off_xb);   // these two
+  }
   // a rank's shard of a gathered vector is written in place
   dec->attn_local = dec->attn_full + (size_t)d->rank * dec->d_local;
   dec->o_local = dec->o_full + (size_t)d->rank * dec->d_local;
   dec->act_local = dec->act_full + (size_t)d->rank * dec->ffn_local;
-  if (d->world > 1) {
+  if (d->world > 1 && nccl_id128 != nullptr) {
     if (!g_nccl.load()) {
       set_last_error_text("libnccl.so.2 could not be loaded");
       mld_decoder_destroy(dec);
@@ -637,7 +733,36 @@ int mld_decoder_destroy(mld_decoder* dec) {
   mld_fc_plan_destroy(dec->p_gu);
   mld_fc_plan_destroy(dec->p_down);
   if (dec->scratch != nullptr) cudaFree(dec->scratch);
+  for (int r = 0; r < 8; ++r)
+    if (dec->xchg_peers[r] != nullptr && dec->xchg_peers[r] != dec->xchg) cudaIpcCloseMemHandle(dec->xchg_peers[r]);
+  if (dec->xchg != nullptr) cudaFree(dec->xchg);
+  if (dec->peer_tickets != nullptr) cudaFree(dec->peer_tickets);
   delete dec;
+  return MLD_OK;
+}
+
+int mld_decoder_ipc_export(mld_decoder* dec, void* handle64) {
+  MLD_REQUIRE(dec != nullptr && handle64 != nullptr, "null argument");
+  MLD_REQUIRE(dec->xchg != nullptr, "a single-rank decoder has nothing to share");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  MLD_CUDA_CHECK(cudaIpcGetMemHandle(&h, dec->xchg));
+  memcpy(handle64, &h, sizeof h);
+  return MLD_OK;
+}
+
+int mld_decoder_ipc_import(mld_decoder* dec, const void* handles) {
+  MLD_REQUIRE(dec != nullptr && handles != nullptr, "null argument");
+  MLD_REQUIRE(dec->xchg != nullptr, "a single-rank decoder has no peers");
+  for (int r = 0; r < dec->d.world; ++r) {
+    if (r == dec->d.rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const uint8_t*>(handles) + (size_t)r * 64, sizeof h);
+    void* p = nullptr;
+    MLD_CUDA_CHECK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    dec->xchg_peers[r] = static_cast<uint8_t*>(p);
+  }
+  dec->peer_mode = true;
   return MLD_OK;
 }
 
@@ -665,17 +790,56 @@ int mld_decoder_step(mld_decoder* dec, const void* x_in, void* x_out, int32_t po
   //   h  = x + Wo attn            (residual added in the projection's dst write)
   //   hn = rmsnorm(h) g2;  act = silu(Wg hn) * (Wu hn)   (fused into the projection's dst write)
   //   x' = h + Wdown act
+  // Sharded: attn, h, act and x' are assembled from every rank's shard, either by an NCCL
+  // all-gather after the producing kernel or, in peer mode, by the producing kernel itself.
+  const bool peer = d.world > 1 && dec->peer_mode;
+  MLD_REQUIRE(d.world == 1 || peer || dec->comm != nullptr, "sharded decoder has neither peers nor an NCCL communicator");
+  enum { kAttn = 0, kH = 1, kAct = 2, kX = 3 };
+  auto scatter_of = [&](int kind, int layer, size_t vec_off, size_t shard_halves) {
+    PeerScatter sc;
+    memset(&sc, 0, sizeof sc);
+    if (!peer) return sc;
+    sc.world = d.world;
+    for (int r = 0; r < d.world; ++r) {
+      sc.y_peers[r] = dec->xchg_peers[r] + vec_off + (size_t)d.rank * shard_halves * 2;
+      sc.flag_peers[r] = reinterpret_cast<unsigned*>(dec->xchg_peers[r] + dec->off_flags) + kind * 8 + d.rank;
+    }
+    sc.ticket = dec->peer_tickets + kind;
+    sc.step = dec->peer_tickets + 4;
+    sc.seq_off = 4 * layer + kind + 1;
+    sc.seq_per_step = 4 * d.layers;
+    return sc;
+  };
+  auto wait_of = [&](int kind, int layer) {
+    PeerWait pw;
+    memset(&pw, 0, sizeof pw);
+    if (!peer || layer < 0) return pw;
+    pw.world = d.world;
+    pw.flags = reinterpret_cast<const unsigned*>(dec->xchg + dec->off_flags) + kind * 8;
+    pw.step = dec->peer_tickets + 4;
+    pw.seq_off = 4 * layer + kind + 1;
+    pw.seq_per_step = 4 * d.layers;
+    return pw;
+  };
   const __half* x = static_cast<const __half*>(x_in);
   int rc;
+  if (peer) {
+    rc = launch_glue(bump_step_kernel, dim3(1), dim3(1), stream, dec->peer_tickets + 4);
+    if (rc != MLD_OK) return rc;
+  }
   for (int l = 0; l < d.layers; ++l) {
     const mld_layer_weights& w = dec->layers[l];
     MLD_REQUIRE(w.wqkv != nullptr, "layer weights not set");
     const bool last = l + 1 == d.layers;
-    // the layer's output vector: the caller's buffer for the last layer, else a ping-pong pair
-    __half* x_next = last ? static_cast<__half*>(x_out) : ((l & 1) ? dec->d_full : dec->o_full);
+    // the layer's output vector: the caller's buffer for the last layer (peers cannot write there, so
+    // peer mode copies it out at the end), else a ping-pong pair
+    __half* x_next = (last && !peer) ? static_cast<__half*>(x_out) : ((l & 1) ? dec->d_full : dec->o_full);
+    const size_t off_x_next = (l & 1) ? dec->off_xb : dec->off_xa;
     rc = launch_glue(add_rmsnorm_kernel, dim3(1), dim3(1024), stream, x, static_cast<const __half*>(nullptr),
-                     static_cast<const __half*>(w.norm1), static_cast<__half*>(nullptr), dec->xn, dm, d.rms_eps);
+                     static_cast<const __half*>(w.norm1), static_cast<__half*>(nullptr), dec->xn, dm, d.rms_eps,
+                     wait_of(kX, l - 1));
     if (rc != MLD_OK) return rc;
+    if (dec->prefetch) mld_fc_plan_prefetch_next(dec->p_qkv, w.wo, dec->bytes_o);
     rc = mld_fc_run(dec->p_qkv, dec->xn, w.wqkv, w.sqkv, nullptr, nullptr, dec->qkv, 1, stream);
     if (rc != MLD_OK) return rc;
     {
@@ -693,28 +857,50 @@ int mld_decoder_step(mld_decoder* dec, const void* x_in, void* x_out, int32_t po
       aa.min_ts = d.rope_min_timescale;
       aa.max_ts = d.rope_max_timescale;
       aa.q_scale = q_scale;
+      aa.scatter = scatter_of(kAttn, l, dec->off_attn, dl);
       rc = launch_glue(attn_step_kernel, dim3(Hl, dec->splits), dim3(128), stream, aa);
       if (rc != MLD_OK) return rc;
     }
-    if ((rc = gather(dec, dec->attn_local, dec->attn_full, dl, stream)) != MLD_OK) return rc;
+    if (!peer && (rc = gather(dec, dec->attn_local, dec->attn_full, dl, stream)) != MLD_OK) return rc;
     // h shard = x shard + Wo attn
     __half* h_local = dec->h + (size_t)d.rank * dl;
-    rc = mld_fc_run(dec->p_o, dec->attn_full, w.wo, w.so, nullptr, x + (size_t)d.rank * dl, h_local, 1, stream);
-    if (rc != MLD_OK) return rc;
-    if ((rc = gather(dec, h_local, dec->h, dl, stream)) != MLD_OK) return rc;
+    {
+      const PeerScatter sc = scatter_of(kH, l, dec->off_h, dl);
+      const PeerWait pw = wait_of(kAttn, l);
+      if (dec->prefetch) mld_fc_plan_prefetch_next(dec->p_o, w.wgu, dec->bytes_gu);
+      rc = fc_run_internal(dec->p_o, dec->attn_full, w.wo, w.so, nullptr, x + (size_t)d.rank * dl, h_local, 1, stream,
+                           peer ? &sc : nullptr, peer ? &pw : nullptr);
+      if (rc != MLD_OK) return rc;
+    }
+    if (!peer && (rc = gather(dec, h_local, dec->h, dl, stream)) != MLD_OK) return rc;
     rc = launch_glue(add_rmsnorm_kernel, dim3(1), dim3(1024), stream, static_cast<const __half*>(dec->h),
                      static_cast<const __half*>(nullptr), static_cast<const __half*>(w.norm2),
-                     static_cast<__half*>(nullptr), dec->hn, dm, d.rms_eps);
+                     static_cast<__half*>(nullptr), dec->hn, dm, d.rms_eps, wait_of(kH, l));
     if (rc != MLD_OK) return rc;
-    rc = mld_fc_run(dec->p_gu, dec->hn, w.wgu, w.sgu, nullptr, nullptr, dec->act_local, 1, stream);
-    if (rc != MLD_OK) return rc;
-    if ((rc = gather(dec, dec->act_local, dec->act_full, fl, stream)) != MLD_OK) return rc;
+    {
+      const PeerScatter sc = scatter_of(kAct, l, dec->off_act, fl);
+      if (dec->prefetch) mld_fc_plan_prefetch_next(dec->p_gu, w.wdown, dec->bytes_down);
+      rc = fc_run_internal(dec->p_gu, dec->hn, w.wgu, w.sgu, nullptr, nullptr, dec->act_local, 1, stream,
+                           peer ? &sc : nullptr, nullptr);
+      if (rc != MLD_OK) return rc;
+    }
+    if (!peer && (rc = gather(dec, dec->act_local, dec->act_full, fl, stream)) != MLD_OK) return rc;
     __half* xn_local = x_next + (size_t)d.rank * dl;
-    rc = mld_fc_run(dec->p_down, dec->act_full, w.wdown, w.sdown, nullptr, dec->h + (size_t)d.rank * dl, xn_local, 1,
-                    stream);
-    if (rc != MLD_OK) return rc;
-    if ((rc = gather(dec, xn_local, x_next, dl, stream)) != MLD_OK) return rc;
+    {
+      const PeerScatter sc = scatter_of(kX, l, off_x_next, dl);
+      const PeerWait pw = wait_of(kAct, l);
+      if (dec->prefetch && !last) mld_fc_plan_prefetch_next(dec->p_down, dec->layers[l + 1].wqkv, dec->bytes_qkv);
+      rc = fc_run_internal(dec->p_down, dec->act_full, w.wdown, w.sdown, nullptr, dec->h + (size_t)d.rank * dl, xn_local,
+                           1, stream, peer ? &sc : nullptr, peer ? &pw : nullptr);
+      if (rc != MLD_OK) return rc;
+    }
+    if (!peer && (rc = gather(dec, xn_local, x_next, dl, stream)) != MLD_OK) return rc;
     x = x_next;
+  }
+  if (peer) {
+    rc = launch_glue(copy_after_wait_kernel, dim3(4), dim3(256), stream, x, static_cast<__half*>(x_out), dm,
+                     wait_of(kX, d.layers - 1));
+    if (rc != MLD_OK) return rc;
   }
   return MLD_OK;
 }

@@ -295,8 +295,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 //   fp16 route: w = half(half(u * scale) + half(-scale * shift)), the
 //     WeightsConverter arithmetic (conv_weights_converter.cc:248-290);
 //   s8 route: w = u - shift (exact).
-// A CTA transposes a 32 x 32 block tile through shared memory so that both the
-// packed reads and the K-major writes are coalesced.
+// A CTA moves a tile of 32 k-slices x 32 output slices: packed rows are read
+// coalesced into shared memory, then each thread turns whole 4x4 blocks into
+// four K-major pieces with packed-half arithmetic; consecutive lanes take
+// consecutive k-slices, so every output row is written in 256-byte runs.
+__device__ __forceinline__ uint32_t dq_pair(uint32_t w, int nib, __half2 s2, __half2 b2) {
+  // nibbles `nib` of the two halves of w (k even / k odd of one output) -> (1024 + u) -> u -> u*s + b
+  const uint32_t m = ((w >> (4 * nib)) & 0x000F000Fu) | 0x64006400u;
+  const __half2 u = __hsub2(*reinterpret_cast<const __half2*>(&m), __float2half2_rn(1024.0f));
+  const __half2 r = __hadd2(__hmul2(u, s2), b2);
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t dq_pair8(uint32_t bytes2, __half2 s2, __half2 b2) {
+  // two bytes (k even in bits 0..7, k odd in bits 16..23) -> halves
+  const uint32_t m = (bytes2 & 0x00FF00FFu) | 0x64006400u;
+  const __half2 u = __hsub2(*reinterpret_cast<const __half2*>(&m), __float2half2_rn(1024.0f));
+  const __half2 r = __hadd2(__hmul2(u, s2), b2);
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 template <int BITS, bool TO_S8>
 __global__ void __launch_bounds__(256) dequant_weights_kernel(const uint8_t* __restrict__ packed,
                                                              const __half* __restrict__ scale, int scale_mode, int G,
@@ -304,10 +321,10 @@ __global__ void __launch_bounds__(256) dequant_weights_kernel(const uint8_t* __r
                                                              int src_slices, int Kp, void* __restrict__ out) {
   constexpr int T = 32;
   constexpr int BLK = BITS == 4 ? 8 : 16;
-  __shared__ __align__(16) uint8_t tile[T][T * BLK + 16];
+  constexpr int PITCH = T * BLK + 8;  // +8 bytes: lanes that walk down a column hit distinct banks
+  __shared__ __align__(16) uint8_t tile[T * PITCH];
   const int ks0 = blockIdx.x * T, ds0 = blockIdx.y * T;
   const int N4 = dst_slices * 4;
-  // load: thread -> (row ks, 8-byte piece); rows are always 8-byte aligned
   constexpr int PIECES = T * BLK / 8;
   for (int idx = threadIdx.x; idx < T * PIECES; idx += blockDim.x) {
     const int r = idx / PIECES, pc = idx % PIECES;
@@ -316,55 +333,78 @@ __global__ void __launch_bounds__(256) dequant_weights_kernel(const uint8_t* __r
     uint2 v = make_uint2(0, 0);
     if (ks < src_slices && byte0 < dst_slices * BLK)
       v = *reinterpret_cast<const uint2*>(packed + (size_t)ks * dst_slices * BLK + byte0);
-    *reinterpret_cast<uint2*>(&tile[r][pc * 8]) = v;
+    *reinterpret_cast<uint2*>(&tile[r * PITCH + pc * 8]) = v;
   }
   __syncthreads();
-  // store: thread -> (output channel n_local, group of 8 k-slices): 32 values = 64 bytes (fp16) / 32 bytes (s8)
   const int shift = BITS == 8 ? 128 : 8;
-  for (int idx = threadIdx.x; idx < T * 4 * (T / 8); idx += blockDim.x) {
-    const int n_local = idx / (T / 8), kg = idx % (T / 8);
-    const int n = ds0 * 4 + n_local;
-    if (n >= N4) continue;
-    const int dsl = n_local >> 2, o = n_local & 3;
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      const int r = kg * 8 + kk;
-      const int ks = ks0 + r;
-      if (ks * 4 >= Kp) break;
-      uint8_t u[4];
-      const uint8_t* b = &tile[r][dsl * BLK];
-      if (BITS == 8) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) u[i] = b[i * 4 + o];
+  const int r = threadIdx.x & 31;  // k-slice inside the tile (fastest over lanes)
+  const int ks = ks0 + r;
+  if (ks * 4 >= Kp) return;
+  for (int dsl = threadIdx.x >> 5; dsl < T; dsl += 8) {
+    const int ds = ds0 + dsl;
+    if (ds >= dst_slices) break;
+    const int n = ds * 4;
+    if constexpr (TO_S8) {
+      uint32_t w[4];
+      if constexpr (BITS == 8) {
+        const uint4 q = make_uint4(*reinterpret_cast<const uint32_t*>(&tile[r * PITCH + dsl * 16]),
+                                   *reinterpret_cast<const uint32_t*>(&tile[r * PITCH + dsl * 16 + 4]),
+                                   *reinterpret_cast<const uint32_t*>(&tile[r * PITCH + dsl * 16 + 8]),
+                                   *reinterpret_cast<const uint32_t*>(&tile[r * PITCH + dsl * 16 + 12]));
+        // rows of q are k (bytes = outputs); transpose 4x4 bytes and re-bias u8 -> s8
+        const uint32_t a = q.x ^ 0x80808080u, b = q.y ^ 0x80808080u, c = q.z ^ 0x80808080u, d = q.w ^ 0x80808080u;
+        const uint32_t ab_lo = __byte_perm(a, b, 0x5140), ab_hi = __byte_perm(a, b, 0x7362);
+        const uint32_t cd_lo = __byte_perm(c, d, 0x5140), cd_hi = __byte_perm(c, d, 0x7362);
+        w[0] = __byte_perm(ab_lo, cd_lo, 0x5410);
+        w[1] = __byte_perm(ab_lo, cd_lo, 0x7632);
+        w[2] = __byte_perm(ab_hi, cd_hi, 0x5410);
+        w[3] = __byte_perm(ab_hi, cd_hi, 0x7632);
       } else {
+        const uint32_t lo = *reinterpret_cast<const uint32_t*>(&tile[r * PITCH + dsl * 8]);
+        const uint32_t hi = *reinterpret_cast<const uint32_t*>(&tile[r * PITCH + dsl * 8 + 4]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint8_t byte = b[2 * i + (o >> 1)];
-          u[i] = (o & 1) ? (byte >> 4) : (byte & 0xF);
+        for (int o = 0; o < 4; ++o) {
+          const int k0 = static_cast<int>((lo >> (4 * o)) & 0xF) - shift, k1 = static_cast<int>((lo >> (16 + 4 * o)) & 0xF) - shift;
+          const int k2 = static_cast<int>((hi >> (4 * o)) & 0xF) - shift, k3 = static_cast<int>((hi >> (16 + 4 * o)) & 0xF) - shift;
+          w[o] = (k0 & 0xFF) | ((k1 & 0xFF) << 8) | ((k2 & 0xFF) << 16) | ((k3 & 0xFF) << 24);
         }
       }
-      if (TO_S8) {
-        uint32_t pk = 0;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) pk |= static_cast<uint32_t>(static_cast<uint8_t>(static_cast<int>(u[i]) - shift)) << (8 * i);
-        *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(out) + (size_t)n * Kp + ks * 4) = pk;
+      for (int o = 0; o < 4; ++o)
+        *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(out) + (size_t)(n + o) * Kp + ks * 4) = w[o];
+    } else {
+      __half sc[4];
+      if (scale_mode == MLD_SCALE_SCALAR) {
+        sc[0] = sc[1] = sc[2] = sc[3] = __float2half_rn(scalar_scale);
       } else {
-        __half s;
-        if (scale_mode == MLD_SCALE_SCALAR) {
-          s = __float2half_rn(scalar_scale);
-        } else {
-          int g = scale_mode == MLD_SCALE_BLOCK ? ks / group_slices : 0;
-          if (g >= G) g = G - 1;
-          s = scale[(size_t)g * N4 + n];
-        }
-        const __half bias = __hmul(__hneg(s), __ushort2half_rn(static_cast<unsigned short>(shift)));
-        __half w[4];
+        int g = scale_mode == MLD_SCALE_BLOCK ? ks / group_slices : 0;
+        if (g >= G) g = G - 1;
+        const uint2 sv = *reinterpret_cast<const uint2*>(scale + (size_t)g * N4 + n);
+        sc[0] = __ushort_as_half(static_cast<unsigned short>(sv.x & 0xFFFF));
+        sc[1] = __ushort_as_half(static_cast<unsigned short>(sv.x >> 16));
+        sc[2] = __ushort_as_half(static_cast<unsigned short>(sv.y & 0xFFFF));
+        sc[3] = __ushort_as_half(static_cast<unsigned short>(sv.y >> 16));
+      }
+      const __half hshift = __ushort2half_rn(static_cast<unsigned short>(shift));
 #pragma unroll
-        for (int i = 0; i < 4; ++i) w[i] = __hadd(__hmul(__ushort2half_rn(u[i]), s), bias);
+      for (int o = 0; o < 4; ++o) {
+        const __half2 s2 = __half2half2(sc[o]);
+        const __half2 b2 = __half2half2(__hmul(__hneg(sc[o]), hshift));
         uint2 pk;
-        pk.x = static_cast<uint32_t>(__half_as_ushort(w[0])) | (static_cast<uint32_t>(__half_as_ushort(w[1])) << 16);
-        pk.y = static_cast<uint32_t>(__half_as_ushort(w[2])) | (static_cast<uint32_t>(__half_as_ushort(w[3])) << 16);
-        *reinterpret_cast<uint2*>(static_cast<__half*>(out) + (size_t)n * Kp + ks * 4) = pk;
+        if constexpr (BITS == 4) {
+          const uint32_t lo = *reinterpret_cast<const uint32_t*>(&tile[r * PITCH + dsl * 8]);
+          const uint32_t hi = *reinterpret_cast<const uint32_t*>(&tile[r * PITCH + dsl * 8 + 4]);
+          pk.x = dq_pair(lo, o, s2, b2);  // (k0, k1) of output o
+          pk.y = dq_pair(hi, o, s2, b2);  // (k2, k3)
+        } else {
+          const uint32_t* q = reinterpret_cast<const uint32_t*>(&tile[r * PITCH + dsl * 16]);
+          // byte o of k-row i: gather (k0, k1) and (k2, k3) into the byte lanes dq_pair8 reads
+          const uint32_t b01 = ((q[0] >> (8 * o)) & 0xFFu) | (((q[1] >> (8 * o)) & 0xFFu) << 16);
+          const uint32_t b23 = ((q[2] >> (8 * o)) & 0xFFu) | (((q[3] >> (8 * o)) & 0xFFu) << 16);
+          pk.x = dq_pair8(b01, s2, b2);
+          pk.y = dq_pair8(b23, s2, b2);
+        }
+        *reinterpret_cast<uint2*>(static_cast<__half*>(out) + (size_t)(n + o) * Kp + ks * 4) = pk;
       }
     }
   }

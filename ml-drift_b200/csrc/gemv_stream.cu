@@ -267,6 +267,10 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
       for (int it = 0; it < head; ++it) issue_weights(it, it);
       if (tr) tr[1] = globaltimer_ns();
       if (a.pdl) pdl_wait();
+      if (a.wait.world > 1) {
+        const unsigned seq = static_cast<unsigned>(*a.wait.step * a.wait.seq_per_step + a.wait.seq_off);
+        if (!wait_peer_flags(a.wait.flags, a.wait.world, seq)) atomicExch(a.error, 4);
+      }
       if (tr) tr[2] = globaltimer_ns();
       for (int it = 0; it < head; ++it) issue_x(it, it);
       int stage = head == a.stages ? 0 : head;
@@ -281,6 +285,18 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
         if (++stage == a.stages) {
           stage = 0;
           phase ^= 1;
+        }
+      }
+      // Everything this CTA needs has been requested: use the memory system's
+      // idle tail (epilogue, the glue kernels that follow) to pull this CTA's
+      // share of the next projection's weights into L2.
+      if (a.next_w != nullptr) {
+        const unsigned long long per = ((a.next_w_bytes / gridDim.x) + 127ull) & ~127ull;
+        unsigned long long lo = per * blockIdx.x, hi = lo + per;
+        if (hi > a.next_w_bytes) hi = a.next_w_bytes & ~15ull;
+        for (; lo < hi; lo += 16384ull) {
+          const unsigned long long n = hi - lo < 16384ull ? hi - lo : 16384ull;
+          bulk_prefetch_l2(static_cast<const uint8_t*>(a.next_w) + lo, static_cast<uint32_t>(n & ~15ull));
         }
       }
     }
@@ -457,10 +473,13 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
           const float u = __half2float(__float2half_rn(su * kOutScale));
           const __half r = __float2half_rn(g / (1.0f + __expf(-g)) * u);
           const int i = n >> 1, tk = a.tok0 + tok;
-          if (a.dst_layout == MLD_LAYOUT_SLICED)
-            static_cast<__half*>(a.y)[((int64_t)(i >> 2) * a.M_total + tk) * 4 + (i & 3)] = r;
-          else
-            static_cast<__half*>(a.y)[(int64_t)tk * (a.N / 2) + i] = r;
+          const int64_t yi = a.dst_layout == MLD_LAYOUT_SLICED ? (((int64_t)(i >> 2) * a.M_total + tk) * 4 + (i & 3))
+                                                               : ((int64_t)tk * (a.N / 2) + i);
+          if (a.scatter.world > 1) {
+            for (int pr = 0; pr < a.scatter.world; ++pr) static_cast<__half*>(a.scatter.y_peers[pr])[yi] = r;
+          } else {
+            static_cast<__half*>(a.y)[yi] = r;
+          }
         }
       }
     } else {
@@ -475,16 +494,36 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
           __half r = __float2half_rn(s * kOutScale);
           if (a.bias != nullptr) r = __hadd(r, static_cast<const __half*>(a.bias)[n]);
           const int tk = a.tok0 + tok;
-          if (a.dst_layout == MLD_LAYOUT_SLICED)
-            static_cast<__half*>(a.y)[((int64_t)(n >> 2) * a.M_total + tk) * 4 + (n & 3)] = r;
-          else if (n < a.N)
-            static_cast<__half*>(a.y)[(int64_t)tk * a.N + n] = r;
+          const int64_t yi = a.dst_layout == MLD_LAYOUT_SLICED ? (((int64_t)(n >> 2) * a.M_total + tk) * 4 + (n & 3))
+                                                               : ((int64_t)tk * a.N + n);
+          if (a.dst_layout == MLD_LAYOUT_SLICED || n < a.N) {
+            if (a.scatter.world > 1) {
+              for (int pr = 0; pr < a.scatter.world; ++pr) static_cast<__half*>(a.scatter.y_peers[pr])[yi] = r;
+            } else {
+              static_cast<__half*>(a.y)[yi] = r;
+            }
+          }
         }
       }
     }
     if (a.ksplit > 1 && kr == 1) mbar_arrive_cluster(bar_remote);  // release: the stores above are visible
     MLD_CONSUMER_BARRIER();
     if (tr && threadIdx.x == 0) tr[5] = globaltimer_ns();
+  }
+  if (a.scatter.world > 1) {
+    // every CTA: make its peer stores visible, then count in; the last one
+    // raises this rank's flag on every rank
+    __threadfence_system();
+    MLD_CONSUMER_BARRIER();
+    if (threadIdx.x == 0) {
+      const int t = atomicAdd(a.scatter.ticket, 1);
+      if (t == static_cast<int>(gridDim.x) - 1) {
+        *a.scatter.ticket = 0;
+        __threadfence_system();
+        const unsigned seq = static_cast<unsigned>(*a.scatter.step * a.scatter.seq_per_step + a.scatter.seq_off);
+        for (int pr = 0; pr < a.scatter.world; ++pr) st_release_sys(a.scatter.flag_peers[pr], seq);
+      }
+    }
   }
 }
 

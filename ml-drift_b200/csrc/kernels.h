@@ -35,6 +35,26 @@ struct GenericArgs {
 };
 int launch_fc_generic(const GenericArgs& a, int bits, bool f32, cudaStream_t stream);
 
+// Sharded decoding without a separate collective: a kernel stores its output
+// shard straight into every rank's copy of the gathered vector (plain peer
+// stores over NVLink) and the last CTA to finish raises this rank's completion
+// flag on every rank; the kernel that consumes the gathered vector waits
+// (bounded) for the flags of all ranks.  world <= 1 disables both.
+struct PeerScatter {
+  int world;
+  void* y_peers[8];          // base of the gathered vector in every rank's memory (index = rank)
+  unsigned* flag_peers[8];   // this rank's flag for that vector in every rank's memory
+  int* ticket;               // local CTA counter, zero between launches
+  const int* step;           // device-side step counter
+  int seq_off, seq_per_step; // flag value = *step * seq_per_step + seq_off
+};
+struct PeerWait {
+  int world;
+  const unsigned* flags;     // local flags, one per rank
+  const int* step;
+  int seq_off, seq_per_step;
+};
+
 struct StripArgs {
   const void* x;      // fp16, sliced [K/4][M_total][4] (for one token a plain vector)
   const void* bias;   // fp16 [N4] or null
@@ -57,6 +77,10 @@ struct StripArgs {
   int epilogue;       // mld_epilogue
   float scalar_scale;
   int pdl;            // launched with programmatic stream serialization
+  PeerScatter scatter;  // world <= 1: outputs go to y only
+  PeerWait wait;        // world <= 1: no flag wait before the activations are read
+  const void* next_w;  // optional: weights of the projection that runs next, pulled into L2 behind this one
+  unsigned long long next_w_bytes;
   unsigned long long* trace;  // optional [grid][8] timestamps (ns) for tuning; null in normal use
 };
 
@@ -69,6 +93,10 @@ struct StripGeometry {
 };
 StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slices, int scale_mode, int sms,
                              bool pdl);
+// mld_fc_run with the sharded-decoder hooks (null = none); not part of the C ABI.
+int fc_run_internal(mld_fc_plan* plan, const void* src, const void* weights, const void* scale, const void* zero_point,
+                    const void* bias, void* dst, int32_t tokens, void* stream, const PeerScatter* scatter,
+                    const PeerWait* wait);
 int launch_fc_strip(int bits, bool subnormal, const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a,
                     const StripGeometry& gm, cudaStream_t stream);
 

@@ -50,7 +50,7 @@ def _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id):
     return dec, keep
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, exchange):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     import __graft_entry__ as g
@@ -60,19 +60,33 @@ def _worker(rank, world, port, out_dir):
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    idt = torch.zeros(128, dtype=torch.uint8)
-    if rank == 0:
-        idt = torch.frombuffer(bytearray(mld.comm_unique_id()), dtype=torch.uint8).clone()
-    dist.broadcast(idt, 0)
+    nccl_id = None
+    if exchange == "nccl":
+        idt = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            idt = torch.frombuffer(bytearray(mld.comm_unique_id()), dtype=torch.uint8).clone()
+        dist.broadcast(idt, 0)
+        nccl_id = idt.numpy().tobytes()
     L, heads, ffn, T, pos = 2, 4, 512, 64, 40
     d = heads * 128
     layers, kc, vc = _model(np.random.default_rng(0), L, heads, ffn, T)
     x = torch.from_numpy(np.random.default_rng(1).standard_normal(d).astype(np.float16)).cuda()
-    dec, keep = _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, idt.numpy().tobytes())
+    dec, keep = _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id)
+    if exchange == "peer":                   # shards go straight into every rank's exchange block
+        mine = torch.frombuffer(bytearray(dec.ipc_export()), dtype=torch.uint8).clone()
+        table = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+        dist.all_gather(table, mine)
+        dec.ipc_import(b"".join(t.numpy().tobytes() for t in table))
+        dist.barrier()
     y = torch.empty(d, dtype=torch.float16, device="cuda")
     for _ in range(3):                       # repeated steps reuse the gather buffers
         dec.step(x, y, pos)
     torch.cuda.synchronize()
+    agree = torch.zeros(d, dtype=torch.float16)
+    agree.copy_(y)
+    both = [torch.zeros_like(agree) for _ in range(world)]
+    dist.all_gather(both, agree)
+    same = all(torch.equal(both[0], b) for b in both)
     dist.barrier()
     if rank == 0:
         single, keep1 = _make_decoder(mld, layers, kc, vc, heads, ffn, T, 0, 1, None)
@@ -81,7 +95,7 @@ def _worker(rank, world, port, out_dir):
         torch.cuda.synchronize()
         err = (y.float() - y1.float()).abs().max().item() / y1.float().abs().max().item()
         with open(os.path.join(out_dir, "result.txt"), "w") as f:
-            f.write(f"{err}\n{int(torch.isfinite(y).all())}")
+            f.write(f"{err}\n{int(torch.isfinite(y).all())}\n{int(same)}")
         single.close()
     dist.barrier()
     dec.close()
@@ -89,10 +103,12 @@ def _worker(rank, world, port, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_sharded_decode_equals_single_gpu(tmp_path):
+@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+def test_two_gpu_sharded_decode_equals_single_gpu(tmp_path, exchange):
     import torch.multiprocessing as mp
-    port = 29700 + (os.getpid() % 2000)
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
-    err, finite = open(tmp_path / "result.txt").read().split()
+    port = 29700 + (os.getpid() % 2000) + (7 if exchange == "peer" else 0)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), exchange), nprocs=2, join=True)
+    err, finite, same = open(tmp_path / "result.txt").read().split()
     assert int(finite) == 1
+    assert int(same) == 1                    # every rank holds the same gathered output
     assert float(err) < 1e-2
