@@ -285,6 +285,17 @@ MLD_API int mld_comm_unique_id(void* id128);
  * an id is given. */
 MLD_API int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_decoder** out);
 MLD_API int mld_decoder_destroy(mld_decoder* dec);
+/* 1 when this decoder runs a step as ONE persistent kernel (single GPU, INT4
+ * block scales, head_dim 128): a producer thread per SM streams every weight
+ * and KV-cache tile of the step through a shared-memory ring while the other
+ * warps compute, with a grid barrier between dependent ops.  0: the step is a
+ * chain of mld_fc_run / attention kernels.  The environment variable
+ * MLD_DECODER_MODE=ops|mega, read at creation, forces one or the other. */
+MLD_API int mld_decoder_is_single_kernel(const mld_decoder* dec);
+/* Synchronous read of the device-side status of the steps run so far: 0, or
+ * the code of the bounded wait that gave up (then cleared, with the kernel's
+ * barrier state reset so that the decoder can be used again). */
+MLD_API int mld_decoder_device_status(mld_decoder* dec, int32_t* code);
 /* Direct shard exchange between the ranks of one node, without a collective
  * library: every kernel that produces a shard stores it straight into each
  * rank's copy of the gathered vector (peer stores over NVLink) and raises a

@@ -224,6 +224,15 @@ class Decoder:
         self._keep.append(tensors)
         _check(lib().mld_decoder_set_layer(self._h, layer, C.byref(lw)), "mld_decoder_set_layer")
 
+    @property
+    def single_kernel(self) -> bool:
+        return bool(lib().mld_decoder_is_single_kernel(self._h))
+
+    def device_status(self) -> int:
+        code = C.c_int32(0)
+        _check(lib().mld_decoder_device_status(self._h, C.byref(code)), "mld_decoder_device_status")
+        return code.value
+
     def ipc_export(self) -> bytes:
         buf = C.create_string_buffer(64)
         _check(lib().mld_decoder_ipc_export(self._h, buf), "mld_decoder_ipc_export")

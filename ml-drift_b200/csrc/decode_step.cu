@@ -454,6 +454,8 @@ struct mld_decoder {
   bool peer_mode;
   size_t off_attn, off_h, off_act, off_xa, off_xb, off_flags, xchg_bytes;
   int* peer_tickets;             // local: [4] CTA counters + [1] step counter
+  // single GPU: the whole step as one persistent kernel (null = op-by-op path)
+  mld::MegaDecoder* mega;
 };
 
 namespace {
@@ -614,6 +616,7 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   dec->xchg = nullptr;
   dec->peer_tickets = nullptr;
   dec->peer_mode = false;
+  dec->mega = nullptr;
   for (int r = 0; r < 8; ++r) dec->xchg_peers[r] = nullptr;
   dec->p_qkv = dec->p_o = dec->p_gu = dec->p_down = nullptr;
   int rc = make_plan(3 * dec->d_local, d->d_model, d->block, device, false, MLD_EPILOGUE_NONE, &dec->p_qkv);
@@ -721,6 +724,23 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
       return MLD_NCCL_ERROR;
     }
   }
+  // One GPU: run the step as one persistent kernel when the shape allows it
+  // (MLD_DECODER_MODE=ops keeps the op-by-op path).
+  const char* mode = getenv("MLD_DECODER_MODE");
+  if (d->world == 1 && mode != nullptr && strcmp(mode, "mega") == 0) {
+    MegaConfig mc = {d->layers, d->d_model, d->heads, d->head_dim, d->ffn, d->max_seq, d->block,
+                     d->rms_eps, d->rope_min_timescale, d->rope_max_timescale, device};
+    if (mega_supported(mc)) {
+      const int mrc = mega_create(mc, &dec->mega);
+      if (mrc != MLD_OK) {
+        dec->mega = nullptr;
+        if (mode != nullptr && strcmp(mode, "mega") == 0) {
+          mld_decoder_destroy(dec);
+          return mrc;
+        }
+      }
+    }
+  }
   *out = dec;
   return MLD_OK;
 }
@@ -733,6 +753,7 @@ int mld_decoder_destroy(mld_decoder* dec) {
   mld_fc_plan_destroy(dec->p_gu);
   mld_fc_plan_destroy(dec->p_down);
   if (dec->scratch != nullptr) cudaFree(dec->scratch);
+  if (dec->mega != nullptr) mega_destroy(dec->mega);
   for (int r = 0; r < 8; ++r)
     if (dec->xchg_peers[r] != nullptr && dec->xchg_peers[r] != dec->xchg) cudaIpcCloseMemHandle(dec->xchg_peers[r]);
   if (dec->xchg != nullptr) cudaFree(dec->xchg);
@@ -775,6 +796,39 @@ int mld_decoder_set_layer(mld_decoder* dec, int32_t layer, const mld_layer_weigh
                   w->norm2 && w->kcache && w->vcache,
               "missing layer tensor");
   dec->layers[layer] = *w;
+  if (dec->mega != nullptr) {
+    MegaLayerPtrs p = {w->wqkv, w->sqkv, w->wo, w->so, w->wgu, w->sgu, w->wdown, w->sdown,
+                       w->norm1, w->norm2, w->kcache, w->vcache};
+    return mega_set_layer(dec->mega, layer, p);
+  }
+  return MLD_OK;
+}
+
+int mld_decoder_is_single_kernel(const mld_decoder* dec) { return dec != nullptr && dec->mega != nullptr ? 1 : 0; }
+
+// Tuning aids (not part of the public header): per-CTA timestamps of the persistent step kernel.
+__attribute__((visibility("default"))) int mld_debug_decoder_trace(mld_decoder* dec, int on) {
+  if (dec == nullptr || dec->mega == nullptr) return MLD_INVALID_ARGUMENT;
+  return mega_enable_trace(dec->mega, on != 0);
+}
+__attribute__((visibility("default"))) int mld_debug_decoder_read_trace(mld_decoder* dec, unsigned long long* out,
+                                                                        size_t count) {
+  if (dec == nullptr || dec->mega == nullptr) return MLD_INVALID_ARGUMENT;
+  return mega_read_trace(dec->mega, out, count);
+}
+__attribute__((visibility("default"))) int mld_debug_decoder_grid(mld_decoder* dec) {
+  return dec != nullptr && dec->mega != nullptr ? mega_grid(dec->mega) : 0;
+}
+
+int mld_decoder_device_status(mld_decoder* dec, int32_t* code) {
+  MLD_REQUIRE(dec != nullptr && code != nullptr, "null argument");
+  *code = 0;
+  if (dec->mega != nullptr) {
+    int c = 0;
+    const int rc = mega_device_status(dec->mega, &c);
+    *code = c;
+    return rc;
+  }
   return MLD_OK;
 }
 
@@ -782,6 +836,7 @@ int mld_decoder_step(mld_decoder* dec, const void* x_in, void* x_out, int32_t po
   MLD_REQUIRE(dec != nullptr && x_in != nullptr && x_out != nullptr, "null argument");
   MLD_REQUIRE(pos >= 0 && pos < dec->d.max_seq, "position beyond the KV cache");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (dec->mega != nullptr) return mega_step(dec->mega, x_in, x_out, pos, stream);
   const mld_decoder_desc& d = dec->d;
   const int dm = d.d_model, Hl = dec->heads_local, dl = dm / d.world, fl = dec->ffn_local;
   const float q_scale = 1.0f / sqrtf(static_cast<float>(d.head_dim));

@@ -100,6 +100,28 @@ int fc_run_internal(mld_fc_plan* plan, const void* src, const void* weights, con
 int launch_fc_strip(int bits, bool subnormal, const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a,
                     const StripGeometry& gm, cudaStream_t stream);
 
+// ------------------------------------------------- persistent decode-step kernel
+struct MegaConfig {
+  int layers, d_model, heads, head_dim, ffn, max_seq, block;
+  float rms_eps, rope_min_timescale, rope_max_timescale;
+  int device;
+};
+struct MegaLayerPtrs {
+  const void *wqkv, *sqkv, *wo, *so, *wgu, *sgu, *wdown, *sdown, *norm1, *norm2;
+  void *kcache, *vcache;
+};
+struct MegaDecoder;
+bool mega_supported(const MegaConfig& c);
+int mega_create(const MegaConfig& c, MegaDecoder** out);
+void mega_destroy(MegaDecoder* m);
+int mega_set_layer(MegaDecoder* m, int layer, const MegaLayerPtrs& p);
+int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream_t stream);
+// Reads (and clears) the kernel's error word: 0 = every wait of the last steps was satisfied.
+int mega_device_status(MegaDecoder* m, int* code);
+int mega_enable_trace(MegaDecoder* m, bool on);
+int mega_read_trace(MegaDecoder* m, unsigned long long* out, size_t count);
+int mega_grid(const MegaDecoder* m);
+
 // ----------------------------------------------------------------- prefill GEMM
 struct GemmGeometry {
   int kp;              // K rounded up so that a K-major row is a multiple of 16 bytes

@@ -18,7 +18,7 @@ def _dev(a, dtype=None):
     return t if dtype is None else t.to(dtype)
 
 
-def build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos, world=1, rank=0):
+def build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos, world=1, rank=0, block=32):
     d = heads * 128
     layers_ref, dec_tensors = [], []
     for _ in range(L):
@@ -26,7 +26,7 @@ def build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos, world=1, rank=0
         dev = {}
         for name, N, K in (("qkv", 3 * d, d), ("o", d, d), ("gu", 2 * ffn, d), ("down", d, ffn)):
             w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
-            q, s = oracle.quantize_int4_sym(w, 32)
+            q, s = oracle.quantize_int4_sym(w, block)
             layer[name] = {"packed": oracle.rearrange_int8_as_uint4(q), "scale": s}
             if name == "gu":   # the device matrix interleaves gate_i, up_i rows for the fused SiLU*mul write
                 order = mld.sharding.gate_up_shard_rows(ffn, 0, 1)
@@ -44,26 +44,47 @@ def build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos, world=1, rank=0
     return layers_ref, dec_tensors, kc, vc
 
 
-def test_decode_step_matches_oracle(mld, oracle):
-    from oracle import decode_ref
-    rng = np.random.default_rng(0)
-    L, heads, ffn, T, pos = 2, 2, 384, 96, 70
-    d = heads * 128
-    layers_ref, dec_tensors, kc, vc = build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos)
-    x = rng.standard_normal(d).astype(np.float16)
-    dec = mld.Decoder(L, d, heads, ffn, T)
-    kcd, vcd = _dev(kc), _dev(vc)
+def _make(mld, monkeypatch, mode, L, d, heads, ffn, T, block, dec_tensors, kcd, vcd):
+    monkeypatch.setenv("MLD_DECODER_MODE", mode)    # read when the decoder is created
+    dec = mld.Decoder(L, d, heads, ffn, T, block=block)
+    assert dec.single_kernel == (mode == "mega")
     for l in range(L):
         t = dec_tensors[l]
         dec.set_layer(l, wqkv=t["wqkv"], sqkv=t["sqkv"], wo=t["wo"], so=t["so"], wgu=t["wgu"], sgu=t["sgu"],
                       wdown=t["wdown"], sdown=t["sdown"], norm1=t["norm1"], norm2=t["norm2"],
                       kcache=kcd[l], vcache=vcd[l])
+    return dec
+
+
+# "ops": a chain of FullyConnected / attention kernels; "mega": the whole step as one persistent kernel.
+# Shapes cover a ragged last k-stage (ffn 1408 -> 352 k-slices), one- and many-tile attention, the first
+# position, tile boundaries, and coarser scale blocks.
+@pytest.mark.parametrize("mode,L,heads,ffn,T,pos,block", [
+    ("ops", 2, 2, 384, 96, 70, 32),
+    ("mega", 2, 2, 384, 96, 70, 32),
+    ("mega", 3, 4, 1408, 200, 0, 32),
+    ("mega", 3, 4, 1408, 200, 31, 32),
+    ("mega", 2, 4, 1408, 200, 32, 32),
+    ("mega", 2, 4, 1408, 200, 199, 32),
+    ("mega", 1, 8, 2816, 1100, 1030, 32),
+    ("mega", 2, 2, 512, 96, 64, 128),
+    ("mega", 2, 2, 256, 96, 65, 256),
+])
+def test_decode_step_matches_oracle(mld, oracle, monkeypatch, mode, L, heads, ffn, T, pos, block):
+    from oracle import decode_ref
+    rng = np.random.default_rng(0)
+    d = heads * 128
+    layers_ref, dec_tensors, kc, vc = build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos, block=block)
+    x = rng.standard_normal(d).astype(np.float16)
+    kcd, vcd = _dev(kc), _dev(vc)
+    dec = _make(mld, monkeypatch, mode, L, d, heads, ffn, T, block, dec_tensors, kcd, vcd)
     xd = _dev(x)
     y = torch.empty(d, dtype=torch.float16, device="cuda")
     dec.step(xd, y, pos)
     torch.cuda.synchronize()
+    assert dec.device_status() == 0
     kref, vref = kc.astype(np.float32), vc.astype(np.float32)
-    ref = decode_ref.decode_step(x.astype(np.float32), layers_ref, kref, vref, pos, heads, 128, ffn)
+    ref = decode_ref.decode_step(x.astype(np.float32), layers_ref, kref, vref, pos, heads, 128, ffn, block=block)
     got = y.float().cpu().numpy()
     assert np.isfinite(got).all()
     assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) < 1e-2
@@ -71,13 +92,41 @@ def test_decode_step_matches_oracle(mld, oracle):
     assert np.max(np.abs(kcd[:, pos].float().cpu().numpy() - kref[:, pos])) < 2e-2
     assert np.max(np.abs(vcd[:, pos].float().cpu().numpy() - vref[:, pos])) < 2e-2
     # a second step at the next position is reproducible
-    y2 = torch.empty_like(y)
-    dec.step(xd, y2, pos + 1)
-    y3 = torch.empty_like(y)
-    dec.step(xd, y3, pos + 1)
-    torch.cuda.synchronize()
-    assert torch.equal(y2, y3)
+    if pos + 1 < T:
+        y2 = torch.empty_like(y)
+        dec.step(xd, y2, pos + 1)
+        y3 = torch.empty_like(y)
+        dec.step(xd, y3, pos + 1)
+        torch.cuda.synchronize()
+        assert dec.device_status() == 0
+        assert torch.equal(y2, y3)
     dec.close()
+
+
+def test_single_kernel_step_agrees_with_op_chain(mld, oracle, monkeypatch):
+    """Both decoders on the same model and cache: same result within fp16 rounding of the partial sums'
+    different order, same cache rows."""
+    rng = np.random.default_rng(3)
+    L, heads, ffn, T, pos = 4, 4, 1024, 300, 257
+    d = heads * 128
+    _, dec_tensors, kc, vc = build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos)
+    xd = _dev(rng.standard_normal(d).astype(np.float16))
+    outs, caches = [], []
+    for mode in ("ops", "mega"):
+        kcd, vcd = _dev(kc), _dev(vc)
+        dec = _make(mld, monkeypatch, mode, L, d, heads, ffn, T, 32, dec_tensors, kcd, vcd)
+        y = torch.empty(d, dtype=torch.float16, device="cuda")
+        for p in (pos, pos + 1, pos + 2):        # three consecutive steps share the cache
+            dec.step(xd, y, p)
+        torch.cuda.synchronize()
+        assert dec.device_status() == 0
+        outs.append(y.float())
+        caches.append((kcd[:, pos:pos + 3].float(), vcd[:, pos:pos + 3].float()))
+        dec.close()
+    scale = outs[0].abs().max().item()
+    assert (outs[0] - outs[1]).abs().max().item() / scale < 1e-2
+    assert (caches[0][0] - caches[1][0]).abs().max().item() < 2e-2
+    assert (caches[0][1] - caches[1][1]).abs().max().item() < 2e-2
 
 
 @pytest.mark.parametrize("heads,n_tokens", [(2, 1), (2, 70), (32, 2049), (4, 515), (64, 33)])
