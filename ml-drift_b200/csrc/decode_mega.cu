@@ -45,7 +45,7 @@ namespace mld {
 
 namespace {
 
-constexpr int kCW = 8;                       // consumer warps
+constexpr int kCW = 11;                      // consumer warps; every ring stage is consumed by ONE warp
 constexpr int kThreads = (kCW + 1) * 32;     // + one producer warp
 constexpr int kRows = 64;                    // k-slices (of 4 inputs) per weight box
 constexpr int kBox = kRows * 128;            // weight box: 64 rows x 128 bytes = 64 outputs x 256 inputs
@@ -55,8 +55,13 @@ constexpr int kHeadDim = 128;
 constexpr int kTile = 32;                    // cached tokens per attention item (K box, V box: 8 KB each)
 constexpr int kAttSlots = 4;                 // heads a CTA's attention range can touch
 constexpr float kOutScale = 16777216.0f;     // subnormal operands carry 2^-24
-
-constexpr int kTraceSlots = 6;                // per (CTA, op): 4 timestamps, wait clocks, stages
+constexpr int kProjSlots = 4;                // column runs whose per-warp sums can be pending at once
+constexpr int kAttnSlots = 2;                // head runs likewise
+constexpr int kAttDump = kHeadDim + 4;       // 128 outputs, then max and sum (padded: rows stay 16-byte aligned)
+constexpr int kDumpFloats = kProjSlots * kCW * 64 > kAttnSlots * kCW * kAttDump ? kProjSlots * kCW * 64
+                                                                                : kAttnSlots * kCW * kAttDump;
+constexpr int kWarpScratch = 3 * kHeadDim;   // attention: rotated q, new k, new v (floats) per warp
+constexpr int kTraceSlots = 8;               // per (CTA, op): 4 timestamps, wait clocks, stages, all-warps-done time
 enum { kQkv = 0, kAttn = 1, kO = 2, kGu = 3, kDown = 4, kOpsPerLayer = 5 };
 
 struct alignas(128) MegaLayer {
@@ -74,22 +79,23 @@ struct MegaArgs {
   int n_layers, d_model, heads, ffn, pos;
   int gs_shift;        // log2(k-slices per scale block)
   int stages;          // ring depth
-  int xs_bytes;        // shared-memory bytes of the input-vector / attention area
+  int xs_bytes;        // shared-memory bytes of the input-vector / attention scratch area
+  int us_floats;       // entries of the per-32-input sums of the input vector
   float rms_eps, min_ts, max_ts, q_scale;
   const __half* x_in;
   __half* x_out;
   __half *qkv, *attn, *h, *act, *xa, *xb;
   float* col_part;     // [grid][2][64]
   int* col_tickets;    // [max columns]
-  float* att_part;     // [grid][kAttSlots][2 + 128]
+  float* att_part;     // [grid][kAttSlots][kAttDump]
   int* att_tickets;    // [heads]
-  unsigned* bar;       // [0] arrivals, [1] generation
+  unsigned* bar;       // 64-bit arrival counter of the grid barrier (8-byte aligned)
   int* error;
   unsigned long long* trace;  // optional [grid][ops][kTraceSlots]
 };
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -99,9 +105,10 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t n) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
+}
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kCW * 32) : "memory"); }
-__device__ __forceinline__ void bar64() { asm volatile("bar.sync 3, 64;" ::: "memory"); }
-__device__ __forceinline__ void bar128() { asm volatile("bar.sync 4, 128;" ::: "memory"); }
 
 // Per-CTA state shared by all waits: once any wait of this CTA has run out,
 // no later wait blocks.
@@ -121,6 +128,19 @@ struct Waiter {
         *s_fail = 1;
         atomicExch(error, code);
         return false;
+      }
+    }
+  }
+  // waits until *counter >= want (a shared-memory counter another warp of this CTA advances)
+  __device__ __forceinline__ void wait_count(volatile int* counter, int want, int code) const {
+    if (*counter - want >= 0 || *s_fail) return;
+    const unsigned long long t0 = globaltimer_ns();
+    while (*counter - want < 0) {
+      if (*s_fail) return;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *s_fail = 1;
+        atomicExch(error, code);
+        return;
       }
     }
   }
@@ -147,7 +167,35 @@ __device__ __forceinline__ ProjShape proj_shape(const MegaArgs& a, int kind) {
   p.I = p.C * p.S;
   return p;
 }
+// A CTA's items of a projection: whole 64-output columns, so that nothing has
+// to be combined between CTAs (a trip through L2 costs more than the imbalance;
+// a projection with fewer columns than CTAs leaves the other CTAs idle).
+__device__ __forceinline__ void proj_range(const ProjShape& p, int cta, int G, int& i0, int& i1) {
+  i0 = range_start(cta, p.C, G) * p.S;
+  i1 = range_start(cta + 1, p.C, G) * p.S;
+}
 __device__ __forceinline__ int map_index(int kind) { return kind == kQkv ? 0 : kind == kO ? 1 : kind == kGu ? 2 : 3; }
+
+// A CTA's item range [i0, i1) of an op, cut into runs: the items of one unit
+// (a projection's 64-output column, an attention head; S items each).  A run
+// that shares its unit with another CTA needs a round trip through L2 to be
+// completed, so such runs come first: the range's last run, when it is cut
+// short, is processed before the others.
+struct Runs {
+  int i0, i1, S, first, R;
+  bool rotate;
+  __device__ __forceinline__ Runs(int i0_, int i1_, int S_) : i0(i0_), i1(i1_), S(S_) {
+    first = i0 / S;
+    R = i1 > i0 ? (i1 - 1) / S - first + 1 : 0;
+    rotate = R > 1 && (i1 % S) != 0;
+  }
+  __device__ __forceinline__ void bounds(int rr, int& unit, int& lo, int& hi) const {
+    const int r = rotate ? (rr == 0 ? R - 1 : rr - 1) : rr;
+    unit = first + r;
+    lo = max(i0, unit * S);
+    hi = min(i1, (unit + 1) * S);
+  }
+};
 
 // ------------------------------------------------------------------ producer
 struct Ring {
@@ -173,32 +221,38 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
     for (int kind = 0; kind < kOpsPerLayer; ++kind) {
       if (kind == kAttn) {
         const int I = a.heads * nt;
-        const int i0 = range_start(cta, I, G), i1 = range_start(cta + 1, I, G);
-        for (int i = i0; i < i1; ++i) {
-          const int head = i / nt, j = i - head * nt;
-          for (int kv = 0; kv < 2; ++kv) {
-            w.wait(&empty[r.stage], r.phase ^ 1, 10);
-            uint8_t* st = ring + (size_t)r.stage * kStageBytes;
-            mbar_arrive_expect_tx(&full[r.stage], kBox);
-            tma_load_2d_hint(st, kv == 0 ? &ly->kc : &ly->vc, &full[r.stage], head * kHeadDim, j * kTile, pol);
-            r.advance(a.stages);
+        const Runs runs(range_start(cta, I, G), range_start(cta + 1, I, G), nt);
+        for (int rr = 0; rr < runs.R; ++rr) {
+          int head, lo, hi;
+          runs.bounds(rr, head, lo, hi);
+          for (int i = lo; i < hi; ++i) {
+            const int j = i - head * nt;
+            for (int kv = 0; kv < 2; ++kv) {
+              w.wait(&empty[r.stage], r.phase ^ 1, 10);
+              uint8_t* st = ring + (size_t)r.stage * kStageBytes;
+              mbar_arrive_expect_tx(&full[r.stage], kBox);
+              tma_load_2d_hint(st, kv == 0 ? &ly->kc : &ly->vc, &full[r.stage], head * kHeadDim, j * kTile, pol);
+              r.advance(a.stages);
+            }
           }
         }
       } else {
         const ProjShape p = proj_shape(a, kind);
         const int mi = map_index(kind);
-        const int i0 = range_start(cta, p.I, G), i1 = range_start(cta + 1, p.I, G);
-        int col = i0 / p.S, ks = i0 - col * p.S;
-        for (int i = i0; i < i1; ++i) {
-          w.wait(&empty[r.stage], r.phase ^ 1, 11);
-          uint8_t* st = ring + (size_t)r.stage * kStageBytes;
-          mbar_arrive_expect_tx(&full[r.stage], proj_bytes);
-          tma_load_2d_hint(st, &ly->w[mi], &full[r.stage], col * 128, ks * kRows, pol);
-          tma_load_2d_hint(st + kBox, &ly->s[mi], &full[r.stage], col * 64, ks * sr, pol);
-          r.advance(a.stages);
-          if (++ks == p.S) {
-            ks = 0;
-            ++col;
+        int pi0, pi1;
+        proj_range(p, cta, G, pi0, pi1);
+        const Runs runs(pi0, pi1, p.S);
+        for (int rr = 0; rr < runs.R; ++rr) {
+          int col, lo, hi;
+          runs.bounds(rr, col, lo, hi);
+          for (int i = lo; i < hi; ++i) {
+            const int ks = i - col * p.S;
+            w.wait(&empty[r.stage], r.phase ^ 1, 11);
+            uint8_t* st = ring + (size_t)r.stage * kStageBytes;
+            mbar_arrive_expect_tx(&full[r.stage], proj_bytes);
+            tma_load_2d_hint(st, &ly->w[mi], &full[r.stage], col * 128, ks * kRows, pol);
+            tma_load_2d_hint(st + kBox, &ly->s[mi], &full[r.stage], col * 64, ks * sr, pol);
+            r.advance(a.stages);
           }
         }
       }
@@ -212,38 +266,46 @@ struct Ctx {
   uint8_t* ring;
   uint64_t* full;
   uint64_t* empty;
-  __half* xs;      // input vector of the running projection / attention scratch
-  float* red;      // [2][kCW][64]
-  int* s_int;      // [0] = "this CTA completes the column / head"
+  __half* xs;          // input vector of the running projection / per-warp attention scratch
+  float* us;           // 8 * 2^-24 * (sum of each 32 inputs of xs): the nibble offset's share of a block
+  const float2* rope;  // [64] (cos, sin) of pos / timescale_i, the rotary embedding of this step
+  float* dump;         // per-warp sums of pending runs: [slot][warp][64] or [slot][warp][kAttDump]
+  int* s_int;          // [0] failure flag, [1..] run bookkeeping (see below)
   Waiter w;
-  Ring r;
-  unsigned gen;    // grid-barrier generation this CTA waits for next
-  int red_buf;
+  int ring_base;       // stages of this CTA consumed by earlier ops (same in every warp)
+  int proj_runs;       // column runs started so far (selects the dump slot)
+  int attn_runs;       // head runs started so far
+  unsigned long long bar_target;  // arrival count that completes the barrier this CTA waits for next (thread 0)
   int op_index;
+  __device__ __forceinline__ int* proj_arrived() const { return s_int + 1; }                     // [kProjSlots]
+  __device__ __forceinline__ volatile int* proj_done() const { return s_int + 1 + kProjSlots; }  // [kProjSlots]
+  __device__ __forceinline__ int* attn_arrived() const { return s_int + 1 + 2 * kProjSlots; }    // [kAttnSlots]
+  __device__ __forceinline__ volatile int* attn_done() const { return s_int + 1 + 2 * kProjSlots + kAttnSlots; }
 };
+constexpr int kSharedInts = 1 + 2 * kProjSlots + 2 * kAttnSlots;
 
 __device__ __forceinline__ void trace_mark(const Ctx& c, int k) {
   if (c.a.trace != nullptr && threadIdx.x == 0)
     c.a.trace[((size_t)blockIdx.x * c.a.n_layers * kOpsPerLayer + c.op_index) * kTraceSlots + k] = globaltimer_ns();
 }
 
-// All consumer threads call this after their last global write of an op.
+// Grid barrier: one 64-bit arrival counter that only grows (launches leave it
+// at a multiple of the grid size).  A CTA adds one with release semantics and
+// no return value, then polls until the count reaches the end of the barrier's
+// round.  All consumer threads call this after their last global write of an op.
 __device__ void grid_barrier(Ctx& c) {
   consumer_bar();
   if (threadIdx.x == 0) {
-    __threadfence();
-    unsigned* cnt = c.a.bar;
-    unsigned* gen = c.a.bar + 1;
-    const unsigned old = atomicAdd(cnt, 1u);
-    if (old == gridDim.x - 1) {
-      atomicExch(cnt, 0u);
-      __threadfence();
-      atomicAdd(gen, 1u);
-    }
-    const unsigned want = c.gen + 1;
+    trace_mark(c, 6);
+    unsigned long long* cnt = reinterpret_cast<unsigned long long*>(c.a.bar);
+    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(cnt), "l"(1ull) : "memory");
+    c.bar_target += gridDim.x;
     if (!*c.w.s_fail) {
       const unsigned long long t0 = globaltimer_ns();
-      while (static_cast<int>(ld_acquire_gpu(gen) - want) < 0) {
+      for (;;) {
+        unsigned long long v;
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cnt) : "memory");
+        if (static_cast<long long>(v - c.bar_target) >= 0) break;
         if (globaltimer_ns() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(c.a.error) != 0) {
           *c.w.s_fail = 1;
           atomicCAS(c.a.error, 0, 20);
@@ -252,8 +314,28 @@ __device__ void grid_barrier(Ctx& c) {
       }
     }
   }
-  c.gen += 1;
   consumer_bar();
+}
+
+// us[u] = 8 * 2^-24 * sum(xs[32u .. 32u+31]); entries past the vector are zero.
+__device__ void unit_sums(Ctx& c, int d) {
+  for (int u = threadIdx.x; u < c.a.us_floats; u += kCW * 32) {
+    float s = 0.0f;
+    if (u * 32 < d) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 v = *reinterpret_cast<const uint4*>(c.xs + u * 32 + q * 8);
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h[j]);
+          s += f.x;
+          s += f.y;
+        }
+      }
+    }
+    c.us[u] = s * (8.0f / kOutScale);
+  }
 }
 
 // xs = fp16(v * rsqrt(mean(v^2) + eps) * gamma)   (reference RMSNorm, fp32 statistics)
@@ -271,7 +353,7 @@ __device__ void load_x_norm(Ctx& c, const __half* x, const __half* gamma, int d)
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  float* part = c.red + 2 * kCW * 64;  // 8 floats after the reduction buffers
+  float* part = c.dump;  // free between ops
   if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
   consumer_bar();
   float tot = 0.0f;
@@ -292,55 +374,144 @@ __device__ void load_x_norm(Ctx& c, const __half* x, const __half* gamma, int d)
     *reinterpret_cast<uint4*>(c.xs + i) = v;
   }
   consumer_bar();
+  unit_sums(c, d);
+  consumer_bar();
 }
 __device__ void load_x_plain(Ctx& c, const __half* x, int d) {
   for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8)
     *reinterpret_cast<uint4*>(c.xs + i) = __ldcg(reinterpret_cast<const uint4*>(x + i));
   consumer_bar();
+  unit_sums(c, d);
+  consumer_bar();
 }
 
-// Threads 0..63 (warps 0 and 1): value `v` of output col*64 + tid summed over
-// this CTA's k-stages [ks0, ks1) of the column.
-__device__ void finish_column(Ctx& c, int kind, const ProjShape& p, int col, int ks0, int ks1, float v, int i0,
-                              const __half* resid, __half* out) {
+// One warp: outputs 2*lane and 2*lane+1 of column `col`, summed over this
+// CTA's k-stages [ks0, ks1) of the column, are completed (if the column is
+// shared with other CTAs: by whichever CTA comes last) and written.
+__device__ void finish_column(const Ctx& c, int kind, const ProjShape& p, int col, int ks0, int ks1, float v0, float v1,
+                              int i0, const __half* resid, __half* out) {
   const MegaArgs& a = c.a;
-  const int tid = threadIdx.x, G = gridDim.x, cta = blockIdx.x;
+  const int lane = threadIdx.x & 31, G = gridDim.x, cta = blockIdx.x;
   if (!(ks0 == 0 && ks1 == p.S)) {
     const int slot = col == i0 / p.S ? 0 : 1;
-    a.col_part[((size_t)cta * 2 + slot) * 64 + tid] = v;
+    *reinterpret_cast<float2*>(a.col_part + ((size_t)cta * 2 + slot) * 64 + 2 * lane) = make_float2(v0, v1);
     __threadfence();
-    bar64();
+    __syncwarp();
     const int first = owner_of(col * p.S, p.I, G), last = owner_of(col * p.S + p.S - 1, p.I, G);
-    if (tid == 0) {
+    int done = 0;
+    if (lane == 0) {
       int need = 0;  // CTAs between first and last whose range is not empty (grids larger than the item count)
       for (int cc = first; cc <= last; ++cc) need += range_start(cc, p.I, G) != range_start(cc + 1, p.I, G) ? 1 : 0;
       const int t = atomicAdd(a.col_tickets + col, 1);
-      const int done = t == need - 1 ? 1 : 0;
+      done = t == need - 1 ? 1 : 0;
       if (done) a.col_tickets[col] = 0;
-      c.s_int[0] = done;
     }
-    bar64();
-    const int done = c.s_int[0];
-    bar64();  // s_int may be rewritten by the next column
+    done = __shfl_sync(0xffffffffu, done, 0);
     if (!done) return;
     __threadfence();
-    v = 0.0f;
+    v0 = v1 = 0.0f;
     for (int cc = first; cc <= last; ++cc) {
       const int c0 = range_start(cc, p.I, G);
       if (c0 == range_start(cc + 1, p.I, G)) continue;
       const int sc = col == c0 / p.S ? 0 : 1;
-      v += __ldcg(a.col_part + ((size_t)cc * 2 + sc) * 64 + tid);
+      const float2 pv = __ldcg(reinterpret_cast<const float2*>(a.col_part + ((size_t)cc * 2 + sc) * 64 + 2 * lane));
+      v0 += pv.x;
+      v1 += pv.y;
     }
   }
-  const int n = col * 64 + tid;
-  const __half r = __float2half_rn(v * kOutScale);
+  const int n = col * 64 + 2 * lane;
+  const __half r0 = __float2half_rn(v0 * kOutScale), r1 = __float2half_rn(v1 * kOutScale);
   if (kind == kGu) {
-    // rows interleave gate_i, up_i: even lanes hold the gate, the next lane its up value
-    const float gf = __half2float(r);
-    const float uf = __shfl_down_sync(0xffffffffu, gf, 1);
-    if ((tid & 1) == 0 && n + 1 < p.N) out[n >> 1] = __float2half_rn(gf / (1.0f + __expf(-gf)) * uf);
+    // rows interleave gate_i, up_i
+    const float gf = __half2float(r0), uf = __half2float(r1);
+    if (n + 1 < p.N) out[n >> 1] = __float2half_rn(gf / (1.0f + __expf(-gf)) * uf);
+  } else if (n + 1 < p.N) {
+    __half2 r = __halves2half2(r0, r1);
+    if (resid != nullptr) r = __hadd2(r, __ldcg(reinterpret_cast<const __half2*>(resid + n)));
+    *reinterpret_cast<__half2*>(out + n) = r;
   } else if (n < p.N) {
-    out[n] = resid != nullptr ? __hadd(r, __ldcg(resid + n)) : r;
+    out[n] = resid != nullptr ? __hadd(r0, __ldcg(resid + n)) : r0;
+  }
+}
+
+// One weight box (64 k-slices x 64 outputs) by one warp.  Lane = 4g + t.  The
+// 16 MMA steps of the box are (p, q): rows 8p + 2t + q of the box (the 128B
+// swizzle makes exactly this pattern conflict-free), A = the nibbles of chunk
+// g as fp16 subnormals (row g: low nibble = output 2f, row g+8: high nibble =
+// output 2f+1), B column p = the inputs of those rows, all other columns zero:
+// accumulator column p collects the 32-input unit p of the box, so each lane
+// ends with (outputs 8g+2f, 8g+2f+1) x (units 2t, 2t+1) and applies the block
+// scales once per box.
+__device__ __forceinline__ void consume_box(const Ctx& c, const uint8_t* st, int ks, int K4, int gs_shift,
+                                            float (&tot)[4][2]) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  // this lane's B values: rows 8g + 2t + q (they feed column g)
+  uint32_t bx[2][2];
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int row = ks * kRows + 8 * g + 2 * t + q;
+    bx[q][0] = bx[q][1] = 0u;
+    if (row < K4) {
+      const uint2 xv = *reinterpret_cast<const uint2*>(c.xs + (size_t)row * 4);
+      bx[q][0] = xv.x;
+      bx[q][1] = xv.y;
+    }
+  }
+  // Two accumulator sets (steps q = 0 / q = 1) give eight independent MMA chains; the
+  // weights are fetched one batch of four steps ahead of the MMAs that use them.
+  float acc[2][4][4];
+#pragma unroll
+  for (int q = 0; q < 2; ++q)
+#pragma unroll
+    for (int f = 0; f < 4; ++f) acc[q][f][0] = acc[q][f][1] = acc[q][f][2] = acc[q][f][3] = 0.0f;
+  const uint8_t* lane_base = st + (2 * t) * 128;           // row 8pp + 2t + q -> + pp*1024 + q*128
+  const int sw0 = (g ^ ((2 * t) & 7)) << 4, sw1 = (g ^ ((2 * t + 1) & 7)) << 4;
+  uint4 wbuf[2][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    wbuf[0][i] = *reinterpret_cast<const uint4*>(lane_base + (i >> 1) * 1024 + (i & 1) * 128 + ((i & 1) ? sw1 : sw0));
+#pragma unroll
+  for (int bt = 0; bt < 4; ++bt) {
+    if (bt + 1 < 4) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        wbuf[(bt + 1) & 1][i] = *reinterpret_cast<const uint4*>(lane_base + (2 * (bt + 1) + (i >> 1)) * 1024 +
+                                                                 (i & 1) * 128 + ((i & 1) ? sw1 : sw0));
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int pp = 2 * bt + (i >> 1), q = i & 1;
+      const uint4 wv = wbuf[bt & 1][i];
+      const uint32_t b0 = g == pp ? bx[q][0] : 0u, b1 = g == pp ? bx[q][1] : 0u;
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        const uint32_t lo = ww[2 * b], hi = ww[2 * b + 1];
+        const uint32_t lo8 = lo >> 8, hi8 = hi >> 8;
+        const uint32_t a0[4] = {lo & 0x000F000Fu, lo & 0x00F000F0u, hi & 0x000F000Fu, hi & 0x00F000F0u};
+        const uint32_t a1[4] = {lo8 & 0x000F000Fu, lo8 & 0x00F000F0u, hi8 & 0x000F000Fu, hi8 & 0x00F000F0u};
+        mma_f16(acc[q][2 * b], a0, b0, b1);
+        mma_f16(acc[q][2 * b + 1], a1, b0, b1);
+      }
+    }
+  }
+  // units 2t and 2t+1 of the box: their offset terms and the scales of this lane's eight outputs
+  const float2 off = *reinterpret_cast<const float2*>(c.us + ks * 8 + 2 * t);
+  const int srow0 = (2 * t) >> (gs_shift - 3), srow1 = (2 * t + 1) >> (gs_shift - 3);
+  const uint4 s0 = *reinterpret_cast<const uint4*>(st + kBox + (srow0 * 64 + 8 * g) * 2);
+  const uint4 s1 = *reinterpret_cast<const uint4*>(st + kBox + (srow1 * 64 + 8 * g) * 2);
+  const __half2* h0 = reinterpret_cast<const __half2*>(&s0);
+  const __half2* h1 = reinterpret_cast<const __half2*>(&s1);
+#pragma unroll
+  for (int f = 0; f < 4; ++f) {
+    const float2 sa = __half22float2(h0[f]), sb = __half22float2(h1[f]);
+    // acc[.][f]: {row g, col 2t}, {row g, col 2t+1}, {row g+8, col 2t}, {row g+8, col 2t+1}; high nibbles carry x16
+    const float e0 = acc[0][f][0] + acc[1][f][0], e1 = acc[0][f][1] + acc[1][f][1];
+    const float o0 = acc[0][f][2] + acc[1][f][2], o1 = acc[0][f][3] + acc[1][f][3];
+    tot[f][0] = fmaf(sa.x, e0 - off.x, tot[f][0]);
+    tot[f][0] = fmaf(sb.x, e1 - off.y, tot[f][0]);
+    tot[f][1] = fmaf(sa.y, fmaf(o0, 0.0625f, -off.x), tot[f][1]);
+    tot[f][1] = fmaf(sb.y, fmaf(o1, 0.0625f, -off.y), tot[f][1]);
   }
 }
 
@@ -350,132 +521,175 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
   const int cta = blockIdx.x, G = gridDim.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int rbase = warp * 8;
-  const int gidx = rbase >> a.gs_shift;
-  const int i0 = range_start(cta, p.I, G), i1 = range_start(cta + 1, p.I, G);
-  int i = i0;
-  long long waited = 0;
+  int i0, i1;
+  proj_range(p, cta, G, i0, i1);
+  const Runs runs(i0, i1, p.S);
+  long long waited = 0, boxed = 0;
   const bool tracing = a.trace != nullptr && threadIdx.x == 0;
-  while (i < i1) {
-    const int col = i / p.S, ks0 = i - col * p.S;
-    const int ks1 = min(p.S, ks0 + (i1 - i));
+  // this warp takes every kCW-th stage of the op's sequence
+  int q = warp;
+  int pos = c.ring_base + warp;
+  int stage = pos % a.stages;
+  uint32_t phase = static_cast<uint32_t>(pos / a.stages) & 1u;
+  int seq_lo = 0;
+  for (int rr = 0; rr < runs.R; ++rr) {
+    int col, lo, hi;
+    runs.bounds(rr, col, lo, hi);
+    const int ks0 = lo - col * p.S, seq_hi = seq_lo + (hi - lo);
     float tot[4][2];
 #pragma unroll
     for (int f = 0; f < 4; ++f) tot[f][0] = tot[f][1] = 0.0f;
-    for (int ks = ks0; ks < ks1; ++ks) {
+    for (; q < seq_hi; q += kCW) {
       const long long w0 = tracing ? clock64() : 0;
-      c.w.wait(&c.full[c.r.stage], c.r.phase, 12);
+      c.w.wait(&c.full[stage], phase, 12);
       if (tracing) waited += clock64() - w0;
-      const uint8_t* st = c.ring + (size_t)c.r.stage * kStageBytes;
-      const int row0 = ks * kRows;
-      uint32_t bx[2][2];
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const int row = row0 + rbase + 2 * t + q;
-        bx[q][0] = bx[q][1] = 0u;
-        if (g == 0 && row < p.K4) {
-          const uint2 xv = *reinterpret_cast<const uint2*>(c.xs + (size_t)row * 4);
-          bx[q][0] = xv.x;
-          bx[q][1] = xv.y;
-        }
+      const long long b0 = tracing ? clock64() : 0;
+      consume_box(c, c.ring + (size_t)stage * kStageBytes, ks0 + (q - seq_lo), p.K4, a.gs_shift, tot);
+      __syncwarp();
+      if (tracing) boxed += clock64() - b0;
+      if (lane == 0) mbar_arrive_n(&c.empty[stage], kCW);
+      stage += kCW;
+      while (stage >= a.stages) {
+        stage -= a.stages;
+        phase ^= 1u;
       }
-      // sum of the inputs times the nibble offset 8, as the same subnormal product
-      float ones[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      {
-        const uint32_t oa[4] = {0x00080008u, 0x00080008u, 0x00080008u, 0x00080008u};
-        mma_f16(ones, oa, bx[0][0], bx[0][1]);
-        mma_f16(ones, oa, bx[1][0], bx[1][1]);
+    }
+    // this warp's share of the run: sum the four unit pairs (lanes t), park it in the run's slot
+    const int run = c.proj_runs + rr, slot = run % kProjSlots, use = run / kProjSlots;
+#pragma unroll
+    for (int f = 0; f < 4; ++f)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        tot[f][e] += __shfl_xor_sync(0xffffffffu, tot[f][e], 1);
+        tot[f][e] += __shfl_xor_sync(0xffffffffu, tot[f][e], 2);
       }
-      float grp[4][4];
+    c.w.wait_count(c.proj_done() + slot, use, 15);  // the slot's previous run has been summed
+    float* mine = c.dump + ((size_t)slot * kCW + warp) * 64;
+    if (t == 0) {
+      *reinterpret_cast<float4*>(mine + 8 * g) = make_float4(tot[0][0], tot[0][1], tot[1][0], tot[1][1]);
+      *reinterpret_cast<float4*>(mine + 8 * g + 4) = make_float4(tot[2][0], tot[2][1], tot[3][0], tot[3][1]);
+    }
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(c.proj_arrived() + slot, 1) == kCW - 1 ? 1 : 0;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      // the last warp of the CTA to get here sums the warps in order and completes the column
+      __threadfence_block();
+      const float* all = c.dump + (size_t)slot * kCW * 64;
+      float v0 = 0.0f, v1 = 0.0f;
 #pragma unroll
-      for (int f = 0; f < 4; ++f) grp[f][0] = grp[f][1] = grp[f][2] = grp[f][3] = 0.0f;
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const int r = rbase + 2 * t + q;
-        const uint4 wv = *reinterpret_cast<const uint4*>(st + r * 128 + ((g ^ (r & 7)) << 4));
-        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-        for (int b = 0; b < 2; ++b) {
-          const uint32_t lo = ww[2 * b], hi = ww[2 * b + 1];
-          const uint32_t lo8 = lo >> 8, hi8 = hi >> 8;
-          const uint32_t a0[4] = {lo & 0x000F000Fu, lo & 0x00F000F0u, hi & 0x000F000Fu, hi & 0x00F000F0u};
-          const uint32_t a1[4] = {lo8 & 0x000F000Fu, lo8 & 0x00F000F0u, hi8 & 0x000F000Fu, hi8 & 0x00F000F0u};
-          mma_f16(grp[2 * b], a0, bx[q][0], bx[q][1]);
-          mma_f16(grp[2 * b + 1], a1, bx[q][0], bx[q][1]);
-        }
-      }
-      // scales of this lane's eight outputs for the block these eight rows are in
-      const uint4 sv = *reinterpret_cast<const uint4*>(st + kBox + (gidx * 64 + 8 * g) * 2);
-      const __half2* sh = reinterpret_cast<const __half2*>(&sv);
-#pragma unroll
-      for (int f = 0; f < 4; ++f) {
-        const float2 s2 = __half22float2(sh[f]);
-        // MMA row g = output 2f (low nibbles), row g+8 = output 2f+1 (high nibbles, carried x16)
-        tot[f][0] = fmaf(s2.x, grp[f][0] - ones[0], tot[f][0]);
-        tot[f][1] = fmaf(s2.y, fmaf(grp[f][2], 0.0625f, -ones[0]), tot[f][1]);
+      for (int wi = 0; wi < kCW; ++wi) {
+        const float2 pv = *reinterpret_cast<const float2*>(all + wi * 64 + 2 * lane);
+        v0 += pv.x;
+        v1 += pv.y;
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&c.empty[c.r.stage]);
-      c.r.advance(a.stages);
-    }
-    // cross-warp sum of the column
-    float* red = c.red + c.red_buf * (kCW * 64);
-    c.red_buf ^= 1;
-    if (t == 0) {
-#pragma unroll
-      for (int f = 0; f < 4; ++f) {
-        red[warp * 64 + 8 * g + 2 * f] = tot[f][0];
-        red[warp * 64 + 8 * g + 2 * f + 1] = tot[f][1];
+      if (lane == 0) {
+        c.proj_arrived()[slot] = 0;
+        __threadfence_block();
+        c.proj_done()[slot] = use + 1;
       }
+      finish_column(c, kind, p, col, ks0, ks0 + (hi - lo), v0, v1, i0, resid, out);
     }
-    consumer_bar();
-    if (threadIdx.x < 64) {
-      float v = 0.0f;
-#pragma unroll
-      for (int wi = 0; wi < kCW; ++wi) v += red[wi * 64 + threadIdx.x];
-      finish_column(c, kind, p, col, ks0, ks1, v, i0, resid, out);
-    }
-    i += ks1 - ks0;
+    seq_lo = seq_hi;
   }
+  c.proj_runs += runs.R;
+  c.ring_base += i1 - i0;
   if (tracing) {
-    unsigned long long* t = a.trace + ((size_t)blockIdx.x * a.n_layers * kOpsPerLayer + c.op_index) * kTraceSlots;
-    t[4] = static_cast<unsigned long long>(waited);
-    t[5] = static_cast<unsigned long long>(i1 - i0);
+    unsigned long long* tr = a.trace + ((size_t)blockIdx.x * a.n_layers * kOpsPerLayer + c.op_index) * kTraceSlots;
+    tr[4] = static_cast<unsigned long long>(waited);
+    tr[5] = static_cast<unsigned long long>(i1 - i0);
+    tr[7] = static_cast<unsigned long long>(boxed);
   }
 }
 
-// Attention over the cached tokens 0..pos-1 plus the new token.  Eight lanes
-// share a cached token (16 dims each); each of the 32 eight-lane groups keeps a
-// running max / sum / output over its rows of the tiles and the groups are
-// merged when the CTA's run over a head ends.
+// One cached token against the head's query for one eight-lane group: lane `sub`
+// holds dims 8*sub..+8 (k0, v0) and 64+8*sub..+8 (k1, v1) as fp16.  Updates the
+// group's running state.
+__device__ __forceinline__ void attend_token(const float (&qv)[16], const uint4& k0, const uint4& k1, const uint4& v0,
+                                             const uint4& v1, unsigned gmask, float& m, float& l, float (&acc)[16]) {
+  const __half2* kh0 = reinterpret_cast<const __half2*>(&k0);
+  const __half2* kh1 = reinterpret_cast<const __half2*>(&k1);
+  float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 a0 = __half22float2(kh0[e]), a1 = __half22float2(kh1[e]);
+    s0 = fmaf(qv[2 * e], a0.x, s0);
+    s0 = fmaf(qv[2 * e + 1], a0.y, s0);
+    s1 = fmaf(qv[8 + 2 * e], a1.x, s1);
+    s1 = fmaf(qv[8 + 2 * e + 1], a1.y, s1);
+  }
+  float s = s0 + s1;
+  s += __shfl_xor_sync(gmask, s, 1);
+  s += __shfl_xor_sync(gmask, s, 2);
+  s += __shfl_xor_sync(gmask, s, 4);
+  const float m_new = fmaxf(m, s);
+  const float corr = __expf(m - m_new), pw = __expf(s - m_new);
+  l = l * corr + pw;
+  const __half2* vh0 = reinterpret_cast<const __half2*>(&v0);
+  const __half2* vh1 = reinterpret_cast<const __half2*>(&v1);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 b0 = __half22float2(vh0[e]), b1 = __half22float2(vh1[e]);
+    acc[2 * e] = fmaf(acc[2 * e], corr, pw * b0.x);
+    acc[2 * e + 1] = fmaf(acc[2 * e + 1], corr, pw * b0.y);
+    acc[8 + 2 * e] = fmaf(acc[8 + 2 * e], corr, pw * b1.x);
+    acc[8 + 2 * e + 1] = fmaf(acc[8 + 2 * e + 1], corr, pw * b1.y);
+  }
+  m = m_new;
+}
+
+// Attention over the cached tokens 0..pos-1 plus the new token.  Every warp
+// works on every (K tile, V tile) pair, so a ring stage is free again a few
+// hundred cycles after it arrived and the cache streams through the ring: the
+// 32 tokens of a tile go to 32 of the CTA's 4*kCW eight-lane groups (rotating
+// from tile to tile), one token per group.  A group keeps two running
+// max / sum / output states (even and odd tiles, so that two tokens are in
+// flight); states, groups, warps and finally CTAs are merged when the CTA's
+// run over a head ends.
 __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
   const MegaArgs& a = c.a;
-  const int cta = blockIdx.x, G = gridDim.x, tid = threadIdx.x;
-  const int lane = tid & 31;
-  const int grp = tid >> 3, sub = tid & 7;
+  const int cta = blockIdx.x, G = gridDim.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane >> 3, sub = lane & 7;
+  constexpr int NS = 4 * kCW;
+  const int myslot = 4 * warp + grp;
   const int nt = a.pos / kTile + 1;
   const int I = a.heads * nt;
   const int width = a.heads * kHeadDim;
   const int i0 = range_start(cta, I, G), i1 = range_start(cta + 1, I, G);
-  float* sq = reinterpret_cast<float*>(c.xs);   // [128] rotated, scaled q
-  float* skn = sq + kHeadDim;                   // [128] rotated new k (as stored: fp16 values)
-  float* svn = skn + kHeadDim;                  // [128] new v
-  float* gm = svn + kHeadDim;                   // [32]
-  float* gl = gm + 32;                          // [32]
-  float* go = gl + 32;                          // [32][128]
+  const Runs runs(i0, i1, nt);
+  float* sq = reinterpret_cast<float*>(c.xs) + warp * kWarpScratch;  // rotated, scaled q of the head
+  __half* skn = reinterpret_cast<__half*>(sq + kHeadDim);            // the new token's rotated k, as a cache row
+  __half* svn = skn + kHeadDim;                                      // the new token's v
   const unsigned gmask = 0xFFu << (lane & 24);
-  int i = i0;
-  while (i < i1) {
-    const int head = i / nt, j0 = i - head * nt;
-    const int j1 = min(nt, j0 + (i1 - i));
-    const bool owns_new = j1 == nt;
-    consumer_bar();  // the previous head's merge has finished reading this scratch
-    if (tid < kHeadDim / 2) {
-      const int e = tid, half = kHeadDim / 2;
-      const float fraction = 2.0f * e / static_cast<float>(kHeadDim);
-      const float timescale = a.min_ts * powf(a.max_ts / a.min_ts, fraction);
-      float sn, cs;
-      sincosf(static_cast<float>(a.pos) / timescale, &sn, &cs);
+  int stage = c.ring_base % a.stages;
+  uint32_t phase = static_cast<uint32_t>(c.ring_base / a.stages) & 1u;
+  auto next = [&](int& st, uint32_t& ph) {
+    if (++st == a.stages) {
+      st = 0;
+      ph ^= 1u;
+    }
+  };
+  for (int rr = 0; rr < runs.R; ++rr) {
+    int head, lo, hi;
+    runs.bounds(rr, head, lo, hi);
+    const int j0 = lo - head * nt, n = hi - lo;
+    // the new token sits in the head's last tile; the group that gets its row brings it in
+    const bool has_new = j0 + n == nt;
+    const int new_slot = has_new ? (kTile * (n - 1) + (a.pos & (kTile - 1))) % NS : -1;
+    const bool owns_new = has_new && (new_slot >> 2) == warp;
+    __syncwarp();
+    // rotary embedding (rope.cc:70-89): dims (e, e + 64) rotate together
+#pragma unroll
+    for (int rep = 0; rep < 2; ++rep) {
+      const int e = lane + 32 * rep, half = kHeadDim / 2;
+      const float2 rot = c.rope[e];
+      const float cs = rot.x, sn = rot.y;
       const __half* qp = a.qkv + (size_t)head * kHeadDim;
       const float q0 = __half2float(__ldcg(qp + e)), q1 = __half2float(__ldcg(qp + e + half));
       // rounded to fp16 where the unfused graph stores the rotated, scaled q
@@ -483,161 +697,240 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
       sq[e + half] = __half2float(__float2half_rn((q1 * cs + q0 * sn) * a.q_scale));
       if (owns_new) {
         const __half* kp = a.qkv + (size_t)(a.heads + head) * kHeadDim;
+        const __half* vp = a.qkv + (size_t)(2 * a.heads + head) * kHeadDim;
         const float k0 = __half2float(__ldcg(kp + e)), k1 = __half2float(__ldcg(kp + e + half));
         const __half r0 = __float2half_rn(k0 * cs - k1 * sn), r1 = __float2half_rn(k1 * cs + k0 * sn);
+        const __half v0 = __ldcg(vp + e), v1 = __ldcg(vp + e + half);
         __half* kc = ly->kcache + (size_t)a.pos * width + head * kHeadDim;
+        __half* vc = ly->vcache + (size_t)a.pos * width + head * kHeadDim;
         kc[e] = r0;
         kc[e + half] = r1;
-        skn[e] = __half2float(r0);
-        skn[e + half] = __half2float(r1);
+        vc[e] = v0;
+        vc[e + half] = v1;
+        skn[e] = r0;
+        skn[e + half] = r1;
+        svn[e] = v0;
+        svn[e + half] = v1;
       }
-    } else if (tid < kHeadDim && owns_new) {
-      const int e = tid - kHeadDim / 2;
-      const __half* vp = a.qkv + (size_t)(2 * a.heads + head) * kHeadDim;
-      __half* vc = ly->vcache + (size_t)a.pos * width + head * kHeadDim;
-      const __half v0 = __ldcg(vp + e), v1 = __ldcg(vp + e + kHeadDim / 2);
-      vc[e] = v0;
-      vc[e + kHeadDim / 2] = v1;
-      svn[e] = __half2float(v0);
-      svn[e + kHeadDim / 2] = __half2float(v1);
     }
-    consumer_bar();
-    // lane `sub` of a group owns dims 8*sub..+8 and 64+8*sub..+8
+    __syncwarp();
     float qv[16];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       qv[e] = sq[sub * 8 + e];
       qv[8 + e] = sq[64 + sub * 8 + e];
     }
-    float m = -INFINITY, l = 0.0f, acc[16];
+    float mA = -INFINITY, lA = 0.0f, accA[16], mB = -INFINITY, lB = 0.0f, accB[16];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) acc[e] = 0.0f;
-    for (int j = j0; j < j1; ++j) {
-      const int ks = c.r.stage;
-      c.w.wait(&c.full[ks], c.r.phase, 13);
-      c.r.advance(a.stages);
-      const int vs = c.r.stage;
-      c.w.wait(&c.full[vs], c.r.phase, 14);
-      c.r.advance(a.stages);
-      const int token = j * kTile + grp;
-      if (token <= a.pos) {
-        float kf[16], vf[16];
-        if (token == a.pos) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            kf[e] = skn[sub * 8 + e];
-            kf[8 + e] = skn[64 + sub * 8 + e];
-            vf[e] = svn[sub * 8 + e];
-            vf[8 + e] = svn[64 + sub * 8 + e];
-          }
-        } else {
-          const uint8_t* kr = c.ring + (size_t)ks * kStageBytes + grp * 256 + sub * 16;
-          const uint8_t* vr = c.ring + (size_t)vs * kStageBytes + grp * 256 + sub * 16;
-          const uint4 k0 = *reinterpret_cast<const uint4*>(kr), k1 = *reinterpret_cast<const uint4*>(kr + 128);
-          const uint4 v0 = *reinterpret_cast<const uint4*>(vr), v1 = *reinterpret_cast<const uint4*>(vr + 128);
-          const __half2* kh0 = reinterpret_cast<const __half2*>(&k0);
-          const __half2* kh1 = reinterpret_cast<const __half2*>(&k1);
-          const __half2* vh0 = reinterpret_cast<const __half2*>(&v0);
-          const __half2* vh1 = reinterpret_cast<const __half2*>(&v1);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 a0 = __half22float2(kh0[e]), a1 = __half22float2(kh1[e]);
-            const float2 b0 = __half22float2(vh0[e]), b1 = __half22float2(vh1[e]);
-            kf[2 * e] = a0.x; kf[2 * e + 1] = a0.y; kf[8 + 2 * e] = a1.x; kf[8 + 2 * e + 1] = a1.y;
-            vf[2 * e] = b0.x; vf[2 * e + 1] = b0.y; vf[8 + 2 * e] = b1.x; vf[8 + 2 * e + 1] = b1.y;
-          }
-        }
-        float s = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 16; ++e) s = fmaf(qv[e], kf[e], s);
-        s += __shfl_xor_sync(gmask, s, 1);
-        s += __shfl_xor_sync(gmask, s, 2);
-        s += __shfl_xor_sync(gmask, s, 4);
-        const float m_new = fmaxf(m, s);
-        const float corr = __expf(m - m_new), pw = __expf(s - m_new);
-        l = l * corr + pw;
-#pragma unroll
-        for (int e = 0; e < 16; ++e) acc[e] = fmaf(acc[e], corr, pw * vf[e]);
-        m = m_new;
+    for (int e = 0; e < 16; ++e) accA[e] = accB[e] = 0.0f;
+    int rowA = myslot;  // row of tile jj that belongs to this group: (myslot - 32 jj) mod NS, if below 32
+    for (int jj = 0; jj < n; jj += 2) {
+      const bool two = jj + 1 < n;
+      int rowB = rowA - kTile;
+      if (rowB < 0) rowB += NS;
+      const int ks = stage;
+      const uint32_t kp = phase;
+      next(stage, phase);
+      const int vs = stage;
+      const uint32_t vp = phase;
+      next(stage, phase);
+      int ks2 = stage, vs2 = stage;
+      uint32_t kp2 = phase, vp2 = phase;
+      if (two) {
+        next(stage, phase);
+        vs2 = stage;
+        vp2 = phase;
+        next(stage, phase);
       }
+      c.w.wait(&c.full[ks], kp, 13);
+      c.w.wait(&c.full[vs], vp, 14);
+      if (two) {
+        c.w.wait(&c.full[ks2], kp2, 13);
+        c.w.wait(&c.full[vs2], vp2, 14);
+      }
+      const int tokA = (j0 + jj) * kTile + rowA, tokB = (j0 + jj + 1) * kTile + rowB;
+      const bool doA = rowA < kTile && tokA <= a.pos;
+      const bool doB = two && rowB < kTile && tokB <= a.pos;
+      // the new token's row comes from this warp's scratch, every other row from the tiles
+      uint4 kA0, kA1, vA0, vA1, kB0, kB1, vB0, vB1;
+      if (doA) {
+        const bool nw = tokA == a.pos;
+        const uint8_t* kr = nw ? reinterpret_cast<const uint8_t*>(skn) : c.ring + (size_t)ks * kStageBytes + rowA * 256;
+        const uint8_t* vr = nw ? reinterpret_cast<const uint8_t*>(svn) : c.ring + (size_t)vs * kStageBytes + rowA * 256;
+        kA0 = *reinterpret_cast<const uint4*>(kr + sub * 16);
+        kA1 = *reinterpret_cast<const uint4*>(kr + 128 + sub * 16);
+        vA0 = *reinterpret_cast<const uint4*>(vr + sub * 16);
+        vA1 = *reinterpret_cast<const uint4*>(vr + 128 + sub * 16);
+      }
+      if (doB) {
+        const bool nw = tokB == a.pos;
+        const uint8_t* kr = nw ? reinterpret_cast<const uint8_t*>(skn) : c.ring + (size_t)ks2 * kStageBytes + rowB * 256;
+        const uint8_t* vr = nw ? reinterpret_cast<const uint8_t*>(svn) : c.ring + (size_t)vs2 * kStageBytes + rowB * 256;
+        kB0 = *reinterpret_cast<const uint4*>(kr + sub * 16);
+        kB1 = *reinterpret_cast<const uint4*>(kr + 128 + sub * 16);
+        vB0 = *reinterpret_cast<const uint4*>(vr + sub * 16);
+        vB1 = *reinterpret_cast<const uint4*>(vr + 128 + sub * 16);
+      }
+      if (doA) attend_token(qv, kA0, kA1, vA0, vA1, gmask, mA, lA, accA);
+      if (doB) attend_token(qv, kB0, kB1, vB0, vB1, gmask, mB, lB, accB);
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&c.empty[ks]);
         mbar_arrive(&c.empty[vs]);
+        if (two) {
+          mbar_arrive(&c.empty[ks2]);
+          mbar_arrive(&c.empty[vs2]);
+        }
       }
+      rowA = rowB - kTile;
+      if (rowA < 0) rowA += NS;
     }
-    // merge the 32 groups
-    if (sub == 0) {
-      gm[grp] = m;
-      gl[grp] = l;
-    }
+    // merge the two states, then the warp's four groups
+    float m, l, acc[16];
+    {
+      m = fmaxf(mA, mB);
+      const float wa = mA == -INFINITY ? 0.0f : __expf(mA - m), wb = mB == -INFINITY ? 0.0f : __expf(mB - m);
+      l = lA * wa + lB * wb;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      go[grp * kHeadDim + sub * 8 + e] = acc[e];
-      go[grp * kHeadDim + 64 + sub * 8 + e] = acc[8 + e];
-    }
-    consumer_bar();
-    if (tid < kHeadDim) {
-      float M = -INFINITY;
-#pragma unroll 8
-      for (int q = 0; q < 32; ++q) M = fmaxf(M, gm[q]);
-      float o = 0.0f, ls = 0.0f;
-#pragma unroll 8
-      for (int q = 0; q < 32; ++q) {
-        const float wq = gm[q] == -INFINITY ? 0.0f : __expf(gm[q] - M);
-        o = fmaf(wq, go[q * kHeadDim + tid], o);
-        ls = fmaf(wq, gl[q], ls);
+      for (int e = 0; e < 16; ++e) acc[e] = accA[e] * wa + accB[e] * wb;
+      float M = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+      M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
+      const float wg = m == -INFINITY ? 0.0f : __expf(m - M);
+      l *= wg;
+      l += __shfl_xor_sync(0xffffffffu, l, 8);
+      l += __shfl_xor_sync(0xffffffffu, l, 16);
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        acc[e] *= wg;
+        acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 8);
+        acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
       }
-      const int first = owner_of(head * nt, I, G), last = owner_of(head * nt + nt - 1, I, G);
+      m = M;
+    }
+    const int run = c.attn_runs + rr, slot = run % kAttnSlots, use = run / kAttnSlots;
+    c.w.wait_count(c.attn_done() + slot, use, 16);
+    float* mine = c.dump + ((size_t)slot * kCW + warp) * kAttDump;
+    if (grp == 0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        mine[sub * 8 + e] = acc[e];
+        mine[64 + sub * 8 + e] = acc[8 + e];
+      }
+      if (sub == 0) {
+        mine[kHeadDim] = m;
+        mine[kHeadDim + 1] = l;
+      }
+    }
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(c.attn_arrived() + slot, 1) == kCW - 1 ? 1 : 0;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      // the CTA's last warp merges the warps in order; lane owns dims 4*lane..+4
+      __threadfence_block();
+      const float* all = c.dump + (size_t)slot * kCW * kAttDump;
+      float M = -INFINITY;
+#pragma unroll
+      for (int wi = 0; wi < kCW; ++wi) M = fmaxf(M, all[wi * kAttDump + kHeadDim]);
+      float o[4] = {0.0f, 0.0f, 0.0f, 0.0f}, ls = 0.0f;
+#pragma unroll
+      for (int wi = 0; wi < kCW; ++wi) {
+        const float mw = all[wi * kAttDump + kHeadDim];
+        const float ww = mw == -INFINITY ? 0.0f : __expf(mw - M);
+        ls = fmaf(ww, all[wi * kAttDump + kHeadDim + 1], ls);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = fmaf(ww, all[wi * kAttDump + 4 * lane + e], o[e]);
+      }
+      __syncwarp();
+      if (lane == 0) {
+        c.attn_arrived()[slot] = 0;
+        __threadfence_block();
+        c.attn_done()[slot] = use + 1;
+      }
+      const int first = owner_of(head * nt, I, G), lastc = owner_of(head * nt + nt - 1, I, G);
       bool write = true;
-      if (first != last) {
-        const int slot = head - i0 / nt;
-        float* mine = a.att_part + ((size_t)cta * kAttSlots + slot) * (2 + kHeadDim);
-        mine[2 + tid] = o;
-        if (tid == 0) {
-          mine[0] = M;
-          mine[1] = ls;
+      if (first != lastc) {
+        const int ps = head - i0 / nt;
+        float* part = a.att_part + ((size_t)cta * kAttSlots + ps) * kAttDump;
+        *reinterpret_cast<float4*>(part + 4 * lane) = make_float4(o[0], o[1], o[2], o[3]);
+        if (lane == 0) {
+          part[kHeadDim] = M;
+          part[kHeadDim + 1] = ls;
         }
         __threadfence();
-        bar128();
-        if (tid == 0) {
+        __syncwarp();
+        int done = 0;
+        if (lane == 0) {
           int need = 0;
-          for (int cc = first; cc <= last; ++cc) need += range_start(cc, I, G) != range_start(cc + 1, I, G) ? 1 : 0;
+          for (int cc = first; cc <= lastc; ++cc) need += range_start(cc, I, G) != range_start(cc + 1, I, G) ? 1 : 0;
           const int tk = atomicAdd(a.att_tickets + head, 1);
-          const int done = tk == need - 1 ? 1 : 0;
+          done = tk == need - 1 ? 1 : 0;
           if (done) a.att_tickets[head] = 0;
-          c.s_int[1] = done;
         }
-        bar128();
-        write = c.s_int[1] != 0;
-        bar128();
+        write = __shfl_sync(0xffffffffu, done, 0) != 0;
         if (write) {
           __threadfence();
+          // contributors are the CTAs first..lastc with a non-empty range; their partials are requested
+          // eight at a time so that the loads overlap
           float TM = -INFINITY;
-          for (int cc = first; cc <= last; ++cc) {
-            const int c0 = range_start(cc, I, G);
-            if (c0 == range_start(cc + 1, I, G)) continue;
-            const int sc = head - c0 / nt;
-            TM = fmaxf(TM, __ldcg(a.att_part + ((size_t)cc * kAttSlots + sc) * (2 + kHeadDim)));
-          }
-          o = 0.0f;
+          o[0] = o[1] = o[2] = o[3] = 0.0f;
           ls = 0.0f;
-          for (int cc = first; cc <= last; ++cc) {
-            const int c0 = range_start(cc, I, G);
-            if (c0 == range_start(cc + 1, I, G)) continue;
-            const int sc = head - c0 / nt;
-            const float* pp = a.att_part + ((size_t)cc * kAttSlots + sc) * (2 + kHeadDim);
-            const float mc = __ldcg(pp);
-            const float wc = mc == -INFINITY ? 0.0f : __expf(mc - TM);
-            o = fmaf(wc, __ldcg(pp + 2 + tid), o);
-            ls = fmaf(wc, __ldcg(pp + 1), ls);
+          for (int base = first; base <= lastc; base += 8) {
+            float mc[8], lc[8];
+            float4 oc[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int cc = base + u;
+              mc[u] = -INFINITY;
+              lc[u] = 0.0f;
+              oc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+              if (cc <= lastc) {
+                const int c0 = range_start(cc, I, G);
+                if (c0 != range_start(cc + 1, I, G)) {
+                  const float* pp = a.att_part + ((size_t)cc * kAttSlots + (head - c0 / nt)) * kAttDump;
+                  mc[u] = __ldcg(pp + kHeadDim);
+                  lc[u] = __ldcg(pp + kHeadDim + 1);
+                  oc[u] = __ldcg(reinterpret_cast<const float4*>(pp + 4 * lane));
+                }
+              }
+            }
+            float NM = TM;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) NM = fmaxf(NM, mc[u]);
+            const float resc = TM == -INFINITY ? 0.0f : __expf(TM - NM);
+            o[0] *= resc;
+            o[1] *= resc;
+            o[2] *= resc;
+            o[3] *= resc;
+            ls *= resc;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const float wc = mc[u] == -INFINITY ? 0.0f : __expf(mc[u] - NM);
+              o[0] = fmaf(wc, oc[u].x, o[0]);
+              o[1] = fmaf(wc, oc[u].y, o[1]);
+              o[2] = fmaf(wc, oc[u].z, o[2]);
+              o[3] = fmaf(wc, oc[u].w, o[3]);
+              ls = fmaf(wc, lc[u], ls);
+            }
+            TM = NM;
           }
         }
       }
-      if (write) a.attn[(size_t)head * kHeadDim + tid] = __float2half_rn(o / ls);
+      if (write) {
+        const float inv = 1.0f / ls;
+        __half2 r01 = __floats2half2_rn(o[0] * inv, o[1] * inv), r23 = __floats2half2_rn(o[2] * inv, o[3] * inv);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&r01);
+        pk.y = *reinterpret_cast<uint32_t*>(&r23);
+        *reinterpret_cast<uint2*>(a.attn + (size_t)head * kHeadDim + 4 * lane) = pk;
+      }
     }
-    i += j1 - j0;
   }
+  c.attn_runs += runs.R;
+  c.ring_base += 2 * (i1 - i0);
 }
 
 __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_constant__ MegaArgs a) {
@@ -645,29 +938,45 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
   __half* xs = reinterpret_cast<__half*>(ring + (size_t)a.stages * kStageBytes);
-  float* red = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xs) + a.xs_bytes);  // [2][kCW][64] + 8
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * kCW * 64 + 8);
+  float* us = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xs) + a.xs_bytes);
+  float* dump = us + a.us_floats;
+  float2* rope = reinterpret_cast<float2*>(dump + kDumpFloats);
+  uint64_t* full = reinterpret_cast<uint64_t*>(rope + kHeadDim / 2);
   uint64_t* empty = full + a.stages;
-  int* s_int = reinterpret_cast<int*>(empty + a.stages);  // [0],[1] tickets' verdicts, [2] failure flag
+  int* s_int = reinterpret_cast<int*>(empty + a.stages);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kCW);
+      mbar_init(&empty[s], kCW);  // attention tiles are read by every warp; a weight box's one reader arrives kCW-fold
     }
-    s_int[0] = s_int[1] = s_int[2] = 0;
+    for (int i = 0; i < kSharedInts; ++i) s_int[i] = 0;
     fence_barrier_init();
   }
+  if (threadIdx.x >= 32 && threadIdx.x < 32 + kHeadDim / 2) {
+    // rotary embedding of this position (rope.cc:70-89): timescale_i = min * (max / min)^(2i / d)
+    const int e = threadIdx.x - 32;
+    const float fraction = 2.0f * e / static_cast<float>(kHeadDim);
+    const float timescale = a.min_ts * powf(a.max_ts / a.min_ts, fraction);
+    float sn, cs;
+    sincosf(static_cast<float>(a.pos) / timescale, &sn, &cs);
+    rope[e] = make_float2(cs, sn);
+  }
   __syncthreads();
-  Waiter w{s_int + 2, a.error};
+  Waiter w{s_int, a.error};
 
   if (warp == kCW) {
     if (lane == 0) producer_loop(a, ring, full, empty, w);
   } else {
-    Ctx c{a, ring, full, empty, xs, red, s_int, w, Ring{0, 0}, 0u, 0, 0};
-    if (threadIdx.x == 0) c.gen = ld_acquire_gpu(a.bar + 1);
-    c.gen = __shfl_sync(0xffffffffu, c.gen, 0);  // only thread 0 uses it
+    Ctx c{a, ring, full, empty, xs, us, rope, dump, s_int, w, 0, 0, 0, 0ull, 0};
+    if (threadIdx.x == 0) {
+      // read before this CTA's first arrival, the count is in [base, base + grid): no barrier of this
+      // launch can complete without this CTA
+      unsigned long long v;
+      asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(a.bar) : "memory");
+      c.bar_target = v - v % gridDim.x;
+    }
     const int d = a.d_model;
     for (int l = 0; l < a.n_layers; ++l) {
       const MegaLayer* ly = a.layers + l;
@@ -720,7 +1029,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
   // A CTA that gave up may still have copies in flight: give them time to land
   // before its shared memory is released.
   __syncthreads();
-  if (s_int[2] != 0) {
+  if (s_int[0] != 0) {
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
@@ -731,7 +1040,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
 // ------------------------------------------------------------------ host side
 struct MegaDecoder {
   MegaConfig cfg;
-  int sms, grid, stages, gs_shift, xs_bytes;
+  int sms, grid, stages, gs_shift, xs_bytes, us_floats;
   size_t smem_bytes;
   MegaLayer* d_layers;
   std::vector<MegaLayer> h_layers;
@@ -774,11 +1083,13 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   int gs = cfg.block / 4;
   m->gs_shift = 0;
   while ((1 << m->gs_shift) < gs) ++m->gs_shift;
-  // shared memory: ring + max(input vector, attention scratch) + reductions + barriers
-  const int att_bytes = (3 * kHeadDim + 64 + 32 * kHeadDim) * 4;
-  const int vec_bytes = (cfg.d_model > cfg.ffn ? cfg.d_model : cfg.ffn) * 2;
+  // shared memory: ring + max(input vector, per-warp attention scratch) + unit sums + run slots + barriers
+  const int att_bytes = kCW * kWarpScratch * 4;
+  const int vec_elems = cfg.d_model > cfg.ffn ? cfg.d_model : cfg.ffn;
+  const int vec_bytes = vec_elems * 2;
   m->xs_bytes = align_n(att_bytes > vec_bytes ? att_bytes : vec_bytes, 128);
-  const int fixed = 1024 + m->xs_bytes + (2 * kCW * 64 + 8) * 4 + 64;
+  m->us_floats = align_n(div_up(vec_elems, 256) * 8, 32);  // whole boxes, so that a ragged last stage reads zeros
+  const int fixed = 1024 + m->xs_bytes + m->us_floats * 4 + kDumpFloats * 4 + (kHeadDim / 2) * 8 + kSharedInts * 4 + 64;
   int max_smem = 0;
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, cfg.device);
   int stages = (max_smem - fixed) / (kStageBytes + 16);
@@ -826,7 +1137,7 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   };
   const size_t o_qkv = take((size_t)3 * d * 2), o_attn = take((size_t)d * 2), o_h = take((size_t)d * 2),
                o_act = take((size_t)ffn * 2), o_xa = take((size_t)d * 2), o_xb = take((size_t)d * 2),
-               o_cp = take((size_t)m->grid * 2 * 64 * 4), o_ap = take((size_t)m->grid * kAttSlots * (2 + kHeadDim) * 4),
+               o_cp = take((size_t)m->grid * 2 * 64 * 4), o_ap = take((size_t)m->grid * kAttSlots * kAttDump * 4),
                o_ct = take((size_t)max_cols * 4), o_at = take((size_t)cfg.heads * 4), o_bar = take(8), o_err = take(4);
   if (cudaMalloc(&m->scratch, off) != cudaSuccess ||
       cudaMalloc(&m->d_layers, sizeof(MegaLayer) * cfg.layers) != cudaSuccess) {
@@ -911,7 +1222,7 @@ int mega_device_status(MegaDecoder* m, int* code) {
     // leave the barrier and tickets consistent for the next step
     const int zero = 0;
     cudaMemcpy(m->error, &zero, sizeof zero, cudaMemcpyHostToDevice);
-    cudaMemset(m->bar, 0, 4);
+    cudaMemset(m->bar, 0, 8);
     cudaMemset(m->col_tickets, 0, (size_t)((3 * m->cfg.d_model > 2 * m->cfg.ffn ? 3 * m->cfg.d_model : 2 * m->cfg.ffn) / 64 + 1) * 4);
     cudaMemset(m->att_tickets, 0, (size_t)m->cfg.heads * 4);
   }
@@ -932,6 +1243,7 @@ int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream
   a.gs_shift = m->gs_shift;
   a.stages = m->stages;
   a.xs_bytes = m->xs_bytes;
+  a.us_floats = m->us_floats;
   a.rms_eps = c.rms_eps;
   a.min_ts = c.rope_min_timescale;
   a.max_ts = c.rope_max_timescale;
