@@ -17,12 +17,17 @@
 //       act  = silu(Wg hn) * (Wu hn), hn = rmsnorm(h) g2
 //       x'   = h + Wdown act
 //     with a grid barrier after each (five per layer);
-//   * work is split in items of one TMA box: a projection's (64-output column,
-//     64-k-slice stage) tiles, attention's (head, 32-token tile) pairs.  Every
-//     CTA takes a contiguous, balanced range of an op's items.  A column (or
-//     head) shared between CTAs is completed by whichever of them finishes
-//     last (a ticket); it sums the partial results in CTA order, so results do
-//     not depend on arrival order.
+//   * work is split in items of one ring stage: a projection's boxes of 16
+//     outputs x 1024 inputs, attention's (head, 32-token tile) pairs.  A CTA owns
+//     whole 16-output strips of a projection (all of K), so projections need
+//     nothing from other CTAs; a head of attention is shared between CTAs and
+//     completed by whichever of them finishes last (a ticket), summing the
+//     partial results in CTA order, so results do not depend on arrival order;
+//   * the decoder keeps its own copy of the projection weights, re-tiled from
+//     the reference layout when a layer is set: box after box, 8 KB of nibbles
+//     in the order the MMA fragments want them followed by the 1 KB of scales
+//     they need, strip after strip.  A box is one contiguous 9 KB bulk copy and a
+//     CTA's share of a projection one contiguous stream.
 //
 // Projection arithmetic is the streaming GEMV's (gemv_stream.cu): weights as
 // the MMA A operand straight from the packed INT4 bytes (fp16 subnormals),
@@ -47,9 +52,10 @@ namespace {
 
 constexpr int kCW = 11;                      // consumer warps; every ring stage is consumed by ONE warp
 constexpr int kThreads = (kCW + 1) * 32;     // + one producer warp
-constexpr int kRows = 64;                    // k-slices (of 4 inputs) per weight box
-constexpr int kBox = kRows * 128;            // weight box: 64 rows x 128 bytes = 64 outputs x 256 inputs
-constexpr int kScaleBox = 1024;              // up to 8 scale rows x 64 outputs x fp16
+constexpr int kStripN = 16;                  // outputs per strip (the MMA's M)
+constexpr int kBoxK = 1024;                  // inputs per box: 32 units of 32 inputs, 64 MMAs
+constexpr int kBox = kStripN * kBoxK / 2;    // 8 KB of nibbles
+constexpr int kScaleBox = 1024;              // 32 units x 16 outputs x fp16
 constexpr int kStageBytes = kBox + kScaleBox;
 constexpr int kHeadDim = 128;
 constexpr int kTile = 32;                    // cached tokens per attention item (K box, V box: 8 KB each)
@@ -58,16 +64,15 @@ constexpr float kOutScale = 16777216.0f;     // subnormal operands carry 2^-24
 constexpr int kProjSlots = 4;                // column runs whose per-warp sums can be pending at once
 constexpr int kAttnSlots = 2;                // head runs likewise
 constexpr int kAttDump = kHeadDim + 4;       // 128 outputs, then max and sum (padded: rows stay 16-byte aligned)
-constexpr int kDumpFloats = kProjSlots * kCW * 64 > kAttnSlots * kCW * kAttDump ? kProjSlots * kCW * 64
+constexpr int kDumpFloats = kProjSlots * kCW * kStripN > kAttnSlots * kCW * kAttDump ? kProjSlots * kCW * kStripN
                                                                                 : kAttnSlots * kCW * kAttDump;
 constexpr int kWarpScratch = 3 * kHeadDim;   // attention: rotated q, new k, new v (floats) per warp
-constexpr int kTraceSlots = 8;               // per (CTA, op): 4 timestamps, wait clocks, stages, all-warps-done time
+constexpr int kTraceSlots = 12;              // per (CTA, op): 4 timestamps, wait clocks, stages, all-warps-done time
 enum { kQkv = 0, kAttn = 1, kO = 2, kGu = 3, kDown = 4, kOpsPerLayer = 5 };
 
 struct alignas(128) MegaLayer {
-  CUtensorMap w[4];   // weights of qkv, o, gu, down: bytes [K/4][2N], box 128 B x 64 rows, 128B swizzle
-  CUtensorMap s[4];   // scales: fp16 [K/block][N], box 64 x (256/block) rows
   CUtensorMap kc, vc; // KV cache: fp16 [max_seq][heads*128], box 128 x 32 rows
+  const uint8_t* w[4];  // re-tiled weights + scales of qkv, o, gu, down: [strip][k box][kStageBytes]
   const __half* norm1;
   const __half* norm2;
   __half* kcache;
@@ -77,7 +82,6 @@ struct alignas(128) MegaLayer {
 struct MegaArgs {
   const MegaLayer* layers;
   int n_layers, d_model, heads, ffn, pos;
-  int gs_shift;        // log2(k-slices per scale block)
   int stages;          // ring depth
   int xs_bytes;        // shared-memory bytes of the input-vector / attention scratch area
   int us_floats;       // entries of the per-32-input sums of the input vector
@@ -85,8 +89,6 @@ struct MegaArgs {
   const __half* x_in;
   __half* x_out;
   __half *qkv, *attn, *h, *act, *xa, *xb;
-  float* col_part;     // [grid][2][64]
-  int* col_tickets;    // [max columns]
   float* att_part;     // [grid][kAttSlots][kAttDump]
   int* att_tickets;    // [heads]
   unsigned* bar;       // 64-bit arrival counter of the grid barrier (8-byte aligned)
@@ -99,11 +101,6 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
 }
 __device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t n) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
@@ -146,38 +143,45 @@ struct Waiter {
   }
 };
 
-// Balanced contiguous split of `items` over the grid.
+// Balanced contiguous split of `items` over the grid (32-bit: the host checks items * grid < 2^31).
 __device__ __forceinline__ int range_start(int cta, int items, int grid) {
-  return static_cast<int>((int64_t)cta * items / grid);
+  return static_cast<int>(static_cast<unsigned>(cta) * static_cast<unsigned>(items) / static_cast<unsigned>(grid));
 }
 __device__ __forceinline__ int owner_of(int item, int items, int grid) {
-  return static_cast<int>((((int64_t)item + 1) * grid - 1) / items);
+  return static_cast<int>(((static_cast<unsigned>(item) + 1u) * static_cast<unsigned>(grid) - 1u) /
+                          static_cast<unsigned>(items));
 }
 
 struct ProjShape {
-  int N, K4, C, S, I;
+  int N, K, C, S, I;  // C strips of 16 outputs, S boxes of 1024 inputs per strip, I = C * S items
 };
 __device__ __forceinline__ ProjShape proj_shape(const MegaArgs& a, int kind) {
   ProjShape p;
   const int d = a.d_model;
   p.N = kind == kQkv ? 3 * d : kind == kGu ? 2 * a.ffn : d;
-  p.K4 = (kind == kDown ? a.ffn : d) >> 2;
-  p.C = (p.N + 63) >> 6;
-  p.S = (p.K4 + kRows - 1) / kRows;
+  p.K = kind == kDown ? a.ffn : d;
+  p.C = p.N / kStripN;
+  p.S = (p.K + kBoxK - 1) / kBoxK;
   p.I = p.C * p.S;
   return p;
 }
-// A CTA's items of a projection: whole 64-output columns, so that nothing has
-// to be combined between CTAs (a trip through L2 costs more than the imbalance;
-// a projection with fewer columns than CTAs leaves the other CTAs idle).
+// A CTA's items of a projection: whole strips, so that nothing has to be
+// combined between CTAs.
 __device__ __forceinline__ void proj_range(const ProjShape& p, int cta, int G, int& i0, int& i1) {
   i0 = range_start(cta, p.C, G) * p.S;
   i1 = range_start(cta + 1, p.C, G) * p.S;
 }
 __device__ __forceinline__ int map_index(int kind) { return kind == kQkv ? 0 : kind == kO ? 1 : kind == kGu ? 2 : 3; }
+__device__ __forceinline__ void bulk_load_1d_hint(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar,
+                                                  uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
 
 // A CTA's item range [i0, i1) of an op, cut into runs: the items of one unit
-// (a projection's 64-output column, an attention head; S items each).  A run
+// (a projection's 16-output strip, an attention head; S items each).  A run
 // that shares its unit with another CTA needs a round trip through L2 to be
 // completed, so such runs come first: the range's last run, when it is cut
 // short, is processed before the others.
@@ -213,8 +217,6 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
   const int cta = blockIdx.x, G = gridDim.x;
   const uint64_t pol = policy_evict_first();
   Ring r{0, 0};
-  const int sr = kRows >> a.gs_shift;  // scale rows per box
-  const uint32_t proj_bytes = kBox + static_cast<uint32_t>(sr) * 128u;
   const int nt = a.pos / kTile + 1;
   for (int l = 0; l < a.n_layers; ++l) {
     const MegaLayer* ly = a.layers + l;
@@ -238,22 +240,16 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
         }
       } else {
         const ProjShape p = proj_shape(a, kind);
-        const int mi = map_index(kind);
+        const uint8_t* wbase = ly->w[map_index(kind)];
         int pi0, pi1;
         proj_range(p, cta, G, pi0, pi1);
-        const Runs runs(pi0, pi1, p.S);
-        for (int rr = 0; rr < runs.R; ++rr) {
-          int col, lo, hi;
-          runs.bounds(rr, col, lo, hi);
-          for (int i = lo; i < hi; ++i) {
-            const int ks = i - col * p.S;
-            w.wait(&empty[r.stage], r.phase ^ 1, 11);
-            uint8_t* st = ring + (size_t)r.stage * kStageBytes;
-            mbar_arrive_expect_tx(&full[r.stage], proj_bytes);
-            tma_load_2d_hint(st, &ly->w[mi], &full[r.stage], col * 128, ks * kRows, pol);
-            tma_load_2d_hint(st + kBox, &ly->s[mi], &full[r.stage], col * 64, ks * sr, pol);
-            r.advance(a.stages);
-          }
+        // boxes are stored strip after strip: the CTA's items are one contiguous stream
+        for (int i = pi0; i < pi1; ++i) {
+          w.wait(&empty[r.stage], r.phase ^ 1, 11);
+          uint8_t* st = ring + (size_t)r.stage * kStageBytes;
+          mbar_arrive_expect_tx(&full[r.stage], kStageBytes);
+          bulk_load_1d_hint(st, wbase + (size_t)i * kStageBytes, kStageBytes, &full[r.stage], pol);
+          r.advance(a.stages);
         }
       }
     }
@@ -269,7 +265,7 @@ struct Ctx {
   __half* xs;          // input vector of the running projection / per-warp attention scratch
   float* us;           // 8 * 2^-24 * (sum of each 32 inputs of xs): the nibble offset's share of a block
   const float2* rope;  // [64] (cos, sin) of pos / timescale_i, the rotary embedding of this step
-  float* dump;         // per-warp sums of pending runs: [slot][warp][64] or [slot][warp][kAttDump]
+  float* dump;         // per-warp sums of pending runs: [slot][warp][kStripN] or [slot][warp][kAttDump]
   int* s_int;          // [0] failure flag, [1..] run bookkeeping (see below)
   Waiter w;
   int ring_base;       // stages of this CTA consumed by earlier ops (same in every warp)
@@ -338,6 +334,12 @@ __device__ void unit_sums(Ctx& c, int d) {
   }
 }
 
+// The vector is padded with zeros to whole boxes (a ragged last box multiplies zeros).
+__device__ __forceinline__ void zero_pad_x(Ctx& c, int d) {
+  const int padded = (d + kBoxK - 1) / kBoxK * kBoxK;
+  for (int i = d + threadIdx.x * 8; i < padded; i += kCW * 32 * 8)
+    *reinterpret_cast<uint4*>(c.xs + i) = make_uint4(0u, 0u, 0u, 0u);
+}
 // xs = fp16(v * rsqrt(mean(v^2) + eps) * gamma)   (reference RMSNorm, fp32 statistics)
 __device__ void load_x_norm(Ctx& c, const __half* x, const __half* gamma, int d) {
   float ss = 0.0f;
@@ -351,6 +353,7 @@ __device__ void load_x_norm(Ctx& c, const __half* x, const __half* gamma, int d)
       ss += f.x * f.x + f.y * f.y;
     }
   }
+  zero_pad_x(c, d);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   float* part = c.dump;  // free between ops
@@ -380,138 +383,92 @@ __device__ void load_x_norm(Ctx& c, const __half* x, const __half* gamma, int d)
 __device__ void load_x_plain(Ctx& c, const __half* x, int d) {
   for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8)
     *reinterpret_cast<uint4*>(c.xs + i) = __ldcg(reinterpret_cast<const uint4*>(x + i));
+  zero_pad_x(c, d);
   consumer_bar();
   unit_sums(c, d);
   consumer_bar();
 }
 
-// One warp: outputs 2*lane and 2*lane+1 of column `col`, summed over this
-// CTA's k-stages [ks0, ks1) of the column, are completed (if the column is
-// shared with other CTAs: by whichever CTA comes last) and written.
-__device__ void finish_column(const Ctx& c, int kind, const ProjShape& p, int col, int ks0, int ks1, float v0, float v1,
-                              int i0, const __half* resid, __half* out) {
-  const MegaArgs& a = c.a;
-  const int lane = threadIdx.x & 31, G = gridDim.x, cta = blockIdx.x;
-  if (!(ks0 == 0 && ks1 == p.S)) {
-    const int slot = col == i0 / p.S ? 0 : 1;
-    *reinterpret_cast<float2*>(a.col_part + ((size_t)cta * 2 + slot) * 64 + 2 * lane) = make_float2(v0, v1);
-    __threadfence();
-    __syncwarp();
-    const int first = owner_of(col * p.S, p.I, G), last = owner_of(col * p.S + p.S - 1, p.I, G);
-    int done = 0;
-    if (lane == 0) {
-      int need = 0;  // CTAs between first and last whose range is not empty (grids larger than the item count)
-      for (int cc = first; cc <= last; ++cc) need += range_start(cc, p.I, G) != range_start(cc + 1, p.I, G) ? 1 : 0;
-      const int t = atomicAdd(a.col_tickets + col, 1);
-      done = t == need - 1 ? 1 : 0;
-      if (done) a.col_tickets[col] = 0;
+// One box (16 outputs x 1024 inputs) by one warp.  Lane = 4g + t.  The box's 64
+// MMAs go by unit (32 inputs, one scale per output): MMA 2u + m covers inputs
+// 32u + 8t' + 4m + {0..3} in its k slots (2t', 2t'+1, 2t'+8, 2t'+9).  Its A
+// fragment is one 32-bit word of the re-tiled weights per lane, whose eight
+// nibbles become fp16 subnormals by masking (rows g+8 sit in the high nibbles
+// and carry x16); its B fragment has the inputs in column u % 8 only, which
+// lane g == u % 8 supplies, so accumulator column j of unit set s collects unit
+// 8s + j.  A lane ends with rows (g, g+8) x units (8s + 2t, 8s + 2t + 1) and
+// applies the scales and the nibble offset once per box.
+__device__ __forceinline__ void consume_box(const Ctx& c, const uint8_t* st, int kb, float (&tot)[2]) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  // inputs of units g, g+8, g+16, g+24 (this lane's column), eight per unit: both MMAs' k slots of row t
+  uint4 xb[4];
+#pragma unroll
+  for (int sidx = 0; sidx < 4; ++sidx)
+    xb[sidx] = *reinterpret_cast<const uint4*>(c.xs + (size_t)kb * kBoxK + (g + 8 * sidx) * 32 + 8 * t);
+  const uint4* wl = reinterpret_cast<const uint4*>(st) + lane;  // load j of the box: wl[32 j]
+  float dsum[4][4];
+  uint4 wbuf[2][4];
+#pragma unroll
+  for (int jj = 0; jj < 4; ++jj) wbuf[0][jj] = wl[32 * jj];
+#pragma unroll
+  for (int bt = 0; bt < 4; ++bt) {  // batch bt = unit set bt (units 8 bt .. 8 bt + 7), 16 MMAs
+    if (bt + 1 < 4) {
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) wbuf[(bt + 1) & 1][jj] = wl[32 * (4 * (bt + 1) + jj)];
     }
-    done = __shfl_sync(0xffffffffu, done, 0);
-    if (!done) return;
-    __threadfence();
-    v0 = v1 = 0.0f;
-    for (int cc = first; cc <= last; ++cc) {
-      const int c0 = range_start(cc, p.I, G);
-      if (c0 == range_start(cc + 1, p.I, G)) continue;
-      const int sc = col == c0 / p.S ? 0 : 1;
-      const float2 pv = __ldcg(reinterpret_cast<const float2*>(a.col_part + ((size_t)cc * 2 + sc) * 64 + 2 * lane));
-      v0 += pv.x;
-      v1 += pv.y;
+    float acc[4][4];  // four independent chains (word i of each load)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const uint4 wv = wbuf[bt & 1][jj];
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        // MMA 16 bt + 4 jj + i: unit 8 bt + 2 jj + (i >> 1), half m = i & 1
+        const bool mine = g == 2 * jj + (i >> 1);
+        const uint32_t x0 = (i & 1) ? xb[bt].z : xb[bt].x, x1 = (i & 1) ? xb[bt].w : xb[bt].y;
+        const uint32_t b0 = mine ? x0 : 0u, b1 = mine ? x1 : 0u;
+        const uint32_t w8 = ww[i] >> 8;
+        const uint32_t af[4] = {ww[i] & 0x000F000Fu, ww[i] & 0x00F000F0u, w8 & 0x000F000Fu, w8 & 0x00F000F0u};
+        mma_f16(acc[i], af, b0, b1);
+      }
     }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) dsum[bt][r] = (acc[0][r] + acc[1][r]) + (acc[2][r] + acc[3][r]);
   }
-  const int n = col * 64 + 2 * lane;
-  const __half r0 = __float2half_rn(v0 * kOutScale), r1 = __float2half_rn(v1 * kOutScale);
-  if (kind == kGu) {
-    // rows interleave gate_i, up_i
-    const float gf = __half2float(r0), uf = __half2float(r1);
-    if (n + 1 < p.N) out[n >> 1] = __float2half_rn(gf / (1.0f + __expf(-gf)) * uf);
-  } else if (n + 1 < p.N) {
-    __half2 r = __halves2half2(r0, r1);
-    if (resid != nullptr) r = __hadd2(r, __ldcg(reinterpret_cast<const __half2*>(resid + n)));
-    *reinterpret_cast<__half2*>(out + n) = r;
-  } else if (n < p.N) {
-    out[n] = resid != nullptr ? __hadd(r0, __ldcg(resid + n)) : r0;
+  // scales of (rows g, g+8) x (units 8s + 2t, 8s + 2t + 1), s = 0..3: 16 halves per lane, in that order
+  const uint4 sc0 = *reinterpret_cast<const uint4*>(st + kBox + lane * 32);
+  const uint4 sc1 = *reinterpret_cast<const uint4*>(st + kBox + lane * 32 + 16);
+  const __half2* sh0 = reinterpret_cast<const __half2*>(&sc0);
+  const __half2* sh1 = reinterpret_cast<const __half2*>(&sc1);
+#pragma unroll
+  for (int sidx = 0; sidx < 4; ++sidx) {
+    const float2 off = *reinterpret_cast<const float2*>(c.us + kb * 32 + 8 * sidx + 2 * t);
+    const __half2* sh = sidx < 2 ? sh0 + 2 * sidx : sh1 + 2 * (sidx - 2);
+    const float2 se = __half22float2(sh[0]);  // unit 8s+2t:   row g, row g+8
+    const float2 so = __half22float2(sh[1]);  // unit 8s+2t+1: row g, row g+8
+    // dsum[s]: {row g, col 2t}, {row g, col 2t+1}, {row g+8, col 2t}, {row g+8, col 2t+1}
+    tot[0] = fmaf(se.x, dsum[sidx][0] - off.x, tot[0]);
+    tot[0] = fmaf(so.x, dsum[sidx][1] - off.y, tot[0]);
+    tot[1] = fmaf(se.y, fmaf(dsum[sidx][2], 0.0625f, -off.x), tot[1]);
+    tot[1] = fmaf(so.y, fmaf(dsum[sidx][3], 0.0625f, -off.y), tot[1]);
   }
 }
 
-// One weight box (64 k-slices x 64 outputs) by one warp.  Lane = 4g + t.  The
-// 16 MMA steps of the box are (p, q): rows 8p + 2t + q of the box (the 128B
-// swizzle makes exactly this pattern conflict-free), A = the nibbles of chunk
-// g as fp16 subnormals (row g: low nibble = output 2f, row g+8: high nibble =
-// output 2f+1), B column p = the inputs of those rows, all other columns zero:
-// accumulator column p collects the 32-input unit p of the box, so each lane
-// ends with (outputs 8g+2f, 8g+2f+1) x (units 2t, 2t+1) and applies the block
-// scales once per box.
-__device__ __forceinline__ void consume_box(const Ctx& c, const uint8_t* st, int ks, int K4, int gs_shift,
-                                            float (&tot)[4][2]) {
-  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  // this lane's B values: rows 8g + 2t + q (they feed column g)
-  uint32_t bx[2][2];
-#pragma unroll
-  for (int q = 0; q < 2; ++q) {
-    const int row = ks * kRows + 8 * g + 2 * t + q;
-    bx[q][0] = bx[q][1] = 0u;
-    if (row < K4) {
-      const uint2 xv = *reinterpret_cast<const uint2*>(c.xs + (size_t)row * 4);
-      bx[q][0] = xv.x;
-      bx[q][1] = xv.y;
-    }
-  }
-  // Two accumulator sets (steps q = 0 / q = 1) give eight independent MMA chains; the
-  // weights are fetched one batch of four steps ahead of the MMAs that use them.
-  float acc[2][4][4];
-#pragma unroll
-  for (int q = 0; q < 2; ++q)
-#pragma unroll
-    for (int f = 0; f < 4; ++f) acc[q][f][0] = acc[q][f][1] = acc[q][f][2] = acc[q][f][3] = 0.0f;
-  const uint8_t* lane_base = st + (2 * t) * 128;           // row 8pp + 2t + q -> + pp*1024 + q*128
-  const int sw0 = (g ^ ((2 * t) & 7)) << 4, sw1 = (g ^ ((2 * t + 1) & 7)) << 4;
-  uint4 wbuf[2][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-    wbuf[0][i] = *reinterpret_cast<const uint4*>(lane_base + (i >> 1) * 1024 + (i & 1) * 128 + ((i & 1) ? sw1 : sw0));
-#pragma unroll
-  for (int bt = 0; bt < 4; ++bt) {
-    if (bt + 1 < 4) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        wbuf[(bt + 1) & 1][i] = *reinterpret_cast<const uint4*>(lane_base + (2 * (bt + 1) + (i >> 1)) * 1024 +
-                                                                 (i & 1) * 128 + ((i & 1) ? sw1 : sw0));
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int pp = 2 * bt + (i >> 1), q = i & 1;
-      const uint4 wv = wbuf[bt & 1][i];
-      const uint32_t b0 = g == pp ? bx[q][0] : 0u, b1 = g == pp ? bx[q][1] : 0u;
-      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-      for (int b = 0; b < 2; ++b) {
-        const uint32_t lo = ww[2 * b], hi = ww[2 * b + 1];
-        const uint32_t lo8 = lo >> 8, hi8 = hi >> 8;
-        const uint32_t a0[4] = {lo & 0x000F000Fu, lo & 0x00F000F0u, hi & 0x000F000Fu, hi & 0x00F000F0u};
-        const uint32_t a1[4] = {lo8 & 0x000F000Fu, lo8 & 0x00F000F0u, hi8 & 0x000F000Fu, hi8 & 0x00F000F0u};
-        mma_f16(acc[q][2 * b], a0, b0, b1);
-        mma_f16(acc[q][2 * b + 1], a1, b0, b1);
-      }
-    }
-  }
-  // units 2t and 2t+1 of the box: their offset terms and the scales of this lane's eight outputs
-  const float2 off = *reinterpret_cast<const float2*>(c.us + ks * 8 + 2 * t);
-  const int srow0 = (2 * t) >> (gs_shift - 3), srow1 = (2 * t + 1) >> (gs_shift - 3);
-  const uint4 s0 = *reinterpret_cast<const uint4*>(st + kBox + (srow0 * 64 + 8 * g) * 2);
-  const uint4 s1 = *reinterpret_cast<const uint4*>(st + kBox + (srow1 * 64 + 8 * g) * 2);
-  const __half2* h0 = reinterpret_cast<const __half2*>(&s0);
-  const __half2* h1 = reinterpret_cast<const __half2*>(&s1);
-#pragma unroll
-  for (int f = 0; f < 4; ++f) {
-    const float2 sa = __half22float2(h0[f]), sb = __half22float2(h1[f]);
-    // acc[.][f]: {row g, col 2t}, {row g, col 2t+1}, {row g+8, col 2t}, {row g+8, col 2t+1}; high nibbles carry x16
-    const float e0 = acc[0][f][0] + acc[1][f][0], e1 = acc[0][f][1] + acc[1][f][1];
-    const float o0 = acc[0][f][2] + acc[1][f][2], o1 = acc[0][f][3] + acc[1][f][3];
-    tot[f][0] = fmaf(sa.x, e0 - off.x, tot[f][0]);
-    tot[f][0] = fmaf(sb.x, e1 - off.y, tot[f][0]);
-    tot[f][1] = fmaf(sa.y, fmaf(o0, 0.0625f, -off.x), tot[f][1]);
-    tot[f][1] = fmaf(sb.y, fmaf(o1, 0.0625f, -off.y), tot[f][1]);
+// Lanes 0..15 of one warp: output strip * 16 + lane, summed over all of K, gets its
+// epilogue and is written.
+__device__ __forceinline__ void finish_strip(int kind, int strip, float v, const __half* resid, __half* out) {
+  const int lane = threadIdx.x & 31;
+  const int n = strip * kStripN + lane;
+  const __half r = __float2half_rn(v * kOutScale);
+  if (kind == kGu) {
+    // rows interleave gate_i, up_i: even lanes hold the gate, the next lane its up value
+    const float gf = __half2float(r);
+    const float uf = __shfl_down_sync(0xffffffffu, gf, 1);
+    if (lane < kStripN && (lane & 1) == 0) out[n >> 1] = __float2half_rn(gf / (1.0f + __expf(-gf)) * uf);
+  } else if (lane < kStripN) {
+    out[n] = resid != nullptr ? __hadd(r, __ldcg(resid + n)) : r;
   }
 }
 
@@ -523,7 +480,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
   const int g = lane >> 2, t = lane & 3;
   int i0, i1;
   proj_range(p, cta, G, i0, i1);
-  const Runs runs(i0, i1, p.S);
+  const int n_runs = (i1 - i0) / p.S;  // whole strips
   long long waited = 0, boxed = 0;
   const bool tracing = a.trace != nullptr && threadIdx.x == 0;
   // this warp takes every kCW-th stage of the op's sequence
@@ -531,20 +488,17 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
   int pos = c.ring_base + warp;
   int stage = pos % a.stages;
   uint32_t phase = static_cast<uint32_t>(pos / a.stages) & 1u;
-  int seq_lo = 0;
-  for (int rr = 0; rr < runs.R; ++rr) {
-    int col, lo, hi;
-    runs.bounds(rr, col, lo, hi);
-    const int ks0 = lo - col * p.S, seq_hi = seq_lo + (hi - lo);
-    float tot[4][2];
-#pragma unroll
-    for (int f = 0; f < 4; ++f) tot[f][0] = tot[f][1] = 0.0f;
+  for (int rr = 0; rr < n_runs; ++rr) {
+    const int strip = i0 / p.S + rr;
+    const int seq_lo = rr * p.S, seq_hi = seq_lo + p.S;
+    if (q >= seq_hi) continue;  // no box of this strip for this warp
+    float tot[2] = {0.0f, 0.0f};
     for (; q < seq_hi; q += kCW) {
       const long long w0 = tracing ? clock64() : 0;
       c.w.wait(&c.full[stage], phase, 12);
       if (tracing) waited += clock64() - w0;
       const long long b0 = tracing ? clock64() : 0;
-      consume_box(c, c.ring + (size_t)stage * kStageBytes, ks0 + (q - seq_lo), p.K4, a.gs_shift, tot);
+      consume_box(c, c.ring + (size_t)stage * kStageBytes, q - seq_lo, tot);
       __syncwarp();
       if (tracing) boxed += clock64() - b0;
       if (lane == 0) mbar_arrive_n(&c.empty[stage], kCW);
@@ -554,50 +508,49 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
         phase ^= 1u;
       }
     }
-    // this warp's share of the run: sum the four unit pairs (lanes t), park it in the run's slot
+    // sum the four unit pairs (lanes t); park this warp's share in the strip's slot
+    tot[0] += __shfl_xor_sync(0xffffffffu, tot[0], 1);
+    tot[0] += __shfl_xor_sync(0xffffffffu, tot[0], 2);
+    tot[1] += __shfl_xor_sync(0xffffffffu, tot[1], 1);
+    tot[1] += __shfl_xor_sync(0xffffffffu, tot[1], 2);
+    const int n_part = p.S < kCW ? p.S : kCW;  // warps that have a box of this strip
     const int run = c.proj_runs + rr, slot = run % kProjSlots, use = run / kProjSlots;
-#pragma unroll
-    for (int f = 0; f < 4; ++f)
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        tot[f][e] += __shfl_xor_sync(0xffffffffu, tot[f][e], 1);
-        tot[f][e] += __shfl_xor_sync(0xffffffffu, tot[f][e], 2);
-      }
-    c.w.wait_count(c.proj_done() + slot, use, 15);  // the slot's previous run has been summed
-    float* mine = c.dump + ((size_t)slot * kCW + warp) * 64;
+    if (n_part == 1) {
+      // the strip is this warp's alone: rows g and g+8 sit in lanes t == 0
+      const float lo = __shfl_sync(0xffffffffu, tot[0], (lane & 7) * 4);
+      const float hi = __shfl_sync(0xffffffffu, tot[1], (lane & 7) * 4);
+      finish_strip(kind, strip, (lane & 8) ? hi : lo, resid, out);
+      continue;
+    }
+    c.w.wait_count(c.proj_done() + slot, use, 15);  // the slot's previous strip has been summed
+    float* mine = c.dump + ((size_t)slot * kCW + warp) * kStripN;
     if (t == 0) {
-      *reinterpret_cast<float4*>(mine + 8 * g) = make_float4(tot[0][0], tot[0][1], tot[1][0], tot[1][1]);
-      *reinterpret_cast<float4*>(mine + 8 * g + 4) = make_float4(tot[2][0], tot[2][1], tot[3][0], tot[3][1]);
+      mine[g] = tot[0];
+      mine[g + 8] = tot[1];
     }
     __syncwarp();
     int last = 0;
     if (lane == 0) {
       __threadfence_block();
-      last = atomicAdd(c.proj_arrived() + slot, 1) == kCW - 1 ? 1 : 0;
+      last = atomicAdd(c.proj_arrived() + slot, 1) == n_part - 1 ? 1 : 0;
     }
     last = __shfl_sync(0xffffffffu, last, 0);
     if (last) {
-      // the last warp of the CTA to get here sums the warps in order and completes the column
+      // the last warp to get here sums the shares in the order of the boxes and completes the strip
       __threadfence_block();
-      const float* all = c.dump + (size_t)slot * kCW * 64;
-      float v0 = 0.0f, v1 = 0.0f;
-#pragma unroll
-      for (int wi = 0; wi < kCW; ++wi) {
-        const float2 pv = *reinterpret_cast<const float2*>(all + wi * 64 + 2 * lane);
-        v0 += pv.x;
-        v1 += pv.y;
-      }
+      const float* all = c.dump + (size_t)slot * kCW * kStripN;
+      float v = 0.0f;
+      for (int k = 0; k < n_part; ++k) v += all[((seq_lo + k) % kCW) * kStripN + (lane & 15)];
       __syncwarp();
       if (lane == 0) {
         c.proj_arrived()[slot] = 0;
         __threadfence_block();
         c.proj_done()[slot] = use + 1;
       }
-      finish_column(c, kind, p, col, ks0, ks0 + (hi - lo), v0, v1, i0, resid, out);
+      finish_strip(kind, strip, v, resid, out);
     }
-    seq_lo = seq_hi;
   }
-  c.proj_runs += runs.R;
+  if (p.S > 1) c.proj_runs += n_runs;  // single-box strips never use a slot
   c.ring_base += i1 - i0;
   if (tracing) {
     unsigned long long* tr = a.trace + ((size_t)blockIdx.x * a.n_layers * kOpsPerLayer + c.op_index) * kTraceSlots;
@@ -828,7 +781,11 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
       last = atomicAdd(c.attn_arrived() + slot, 1) == kCW - 1 ? 1 : 0;
     }
     last = __shfl_sync(0xffffffffu, last, 0);
+    unsigned long long* trs = a.trace != nullptr && lane == 0
+                                  ? a.trace + ((size_t)blockIdx.x * a.n_layers * kOpsPerLayer + c.op_index) * kTraceSlots
+                                  : nullptr;
     if (last) {
+      if (trs) trs[8] = globaltimer_ns();
       // the CTA's last warp merges the warps in order; lane owns dims 4*lane..+4
       __threadfence_block();
       const float* all = c.dump + (size_t)slot * kCW * kAttDump;
@@ -860,41 +817,52 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
           part[kHeadDim] = M;
           part[kHeadDim + 1] = ls;
         }
+        if (trs) trs[9] = globaltimer_ns();
         __threadfence();
         __syncwarp();
+        // contributors: the CTAs first..lastc whose range is not empty; lane u looks at CTA base + u
+        int need = 0;
+        for (int base = first; base <= lastc; base += 32) {
+          const int cc = base + lane;
+          const bool has = cc <= lastc && range_start(cc, I, G) != range_start(cc + 1, I, G);
+          need += __popc(__ballot_sync(0xffffffffu, has));
+        }
         int done = 0;
         if (lane == 0) {
-          int need = 0;
-          for (int cc = first; cc <= lastc; ++cc) need += range_start(cc, I, G) != range_start(cc + 1, I, G) ? 1 : 0;
           const int tk = atomicAdd(a.att_tickets + head, 1);
+          if (trs) trs[10] = globaltimer_ns();
           done = tk == need - 1 ? 1 : 0;
           if (done) a.att_tickets[head] = 0;
         }
         write = __shfl_sync(0xffffffffu, done, 0) != 0;
         if (write) {
           __threadfence();
-          // contributors are the CTAs first..lastc with a non-empty range; their partials are requested
-          // eight at a time so that the loads overlap
           float TM = -INFINITY;
           o[0] = o[1] = o[2] = o[3] = 0.0f;
           ls = 0.0f;
           for (int base = first; base <= lastc; base += 8) {
+            // lane u < 8 finds the partial of CTA base + u (offset in floats, -1 if none); all lanes then load
+            int myoff = -1;
+            {
+              const int cc = base + (lane & 7);
+              if (cc <= lastc) {
+                const int c0 = range_start(cc, I, G);
+                if (c0 != range_start(cc + 1, I, G)) myoff = (cc * kAttSlots + (head - c0 / nt)) * kAttDump;
+              }
+            }
             float mc[8], lc[8];
             float4 oc[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-              const int cc = base + u;
+              const int off = __shfl_sync(0xffffffffu, myoff, u);
               mc[u] = -INFINITY;
               lc[u] = 0.0f;
               oc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-              if (cc <= lastc) {
-                const int c0 = range_start(cc, I, G);
-                if (c0 != range_start(cc + 1, I, G)) {
-                  const float* pp = a.att_part + ((size_t)cc * kAttSlots + (head - c0 / nt)) * kAttDump;
-                  mc[u] = __ldcg(pp + kHeadDim);
-                  lc[u] = __ldcg(pp + kHeadDim + 1);
-                  oc[u] = __ldcg(reinterpret_cast<const float4*>(pp + 4 * lane));
-                }
+              if (off >= 0) {
+                const float* pp = a.att_part + off;
+                mc[u] = __ldcg(pp + kHeadDim);
+                lc[u] = __ldcg(pp + kHeadDim + 1);
+                oc[u] = __ldcg(reinterpret_cast<const float4*>(pp + 4 * lane));
               }
             }
             float NM = TM;
@@ -926,6 +894,7 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
         pk.x = *reinterpret_cast<uint32_t*>(&r01);
         pk.y = *reinterpret_cast<uint32_t*>(&r23);
         *reinterpret_cast<uint2*>(a.attn + (size_t)head * kHeadDim + 4 * lane) = pk;
+        if (trs) trs[11] = globaltimer_ns();
       }
     }
   }
@@ -1035,20 +1004,83 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
   }
 }
 
+// ------------------------------------------------------------ weight re-tiling
+// Reference layout in: weights [K/4][N/4] blocks of 4 inputs x 4 outputs, 8
+// bytes each (nibble (k%4)*4 + (n%4), even nibbles in the low half of a byte;
+// fully_connected_util.cc / tensor_utils.h RearrangeWeights... I4O4 layouts),
+// scales fp16 [K/block][N].  Out: [strip][k box] records of kStageBytes, laid
+// out as consume_box reads them.  One thread per 32-bit word of the output.
+__global__ void __launch_bounds__(256) retile_weights_kernel(const uint8_t* __restrict__ w, const __half* __restrict__ sc,
+                                                             uint8_t* __restrict__ out, int N, int K, int block) {
+  const int S = (K + kBoxK - 1) / kBoxK;
+  const int64_t words_per_box = kStageBytes / 4;
+  const int64_t total = (int64_t)(N / kStripN) * S * words_per_box;
+  const int N4 = N / 4;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t box = idx / words_per_box;
+    const int wi = static_cast<int>(idx - box * words_per_box);
+    const int strip = static_cast<int>(box / S), kb = static_cast<int>(box - (int64_t)strip * S);
+    uint32_t word = 0;
+    if (wi < kBox / 4) {
+      // weights: word = [load j][lane][i]; MMA 4j + i = unit u, half m
+      const int j = wi >> 7, lane = (wi >> 2) & 31, i = wi & 3;
+      const int g = lane >> 2, t = lane & 3;
+      const int mi = 4 * j + i, u = mi >> 1, m = mi & 1;
+#pragma unroll
+      for (int nib = 0; nib < 8; ++nib) {
+        // nibble -> (row, k slot): 0:(g,0) 1:(g+8,0) 2:(g,2) 3:(g+8,2) 4:(g,1) 5:(g+8,1) 6:(g,3) 7:(g+8,3)
+        const int row = (nib & 1) ? g + 8 : g;
+        const int slot = ((nib >> 2) & 1) | (((nib >> 1) & 1) << 1);
+        const int k = kb * kBoxK + u * 32 + 8 * t + 4 * m + slot;
+        const int n = strip * kStripN + row;
+        uint32_t v = 0;
+        if (k < K) {
+          const uint8_t* blk = w + ((size_t)(k >> 2) * N4 + (n >> 2)) * 8;
+          const int e = (k & 3) * 4 + (n & 3);
+          const uint8_t byte = blk[e >> 1];
+          v = (e & 1) ? (byte >> 4) : (byte & 15);
+        }
+        word |= v << (4 * nib);
+      }
+    } else {
+      // scales: [lane][s][unit parity e][row g / g+8] halves, two per word
+      const int hi = (wi - kBox / 4) * 2;  // first half index of this word
+      uint32_t pair = 0;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int h = hi + q;
+        const int lane = h >> 4, r = h & 15;
+        const int g = lane >> 2, t = lane & 3;
+        const int sidx = r >> 2, e = (r >> 1) & 1, rsel = r & 1;
+        const int u = 8 * sidx + 2 * t + e;
+        const int k = kb * kBoxK + u * 32;
+        const int n = strip * kStripN + (rsel ? g + 8 : g);
+        uint16_t bits = 0;
+        if (k < K) bits = __half_as_ushort(sc[(size_t)(k / block) * N + n]);
+        pair |= static_cast<uint32_t>(bits) << (16 * q);
+      }
+      word = pair;
+    }
+    reinterpret_cast<uint32_t*>(out)[idx] = word;
+  }
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------ host side
 struct MegaDecoder {
   MegaConfig cfg;
-  int sms, grid, stages, gs_shift, xs_bytes, us_floats;
+  int sms, grid, stages, xs_bytes, us_floats;
   size_t smem_bytes;
   MegaLayer* d_layers;
   std::vector<MegaLayer> h_layers;
   std::vector<char> layer_set;
   uint8_t* scratch;
+  uint8_t* prepared;          // re-tiled weights of all layers
+  size_t proj_bytes[4], layer_bytes;
   __half *qkv, *attn, *h, *act, *xa, *xb;
-  float *col_part, *att_part;
-  int *col_tickets, *att_tickets, *error;
+  float* att_part;
+  int *att_tickets, *error;
   unsigned* bar;
   unsigned long long* trace;
 };
@@ -1056,10 +1088,8 @@ struct MegaDecoder {
 bool mega_supported(const MegaConfig& c) {
   if (c.head_dim != kHeadDim || c.heads < 1) return false;
   if (c.d_model != c.heads * kHeadDim) return false;
-  if (c.d_model % 64 != 0 || c.ffn % 32 != 0) return false;
-  int gs = c.block / 4, shift = 0;
-  while ((1 << shift) < gs) ++shift;
-  if ((1 << shift) != gs || gs < 8 || gs > kRows) return false;  // blocks of 32..256 inputs
+  if (c.ffn % 32 != 0) return false;
+  if (c.block != 32 && c.block != 64 && c.block != 128 && c.block != 256) return false;
   if (c.d_model % c.block != 0 || c.ffn % c.block != 0) return false;
   return get_encode_tiled() != nullptr;
 }
@@ -1068,6 +1098,7 @@ void mega_destroy(MegaDecoder* m) {
   if (m == nullptr) return;
   if (m->d_layers != nullptr) cudaFree(m->d_layers);
   if (m->scratch != nullptr) cudaFree(m->scratch);
+  if (m->prepared != nullptr) cudaFree(m->prepared);
   if (m->trace != nullptr) cudaFree(m->trace);
   delete m;
 }
@@ -1078,17 +1109,16 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   m->cfg = cfg;
   m->d_layers = nullptr;
   m->scratch = nullptr;
+  m->prepared = nullptr;
   m->trace = nullptr;
   m->sms = sm_count(cfg.device);
-  int gs = cfg.block / 4;
-  m->gs_shift = 0;
-  while ((1 << m->gs_shift) < gs) ++m->gs_shift;
-  // shared memory: ring + max(input vector, per-warp attention scratch) + unit sums + run slots + barriers
+  // shared memory: ring + max(input vector padded to whole boxes, per-warp attention scratch) + unit sums +
+  // run slots + rope table + barriers
   const int att_bytes = kCW * kWarpScratch * 4;
-  const int vec_elems = cfg.d_model > cfg.ffn ? cfg.d_model : cfg.ffn;
+  const int vec_elems = align_n(cfg.d_model > cfg.ffn ? cfg.d_model : cfg.ffn, kBoxK);
   const int vec_bytes = vec_elems * 2;
   m->xs_bytes = align_n(att_bytes > vec_bytes ? att_bytes : vec_bytes, 128);
-  m->us_floats = align_n(div_up(vec_elems, 256) * 8, 32);  // whole boxes, so that a ragged last stage reads zeros
+  m->us_floats = vec_elems / 32;
   const int fixed = 1024 + m->xs_bytes + m->us_floats * 4 + kDumpFloats * 4 + (kHeadDim / 2) * 8 + kSharedInts * 4 + 64;
   int max_smem = 0;
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, cfg.device);
@@ -1122,13 +1152,18 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   }
   // an attention range must not touch more than kAttSlots heads: ceil(n/nt)+1 with n = ceil(heads*nt/grid)
   // is at most ceil(heads/grid + 1/nt) + 1 <= heads/grid + 3
+  if ((int64_t)cfg.heads * (cfg.max_seq / kTile + 1) * m->grid >= (int64_t(1) << 31) ||
+      (int64_t)(3 * cfg.d_model > 2 * cfg.ffn ? 3 * cfg.d_model : 2 * cfg.ffn) / kStripN * m->grid >= (int64_t(1) << 31)) {
+    set_last_error_text("decoder too large for the persistent step kernel's 32-bit work split");
+    mega_destroy(m);
+    return MLD_UNIMPLEMENTED;
+  }
   if (cfg.heads / m->grid + 3 > kAttSlots) {
     set_last_error_text("too many heads per CTA for the persistent step kernel");
     mega_destroy(m);
     return MLD_UNIMPLEMENTED;
   }
   const int d = cfg.d_model, ffn = cfg.ffn;
-  const int max_cols = (3 * d > 2 * ffn ? 3 * d : 2 * ffn) / 64 + 1;
   size_t off = 0;
   auto take = [&](size_t bytes) {
     const size_t o = off;
@@ -1137,10 +1172,18 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   };
   const size_t o_qkv = take((size_t)3 * d * 2), o_attn = take((size_t)d * 2), o_h = take((size_t)d * 2),
                o_act = take((size_t)ffn * 2), o_xa = take((size_t)d * 2), o_xb = take((size_t)d * 2),
-               o_cp = take((size_t)m->grid * 2 * 64 * 4), o_ap = take((size_t)m->grid * kAttSlots * kAttDump * 4),
-               o_ct = take((size_t)max_cols * 4), o_at = take((size_t)cfg.heads * 4), o_bar = take(8), o_err = take(4);
+               o_ap = take((size_t)m->grid * kAttSlots * kAttDump * 4), o_at = take((size_t)cfg.heads * 4),
+               o_bar = take(8), o_err = take(4);
+  const int Ns[4] = {3 * d, d, 2 * ffn, d};
+  const int Ks[4] = {d, d, d, ffn};
+  m->layer_bytes = 0;
+  for (int i = 0; i < 4; ++i) {
+    m->proj_bytes[i] = (size_t)(Ns[i] / kStripN) * div_up(Ks[i], kBoxK) * kStageBytes;
+    m->layer_bytes += m->proj_bytes[i];
+  }
   if (cudaMalloc(&m->scratch, off) != cudaSuccess ||
-      cudaMalloc(&m->d_layers, sizeof(MegaLayer) * cfg.layers) != cudaSuccess) {
+      cudaMalloc(&m->d_layers, sizeof(MegaLayer) * cfg.layers) != cudaSuccess ||
+      cudaMalloc(&m->prepared, m->layer_bytes * cfg.layers) != cudaSuccess) {
     set_last_error_text("persistent step kernel: device allocation failed");
     mega_destroy(m);
     return MLD_CUDA_ERROR;
@@ -1152,9 +1195,7 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   m->act = reinterpret_cast<__half*>(m->scratch + o_act);
   m->xa = reinterpret_cast<__half*>(m->scratch + o_xa);
   m->xb = reinterpret_cast<__half*>(m->scratch + o_xb);
-  m->col_part = reinterpret_cast<float*>(m->scratch + o_cp);
   m->att_part = reinterpret_cast<float*>(m->scratch + o_ap);
-  m->col_tickets = reinterpret_cast<int*>(m->scratch + o_ct);
   m->att_tickets = reinterpret_cast<int*>(m->scratch + o_at);
   m->bar = reinterpret_cast<unsigned*>(m->scratch + o_bar);
   m->error = reinterpret_cast<int*>(m->scratch + o_err);
@@ -1173,14 +1214,15 @@ int mega_set_layer(MegaDecoder* m, int layer, const MegaLayerPtrs& p) {
   const int Ks[4] = {d, d, d, ffn};
   const void* ws[4] = {p.wqkv, p.wo, p.wgu, p.wdown};
   const void* ss[4] = {p.sqkv, p.so, p.sgu, p.sdown};
-  const int sr = kRows >> m->gs_shift;
+  uint8_t* dst = m->prepared + (size_t)layer * m->layer_bytes;
   for (int i = 0; i < 4; ++i) {
-    const uint64_t row_bytes = (uint64_t)Ns[i] * 2;  // N/4 blocks of 8 bytes
-    int rc = make_tmap_2d(&L.w[i], ws[i], row_bytes, Ks[i] / 4, row_bytes, 128, kRows, 1, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != MLD_OK) return rc;
-    rc = make_tmap_2d(&L.s[i], ss[i], (uint64_t)Ns[i] * 2, Ks[i] / c.block, (uint64_t)Ns[i] * 2, 128, sr, 2,
-                      CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc != MLD_OK) return rc;
+    const int64_t words = static_cast<int64_t>(m->proj_bytes[i] / 4);
+    const int blocks = static_cast<int>(words / 256 < 4096 ? (words + 255) / 256 : 4096);
+    retile_weights_kernel<<<blocks, 256>>>(static_cast<const uint8_t*>(ws[i]), static_cast<const __half*>(ss[i]), dst,
+                                           Ns[i], Ks[i], c.block);
+    MLD_LAUNCH_CHECK();
+    L.w[i] = dst;
+    dst += m->proj_bytes[i];
   }
   const uint64_t kv_row = (uint64_t)c.heads * kHeadDim * 2;
   int rc = make_tmap_2d(&L.kc, p.kcache, kv_row, c.max_seq, kv_row, kHeadDim * 2, kTile, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
@@ -1223,7 +1265,6 @@ int mega_device_status(MegaDecoder* m, int* code) {
     const int zero = 0;
     cudaMemcpy(m->error, &zero, sizeof zero, cudaMemcpyHostToDevice);
     cudaMemset(m->bar, 0, 8);
-    cudaMemset(m->col_tickets, 0, (size_t)((3 * m->cfg.d_model > 2 * m->cfg.ffn ? 3 * m->cfg.d_model : 2 * m->cfg.ffn) / 64 + 1) * 4);
     cudaMemset(m->att_tickets, 0, (size_t)m->cfg.heads * 4);
   }
   return MLD_OK;
@@ -1240,7 +1281,6 @@ int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream
   a.heads = c.heads;
   a.ffn = c.ffn;
   a.pos = pos;
-  a.gs_shift = m->gs_shift;
   a.stages = m->stages;
   a.xs_bytes = m->xs_bytes;
   a.us_floats = m->us_floats;
@@ -1256,8 +1296,6 @@ int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream
   a.act = m->act;
   a.xa = m->xa;
   a.xb = m->xb;
-  a.col_part = m->col_part;
-  a.col_tickets = m->col_tickets;
   a.att_part = m->att_part;
   a.att_tickets = m->att_tickets;
   a.bar = m->bar;
