@@ -83,6 +83,7 @@ struct MegaArgs {
   const MegaLayer* layers;
   int n_layers, d_model, heads, ffn, pos;
   int stages;          // ring depth
+  int l2_ahead;        // ops by which the L2 prefetch runs ahead of the ring's loads (0 = none)
   int xs_bytes;        // shared-memory bytes of the input-vector / attention scratch area
   int us_floats;       // entries of the per-32-input sums of the input vector
   float rms_eps, min_ts, max_ts, q_scale;
@@ -213,6 +214,41 @@ struct Ring {
   }
 };
 
+// Asks L2 for this CTA's whole share of an op: HBM then runs an op ahead of the
+// ring, which only has to cover the L2 -> shared memory latency.
+__device__ void prefetch_op_l2(const MegaArgs& a, int l, int kind) {
+  const int cta = blockIdx.x, G = gridDim.x;
+  const MegaLayer* ly = a.layers + l;
+  if (kind == kAttn) {
+    const int nt = a.pos / kTile + 1;
+    const int I = a.heads * nt;
+    const int i0 = range_start(cta, I, G), i1 = range_start(cta + 1, I, G);
+    for (int i = i0; i < i1; ++i) {
+      const int head = i / nt, j = i - head * nt;
+      asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                       reinterpret_cast<uint64_t>(&ly->kc)),
+                   "r"(head * kHeadDim), "r"(j * kTile)
+                   : "memory");
+      asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                       reinterpret_cast<uint64_t>(&ly->vc)),
+                   "r"(head * kHeadDim), "r"(j * kTile)
+                   : "memory");
+    }
+  } else {
+    const ProjShape p = proj_shape(a, kind);
+    int i0, i1;
+    proj_range(p, cta, G, i0, i1);
+    const uint8_t* src = ly->w[map_index(kind)] + (size_t)i0 * kStageBytes;
+    size_t bytes = (size_t)(i1 - i0) * kStageBytes;
+    while (bytes > 0) {
+      const uint32_t n = bytes < 18432 ? static_cast<uint32_t>(bytes) : 18432u;
+      bulk_prefetch_l2(src, n);
+      src += n;
+      bytes -= n;
+    }
+  }
+}
+
 __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, uint64_t* empty, const Waiter& w) {
   const int cta = blockIdx.x, G = gridDim.x;
   const uint64_t pol = policy_evict_first();
@@ -221,6 +257,11 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
   for (int l = 0; l < a.n_layers; ++l) {
     const MegaLayer* ly = a.layers + l;
     for (int kind = 0; kind < kOpsPerLayer; ++kind) {
+      if (a.l2_ahead > 0) {
+        // the op `l2_ahead` ops after this one
+        const int o = l * kOpsPerLayer + kind + a.l2_ahead;
+        if (o < a.n_layers * kOpsPerLayer) prefetch_op_l2(a, o / kOpsPerLayer, o % kOpsPerLayer);
+      }
       if (kind == kAttn) {
         const int I = a.heads * nt;
         const Runs runs(range_start(cta, I, G), range_start(cta + 1, I, G), nt);
@@ -1070,7 +1111,7 @@ __global__ void __launch_bounds__(256) retile_weights_kernel(const uint8_t* __re
 // ------------------------------------------------------------------ host side
 struct MegaDecoder {
   MegaConfig cfg;
-  int sms, grid, stages, xs_bytes, us_floats;
+  int sms, grid, stages, xs_bytes, us_floats, l2_ahead;
   size_t smem_bytes;
   MegaLayer* d_layers;
   std::vector<MegaLayer> h_layers;
@@ -1134,6 +1175,8 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
     return MLD_UNIMPLEMENTED;
   }
   m->stages = stages;
+  m->l2_ahead = 0;  // measured: asking L2 for the next op ahead of the ring's loads slows the step down
+  if (const char* e2 = getenv("MLD_MEGA_L2_AHEAD")) m->l2_ahead = atoi(e2) < 0 ? 0 : atoi(e2);
   m->smem_bytes = (size_t)fixed + (size_t)stages * (kStageBytes + 16);
   cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(m->smem_bytes));
@@ -1282,6 +1325,7 @@ int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream
   a.ffn = c.ffn;
   a.pos = pos;
   a.stages = m->stages;
+  a.l2_ahead = m->l2_ahead;
   a.xs_bytes = m->xs_bytes;
   a.us_floats = m->us_floats;
   a.rms_eps = c.rms_eps;

@@ -727,7 +727,7 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   // One GPU: run the step as one persistent kernel when the shape allows it
   // (MLD_DECODER_MODE=ops keeps the op-by-op path).
   const char* mode = getenv("MLD_DECODER_MODE");
-  if (d->world == 1 && mode != nullptr && strcmp(mode, "mega") == 0) {
+  if (d->world == 1 && !(mode != nullptr && strcmp(mode, "ops") == 0)) {
     MegaConfig mc = {d->layers, d->d_model, d->heads, d->head_dim, d->ffn, d->max_seq, d->block,
                      d->rms_eps, d->rope_min_timescale, d->rope_max_timescale, device};
     if (mega_supported(mc)) {
