@@ -71,7 +71,7 @@ constexpr int kTraceSlots = 12;              // per (CTA, op): 4 timestamps, wai
 enum { kQkv = 0, kAttn = 1, kO = 2, kGu = 3, kDown = 4, kOpsPerLayer = 5 };
 
 struct alignas(128) MegaLayer {
-  CUtensorMap kc, vc; // KV cache: fp16 [max_seq][heads*128], box 128 x 32 rows
+  CUtensorMap kc, vc; // KV cache: fp16 [max_seq][heads*128], box 64 dims x 32 rows, 128-byte swizzle
   const uint8_t* w[4];  // re-tiled weights + scales of qkv, o, gu, down: [strip][k box][kStageBytes]
   const __half* norm1;
   const __half* norm2;
@@ -274,7 +274,9 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
               w.wait(&empty[r.stage], r.phase ^ 1, 10);
               uint8_t* st = ring + (size_t)r.stage * kStageBytes;
               mbar_arrive_expect_tx(&full[r.stage], kBox);
-              tma_load_2d_hint(st, kv == 0 ? &ly->kc : &ly->vc, &full[r.stage], head * kHeadDim, j * kTile, pol);
+              const CUtensorMap* map = kv == 0 ? &ly->kc : &ly->vc;
+              tma_load_2d_hint(st, map, &full[r.stage], head * kHeadDim, j * kTile, pol);
+              tma_load_2d_hint(st + 4096, map, &full[r.stage], head * kHeadDim + 64, j * kTile, pol);
               r.advance(a.stages);
             }
           }
@@ -601,216 +603,221 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
   }
 }
 
-// One cached token against the head's query for one eight-lane group: lane `sub`
-// holds dims 8*sub..+8 (k0, v0) and 64+8*sub..+8 (k1, v1) as fp16.  Updates the
-// group's running state.
-__device__ __forceinline__ void attend_token(const float (&qv)[16], const uint4& k0, const uint4& k1, const uint4& v0,
-                                             const uint4& v1, unsigned gmask, float& m, float& l, float (&acc)[16]) {
-  const __half2* kh0 = reinterpret_cast<const __half2*>(&k0);
-  const __half2* kh1 = reinterpret_cast<const __half2*>(&k1);
-  float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float2 a0 = __half22float2(kh0[e]), a1 = __half22float2(kh1[e]);
-    s0 = fmaf(qv[2 * e], a0.x, s0);
-    s0 = fmaf(qv[2 * e + 1], a0.y, s0);
-    s1 = fmaf(qv[8 + 2 * e], a1.x, s1);
-    s1 = fmaf(qv[8 + 2 * e + 1], a1.y, s1);
-  }
-  float s = s0 + s1;
-  s += __shfl_xor_sync(gmask, s, 1);
-  s += __shfl_xor_sync(gmask, s, 2);
-  s += __shfl_xor_sync(gmask, s, 4);
-  const float m_new = fmaxf(m, s);
-  const float corr = __expf(m - m_new), pw = __expf(s - m_new);
-  l = l * corr + pw;
-  const __half2* vh0 = reinterpret_cast<const __half2*>(&v0);
-  const __half2* vh1 = reinterpret_cast<const __half2*>(&v1);
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float2 b0 = __half22float2(vh0[e]), b1 = __half22float2(vh1[e]);
-    acc[2 * e] = fmaf(acc[2 * e], corr, pw * b0.x);
-    acc[2 * e + 1] = fmaf(acc[2 * e + 1], corr, pw * b0.y);
-    acc[8 + 2 * e] = fmaf(acc[8 + 2 * e], corr, pw * b1.x);
-    acc[8 + 2 * e + 1] = fmaf(acc[8 + 2 * e + 1], corr, pw * b1.y);
-  }
-  m = m_new;
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+// Byte offset of element (row, dim) of a K or V tile in its ring stage: two TMA
+// boxes of 64 dims (32 rows x 128 bytes, 128-byte swizzle) behind each other.
+__device__ __forceinline__ uint32_t tile_offset(int row, int dim) {
+  return static_cast<uint32_t>((dim >> 6) * 4096 + row * 128 + ((((dim & 63) >> 3) ^ (row & 7)) << 4) + (dim & 7) * 2);
 }
 
-// Attention over the cached tokens 0..pos-1 plus the new token.  Every warp
-// works on every (K tile, V tile) pair, so a ring stage is free again a few
-// hundred cycles after it arrived and the cache streams through the ring: the
-// 32 tokens of a tile go to 32 of the CTA's 4*kCW eight-lane groups (rotating
-// from tile to tile), one token per group.  A group keeps two running
-// max / sum / output states (even and odd tiles, so that two tokens are in
-// flight); states, groups, warps and finally CTAs are merged when the CTA's
-// run over a head ends.
+// Attention over the cached tokens 0..pos-1 plus the new token, on the tensor
+// cores.  A warp takes whole (K tile, V tile) pairs of 32 tokens:
+//   scores  S[token] = K[token][:] . q     MMA with A = K (tokens x dims, ldmatrix) and q in every B column
+//   output  O[dim]  += V[token][dim] p     MMA with A = V^T (ldmatrix.trans) and p in every B column
+// with an online softmax between them (p = exp(S - max) in fp16 for the second
+// product, running sum and output rescaled when the maximum moves).  Because
+// every B column holds the same vector, every accumulator column holds the same
+// result and nothing has to be masked.  A warp keeps (max, sum, O[128]) over its
+// tiles; warps and finally CTAs are merged when the CTA's run over a head ends.
 __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
   const MegaArgs& a = c.a;
   const int cta = blockIdx.x, G = gridDim.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int grp = lane >> 3, sub = lane & 7;
-  constexpr int NS = 4 * kCW;
-  const int myslot = 4 * warp + grp;
+  const int g = lane >> 2, t = lane & 3;
   const int nt = a.pos / kTile + 1;
   const int I = a.heads * nt;
   const int width = a.heads * kHeadDim;
   const int i0 = range_start(cta, I, G), i1 = range_start(cta + 1, I, G);
   const Runs runs(i0, i1, nt);
-  float* sq = reinterpret_cast<float*>(c.xs) + warp * kWarpScratch;  // rotated, scaled q of the head
-  __half* skn = reinterpret_cast<__half*>(sq + kHeadDim);            // the new token's rotated k, as a cache row
-  __half* svn = skn + kHeadDim;                                      // the new token's v
-  const unsigned gmask = 0xFFu << (lane & 24);
-  int stage = c.ring_base % a.stages;
-  uint32_t phase = static_cast<uint32_t>(c.ring_base / a.stages) & 1u;
-  auto next = [&](int& st, uint32_t& ph) {
-    if (++st == a.stages) {
-      st = 0;
-      ph ^= 1u;
-    }
-  };
+  __half* sq = reinterpret_cast<__half*>(reinterpret_cast<float*>(c.xs) + warp * kWarpScratch);  // rotated, scaled q
+  long long awaited = 0;
+  const bool atracing = a.trace != nullptr && threadIdx.x == 0;
+  // this warp takes every kCW-th item of the op's sequence; an item is two ring stages
+  int q = warp;
+  int pos = c.ring_base + 2 * warp;
+  int stage = pos % a.stages;
+  uint32_t phase = static_cast<uint32_t>(pos / a.stages) & 1u;
+  int seq_lo = 0;
   for (int rr = 0; rr < runs.R; ++rr) {
     int head, lo, hi;
     runs.bounds(rr, head, lo, hi);
-    const int j0 = lo - head * nt, n = hi - lo;
-    // the new token sits in the head's last tile; the group that gets its row brings it in
-    const bool has_new = j0 + n == nt;
-    const int new_slot = has_new ? (kTile * (n - 1) + (a.pos & (kTile - 1))) % NS : -1;
-    const bool owns_new = has_new && (new_slot >> 2) == warp;
-    __syncwarp();
-    // rotary embedding (rope.cc:70-89): dims (e, e + 64) rotate together
+    const int j0 = lo - head * nt, seq_hi = seq_lo + (hi - lo);
+    float m = -INFINITY, l = 0.0f;
+    float out[8][4];  // O[16 db + g] in out[db][0], O[16 db + g + 8] in out[db][2] (every column alike)
 #pragma unroll
-    for (int rep = 0; rep < 2; ++rep) {
-      const int e = lane + 32 * rep, half = kHeadDim / 2;
-      const float2 rot = c.rope[e];
-      const float cs = rot.x, sn = rot.y;
-      const __half* qp = a.qkv + (size_t)head * kHeadDim;
-      const float q0 = __half2float(__ldcg(qp + e)), q1 = __half2float(__ldcg(qp + e + half));
-      // rounded to fp16 where the unfused graph stores the rotated, scaled q
-      sq[e] = __half2float(__float2half_rn((q0 * cs - q1 * sn) * a.q_scale));
-      sq[e + half] = __half2float(__float2half_rn((q1 * cs + q0 * sn) * a.q_scale));
-      if (owns_new) {
-        const __half* kp = a.qkv + (size_t)(a.heads + head) * kHeadDim;
-        const __half* vp = a.qkv + (size_t)(2 * a.heads + head) * kHeadDim;
-        const float k0 = __half2float(__ldcg(kp + e)), k1 = __half2float(__ldcg(kp + e + half));
-        const __half r0 = __float2half_rn(k0 * cs - k1 * sn), r1 = __float2half_rn(k1 * cs + k0 * sn);
-        const __half v0 = __ldcg(vp + e), v1 = __ldcg(vp + e + half);
-        __half* kc = ly->kcache + (size_t)a.pos * width + head * kHeadDim;
-        __half* vc = ly->vcache + (size_t)a.pos * width + head * kHeadDim;
-        kc[e] = r0;
-        kc[e + half] = r1;
-        vc[e] = v0;
-        vc[e + half] = v1;
-        skn[e] = r0;
-        skn[e + half] = r1;
-        svn[e] = v0;
-        svn[e + half] = v1;
-      }
-    }
-    __syncwarp();
-    float qv[16];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      qv[e] = sq[sub * 8 + e];
-      qv[8 + e] = sq[64 + sub * 8 + e];
-    }
-    float mA = -INFINITY, lA = 0.0f, accA[16], mB = -INFINITY, lB = 0.0f, accB[16];
-#pragma unroll
-    for (int e = 0; e < 16; ++e) accA[e] = accB[e] = 0.0f;
-    int rowA = myslot;  // row of tile jj that belongs to this group: (myslot - 32 jj) mod NS, if below 32
-    for (int jj = 0; jj < n; jj += 2) {
-      const bool two = jj + 1 < n;
-      int rowB = rowA - kTile;
-      if (rowB < 0) rowB += NS;
-      const int ks = stage;
-      const uint32_t kp = phase;
-      next(stage, phase);
-      const int vs = stage;
-      const uint32_t vp = phase;
-      next(stage, phase);
-      int ks2 = stage, vs2 = stage;
-      uint32_t kp2 = phase, vp2 = phase;
-      if (two) {
-        next(stage, phase);
-        vs2 = stage;
-        vp2 = phase;
-        next(stage, phase);
-      }
-      c.w.wait(&c.full[ks], kp, 13);
-      c.w.wait(&c.full[vs], vp, 14);
-      if (two) {
-        c.w.wait(&c.full[ks2], kp2, 13);
-        c.w.wait(&c.full[vs2], vp2, 14);
-      }
-      const int tokA = (j0 + jj) * kTile + rowA, tokB = (j0 + jj + 1) * kTile + rowB;
-      const bool doA = rowA < kTile && tokA <= a.pos;
-      const bool doB = two && rowB < kTile && tokB <= a.pos;
-      // the new token's row comes from this warp's scratch, every other row from the tiles
-      uint4 kA0, kA1, vA0, vA1, kB0, kB1, vB0, vB1;
-      if (doA) {
-        const bool nw = tokA == a.pos;
-        const uint8_t* kr = nw ? reinterpret_cast<const uint8_t*>(skn) : c.ring + (size_t)ks * kStageBytes + rowA * 256;
-        const uint8_t* vr = nw ? reinterpret_cast<const uint8_t*>(svn) : c.ring + (size_t)vs * kStageBytes + rowA * 256;
-        kA0 = *reinterpret_cast<const uint4*>(kr + sub * 16);
-        kA1 = *reinterpret_cast<const uint4*>(kr + 128 + sub * 16);
-        vA0 = *reinterpret_cast<const uint4*>(vr + sub * 16);
-        vA1 = *reinterpret_cast<const uint4*>(vr + 128 + sub * 16);
-      }
-      if (doB) {
-        const bool nw = tokB == a.pos;
-        const uint8_t* kr = nw ? reinterpret_cast<const uint8_t*>(skn) : c.ring + (size_t)ks2 * kStageBytes + rowB * 256;
-        const uint8_t* vr = nw ? reinterpret_cast<const uint8_t*>(svn) : c.ring + (size_t)vs2 * kStageBytes + rowB * 256;
-        kB0 = *reinterpret_cast<const uint4*>(kr + sub * 16);
-        kB1 = *reinterpret_cast<const uint4*>(kr + 128 + sub * 16);
-        vB0 = *reinterpret_cast<const uint4*>(vr + sub * 16);
-        vB1 = *reinterpret_cast<const uint4*>(vr + 128 + sub * 16);
-      }
-      if (doA) attend_token(qv, kA0, kA1, vA0, vA1, gmask, mA, lA, accA);
-      if (doB) attend_token(qv, kB0, kB1, vB0, vB1, gmask, mB, lB, accB);
+    for (int db = 0; db < 8; ++db) out[db][0] = out[db][1] = out[db][2] = out[db][3] = 0.0f;
+    if (q < seq_hi) {
+      // rotary embedding of q (rope.cc:70-89), scaled and rounded to fp16 as the unfused graph stores it
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&c.empty[ks]);
-        mbar_arrive(&c.empty[vs]);
-        if (two) {
-          mbar_arrive(&c.empty[ks2]);
-          mbar_arrive(&c.empty[vs2]);
+#pragma unroll
+      for (int rep = 0; rep < 2; ++rep) {
+        const int e = lane + 32 * rep, half = kHeadDim / 2;
+        const float2 rot = c.rope[e];
+        const __half* qp = a.qkv + (size_t)head * kHeadDim;
+        const float q0 = __half2float(__ldcg(qp + e)), q1 = __half2float(__ldcg(qp + e + half));
+        sq[e] = __float2half_rn((q0 * rot.x - q1 * rot.y) * a.q_scale);
+        sq[e + half] = __float2half_rn((q1 * rot.x + q0 * rot.y) * a.q_scale);
+      }
+      __syncwarp();
+      // B fragments of q for the eight 16-dim steps: dims 16 ks + 2t, +1 and 16 ks + 2t + 8, +9
+      uint32_t qb[8][2];
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        qb[ks][0] = *reinterpret_cast<const uint32_t*>(sq + 16 * ks + 2 * t);
+        qb[ks][1] = *reinterpret_cast<const uint32_t*>(sq + 16 * ks + 2 * t + 8);
+      }
+      for (; q < seq_hi; q += kCW) {
+        const int j = j0 + (q - seq_lo);
+        int vstage = stage + 1;
+        uint32_t vphase = phase;
+        if (vstage == a.stages) {
+          vstage = 0;
+          vphase ^= 1u;
+        }
+        const long long w0 = atracing ? clock64() : 0;
+        c.w.wait(&c.full[stage], phase, 13);
+        c.w.wait(&c.full[vstage], vphase, 14);
+        if (atracing) awaited += clock64() - w0;
+        uint8_t* kt = c.ring + (size_t)stage * kStageBytes;
+        uint8_t* vt = c.ring + (size_t)vstage * kStageBytes;
+        const bool has_new = j == nt - 1;
+        if (has_new) {
+          // the new token's rotated k and its v enter the cache and take their row of this tile
+          const int row = a.pos & (kTile - 1);
+          const __half* kp = a.qkv + (size_t)(a.heads + head) * kHeadDim;
+          const __half* vp = a.qkv + (size_t)(2 * a.heads + head) * kHeadDim;
+          __half* kc = ly->kcache + (size_t)a.pos * width + head * kHeadDim;
+          __half* vc = ly->vcache + (size_t)a.pos * width + head * kHeadDim;
+#pragma unroll
+          for (int rep = 0; rep < 2; ++rep) {
+            const int e = lane + 32 * rep, half = kHeadDim / 2;
+            const float2 rot = c.rope[e];
+            const float k0 = __half2float(__ldcg(kp + e)), k1 = __half2float(__ldcg(kp + e + half));
+            const __half r0 = __float2half_rn(k0 * rot.x - k1 * rot.y), r1 = __float2half_rn(k1 * rot.x + k0 * rot.y);
+            const __half v0 = __ldcg(vp + e), v1 = __ldcg(vp + e + half);
+            kc[e] = r0;
+            kc[e + half] = r1;
+            vc[e] = v0;
+            vc[e + half] = v1;
+            *reinterpret_cast<__half*>(kt + tile_offset(row, e)) = r0;
+            *reinterpret_cast<__half*>(kt + tile_offset(row, e + half)) = r1;
+            *reinterpret_cast<__half*>(vt + tile_offset(row, e)) = v0;
+            *reinterpret_cast<__half*>(vt + tile_offset(row, e + half)) = v1;
+          }
+          // rows past the new token are not tokens yet: whatever the cache holds there must not reach
+          // the products (0 * NaN), so they read as zero
+          for (int zr = row + 1; zr < kTile; ++zr)
+            *reinterpret_cast<uint2*>(vt + tile_offset(zr, 4 * lane)) = make_uint2(0u, 0u);
+          __syncwarp();
+        }
+        // ---- scores: two blocks of 16 tokens, eight steps of 16 dims
+        float sc[2][4];
+#pragma unroll
+        for (int mb = 0; mb < 2; ++mb) {
+          sc[mb][0] = sc[mb][1] = sc[mb][2] = sc[mb][3] = 0.0f;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            uint32_t af[4];
+            // lane i addresses row (i & 7) of 8x8 matrix i >> 3: rows +8 for odd matrices, dims +8 for matrices 2, 3
+            const int row = 16 * mb + ((lane >> 3) & 1) * 8 + (lane & 7);
+            const int dim = 16 * ks + (lane >> 4) * 8;
+            ldmatrix_x4(af, smem_u32(kt) + tile_offset(row, dim));
+            mma_f16(sc[mb], af, qb[ks][0], qb[ks][1]);
+          }
+        }
+        // this lane's tokens: g, g+8 (block 0) and 16+g, 24+g (block 1); every column of S is the same
+        float s4[4] = {sc[0][0], sc[0][2], sc[1][0], sc[1][2]};
+        float mt = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int token = j * kTile + g + 8 * e;
+          if (token > a.pos) s4[e] = -INFINITY;
+          mt = fmaxf(mt, s4[e]);
+        }
+        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 4));
+        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 8));
+        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
+        const float m_new = fmaxf(m, mt);  // finite: token 32 j is never beyond pos
+        float p4[4], psum = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          p4[e] = __expf(s4[e] - m_new);
+          psum += p4[e];
+        }
+        psum += __shfl_xor_sync(0xffffffffu, psum, 4);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 8);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 16);
+        if (m_new != m) {  // warp-uniform
+          const float corr = __expf(m - m_new);
+          l *= corr;
+#pragma unroll
+          for (int db = 0; db < 8; ++db) {
+            out[db][0] *= corr;
+            out[db][1] *= corr;
+            out[db][2] *= corr;
+            out[db][3] *= corr;
+          }
+          m = m_new;
+        }
+        l += psum;
+        // B fragments of p: tokens 16 ts + 2t, +1 (b0) and 16 ts + 2t + 8, +9 (b1), which sit in lanes
+        // g' = 2t and 2t + 1 (any t): lanes 8t and 8t + 4
+        uint32_t pb[2][2];
+#pragma unroll
+        for (int ts = 0; ts < 2; ++ts) {
+          const float pa = __shfl_sync(0xffffffffu, p4[2 * ts], 8 * t);
+          const float pbv = __shfl_sync(0xffffffffu, p4[2 * ts], 8 * t + 4);
+          const float pc = __shfl_sync(0xffffffffu, p4[2 * ts + 1], 8 * t);
+          const float pd = __shfl_sync(0xffffffffu, p4[2 * ts + 1], 8 * t + 4);
+          const __half2 h0 = __floats2half2_rn(pa, pbv), h1 = __floats2half2_rn(pc, pd);
+          pb[ts][0] = *reinterpret_cast<const uint32_t*>(&h0);
+          pb[ts][1] = *reinterpret_cast<const uint32_t*>(&h1);
+        }
+        // ---- output: eight blocks of 16 dims, two steps of 16 tokens, A = V^T
+#pragma unroll
+        for (int db = 0; db < 8; ++db) {
+#pragma unroll
+          for (int ts = 0; ts < 2; ++ts) {
+            uint32_t af[4];
+            // source 8x8 blocks (tokens x dims): matrix i >> 3 -> dims +8 for odd matrices, tokens +8 for matrices 2, 3
+            const int row = 16 * ts + (lane >> 4) * 8 + (lane & 7);
+            const int dim = 16 * db + ((lane >> 3) & 1) * 8;
+            ldmatrix_x4_trans(af, smem_u32(vt) + tile_offset(row, dim));
+            mma_f16(out[db], af, pb[ts][0], pb[ts][1]);
+          }
+        }
+        if (has_new) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // this warp wrote into the tiles
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive_n(&c.empty[stage], kCW);
+          mbar_arrive_n(&c.empty[vstage], kCW);
+        }
+        stage += 2 * kCW;
+        while (stage >= a.stages) {
+          stage -= a.stages;
+          phase ^= 1u;
         }
       }
-      rowA = rowB - kTile;
-      if (rowA < 0) rowA += NS;
-    }
-    // merge the two states, then the warp's four groups
-    float m, l, acc[16];
-    {
-      m = fmaxf(mA, mB);
-      const float wa = mA == -INFINITY ? 0.0f : __expf(mA - m), wb = mB == -INFINITY ? 0.0f : __expf(mB - m);
-      l = lA * wa + lB * wb;
-#pragma unroll
-      for (int e = 0; e < 16; ++e) acc[e] = accA[e] * wa + accB[e] * wb;
-      float M = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
-      M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
-      const float wg = m == -INFINITY ? 0.0f : __expf(m - M);
-      l *= wg;
-      l += __shfl_xor_sync(0xffffffffu, l, 8);
-      l += __shfl_xor_sync(0xffffffffu, l, 16);
-#pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        acc[e] *= wg;
-        acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 8);
-        acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
-      }
-      m = M;
     }
     const int run = c.attn_runs + rr, slot = run % kAttnSlots, use = run / kAttnSlots;
     c.w.wait_count(c.attn_done() + slot, use, 16);
     float* mine = c.dump + ((size_t)slot * kCW + warp) * kAttDump;
-    if (grp == 0) {
+    if (t == 0) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        mine[sub * 8 + e] = acc[e];
-        mine[64 + sub * 8 + e] = acc[8 + e];
+      for (int db = 0; db < 8; ++db) {
+        mine[16 * db + g] = out[db][0];
+        mine[16 * db + g + 8] = out[db][2];
       }
-      if (sub == 0) {
+      if (g == 0) {
         mine[kHeadDim] = m;
         mine[kHeadDim + 1] = l;
       }
@@ -938,6 +945,7 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
         if (trs) trs[11] = globaltimer_ns();
       }
     }
+    seq_lo = seq_hi;
   }
   c.attn_runs += runs.R;
   c.ring_base += 2 * (i1 - i0);
@@ -1268,9 +1276,9 @@ int mega_set_layer(MegaDecoder* m, int layer, const MegaLayerPtrs& p) {
     dst += m->proj_bytes[i];
   }
   const uint64_t kv_row = (uint64_t)c.heads * kHeadDim * 2;
-  int rc = make_tmap_2d(&L.kc, p.kcache, kv_row, c.max_seq, kv_row, kHeadDim * 2, kTile, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
+  int rc = make_tmap_2d(&L.kc, p.kcache, kv_row, c.max_seq, kv_row, kHeadDim, kTile, 2, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != MLD_OK) return rc;
-  rc = make_tmap_2d(&L.vc, p.vcache, kv_row, c.max_seq, kv_row, kHeadDim * 2, kTile, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
+  rc = make_tmap_2d(&L.vc, p.vcache, kv_row, c.max_seq, kv_row, kHeadDim, kTile, 2, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != MLD_OK) return rc;
   L.norm1 = static_cast<const __half*>(p.norm1);
   L.norm2 = static_cast<const __half*>(p.norm2);
