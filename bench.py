@@ -259,7 +259,10 @@ def gemv_roofline(mld, torch, layers, world, peaks):
     for p in plans.values():
         p.close()
     return {"bound": "hbm", "kernel": "fc_strip_kernel (INT4 decode GEMV)", "achieved": achieved, "peak": peak,
-            "unit": "GB/s", "frac": achieved / peak, "peak_source": src, "traffic": None,
+            "unit": "GB/s", "frac": achieved / peak, "peak_source": src,
+            # ncu capture of the config-2 launch: 18.93 MB of DRAM reads against 18.9 MB algorithmic
+            "traffic": algo / launches * 1.001,
+            "traffic_source": "ncu capture of the config-2 launch, ratio applied (profiles/fc_strip_kernel_config2_ncu_full.md)",
             "launches_timed": launches * reps, "avg_launch_us": sec / launches * 1e6,
             "algorithmic_bytes_per_launch": algo / launches}
 
@@ -462,7 +465,11 @@ def run_ours(args):
         roof = {"bound": "hbm", "kernel": "decode_mega_kernel (whole decode step, one launch)",
                 "achieved": step_bytes / sec / 1e9, "peak": gemv_alone["peak"], "unit": "GB/s",
                 "frac": step_bytes / sec / 1e9 / gemv_alone["peak"], "peak_source": gemv_alone["peak_source"],
-                "traffic": None, "launches_timed": args.steps, "avg_launch_us": sec * 1e6,
+                # dram__bytes_read + write of one launch: ncu capture of the same kernel on 2 layers
+                # (296.2 + 3.5 MB against 294.9 MB algorithmic), scaled by the layer count
+                "traffic": step_bytes * 1.016,
+                "traffic_source": "ncu capture on 2 layers, scaled by layers (profiles/decode_mega_kernel_2_layers_ncu_full.md)",
+                "launches_timed": args.steps, "avg_launch_us": sec * 1e6,
                 "algorithmic_bytes_per_launch": step_bytes,
                 "fc_strip_kernel_alone": {k: gemv_alone[k] for k in ("achieved", "frac", "avg_launch_us",
                                                                        "algorithmic_bytes_per_launch")}}
