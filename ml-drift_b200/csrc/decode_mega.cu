@@ -60,7 +60,6 @@ constexpr int kStageBytes = kBox + kScaleBox;
 constexpr int kHeadDim = 128;
 constexpr int kTile = 32;                    // cached tokens per attention item (K box, V box: 8 KB each)
 constexpr int kAttSlots = 4;                 // heads a CTA's attention range can touch
-constexpr float kOutScale = 16777216.0f;     // subnormal operands carry 2^-24
 constexpr int kProjSlots = 4;                // column runs whose per-warp sums can be pending at once
 constexpr int kAttnSlots = 2;                // head runs likewise
 constexpr int kAttDump = kHeadDim + 4;       // 128 outputs, then max and sum (padded: rows stay 16-byte aligned)
@@ -306,7 +305,8 @@ struct Ctx {
   uint64_t* full;
   uint64_t* empty;
   __half* xs;          // input vector of the running projection / per-warp attention scratch
-  float* us;           // 8 * 2^-24 * (sum of each 32 inputs of xs): the nibble offset's share of a block
+  int* isum;           // [box][t][set]: 8 * (sum of the integers of unit 4 set + t of the box), see digitise_x
+  float sx;            // scale of the digitised input vector
   const float2* rope;  // [64] (cos, sin) of pos / timescale_i, the rotary embedding of this step
   float* dump;         // per-warp sums of pending runs: [slot][warp][kStripN] or [slot][warp][kAttDump]
   int* s_int;          // [0] failure flag, [1..] run bookkeeping (see below)
@@ -356,155 +356,307 @@ __device__ void grid_barrier(Ctx& c) {
   consumer_bar();
 }
 
-// us[u] = 8 * 2^-24 * sum(xs[32u .. 32u+31]); entries past the vector are zero.
-__device__ void unit_sums(Ctx& c, int d) {
-  for (int u = threadIdx.x; u < c.a.us_floats; u += kCW * 32) {
-    float s = 0.0f;
-    if (u * 32 < d) {
+// Eight inputs (chunk ci = inputs 8 ci .. 8 ci + 7, fp16 in v) become digits in place; the four lanes
+// of a unit (consecutive chunks, one warp) also add up the unit's integers.  All lanes of the warp call.
+__device__ __forceinline__ void digitise_chunk(Ctx& c, int ci, const uint4& v, float inv) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+  // z = round(x / sx) + 128 in the low 16 bits of the float's mantissa: high byte = hi digit, low byte ^ 0x80 = lo digit
+  uint32_t z[8];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint4 v = *reinterpret_cast<const uint4*>(c.xs + u * 32 + q * 8);
-        const __half2* h = reinterpret_cast<const __half2*>(&v);
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(h[j]);
+    z[2 * j] = __float_as_uint(fmaf(f.x, inv, 12583040.0f));
+    z[2 * j + 1] = __float_as_uint(fmaf(f.y, inv, 12583040.0f));
+  }
+  uint32_t hiw[2], low[2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __half22float2(h[j]);
-          s += f.x;
-          s += f.y;
-        }
-      }
-    }
-    c.us[u] = s * (8.0f / kOutScale);
+  for (int e = 0; e < 2; ++e) {
+    const uint32_t h01 = __byte_perm(z[4 * e], z[4 * e + 1], 0x0051), h23 = __byte_perm(z[4 * e + 2], z[4 * e + 3], 0x0051);
+    const uint32_t l01 = __byte_perm(z[4 * e], z[4 * e + 1], 0x0040), l23 = __byte_perm(z[4 * e + 2], z[4 * e + 3], 0x0040);
+    hiw[e] = __byte_perm(h01, h23, 0x5410);
+    low[e] = __byte_perm(l01, l23, 0x5410) ^ 0x80808080u;
+  }
+  int sum = __dp4a(static_cast<int>(hiw[0]), 0x01010101, 0);
+  sum = __dp4a(static_cast<int>(hiw[1]), 0x01010101, sum) * 256;
+  sum = __dp4a(static_cast<int>(low[0]), 0x01010101, sum);
+  sum = __dp4a(static_cast<int>(low[1]), 0x01010101, sum);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+  // chunk q of the unit holds inputs 8q..8q+7: half q >> 1, lanes t = 2 (q & 1) and 2 (q & 1) + 1
+  const int unit = ci >> 2, q = ci & 3;
+  uint32_t* ub = reinterpret_cast<uint32_t*>(c.xs + unit * 32);
+  const int w0 = 2 * (2 * (q & 1)) + (q >> 1);  // word index of (t, half): 2 t + half
+  ub[w0] = hiw[0];
+  ub[w0 + 2] = hiw[1];
+  ub[8 + w0] = low[0];
+  ub[8 + w0 + 2] = low[1];
+  if (q == 0) {
+    const int m = unit & 31;
+    c.isum[(unit >> 5) * 32 + (m & 3) * 8 + (m >> 2)] = 8 * sum;
   }
 }
 
-// The vector is padded with zeros to whole boxes (a ragged last box multiplies zeros).
-__device__ __forceinline__ void zero_pad_x(Ctx& c, int d) {
-  const int padded = (d + kBoxK - 1) / kBoxK * kBoxK;
-  for (int i = d + threadIdx.x * 8; i < padded; i += kCW * 32 * 8)
-    *reinterpret_cast<uint4*>(c.xs + i) = make_uint4(0u, 0u, 0u, 0u);
-}
-// xs = fp16(v * rsqrt(mean(v^2) + eps) * gamma)   (reference RMSNorm, fp32 statistics)
-__device__ void load_x_norm(Ctx& c, const __half* x, const __half* gamma, int d) {
-  float ss = 0.0f;
-  for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8) {
-    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(x + i));
-    *reinterpret_cast<uint4*>(c.xs + i) = v;
+// Turns the fp16 vector in xs into what the integer MMAs read, in place.  The
+// vector becomes 16-bit fixed point with one scale for the whole vector,
+// x ~ sx * (256 hi + lo) with hi, lo in [-128, 127] (sx = max|x| / 32512: the
+// error is at most 1.6e-5 of the largest element, far below the fp16 rounding
+// of the outputs), and every unit of 32 inputs (64 bytes either way) is
+// rewritten as [hi: 32 bytes][lo: 32 bytes], each in the order the B fragments
+// take them (8 bytes per lane t: inputs 4t..4t+3 and 16+4t..16+4t+3).
+// isum[box][t][set] = 8 * sum of the unit's integers: the nibble offset's share.
+__device__ void digitise_x(Ctx& c, int d) {
+  const int chunks = (d + kBoxK - 1) / kBoxK * kBoxK / 8;  // 8 inputs (16 bytes) per thread and round
+  float amax = 0.0f;
+  for (int ci = threadIdx.x; ci < chunks; ci += kCW * 32) {
+    const uint4 v = *reinterpret_cast<const uint4*>(c.xs + ci * 8);
     const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float2 f = __half22float2(h[j]);
-      ss += f.x * f.x + f.y * f.y;
+      const float2 f = __half22float2(__habs2(h[j]));
+      amax = fmaxf(amax, fmaxf(f.x, f.y));
     }
   }
-  zero_pad_x(c, d);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  float* part = c.dump;  // free between ops
-  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  float* part = c.dump + 32;  // free between ops (the first entries serve the RMSNorm sum)
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = amax;
   consumer_bar();
-  float tot = 0.0f;
+  amax = 0.0f;
 #pragma unroll
-  for (int wi = 0; wi < kCW; ++wi) tot += part[wi];
-  const float inv = rsqrtf(tot / static_cast<float>(d) + c.a.rms_eps);
-  for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8) {
-    uint4 v = *reinterpret_cast<uint4*>(c.xs + i);
-    const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gamma + i));
-    __half2* h = reinterpret_cast<__half2*>(&v);
-    const __half2* gh = reinterpret_cast<const __half2*>(&gv);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __half22float2(h[j]);
-      const float2 g = __half22float2(gh[j]);
-      h[j] = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
-    }
-    *reinterpret_cast<uint4*>(c.xs + i) = v;
+  for (int wi = 0; wi < kCW; ++wi) amax = fmaxf(amax, part[wi]);
+  const float sx = amax > 0.0f ? amax / 32512.0f : 1.0f;
+  const float inv = 1.0f / sx;
+  c.sx = sx;
+  for (int ci = threadIdx.x; ci < chunks; ci += kCW * 32) {
+    const uint4 v = *reinterpret_cast<const uint4*>(c.xs + ci * 8);
+    __syncwarp();  // rounds are warp-uniform (whole boxes): the unit's four lanes have read before any rewrites
+    digitise_chunk(c, ci, v, inv);
   }
-  consumer_bar();
-  unit_sums(c, d);
-  consumer_bar();
 }
-__device__ void load_x_plain(Ctx& c, const __half* x, int d) {
-  for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8)
-    *reinterpret_cast<uint4*>(c.xs + i) = __ldcg(reinterpret_cast<const uint4*>(x + i));
-  zero_pad_x(c, d);
+
+constexpr int kRegChunks = 4;  // chunks of 8 inputs a thread can hold: vectors up to 4 * 8 * 32 * kCW inputs
+
+// Block-wide reduction of one float per thread over the consumer warps (slot: 0 sum, 1 max).
+__device__ __forceinline__ float consumer_reduce(Ctx& c, float v, int slot) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float w = __shfl_xor_sync(0xffffffffu, v, o);
+    v = slot == 0 ? v + w : fmaxf(v, w);
+  }
+  float* part = c.dump + 32 * slot;  // free between ops
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
   consumer_bar();
-  unit_sums(c, d);
+  float r = slot == 0 ? 0.0f : 0.0f;
+#pragma unroll
+  for (int wi = 0; wi < kCW; ++wi) r = slot == 0 ? r + part[wi] : fmaxf(r, part[wi]);
+  return r;
+}
+
+// Sum of `a` and maximum of `b` over the consumer warps with one barrier.
+__device__ __forceinline__ void consumer_reduce2(Ctx& c, float& a, float& b) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, o));
+  }
+  float* part = c.dump + 64;  // free between ops
+  if ((threadIdx.x & 31) == 0) {
+    part[threadIdx.x >> 5] = a;
+    part[32 + (threadIdx.x >> 5)] = b;
+  }
+  consumer_bar();
+  a = 0.0f;
+  b = 0.0f;
+#pragma unroll
+  for (int wi = 0; wi < kCW; ++wi) {
+    a += part[wi];
+    b = fmaxf(b, part[32 + wi]);
+  }
+}
+
+// Loads the d-element input vector of a projection and leaves it digitised in xs (digitise_x).
+// NORM: the reference RMSNorm first, xs = fp16(v * rsqrt(mean(v^2) + eps) * gamma), fp32 statistics.
+// Vectors of up to kRegChunks chunks per thread stay in registers between the passes.
+template <bool NORM>
+__device__ void load_x(Ctx& c, const __half* x, const __half* gamma, int d) {
+  const int padded = (d + kBoxK - 1) / kBoxK * kBoxK;
+  const int chunks = padded / 8;
+  if (chunks > kRegChunks * kCW * 32) {
+    // general path through shared memory
+    float ss = 0.0f;
+    for (int i = threadIdx.x * 8; i < padded; i += kCW * 32 * 8) {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (i < d) v = __ldcg(reinterpret_cast<const uint4*>(x + i));
+      *reinterpret_cast<uint4*>(c.xs + i) = v;
+      const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+    if (NORM) {
+      const float inv = rsqrtf(consumer_reduce(c, ss, 0) / static_cast<float>(d) + c.a.rms_eps);
+      for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8) {
+        uint4 v = *reinterpret_cast<uint4*>(c.xs + i);
+        const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gamma + i));
+        __half2* h = reinterpret_cast<__half2*>(&v);
+        const __half2* gh = reinterpret_cast<const __half2*>(&gv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h[j]);
+          const float2 g = __half22float2(gh[j]);
+          h[j] = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
+        }
+        *reinterpret_cast<uint4*>(c.xs + i) = v;
+      }
+    }
+    consumer_bar();
+    digitise_x(c, d);
+    consumer_bar();
+    return;
+  }
+  uint4 v[kRegChunks];
+  float amax = 0.0f;
+  if (NORM) {
+    // one pass: sum of squares for the statistics and max |v * gamma| for the digit scale; the largest
+    // normalised element is that maximum times the inverse RMS (up to fp16 rounding, for which the digit
+    // range keeps head-room)
+    uint4 gv[kRegChunks];
+    float ss = 0.0f, gmax = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kRegChunks; ++r) {
+      const int ci = threadIdx.x + r * kCW * 32;
+      v[r] = make_uint4(0u, 0u, 0u, 0u);
+      gv[r] = make_uint4(0u, 0u, 0u, 0u);
+      if (ci * 8 < d) {
+        v[r] = __ldcg(reinterpret_cast<const uint4*>(x + ci * 8));
+        gv[r] = __ldg(reinterpret_cast<const uint4*>(gamma + ci * 8));
+      }
+      const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+      const __half2* gh = reinterpret_cast<const __half2*>(&gv[r]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        const float2 g = __half22float2(gh[j]);
+        ss += f.x * f.x + f.y * f.y;
+        gmax = fmaxf(gmax, fmaxf(fabsf(f.x * g.x), fabsf(f.y * g.y)));
+      }
+    }
+    consumer_reduce2(c, ss, gmax);
+    const float inv = rsqrtf(ss / static_cast<float>(d) + c.a.rms_eps);
+    amax = gmax * inv * 1.001f;
+#pragma unroll
+    for (int r = 0; r < kRegChunks; ++r) {
+      __half2* h = reinterpret_cast<__half2*>(&v[r]);
+      const __half2* gh = reinterpret_cast<const __half2*>(&gv[r]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        const float2 g = __half22float2(gh[j]);
+        h[j] = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < kRegChunks; ++r) {
+      const int ci = threadIdx.x + r * kCW * 32;
+      v[r] = make_uint4(0u, 0u, 0u, 0u);
+      if (ci * 8 < d) v[r] = __ldcg(reinterpret_cast<const uint4*>(x + ci * 8));
+      const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(__habs2(h[j]));
+        amax = fmaxf(amax, fmaxf(f.x, f.y));
+      }
+    }
+    amax = consumer_reduce(c, amax, 1);
+  }
+  const float sx = amax > 0.0f ? amax / 32512.0f : 1.0f;
+  const float inv_sx = 1.0f / sx;
+  c.sx = sx;
+#pragma unroll
+  for (int r = 0; r < kRegChunks; ++r) {
+    const int ci = threadIdx.x + r * kCW * 32;
+    if (ci < chunks) digitise_chunk(c, ci, v[r], inv_sx);  // warp-uniform: chunks is a multiple of 32
+  }
   consumer_bar();
 }
 
-// One box (16 outputs x 1024 inputs) by one warp.  Lane = 4g + t.  The box's 64
-// MMAs go by unit (32 inputs, one scale per output): MMA 2u + m covers inputs
-// 32u + 8t' + 4m + {0..3} in its k slots (2t', 2t'+1, 2t'+8, 2t'+9).  Its A
-// fragment is one 32-bit word of the re-tiled weights per lane, whose eight
-// nibbles become fp16 subnormals by masking (rows g+8 sit in the high nibbles
-// and carry x16); its B fragment has the inputs in column u % 8 only, which
-// lane g == u % 8 supplies, so accumulator column j of unit set s collects unit
-// 8s + j.  A lane ends with rows (g, g+8) x units (8s + 2t, 8s + 2t + 1) and
-// applies the scales and the nibble offset once per box.
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// One box (16 outputs x 1024 inputs) by one warp.  Lane = 4g + t.  A unit of 32
+// inputs (one scale per output) is exactly one integer MMA m16n8k32: A = the
+// unit's nibbles as bytes (a 32-bit word of the re-tiled weights holds four
+// inputs of row g in its low nibbles and of row g+8 in its high nibbles), B =
+// the digitised inputs, exact in int32.  The 32 units of a box go in eight sets
+// of four; B column 2j holds the high digit and 2j + 1 the low digit of unit j
+// of the set (lane g supplies column g, zero for the other units), so a lane
+// ends a set with both digits of unit t for rows g and g+8, combines them,
+// takes off the nibble offset and applies the unit's scale.
 __device__ __forceinline__ void consume_box(const Ctx& c, const uint8_t* st, int kb, float (&tot)[2]) {
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  // inputs of units g, g+8, g+16, g+24 (this lane's column), eight per unit: both MMAs' k slots of row t
-  uint4 xb[4];
+  // this lane's digit bytes for the eight sets: unit 4 set + (g >> 1), digit g & 1, inputs 4t.. and 16+4t..
+  const uint2* xd = reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(c.xs) + (size_t)kb * 2 * kBoxK) + lane;
+  uint2 xb[8];
 #pragma unroll
-  for (int sidx = 0; sidx < 4; ++sidx)
-    xb[sidx] = *reinterpret_cast<const uint4*>(c.xs + (size_t)kb * kBoxK + (g + 8 * sidx) * 32 + 8 * t);
-  const uint4* wl = reinterpret_cast<const uint4*>(st) + lane;  // load j of the box: wl[32 j]
-  float dsum[4][4];
+  for (int sidx = 0; sidx < 8; ++sidx) xb[sidx] = xd[32 * sidx];
+  const uint4* wl = reinterpret_cast<const uint4*>(st) + lane;  // load j of the box: wl[32 j], units 2j and 2j + 1
+  int acc[8][4];
+#pragma unroll
+  for (int sidx = 0; sidx < 8; ++sidx) acc[sidx][0] = acc[sidx][1] = acc[sidx][2] = acc[sidx][3] = 0;
   uint4 wbuf[2][4];
 #pragma unroll
   for (int jj = 0; jj < 4; ++jj) wbuf[0][jj] = wl[32 * jj];
 #pragma unroll
-  for (int bt = 0; bt < 4; ++bt) {  // batch bt = unit set bt (units 8 bt .. 8 bt + 7), 16 MMAs
+  for (int bt = 0; bt < 4; ++bt) {  // four loads = eight units = two sets per batch, fetched a batch ahead
     if (bt + 1 < 4) {
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) wbuf[(bt + 1) & 1][jj] = wl[32 * (4 * (bt + 1) + jj)];
     }
-    float acc[4][4];  // four independent chains (word i of each load)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
       const uint4 wv = wbuf[bt & 1][jj];
-      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+      const int sidx = 2 * bt + (jj >> 1);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        // MMA 16 bt + 4 jj + i: unit 8 bt + 2 jj + (i >> 1), half m = i & 1
-        const bool mine = g == 2 * jj + (i >> 1);
-        const uint32_t x0 = (i & 1) ? xb[bt].z : xb[bt].x, x1 = (i & 1) ? xb[bt].w : xb[bt].y;
-        const uint32_t b0 = mine ? x0 : 0u, b1 = mine ? x1 : 0u;
-        const uint32_t w8 = ww[i] >> 8;
-        const uint32_t af[4] = {ww[i] & 0x000F000Fu, ww[i] & 0x00F000F0u, w8 & 0x000F000Fu, w8 & 0x00F000F0u};
-        mma_f16(acc[i], af, b0, b1);
+      for (int h = 0; h < 2; ++h) {
+        const int us = 2 * (jj & 1) + h;  // unit within the set
+        const uint32_t w0 = h ? wv.z : wv.x, w1 = h ? wv.w : wv.y;
+        const uint32_t af[4] = {w0 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu};
+        const bool mine = (g >> 1) == us;
+        mma_u8s8(acc[sidx], af, mine ? xb[sidx].x : 0u, mine ? xb[sidx].y : 0u);
       }
     }
-#pragma unroll
-    for (int r = 0; r < 4; ++r) dsum[bt][r] = (acc[0][r] + acc[1][r]) + (acc[2][r] + acc[3][r]);
   }
-  // scales of (rows g, g+8) x (units 8s + 2t, 8s + 2t + 1), s = 0..3: 16 halves per lane, in that order
+  // unit 4 set + t: scales of rows g and g+8 (16 halves per lane: [set][row]) and the offset term
   const uint4 sc0 = *reinterpret_cast<const uint4*>(st + kBox + lane * 32);
   const uint4 sc1 = *reinterpret_cast<const uint4*>(st + kBox + lane * 32 + 16);
+  const int4 of0 = *reinterpret_cast<const int4*>(c.isum + kb * 32 + t * 8);
+  const int4 of1 = *reinterpret_cast<const int4*>(c.isum + kb * 32 + t * 8 + 4);
   const __half2* sh0 = reinterpret_cast<const __half2*>(&sc0);
   const __half2* sh1 = reinterpret_cast<const __half2*>(&sc1);
+  const int offs[8] = {of0.x, of0.y, of0.z, of0.w, of1.x, of1.y, of1.z, of1.w};
 #pragma unroll
-  for (int sidx = 0; sidx < 4; ++sidx) {
-    const float2 off = *reinterpret_cast<const float2*>(c.us + kb * 32 + 8 * sidx + 2 * t);
-    const __half2* sh = sidx < 2 ? sh0 + 2 * sidx : sh1 + 2 * (sidx - 2);
-    const float2 se = __half22float2(sh[0]);  // unit 8s+2t:   row g, row g+8
-    const float2 so = __half22float2(sh[1]);  // unit 8s+2t+1: row g, row g+8
-    // dsum[s]: {row g, col 2t}, {row g, col 2t+1}, {row g+8, col 2t}, {row g+8, col 2t+1}
-    tot[0] = fmaf(se.x, dsum[sidx][0] - off.x, tot[0]);
-    tot[0] = fmaf(so.x, dsum[sidx][1] - off.y, tot[0]);
-    tot[1] = fmaf(se.y, fmaf(dsum[sidx][2], 0.0625f, -off.x), tot[1]);
-    tot[1] = fmaf(so.y, fmaf(dsum[sidx][3], 0.0625f, -off.y), tot[1]);
+  for (int sidx = 0; sidx < 8; ++sidx) {
+    const float2 sc = __half22float2(sidx < 4 ? sh0[sidx] : sh1[sidx - 4]);
+    // acc: {row g, high digit}, {row g, low digit}, {row g+8, high digit}, {row g+8, low digit}
+    const int r0 = acc[sidx][0] * 256 + acc[sidx][1] - offs[sidx];
+    const int r1 = acc[sidx][2] * 256 + acc[sidx][3] - offs[sidx];
+    tot[0] = fmaf(sc.x, static_cast<float>(r0), tot[0]);
+    tot[1] = fmaf(sc.y, static_cast<float>(r1), tot[1]);
   }
 }
 
 // Lanes 0..15 of one warp: output strip * 16 + lane, summed over all of K, gets its
 // epilogue and is written.
-__device__ __forceinline__ void finish_strip(int kind, int strip, float v, const __half* resid, __half* out) {
+__device__ __forceinline__ void finish_strip(int kind, int strip, float v, float sx, const __half* resid, __half* out) {
   const int lane = threadIdx.x & 31;
   const int n = strip * kStripN + lane;
-  const __half r = __float2half_rn(v * kOutScale);
+  const __half r = __float2half_rn(v * sx);
   if (kind == kGu) {
     // rows interleave gate_i, up_i: even lanes hold the gate, the next lane its up value
     const float gf = __half2float(r);
@@ -562,7 +714,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
       // the strip is this warp's alone: rows g and g+8 sit in lanes t == 0
       const float lo = __shfl_sync(0xffffffffu, tot[0], (lane & 7) * 4);
       const float hi = __shfl_sync(0xffffffffu, tot[1], (lane & 7) * 4);
-      finish_strip(kind, strip, (lane & 8) ? hi : lo, resid, out);
+      finish_strip(kind, strip, (lane & 8) ? hi : lo, c.sx, resid, out);
       continue;
     }
     c.w.wait_count(c.proj_done() + slot, use, 15);  // the slot's previous strip has been summed
@@ -590,7 +742,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
         __threadfence_block();
         c.proj_done()[slot] = use + 1;
       }
-      finish_strip(kind, strip, v, resid, out);
+      finish_strip(kind, strip, v, c.sx, resid, out);
     }
   }
   if (p.S > 1) c.proj_runs += n_runs;  // single-box strips never use a slot
@@ -987,7 +1139,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
   if (warp == kCW) {
     if (lane == 0) producer_loop(a, ring, full, empty, w);
   } else {
-    Ctx c{a, ring, full, empty, xs, us, rope, dump, s_int, w, 0, 0, 0, 0ull, 0};
+    Ctx c{a, ring, full, empty, xs, reinterpret_cast<int*>(us), 1.0f, rope, dump, s_int, w, 0, 0, 0, 0ull, 0};
     if (threadIdx.x == 0) {
       // read before this CTA's first arrival, the count is in [base, base + grid): no barrier of this
       // launch can complete without this CTA
@@ -1002,7 +1154,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
       __half* x_next = l + 1 == a.n_layers ? a.x_out : ((l & 1) ? a.xb : a.xa);
       c.op_index = l * kOpsPerLayer;
       trace_mark(c, 0);
-      load_x_norm(c, x_cur, ly->norm1, d);
+      load_x<true>(c, x_cur, ly->norm1, d);
       trace_mark(c, 1);
       run_projection(c, kQkv, nullptr, a.qkv);
       trace_mark(c, 2);
@@ -1018,7 +1170,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
 
       c.op_index += 1;
       trace_mark(c, 0);
-      load_x_plain(c, a.attn, d);
+      load_x<false>(c, a.attn, nullptr, d);
       trace_mark(c, 1);
       run_projection(c, kO, x_cur, a.h);
       trace_mark(c, 2);
@@ -1027,7 +1179,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
 
       c.op_index += 1;
       trace_mark(c, 0);
-      load_x_norm(c, a.h, ly->norm2, d);
+      load_x<true>(c, a.h, ly->norm2, d);
       trace_mark(c, 1);
       run_projection(c, kGu, nullptr, a.act);
       trace_mark(c, 2);
@@ -1036,7 +1188,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
 
       c.op_index += 1;
       trace_mark(c, 0);
-      load_x_plain(c, a.act, a.ffn);
+      load_x<false>(c, a.act, nullptr, a.ffn);
       trace_mark(c, 1);
       run_projection(c, kDown, a.h, x_next);
       trace_mark(c, 2);
@@ -1071,16 +1223,15 @@ __global__ void __launch_bounds__(256) retile_weights_kernel(const uint8_t* __re
     const int strip = static_cast<int>(box / S), kb = static_cast<int>(box - (int64_t)strip * S);
     uint32_t word = 0;
     if (wi < kBox / 4) {
-      // weights: word = [load j][lane][i]; MMA 4j + i = unit u, half m
-      const int j = wi >> 7, lane = (wi >> 2) & 31, i = wi & 3;
+      // weights: word = [load j][lane][q]; unit 2j + (q >> 1) of the box, inputs 16 (q & 1) + 4t + {0..3} of the
+      // unit: byte b = input b, low nibble row g, high nibble row g + 8
+      const int j = wi >> 7, lane = (wi >> 2) & 31, q = wi & 3;
       const int g = lane >> 2, t = lane & 3;
-      const int mi = 4 * j + i, u = mi >> 1, m = mi & 1;
+      const int unit = 2 * j + (q >> 1);
 #pragma unroll
       for (int nib = 0; nib < 8; ++nib) {
-        // nibble -> (row, k slot): 0:(g,0) 1:(g+8,0) 2:(g,2) 3:(g+8,2) 4:(g,1) 5:(g+8,1) 6:(g,3) 7:(g+8,3)
         const int row = (nib & 1) ? g + 8 : g;
-        const int slot = ((nib >> 2) & 1) | (((nib >> 1) & 1) << 1);
-        const int k = kb * kBoxK + u * 32 + 8 * t + 4 * m + slot;
+        const int k = kb * kBoxK + unit * 32 + (q & 1) * 16 + 4 * t + (nib >> 1);
         const int n = strip * kStripN + row;
         uint32_t v = 0;
         if (k < K) {
@@ -1092,7 +1243,7 @@ __global__ void __launch_bounds__(256) retile_weights_kernel(const uint8_t* __re
         word |= v << (4 * nib);
       }
     } else {
-      // scales: [lane][s][unit parity e][row g / g+8] halves, two per word
+      // scales: [lane][set][row g / g+8] halves (unit 4 set + t), two per word
       const int hi = (wi - kBox / 4) * 2;  // first half index of this word
       uint32_t pair = 0;
 #pragma unroll
@@ -1100,10 +1251,9 @@ __global__ void __launch_bounds__(256) retile_weights_kernel(const uint8_t* __re
         const int h = hi + q;
         const int lane = h >> 4, r = h & 15;
         const int g = lane >> 2, t = lane & 3;
-        const int sidx = r >> 2, e = (r >> 1) & 1, rsel = r & 1;
-        const int u = 8 * sidx + 2 * t + e;
+        const int u = 4 * (r >> 1) + t;
         const int k = kb * kBoxK + u * 32;
-        const int n = strip * kStripN + (rsel ? g + 8 : g);
+        const int n = strip * kStripN + ((r & 1) ? g + 8 : g);
         uint16_t bits = 0;
         if (k < K) bits = __half_as_ushort(sc[(size_t)(k / block) * N + n]);
         pair |= static_cast<uint32_t>(bits) << (16 * q);
