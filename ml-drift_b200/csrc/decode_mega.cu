@@ -91,6 +91,7 @@ struct MegaArgs {
   __half *qkv, *attn, *h, *act, *xa, *xb;
   float* att_part;     // [grid][kAttSlots][kAttDump]
   int* att_tickets;    // [heads]
+  unsigned* att_flags; // [heads][grid / heads]: epoch of the attention whose partial the part has published
   unsigned* bar;       // 64-bit arrival counter of the grid barrier (8-byte aligned)
   int* error;
   unsigned long long* trace;  // optional [grid][ops][kTraceSlots]
@@ -201,6 +202,43 @@ struct Runs {
   }
 };
 
+// A CTA's attention items.  With at least as many CTAs as heads, P = grid / heads CTAs share a head
+// (CTA c: head c / P, tiles [part nt / P, (part + 1) nt / P)) and every CTA has one run; otherwise the
+// items (head-major) are split evenly and a CTA may touch several heads.
+struct AttnSplit {
+  int nt, I, G, heads, P;
+  __device__ __forceinline__ AttnSplit(int heads_, int nt_, int G_) : nt(nt_), I(heads_ * nt_), G(G_), heads(heads_) {
+    P = G >= heads ? G / heads : 0;
+  }
+  __device__ __forceinline__ void range(int cta, int& i0, int& i1) const {
+    if (P > 0) {
+      const int head = cta / P, part = cta - head * P;
+      if (head >= heads) {
+        i0 = i1 = 0;
+        return;
+      }
+      // nt / P tiles each, the remainder one by one to the first parts (the last non-empty part also
+      // brings in the new token and merges the head)
+      const int base = nt / P, rem = nt - base * P;
+      i0 = head * nt + part * base + (part < rem ? part : rem);
+      i1 = i0 + base + (part < rem ? 1 : 0);
+    } else {
+      i0 = range_start(cta, I, G);
+      i1 = range_start(cta + 1, I, G);
+    }
+  }
+  // CTAs that may hold items of `head`: first..last (P > 0: exactly the non-empty parts)
+  __device__ __forceinline__ void contributors(int head, int& first, int& last) const {
+    if (P > 0) {
+      first = head * P;
+      last = first + (nt < P ? nt : P) - 1;
+    } else {
+      first = owner_of(head * nt, I, G);
+      last = owner_of(head * nt + nt - 1, I, G);
+    }
+  }
+};
+
 // ------------------------------------------------------------------ producer
 struct Ring {
   int stage;
@@ -220,8 +258,9 @@ __device__ void prefetch_op_l2(const MegaArgs& a, int l, int kind) {
   const MegaLayer* ly = a.layers + l;
   if (kind == kAttn) {
     const int nt = a.pos / kTile + 1;
-    const int I = a.heads * nt;
-    const int i0 = range_start(cta, I, G), i1 = range_start(cta + 1, I, G);
+    const AttnSplit split(a.heads, nt, G);
+    int i0, i1;
+    split.range(cta, i0, i1);
     for (int i = i0; i < i1; ++i) {
       const int head = i / nt, j = i - head * nt;
       asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
@@ -262,8 +301,10 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
         if (o < a.n_layers * kOpsPerLayer) prefetch_op_l2(a, o / kOpsPerLayer, o % kOpsPerLayer);
       }
       if (kind == kAttn) {
-        const int I = a.heads * nt;
-        const Runs runs(range_start(cta, I, G), range_start(cta + 1, I, G), nt);
+        const AttnSplit split(a.heads, nt, G);
+        int ai0, ai1;
+        split.range(cta, ai0, ai1);
+        const Runs runs(ai0, ai1, nt);
         for (int rr = 0; rr < runs.R; ++rr) {
           int head, lo, hi;
           runs.bounds(rr, head, lo, hi);
@@ -314,14 +355,15 @@ struct Ctx {
   int ring_base;       // stages of this CTA consumed by earlier ops (same in every warp)
   int proj_runs;       // column runs started so far (selects the dump slot)
   int attn_runs;       // head runs started so far
-  unsigned long long bar_target;  // arrival count that completes the barrier this CTA waits for next (thread 0)
+  unsigned long long bar_target;  // arrival count that completes the barrier this CTA waits for next
+  unsigned epoch_base;            // barriers completed by earlier launches: op k of this launch has epoch_base + k + 1
   int op_index;
   __device__ __forceinline__ int* proj_arrived() const { return s_int + 1; }                     // [kProjSlots]
   __device__ __forceinline__ volatile int* proj_done() const { return s_int + 1 + kProjSlots; }  // [kProjSlots]
   __device__ __forceinline__ int* attn_arrived() const { return s_int + 1 + 2 * kProjSlots; }    // [kAttnSlots]
   __device__ __forceinline__ volatile int* attn_done() const { return s_int + 1 + 2 * kProjSlots + kAttnSlots; }
 };
-constexpr int kSharedInts = 1 + 2 * kProjSlots + 2 * kAttnSlots;
+constexpr int kSharedInts = 1 + 2 * kProjSlots + 2 * kAttnSlots;  // (odd) + 3 behind them: pad, 64-bit barrier base
 
 __device__ __forceinline__ void trace_mark(const Ctx& c, int k) {
   if (c.a.trace != nullptr && threadIdx.x == 0)
@@ -338,13 +380,13 @@ __device__ void grid_barrier(Ctx& c) {
     trace_mark(c, 6);
     unsigned long long* cnt = reinterpret_cast<unsigned long long*>(c.a.bar);
     asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(cnt), "l"(1ull) : "memory");
-    c.bar_target += gridDim.x;
+    const unsigned long long target = c.bar_target + gridDim.x;
     if (!*c.w.s_fail) {
       const unsigned long long t0 = globaltimer_ns();
       for (;;) {
         unsigned long long v;
         asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cnt) : "memory");
-        if (static_cast<long long>(v - c.bar_target) >= 0) break;
+        if (static_cast<long long>(v - target) >= 0) break;
         if (globaltimer_ns() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(c.a.error) != 0) {
           *c.w.s_fail = 1;
           atomicCAS(c.a.error, 0, 20);
@@ -353,6 +395,7 @@ __device__ void grid_barrier(Ctx& c) {
       }
     }
   }
+  c.bar_target += gridDim.x;
   consumer_bar();
 }
 
@@ -653,7 +696,7 @@ __device__ __forceinline__ void consume_box(const Ctx& c, const uint8_t* st, int
 
 // Lanes 0..15 of one warp: output strip * 16 + lane, summed over all of K, gets its
 // epilogue and is written.
-__device__ __forceinline__ void finish_strip(int kind, int strip, float v, float sx, const __half* resid, __half* out) {
+__device__ __forceinline__ void finish_strip(int kind, int strip, float v, float sx, bool has_resid, __half resid, __half* out) {
   const int lane = threadIdx.x & 31;
   const int n = strip * kStripN + lane;
   const __half r = __float2half_rn(v * sx);
@@ -663,7 +706,7 @@ __device__ __forceinline__ void finish_strip(int kind, int strip, float v, float
     const float uf = __shfl_down_sync(0xffffffffu, gf, 1);
     if (lane < kStripN && (lane & 1) == 0) out[n >> 1] = __float2half_rn(gf / (1.0f + __expf(-gf)) * uf);
   } else if (lane < kStripN) {
-    out[n] = resid != nullptr ? __hadd(r, __ldcg(resid + n)) : r;
+    out[n] = has_resid ? __hadd(r, resid) : r;
   }
 }
 
@@ -687,6 +730,9 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
     const int strip = i0 / p.S + rr;
     const int seq_lo = rr * p.S, seq_hi = seq_lo + p.S;
     if (q >= seq_hi) continue;  // no box of this strip for this warp
+    // the strip's residual values are fetched now: whichever warp completes the strip has them at hand
+    __half rv = __float2half_rn(0.0f);
+    if (resid != nullptr && lane < kStripN) rv = __ldcg(resid + strip * kStripN + lane);
     float tot[2] = {0.0f, 0.0f};
     for (; q < seq_hi; q += kCW) {
       const long long w0 = tracing ? clock64() : 0;
@@ -714,7 +760,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
       // the strip is this warp's alone: rows g and g+8 sit in lanes t == 0
       const float lo = __shfl_sync(0xffffffffu, tot[0], (lane & 7) * 4);
       const float hi = __shfl_sync(0xffffffffu, tot[1], (lane & 7) * 4);
-      finish_strip(kind, strip, (lane & 8) ? hi : lo, c.sx, resid, out);
+      finish_strip(kind, strip, (lane & 8) ? hi : lo, c.sx, resid != nullptr, rv, out);
       continue;
     }
     c.w.wait_count(c.proj_done() + slot, use, 15);  // the slot's previous strip has been summed
@@ -742,7 +788,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
         __threadfence_block();
         c.proj_done()[slot] = use + 1;
       }
-      finish_strip(kind, strip, v, c.sx, resid, out);
+      finish_strip(kind, strip, v, c.sx, resid != nullptr, rv, out);
     }
   }
   if (p.S > 1) c.proj_runs += n_runs;  // single-box strips never use a slot
@@ -786,9 +832,10 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int nt = a.pos / kTile + 1;
-  const int I = a.heads * nt;
   const int width = a.heads * kHeadDim;
-  const int i0 = range_start(cta, I, G), i1 = range_start(cta + 1, I, G);
+  const AttnSplit split(a.heads, nt, G);
+  int i0, i1;
+  split.range(cta, i0, i1);
   const Runs runs(i0, i1, nt);
   __half* sq = reinterpret_cast<__half*>(reinterpret_cast<float*>(c.xs) + warp * kWarpScratch);  // rotated, scaled q
   long long awaited = 0;
@@ -1007,9 +1054,97 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
         __threadfence_block();
         c.attn_done()[slot] = use + 1;
       }
-      const int first = owner_of(head * nt, I, G), lastc = owner_of(head * nt + nt - 1, I, G);
+      int first, lastc;
+      split.contributors(head, first, lastc);
       bool write = true;
-      if (first != lastc) {
+      if (split.P > 1 && lastc > first) {
+        // The head's parts publish their partial and a flag; the part with the last tile (which also has
+        // the new token, so the most to do) waits for them and merges: parts in order, its own last.
+        const unsigned epoch = c.epoch_base + static_cast<unsigned>(c.op_index) + 1u;
+        const int part = cta - first, pm = lastc - first;  // pm: the part with the head's last tile
+        unsigned* flags = a.att_flags + (size_t)head * split.P;
+        if (part < pm) {
+          float* pp = a.att_part + (size_t)cta * kAttSlots * kAttDump;
+          *reinterpret_cast<float4*>(pp + 4 * lane) = make_float4(o[0], o[1], o[2], o[3]);
+          if (lane == 0) {
+            pp[kHeadDim] = M;
+            pp[kHeadDim + 1] = ls;
+          }
+          if (trs) trs[9] = globaltimer_ns();
+          __syncwarp();  // the release below is cumulative over the other lanes' stores
+          if (lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + part), "r"(epoch) : "memory");
+          if (trs) trs[10] = globaltimer_ns();
+          write = false;
+        } else {
+          if (trs) trs[9] = globaltimer_ns();
+          for (int base = 0; base < pm; base += 32) {
+            const int u = base + lane;
+            if (u < pm && !*c.w.s_fail) {
+              const unsigned long long t0 = globaltimer_ns();
+              for (;;) {
+                unsigned fv;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(fv) : "l"(flags + u) : "memory");
+                if (fv == epoch) break;
+                if (globaltimer_ns() - t0 > kWaitLimitNs || *c.w.s_fail) {
+                  *c.w.s_fail = 1;
+                  atomicCAS(a.error, 0, 21);
+                  break;
+                }
+              }
+            }
+          }
+          __syncwarp();
+          if (trs) trs[10] = globaltimer_ns();
+          float TM = -INFINITY, po[4] = {0.0f, 0.0f, 0.0f, 0.0f}, pl = 0.0f;
+          for (int base = 0; base < pm; base += 8) {
+            int myoff = -1;
+            {
+              const int u = base + (lane & 7);
+              if (u < pm) myoff = (first + u) * kAttSlots * kAttDump;
+            }
+            float mc[8], lc[8];
+            float4 oc[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int off = __shfl_sync(0xffffffffu, myoff, u);
+              mc[u] = -INFINITY;
+              lc[u] = 0.0f;
+              oc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+              if (off >= 0) {
+                const float* pp = a.att_part + off;
+                mc[u] = __ldcg(pp + kHeadDim);
+                lc[u] = __ldcg(pp + kHeadDim + 1);
+                oc[u] = __ldcg(reinterpret_cast<const float4*>(pp + 4 * lane));
+              }
+            }
+            float NM = TM;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) NM = fmaxf(NM, mc[u]);
+            const float resc = TM == -INFINITY ? 0.0f : __expf(TM - NM);
+            po[0] *= resc;
+            po[1] *= resc;
+            po[2] *= resc;
+            po[3] *= resc;
+            pl *= resc;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const float wc = mc[u] == -INFINITY ? 0.0f : __expf(mc[u] - NM);
+              po[0] = fmaf(wc, oc[u].x, po[0]);
+              po[1] = fmaf(wc, oc[u].y, po[1]);
+              po[2] = fmaf(wc, oc[u].z, po[2]);
+              po[3] = fmaf(wc, oc[u].w, po[3]);
+              pl = fmaf(wc, lc[u], pl);
+            }
+            TM = NM;
+          }
+          // this part's own share last
+          const float FM = fmaxf(TM, M);
+          const float wa = TM == -INFINITY ? 0.0f : __expf(TM - FM), wb = M == -INFINITY ? 0.0f : __expf(M - FM);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = po[e] * wa + o[e] * wb;
+          ls = pl * wa + ls * wb;
+        }
+      } else if (split.P == 0 && first != lastc) {
         const int ps = head - i0 / nt;
         float* part = a.att_part + ((size_t)cta * kAttSlots + ps) * kAttDump;
         *reinterpret_cast<float4*>(part + 4 * lane) = make_float4(o[0], o[1], o[2], o[3]);
@@ -1024,7 +1159,12 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
         int need = 0;
         for (int base = first; base <= lastc; base += 32) {
           const int cc = base + lane;
-          const bool has = cc <= lastc && range_start(cc, I, G) != range_start(cc + 1, I, G);
+          bool has = false;
+          if (cc <= lastc) {
+            int c0, c1;
+            split.range(cc, c0, c1);
+            has = c0 != c1;
+          }
           need += __popc(__ballot_sync(0xffffffffu, has));
         }
         int done = 0;
@@ -1046,8 +1186,9 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
             {
               const int cc = base + (lane & 7);
               if (cc <= lastc) {
-                const int c0 = range_start(cc, I, G);
-                if (c0 != range_start(cc + 1, I, G)) myoff = (cc * kAttSlots + (head - c0 / nt)) * kAttDump;
+                int c0, c1;
+                split.range(cc, c0, c1);
+                if (c0 != c1) myoff = (cc * kAttSlots + (head - c0 / nt)) * kAttDump;
               }
             }
             float mc[8], lc[8];
@@ -1122,6 +1263,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
       mbar_init(&empty[s], kCW);  // attention tiles are read by every warp; a weight box's one reader arrives kCW-fold
     }
     for (int i = 0; i < kSharedInts; ++i) s_int[i] = 0;
+    // Arrival count of the grid barrier when this launch began (a multiple of the grid size; read before
+    // this CTA's first arrival it lies in [base, base + grid)).  base / grid numbers the barriers of all
+    // launches so far and gives every op of every launch a unique epoch.
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(a.bar) : "memory");
+    v -= v % gridDim.x;
+    *reinterpret_cast<unsigned long long*>(s_int + kSharedInts + 1) = v;
     fence_barrier_init();
   }
   if (threadIdx.x >= 32 && threadIdx.x < 32 + kHeadDim / 2) {
@@ -1139,14 +1287,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
   if (warp == kCW) {
     if (lane == 0) producer_loop(a, ring, full, empty, w);
   } else {
-    Ctx c{a, ring, full, empty, xs, reinterpret_cast<int*>(us), 1.0f, rope, dump, s_int, w, 0, 0, 0, 0ull, 0};
-    if (threadIdx.x == 0) {
-      // read before this CTA's first arrival, the count is in [base, base + grid): no barrier of this
-      // launch can complete without this CTA
-      unsigned long long v;
-      asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(a.bar) : "memory");
-      c.bar_target = v - v % gridDim.x;
-    }
+    Ctx c{a, ring, full, empty, xs, reinterpret_cast<int*>(us), 1.0f, rope, dump, s_int, w, 0, 0, 0, 0ull, 0u, 0};
+    c.bar_target = *reinterpret_cast<const unsigned long long*>(s_int + kSharedInts + 1);
+    c.epoch_base = static_cast<unsigned>(c.bar_target / gridDim.x);
     const int d = a.d_model;
     for (int l = 0; l < a.n_layers; ++l) {
       const MegaLayer* ly = a.layers + l;
@@ -1280,6 +1423,7 @@ struct MegaDecoder {
   __half *qkv, *attn, *h, *act, *xa, *xb;
   float* att_part;
   int *att_tickets, *error;
+  unsigned* att_flags;
   unsigned* bar;
   unsigned long long* trace;
 };
@@ -1318,7 +1462,7 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   const int vec_bytes = vec_elems * 2;
   m->xs_bytes = align_n(att_bytes > vec_bytes ? att_bytes : vec_bytes, 128);
   m->us_floats = vec_elems / 32;
-  const int fixed = 1024 + m->xs_bytes + m->us_floats * 4 + kDumpFloats * 4 + (kHeadDim / 2) * 8 + kSharedInts * 4 + 64;
+  const int fixed = 1024 + m->xs_bytes + m->us_floats * 4 + kDumpFloats * 4 + (kHeadDim / 2) * 8 + (kSharedInts + 3) * 4 + 64;
   int max_smem = 0;
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, cfg.device);
   int stages = (max_smem - fixed) / (kStageBytes + 16);
@@ -1373,7 +1517,7 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   };
   const size_t o_qkv = take((size_t)3 * d * 2), o_attn = take((size_t)d * 2), o_h = take((size_t)d * 2),
                o_act = take((size_t)ffn * 2), o_xa = take((size_t)d * 2), o_xb = take((size_t)d * 2),
-               o_ap = take((size_t)m->grid * kAttSlots * kAttDump * 4), o_at = take((size_t)cfg.heads * 4),
+               o_ap = take((size_t)m->grid * kAttSlots * kAttDump * 4), o_at = take((size_t)cfg.heads * 4), o_af = take((size_t)(m->grid + cfg.heads) * 4),
                o_bar = take(8), o_err = take(4);
   const int Ns[4] = {3 * d, d, 2 * ffn, d};
   const int Ks[4] = {d, d, d, ffn};
@@ -1398,6 +1542,7 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   m->xb = reinterpret_cast<__half*>(m->scratch + o_xb);
   m->att_part = reinterpret_cast<float*>(m->scratch + o_ap);
   m->att_tickets = reinterpret_cast<int*>(m->scratch + o_at);
+  m->att_flags = reinterpret_cast<unsigned*>(m->scratch + o_af);
   m->bar = reinterpret_cast<unsigned*>(m->scratch + o_bar);
   m->error = reinterpret_cast<int*>(m->scratch + o_err);
   m->h_layers.resize(cfg.layers);
@@ -1500,6 +1645,7 @@ int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream
   a.xb = m->xb;
   a.att_part = m->att_part;
   a.att_tickets = m->att_tickets;
+  a.att_flags = m->att_flags;
   a.bar = m->bar;
   a.error = m->error;
   a.trace = m->trace;
