@@ -345,6 +345,9 @@ def run_ours(args):
     # every rank's memory over NVLink; "nccl" = an all-gather after each producing kernel
     exchange = os.environ.get("MLD_SHARD_EXCHANGE", "peer") if world > 1 else "none"
     if world > 1:
+        # the persistent step kernel exchanges shards itself (peer stores); the NCCL variant is a kernel chain
+        os.environ["MLD_DECODER_MODE"] = "ops" if exchange == "nccl" else os.environ.get("MLD_DECODER_MODE", "mega")
+    if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
         if exchange == "nccl":
@@ -392,7 +395,7 @@ def run_ours(args):
     # capture one step in a CUDA graph; fall back to direct launches if capture is refused
     stream = torch.cuda.Stream()
     graph = None
-    single = world == 1 and dec.single_kernel
+    single = dec.single_kernel
     try:
         if single:
             raise RuntimeError("the step is one cooperative launch; nothing to capture")
@@ -459,10 +462,10 @@ def run_ours(args):
         for n, kk in ((3 * d_, d_), (d_, d_), (2 * f_, d_), (d_, f_)):
             per_layer += n * kk // 2 + (kk // blk_) * n * 2
         per_layer += 2 * (pos + 1) * d_ * 2
-        step_bytes = per_layer * n_layers
+        step_bytes = per_layer * n_layers // world     # per launch = per GPU: a rank streams its own shard
         gemv_alone = roof
         sec = ms * 1e-3 / args.steps
-        roof = {"bound": "hbm", "kernel": "decode_mega_kernel (whole decode step, one launch)",
+        roof = {"bound": "hbm", "kernel": "decode_mega_kernel (whole decode step, one launch per GPU)",
                 "achieved": step_bytes / sec / 1e9, "peak": gemv_alone["peak"], "unit": "GB/s",
                 "frac": step_bytes / sec / 1e9 / gemv_alone["peak"], "peak_source": gemv_alone["peak_source"],
                 # dram__bytes_read + write of one launch: ncu capture of the same kernel on 2 layers

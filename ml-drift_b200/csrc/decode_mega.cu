@@ -86,9 +86,17 @@ struct MegaArgs {
   int xs_bytes;        // shared-memory bytes of the input-vector / attention scratch area
   int us_floats;       // entries of the per-32-input sums of the input vector
   float rms_eps, min_ts, max_ts, q_scale;
+  // Sharding: this rank computes heads [rank * heads, ...), outputs [rank * d_local, ...) of o / down and
+  // FFN units [rank * ffn_local, ...); heads is the LOCAL head count, d_model and ffn are global (they are
+  // the input lengths of the projections).  The vectors every rank needs in full (attn, h, act, xa, xb)
+  // and the cross-rank barrier counter live in an exchange block with the same layout on every rank;
+  // peers[r] is rank r's block as mapped here (peers[rank] = the local one).
+  int world, rank, d_local, ffn_local;
+  uint8_t* peers[8];
+  unsigned long long off_attn, off_h, off_act, off_xa, off_xb, off_xbar;  // byte offsets in the exchange block
   const __half* x_in;
   __half* x_out;
-  __half *qkv, *attn, *h, *act, *xa, *xb;
+  __half *qkv, *attn, *h, *act, *xa, *xb;  // local copies (attn .. xb inside the local exchange block)
   float* att_part;     // [grid][kAttSlots][kAttDump]
   int* att_tickets;    // [heads]
   unsigned* att_flags; // [heads][grid / heads]: epoch of the attention whose partial the part has published
@@ -158,9 +166,8 @@ struct ProjShape {
 };
 __device__ __forceinline__ ProjShape proj_shape(const MegaArgs& a, int kind) {
   ProjShape p;
-  const int d = a.d_model;
-  p.N = kind == kQkv ? 3 * d : kind == kGu ? 2 * a.ffn : d;
-  p.K = kind == kDown ? a.ffn : d;
+  p.N = kind == kQkv ? 3 * a.d_local : kind == kGu ? 2 * a.ffn_local : a.d_local;
+  p.K = kind == kDown ? a.ffn : a.d_model;
   p.C = p.N / kStripN;
   p.S = (p.K + kBoxK - 1) / kBoxK;
   p.I = p.C * p.S;
@@ -356,14 +363,15 @@ struct Ctx {
   int proj_runs;       // column runs started so far (selects the dump slot)
   int attn_runs;       // head runs started so far
   unsigned long long bar_target;  // arrival count that completes the barrier this CTA waits for next
-  unsigned epoch_base;            // barriers completed by earlier launches: op k of this launch has epoch_base + k + 1
+  unsigned long long xbar_target; // the same for the barrier across ranks
+  unsigned epoch_base;            // unique per launch: op k of this launch has epoch epoch_base + k + 1
   int op_index;
   __device__ __forceinline__ int* proj_arrived() const { return s_int + 1; }                     // [kProjSlots]
   __device__ __forceinline__ volatile int* proj_done() const { return s_int + 1 + kProjSlots; }  // [kProjSlots]
   __device__ __forceinline__ int* attn_arrived() const { return s_int + 1 + 2 * kProjSlots; }    // [kAttnSlots]
   __device__ __forceinline__ volatile int* attn_done() const { return s_int + 1 + 2 * kProjSlots + kAttnSlots; }
 };
-constexpr int kSharedInts = 1 + 2 * kProjSlots + 2 * kAttnSlots;  // (odd) + 3 behind them: pad, 64-bit barrier base
+constexpr int kSharedInts = 1 + 2 * kProjSlots + 2 * kAttnSlots;  // (odd) + 5 behind them: pad, two 64-bit barrier bases
 
 __device__ __forceinline__ void trace_mark(const Ctx& c, int k) {
   if (c.a.trace != nullptr && threadIdx.x == 0)
@@ -374,18 +382,33 @@ __device__ __forceinline__ void trace_mark(const Ctx& c, int k) {
 // at a multiple of the grid size).  A CTA adds one with release semantics and
 // no return value, then polls until the count reaches the end of the barrier's
 // round.  All consumer threads call this after their last global write of an op.
-__device__ void grid_barrier(Ctx& c) {
+// cross (sharded decoder only): the barrier spans the CTAs of all ranks and orders their peer stores: a
+// CTA adds one to the counter in every rank's exchange block (release at system scope) and polls its own.
+__device__ void grid_barrier(Ctx& c, bool cross = false) {
   consumer_bar();
+  cross = cross && c.a.world > 1;
   if (threadIdx.x == 0) {
     trace_mark(c, 6);
     unsigned long long* cnt = reinterpret_cast<unsigned long long*>(c.a.bar);
-    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(cnt), "l"(1ull) : "memory");
-    const unsigned long long target = c.bar_target + gridDim.x;
+    unsigned long long target = c.bar_target + gridDim.x;
+    if (cross) {
+      cnt = reinterpret_cast<unsigned long long*>(c.a.peers[c.a.rank] + c.a.off_xbar);
+      target = c.xbar_target + (unsigned long long)gridDim.x * c.a.world;
+      // one system-scope fence (this CTA's stores, the peer stores among them, are performed), then the arrivals
+      asm volatile("fence.acq_rel.sys;" ::: "memory");
+      for (int r = 0; r < c.a.world; ++r)
+        asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(c.a.peers[r] + c.a.off_xbar), "l"(1ull) : "memory");
+    } else {
+      asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(cnt), "l"(1ull) : "memory");
+    }
     if (!*c.w.s_fail) {
       const unsigned long long t0 = globaltimer_ns();
       for (;;) {
         unsigned long long v;
-        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cnt) : "memory");
+        if (cross)
+          asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(cnt) : "memory");
+        else
+          asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cnt) : "memory");
         if (static_cast<long long>(v - target) >= 0) break;
         if (globaltimer_ns() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(c.a.error) != 0) {
           *c.w.s_fail = 1;
@@ -395,7 +418,10 @@ __device__ void grid_barrier(Ctx& c) {
       }
     }
   }
-  c.bar_target += gridDim.x;
+  if (cross)
+    c.xbar_target += (unsigned long long)gridDim.x * c.a.world;
+  else
+    c.bar_target += gridDim.x;
   consumer_bar();
 }
 
@@ -694,9 +720,25 @@ __device__ __forceinline__ void consume_box(const Ctx& c, const uint8_t* st, int
   }
 }
 
+// Where a projection's outputs go: a local vector, or (sharded, `all`) the same place in every rank's
+// exchange block, written with plain peer stores.
+struct Dest {
+  __half* local;
+  unsigned long long off;  // byte offset in the exchange block of output 0 of this rank's shard
+  bool all;
+};
+__device__ __forceinline__ void store_out(const MegaArgs& a, const Dest& dst, int idx, __half v) {
+  if (dst.all) {
+    for (int r = 0; r < a.world; ++r) reinterpret_cast<__half*>(a.peers[r] + dst.off)[idx] = v;
+  } else {
+    dst.local[idx] = v;
+  }
+}
+
 // Lanes 0..15 of one warp: output strip * 16 + lane, summed over all of K, gets its
 // epilogue and is written.
-__device__ __forceinline__ void finish_strip(int kind, int strip, float v, float sx, bool has_resid, __half resid, __half* out) {
+__device__ __forceinline__ void finish_strip(const MegaArgs& a, int kind, int strip, float v, float sx, bool has_resid,
+                                             __half resid, const Dest& out) {
   const int lane = threadIdx.x & 31;
   const int n = strip * kStripN + lane;
   const __half r = __float2half_rn(v * sx);
@@ -704,13 +746,13 @@ __device__ __forceinline__ void finish_strip(int kind, int strip, float v, float
     // rows interleave gate_i, up_i: even lanes hold the gate, the next lane its up value
     const float gf = __half2float(r);
     const float uf = __shfl_down_sync(0xffffffffu, gf, 1);
-    if (lane < kStripN && (lane & 1) == 0) out[n >> 1] = __float2half_rn(gf / (1.0f + __expf(-gf)) * uf);
+    if (lane < kStripN && (lane & 1) == 0) store_out(a, out, n >> 1, __float2half_rn(gf / (1.0f + __expf(-gf)) * uf));
   } else if (lane < kStripN) {
-    out[n] = has_resid ? __hadd(r, resid) : r;
+    store_out(a, out, n, has_resid ? __hadd(r, resid) : r);
   }
 }
 
-__device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* out) {
+__device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest& out) {
   const MegaArgs& a = c.a;
   const ProjShape p = proj_shape(a, kind);
   const int cta = blockIdx.x, G = gridDim.x;
@@ -760,7 +802,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
       // the strip is this warp's alone: rows g and g+8 sit in lanes t == 0
       const float lo = __shfl_sync(0xffffffffu, tot[0], (lane & 7) * 4);
       const float hi = __shfl_sync(0xffffffffu, tot[1], (lane & 7) * 4);
-      finish_strip(kind, strip, (lane & 8) ? hi : lo, c.sx, resid != nullptr, rv, out);
+      finish_strip(a, kind, strip, (lane & 8) ? hi : lo, c.sx, resid != nullptr, rv, out);
       continue;
     }
     c.w.wait_count(c.proj_done() + slot, use, 15);  // the slot's previous strip has been summed
@@ -788,7 +830,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, __half* ou
         __threadfence_block();
         c.proj_done()[slot] = use + 1;
       }
-      finish_strip(kind, strip, v, c.sx, resid != nullptr, rv, out);
+      finish_strip(a, kind, strip, v, c.sx, resid != nullptr, rv, out);
     }
   }
   if (p.S > 1) c.proj_runs += n_runs;  // single-box strips never use a slot
@@ -1234,7 +1276,10 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
         uint2 pk;
         pk.x = *reinterpret_cast<uint32_t*>(&r01);
         pk.y = *reinterpret_cast<uint32_t*>(&r23);
-        *reinterpret_cast<uint2*>(a.attn + (size_t)head * kHeadDim + 4 * lane) = pk;
+        // this rank's heads sit at rank * d_local in the full vector, which every rank needs
+        const size_t at = (size_t)a.rank * a.d_local + (size_t)head * kHeadDim + 4 * lane;
+        for (int r = 0; r < a.world; ++r)
+          *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(a.peers[r] + a.off_attn) + at) = pk;
         if (trs) trs[11] = globaltimer_ns();
       }
     }
@@ -1270,6 +1315,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(a.bar) : "memory");
     v -= v % gridDim.x;
     *reinterpret_cast<unsigned long long*>(s_int + kSharedInts + 1) = v;
+    unsigned long long xv = 0;
+    if (a.world > 1) {  // the cross-rank counter: arrivals of all ranks' CTAs
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(xv) : "l"(a.peers[a.rank] + a.off_xbar) : "memory");
+      xv -= xv % ((unsigned long long)gridDim.x * a.world);
+    }
+    *reinterpret_cast<unsigned long long*>(s_int + kSharedInts + 3) = xv;
     fence_barrier_init();
   }
   if (threadIdx.x >= 32 && threadIdx.x < 32 + kHeadDim / 2) {
@@ -1287,56 +1338,71 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
   if (warp == kCW) {
     if (lane == 0) producer_loop(a, ring, full, empty, w);
   } else {
-    Ctx c{a, ring, full, empty, xs, reinterpret_cast<int*>(us), 1.0f, rope, dump, s_int, w, 0, 0, 0, 0ull, 0u, 0};
+    Ctx c{a, ring, full, empty, xs, reinterpret_cast<int*>(us), 1.0f, rope, dump, s_int, w, 0, 0, 0, 0ull, 0ull, 0u, 0};
     c.bar_target = *reinterpret_cast<const unsigned long long*>(s_int + kSharedInts + 1);
-    c.epoch_base = static_cast<unsigned>(c.bar_target / gridDim.x);
+    c.xbar_target = *reinterpret_cast<const unsigned long long*>(s_int + kSharedInts + 3);
+    // every launch completes at least one local barrier, so five epochs per barrier keep launches apart
+    c.epoch_base = static_cast<unsigned>(c.bar_target / gridDim.x) * kOpsPerLayer;
     const int d = a.d_model;
+    const bool sharded = a.world > 1;
+    const size_t shard = (size_t)a.rank * a.d_local;  // first output of this rank in h / x
     for (int l = 0; l < a.n_layers; ++l) {
       const MegaLayer* ly = a.layers + l;
+      const bool last = l + 1 == a.n_layers;
       const __half* x_cur = l == 0 ? a.x_in : (((l - 1) & 1) ? a.xb : a.xa);
-      __half* x_next = l + 1 == a.n_layers ? a.x_out : ((l & 1) ? a.xb : a.xa);
+      // the last layer writes the caller's vector directly, unless peers have to write it too
+      __half* x_next = (last && !sharded) ? a.x_out : ((l & 1) ? a.xb : a.xa);
+      const Dest d_qkv{a.qkv, 0ull, false};
+      const Dest d_h{a.h + shard, a.off_h + shard * 2, sharded};
+      const Dest d_act{a.act + (size_t)a.rank * a.ffn_local, a.off_act + (size_t)a.rank * a.ffn_local * 2, sharded};
+      const Dest d_x{x_next + shard, ((l & 1) ? a.off_xb : a.off_xa) + shard * 2, sharded};
       c.op_index = l * kOpsPerLayer;
       trace_mark(c, 0);
       load_x<true>(c, x_cur, ly->norm1, d);
       trace_mark(c, 1);
-      run_projection(c, kQkv, nullptr, a.qkv);
+      run_projection(c, kQkv, nullptr, d_qkv);
       trace_mark(c, 2);
-      grid_barrier(c);
+      grid_barrier(c);  // q, k, v stay on this rank
       trace_mark(c, 3);
 
       c.op_index += 1;
       trace_mark(c, 0);
       run_attention(c, ly);
       trace_mark(c, 2);
-      grid_barrier(c);
+      grid_barrier(c, true);
       trace_mark(c, 3);
 
       c.op_index += 1;
       trace_mark(c, 0);
       load_x<false>(c, a.attn, nullptr, d);
       trace_mark(c, 1);
-      run_projection(c, kO, x_cur, a.h);
+      run_projection(c, kO, x_cur + shard, d_h);
       trace_mark(c, 2);
-      grid_barrier(c);
+      grid_barrier(c, true);
       trace_mark(c, 3);
 
       c.op_index += 1;
       trace_mark(c, 0);
       load_x<true>(c, a.h, ly->norm2, d);
       trace_mark(c, 1);
-      run_projection(c, kGu, nullptr, a.act);
+      run_projection(c, kGu, nullptr, d_act);
       trace_mark(c, 2);
-      grid_barrier(c);
+      grid_barrier(c, true);
       trace_mark(c, 3);
 
       c.op_index += 1;
       trace_mark(c, 0);
       load_x<false>(c, a.act, nullptr, a.ffn);
       trace_mark(c, 1);
-      run_projection(c, kDown, a.h, x_next);
+      run_projection(c, kDown, a.h + shard, d_x);
       trace_mark(c, 2);
-      grid_barrier(c);
+      grid_barrier(c, true);
       trace_mark(c, 3);
+      if (last && sharded && blockIdx.x == 0) {
+        // the step's result, assembled from all ranks' shards, goes to the caller's vector
+        for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8)
+          *reinterpret_cast<uint4*>(a.x_out + i) = __ldcg(reinterpret_cast<const uint4*>(x_next + i));
+      }
     }
   }
   // A CTA that gave up may still have copies in flight: give them time to land
@@ -1418,6 +1484,11 @@ struct MegaDecoder {
   std::vector<MegaLayer> h_layers;
   std::vector<char> layer_set;
   uint8_t* scratch;
+  uint8_t* xchg;              // exchange block (vectors every rank needs + the cross-rank barrier counter)
+  uint8_t* peers[8];          // every rank's exchange block as mapped here (own entry = xchg)
+  size_t off_attn, off_h, off_act, off_xa, off_xb, off_xbar;
+  int heads_local, d_local, ffn_local;
+  bool peers_ready;
   uint8_t* prepared;          // re-tiled weights of all layers
   size_t proj_bytes[4], layer_bytes;
   __half *qkv, *attn, *h, *act, *xa, *xb;
@@ -1431,7 +1502,8 @@ struct MegaDecoder {
 bool mega_supported(const MegaConfig& c) {
   if (c.head_dim != kHeadDim || c.heads < 1) return false;
   if (c.d_model != c.heads * kHeadDim) return false;
-  if (c.ffn % 32 != 0) return false;
+  if (c.world < 1 || c.world > 8 || c.rank < 0 || c.rank >= c.world) return false;
+  if (c.heads % c.world != 0 || c.ffn % (32 * c.world) != 0) return false;
   if (c.block != 32 && c.block != 64 && c.block != 128 && c.block != 256) return false;
   if (c.d_model % c.block != 0 || c.ffn % c.block != 0) return false;
   return get_encode_tiled() != nullptr;
@@ -1441,6 +1513,9 @@ void mega_destroy(MegaDecoder* m) {
   if (m == nullptr) return;
   if (m->d_layers != nullptr) cudaFree(m->d_layers);
   if (m->scratch != nullptr) cudaFree(m->scratch);
+  for (int r = 0; r < 8; ++r)
+    if (m->peers[r] != nullptr && m->peers[r] != m->xchg) cudaIpcCloseMemHandle(m->peers[r]);
+  if (m->xchg != nullptr) cudaFree(m->xchg);
   if (m->prepared != nullptr) cudaFree(m->prepared);
   if (m->trace != nullptr) cudaFree(m->trace);
   delete m;
@@ -1452,8 +1527,14 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   m->cfg = cfg;
   m->d_layers = nullptr;
   m->scratch = nullptr;
+  m->xchg = nullptr;
+  for (int r = 0; r < 8; ++r) m->peers[r] = nullptr;
+  m->peers_ready = cfg.world == 1;
   m->prepared = nullptr;
   m->trace = nullptr;
+  m->heads_local = cfg.heads / cfg.world;
+  m->d_local = cfg.d_model / cfg.world;
+  m->ffn_local = cfg.ffn / cfg.world;
   m->sms = sm_count(cfg.device);
   // shared memory: ring + max(input vector padded to whole boxes, per-warp attention scratch) + unit sums +
   // run slots + rope table + barriers
@@ -1462,7 +1543,7 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   const int vec_bytes = vec_elems * 2;
   m->xs_bytes = align_n(att_bytes > vec_bytes ? att_bytes : vec_bytes, 128);
   m->us_floats = vec_elems / 32;
-  const int fixed = 1024 + m->xs_bytes + m->us_floats * 4 + kDumpFloats * 4 + (kHeadDim / 2) * 8 + (kSharedInts + 3) * 4 + 64;
+  const int fixed = 1024 + m->xs_bytes + m->us_floats * 4 + kDumpFloats * 4 + (kHeadDim / 2) * 8 + (kSharedInts + 5) * 4 + 64;
   int max_smem = 0;
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, cfg.device);
   int stages = (max_smem - fixed) / (kStageBytes + 16);
@@ -1497,13 +1578,13 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   }
   // an attention range must not touch more than kAttSlots heads: ceil(n/nt)+1 with n = ceil(heads*nt/grid)
   // is at most ceil(heads/grid + 1/nt) + 1 <= heads/grid + 3
-  if ((int64_t)cfg.heads * (cfg.max_seq / kTile + 1) * m->grid >= (int64_t(1) << 31) ||
+  if ((int64_t)m->heads_local * (cfg.max_seq / kTile + 1) * m->grid >= (int64_t(1) << 31) ||
       (int64_t)(3 * cfg.d_model > 2 * cfg.ffn ? 3 * cfg.d_model : 2 * cfg.ffn) / kStripN * m->grid >= (int64_t(1) << 31)) {
     set_last_error_text("decoder too large for the persistent step kernel's 32-bit work split");
     mega_destroy(m);
     return MLD_UNIMPLEMENTED;
   }
-  if (cfg.heads / m->grid + 3 > kAttSlots) {
+  if (m->heads_local / m->grid + 3 > kAttSlots) {
     set_last_error_text("too many heads per CTA for the persistent step kernel");
     mega_destroy(m);
     return MLD_UNIMPLEMENTED;
@@ -1515,31 +1596,42 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
     off += (bytes + 255) & ~size_t(255);
     return o;
   };
-  const size_t o_qkv = take((size_t)3 * d * 2), o_attn = take((size_t)d * 2), o_h = take((size_t)d * 2),
-               o_act = take((size_t)ffn * 2), o_xa = take((size_t)d * 2), o_xb = take((size_t)d * 2),
-               o_ap = take((size_t)m->grid * kAttSlots * kAttDump * 4), o_at = take((size_t)cfg.heads * 4), o_af = take((size_t)(m->grid + cfg.heads) * 4),
+  const int dl = m->d_local, fl = m->ffn_local;
+  const size_t o_qkv = take((size_t)3 * dl * 2), o_ap = take((size_t)m->grid * kAttSlots * kAttDump * 4),
+               o_at = take((size_t)m->heads_local * 4), o_af = take((size_t)(m->grid + m->heads_local) * 4),
                o_bar = take(8), o_err = take(4);
-  const int Ns[4] = {3 * d, d, 2 * ffn, d};
+  const size_t scratch_bytes = off;
+  off = 0;  // the exchange block: same layout on every rank
+  m->off_attn = take((size_t)d * 2);
+  m->off_h = take((size_t)d * 2);
+  m->off_act = take((size_t)ffn * 2);
+  m->off_xa = take((size_t)d * 2);
+  m->off_xb = take((size_t)d * 2);
+  m->off_xbar = take(8);
+  const size_t xchg_bytes = off;
+  const int Ns[4] = {3 * dl, dl, 2 * fl, dl};
   const int Ks[4] = {d, d, d, ffn};
   m->layer_bytes = 0;
   for (int i = 0; i < 4; ++i) {
     m->proj_bytes[i] = (size_t)(Ns[i] / kStripN) * div_up(Ks[i], kBoxK) * kStageBytes;
     m->layer_bytes += m->proj_bytes[i];
   }
-  if (cudaMalloc(&m->scratch, off) != cudaSuccess ||
+  if (cudaMalloc(&m->scratch, scratch_bytes) != cudaSuccess || cudaMalloc(&m->xchg, xchg_bytes) != cudaSuccess ||
       cudaMalloc(&m->d_layers, sizeof(MegaLayer) * cfg.layers) != cudaSuccess ||
       cudaMalloc(&m->prepared, m->layer_bytes * cfg.layers) != cudaSuccess) {
     set_last_error_text("persistent step kernel: device allocation failed");
     mega_destroy(m);
     return MLD_CUDA_ERROR;
   }
-  cudaMemset(m->scratch, 0, off);
+  cudaMemset(m->scratch, 0, scratch_bytes);
+  cudaMemset(m->xchg, 0, xchg_bytes);
+  m->peers[cfg.rank] = m->xchg;
   m->qkv = reinterpret_cast<__half*>(m->scratch + o_qkv);
-  m->attn = reinterpret_cast<__half*>(m->scratch + o_attn);
-  m->h = reinterpret_cast<__half*>(m->scratch + o_h);
-  m->act = reinterpret_cast<__half*>(m->scratch + o_act);
-  m->xa = reinterpret_cast<__half*>(m->scratch + o_xa);
-  m->xb = reinterpret_cast<__half*>(m->scratch + o_xb);
+  m->attn = reinterpret_cast<__half*>(m->xchg + m->off_attn);
+  m->h = reinterpret_cast<__half*>(m->xchg + m->off_h);
+  m->act = reinterpret_cast<__half*>(m->xchg + m->off_act);
+  m->xa = reinterpret_cast<__half*>(m->xchg + m->off_xa);
+  m->xb = reinterpret_cast<__half*>(m->xchg + m->off_xb);
   m->att_part = reinterpret_cast<float*>(m->scratch + o_ap);
   m->att_tickets = reinterpret_cast<int*>(m->scratch + o_at);
   m->att_flags = reinterpret_cast<unsigned*>(m->scratch + o_af);
@@ -1556,7 +1648,7 @@ int mega_set_layer(MegaDecoder* m, int layer, const MegaLayerPtrs& p) {
   MegaLayer& L = m->h_layers[layer];
   memset(&L, 0, sizeof L);
   const int d = c.d_model, ffn = c.ffn;
-  const int Ns[4] = {3 * d, d, 2 * ffn, d};
+  const int Ns[4] = {3 * m->d_local, m->d_local, 2 * m->ffn_local, m->d_local};
   const int Ks[4] = {d, d, d, ffn};
   const void* ws[4] = {p.wqkv, p.wo, p.wgu, p.wdown};
   const void* ss[4] = {p.sqkv, p.so, p.sgu, p.sdown};
@@ -1570,7 +1662,7 @@ int mega_set_layer(MegaDecoder* m, int layer, const MegaLayerPtrs& p) {
     L.w[i] = dst;
     dst += m->proj_bytes[i];
   }
-  const uint64_t kv_row = (uint64_t)c.heads * kHeadDim * 2;
+  const uint64_t kv_row = (uint64_t)m->heads_local * kHeadDim * 2;
   int rc = make_tmap_2d(&L.kc, p.kcache, kv_row, c.max_seq, kv_row, kHeadDim, kTile, 2, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != MLD_OK) return rc;
   rc = make_tmap_2d(&L.vc, p.vcache, kv_row, c.max_seq, kv_row, kHeadDim, kTile, 2, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -1581,6 +1673,25 @@ int mega_set_layer(MegaDecoder* m, int layer, const MegaLayerPtrs& p) {
   L.vcache = static_cast<__half*>(p.vcache);
   MLD_CUDA_CHECK(cudaMemcpy(m->d_layers + layer, &L, sizeof L, cudaMemcpyHostToDevice));
   m->layer_set[layer] = 1;
+  return MLD_OK;
+}
+
+int mega_ipc_export(MegaDecoder* m, void* handle64) {
+  cudaIpcMemHandle_t h;
+  MLD_CUDA_CHECK(cudaIpcGetMemHandle(&h, m->xchg));
+  memcpy(handle64, &h, sizeof h);
+  return MLD_OK;
+}
+int mega_ipc_import(MegaDecoder* m, const void* handles) {
+  for (int r = 0; r < m->cfg.world; ++r) {
+    if (r == m->cfg.rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const uint8_t*>(handles) + (size_t)r * 64, sizeof h);
+    void* p = nullptr;
+    MLD_CUDA_CHECK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    m->peers[r] = static_cast<uint8_t*>(p);
+  }
+  m->peers_ready = true;
   return MLD_OK;
 }
 
@@ -1611,7 +1722,8 @@ int mega_device_status(MegaDecoder* m, int* code) {
     const int zero = 0;
     cudaMemcpy(m->error, &zero, sizeof zero, cudaMemcpyHostToDevice);
     cudaMemset(m->bar, 0, 8);
-    cudaMemset(m->att_tickets, 0, (size_t)m->cfg.heads * 4);
+    cudaMemset(m->att_tickets, 0, (size_t)m->heads_local * 4);
+    cudaMemset(m->xchg + m->off_xbar, 0, 8);  // ranks must reset together (after a failed step on any rank)
   }
   return MLD_OK;
 }
@@ -1623,9 +1735,21 @@ int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream
   const MegaConfig& c = m->cfg;
   a.layers = m->d_layers;
   a.n_layers = c.layers;
+  MLD_REQUIRE(m->peers_ready, "sharded decoder: exchange blocks not imported yet (mld_decoder_ipc_import)");
   a.d_model = c.d_model;
-  a.heads = c.heads;
+  a.heads = m->heads_local;
   a.ffn = c.ffn;
+  a.world = c.world;
+  a.rank = c.rank;
+  a.d_local = m->d_local;
+  a.ffn_local = m->ffn_local;
+  for (int r = 0; r < 8; ++r) a.peers[r] = m->peers[r];
+  a.off_attn = m->off_attn;
+  a.off_h = m->off_h;
+  a.off_act = m->off_act;
+  a.off_xa = m->off_xa;
+  a.off_xb = m->off_xb;
+  a.off_xbar = m->off_xbar;
   a.pos = pos;
   a.stages = m->stages;
   a.l2_ahead = m->l2_ahead;

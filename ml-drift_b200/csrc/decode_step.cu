@@ -727,9 +727,13 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   // One GPU: run the step as one persistent kernel when the shape allows it
   // (MLD_DECODER_MODE=ops keeps the op-by-op path).
   const char* mode = getenv("MLD_DECODER_MODE");
-  if (d->world == 1 && !(mode != nullptr && strcmp(mode, "ops") == 0)) {
+  // (a sharded decoder does so when asked with MLD_DECODER_MODE=mega and created without an NCCL id: its
+  // ranks exchange shards with peer stores, see mld_decoder_ipc_export).
+  const bool want_mega = d->world == 1 ? !(mode != nullptr && strcmp(mode, "ops") == 0)
+                                       : (mode != nullptr && strcmp(mode, "mega") == 0 && nccl_id128 == nullptr);
+  if (want_mega) {
     MegaConfig mc = {d->layers, d->d_model, d->heads, d->head_dim, d->ffn, d->max_seq, d->block,
-                     d->rms_eps, d->rope_min_timescale, d->rope_max_timescale, device};
+                     d->rms_eps, d->rope_min_timescale, d->rope_max_timescale, device, d->rank, d->world};
     if (mega_supported(mc)) {
       const int mrc = mega_create(mc, &dec->mega);
       if (mrc != MLD_OK) {
@@ -764,6 +768,7 @@ int mld_decoder_destroy(mld_decoder* dec) {
 
 int mld_decoder_ipc_export(mld_decoder* dec, void* handle64) {
   MLD_REQUIRE(dec != nullptr && handle64 != nullptr, "null argument");
+  if (dec->mega != nullptr && dec->d.world > 1) return mega_ipc_export(dec->mega, handle64);
   MLD_REQUIRE(dec->xchg != nullptr, "a single-rank decoder has nothing to share");
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
   cudaIpcMemHandle_t h;
@@ -774,6 +779,7 @@ int mld_decoder_ipc_export(mld_decoder* dec, void* handle64) {
 
 int mld_decoder_ipc_import(mld_decoder* dec, const void* handles) {
   MLD_REQUIRE(dec != nullptr && handles != nullptr, "null argument");
+  if (dec->mega != nullptr && dec->d.world > 1) return mega_ipc_import(dec->mega, handles);
   MLD_REQUIRE(dec->xchg != nullptr, "a single-rank decoder has no peers");
   for (int r = 0; r < dec->d.world; ++r) {
     if (r == dec->d.rank) continue;

@@ -105,6 +105,7 @@ struct MegaConfig {
   int layers, d_model, heads, head_dim, ffn, max_seq, block;
   float rms_eps, rope_min_timescale, rope_max_timescale;
   int device;
+  int rank, world;  // column sharding: heads, o/down outputs and FFN units are split evenly over the ranks
 };
 struct MegaLayerPtrs {
   const void *wqkv, *sqkv, *wo, *so, *wgu, *sgu, *wdown, *sdown, *norm1, *norm2;
@@ -118,6 +119,9 @@ int mega_set_layer(MegaDecoder* m, int layer, const MegaLayerPtrs& p);
 int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream_t stream);
 // Reads (and clears) the kernel's error word: 0 = every wait of the last steps was satisfied.
 int mega_device_status(MegaDecoder* m, int* code);
+// Sharded: every rank exports its exchange block (64-byte IPC handle) and imports all of them (rank order).
+int mega_ipc_export(MegaDecoder* m, void* handle64);
+int mega_ipc_import(MegaDecoder* m, const void* handles);
 int mega_enable_trace(MegaDecoder* m, bool on);
 int mega_read_trace(MegaDecoder* m, unsigned long long* out, size_t count);
 int mega_grid(const MegaDecoder* m);

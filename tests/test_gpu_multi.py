@@ -61,6 +61,9 @@ def _worker(rank, world, port, out_dir, exchange):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("gloo", rank=rank, world_size=world)
     nccl_id = None
+    # "mega": every rank runs the whole step as one persistent kernel, shards go to the peers with plain
+    # stores and the kernel's barriers span the ranks; "peer" / "nccl": the chain of kernels
+    os.environ["MLD_DECODER_MODE"] = "mega" if exchange == "mega" else "ops"
     if exchange == "nccl":
         idt = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:
@@ -72,7 +75,8 @@ def _worker(rank, world, port, out_dir, exchange):
     layers, kc, vc = _model(np.random.default_rng(0), L, heads, ffn, T)
     x = torch.from_numpy(np.random.default_rng(1).standard_normal(d).astype(np.float16)).cuda()
     dec, keep = _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id)
-    if exchange == "peer":                   # shards go straight into every rank's exchange block
+    assert dec.single_kernel == (exchange == "mega")
+    if exchange in ("peer", "mega"):         # shards go straight into every rank's exchange block
         mine = torch.frombuffer(bytearray(dec.ipc_export()), dtype=torch.uint8).clone()
         table = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
         dist.all_gather(table, mine)
@@ -88,7 +92,9 @@ def _worker(rank, world, port, out_dir, exchange):
     dist.all_gather(both, agree)
     same = all(torch.equal(both[0], b) for b in both)
     dist.barrier()
+    assert dec.device_status() == 0
     if rank == 0:
+        os.environ["MLD_DECODER_MODE"] = "ops"
         single, keep1 = _make_decoder(mld, layers, kc, vc, heads, ffn, T, 0, 1, None)
         y1 = torch.empty_like(y)
         single.step(x, y1, pos)
@@ -103,10 +109,10 @@ def _worker(rank, world, port, out_dir, exchange):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+@pytest.mark.parametrize("exchange", ["nccl", "peer", "mega"])
 def test_two_gpu_sharded_decode_equals_single_gpu(tmp_path, exchange):
     import torch.multiprocessing as mp
-    port = 29700 + (os.getpid() % 2000) + (7 if exchange == "peer" else 0)
+    port = 29700 + (os.getpid() % 2000) + {"nccl": 0, "peer": 7, "mega": 13}[exchange]
     mp.spawn(_worker, args=(2, port, str(tmp_path), exchange), nprocs=2, join=True)
     err, finite, same = open(tmp_path / "result.txt").read().split()
     assert int(finite) == 1
