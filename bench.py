@@ -177,7 +177,7 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def build_model(mld, torch, rank, world, n_layers, dev):
+def build_model(mld, torch, rank, world, n_layers, dev, shard_layout=0):
     """Random-init 7B-geometry model, quantised and packed on the GPU by the library.  The model is
     defined globally (one seed per projection); a rank keeps the rows of its column shard, so every
     world size runs the same model."""
@@ -188,11 +188,14 @@ def build_model(mld, torch, rank, world, n_layers, dev):
     layers = []
     gen = torch.Generator(device=dev)
 
-    def qpack(n_full, K, seed, rows):
+    def qpack(n_full, K, seed, rows, cols=None):
         gen.manual_seed(seed)
         w = torch.randn((n_full, K), generator=gen, device=dev, dtype=torch.float32) * 0.02
         if len(rows) != n_full or (rows[:-1] > rows[1:]).any():     # a shard, or the interleaved gate/up order
             w = w.index_select(0, torch.from_numpy(rows).to(dev))
+        if cols is not None:                                        # a shard by input columns
+            w = w.index_select(1, torch.from_numpy(cols).to(dev)).contiguous()
+            K = len(cols)
         q, s = mld.quantize_weights(w, 4, blk)
         packed, _ = mld.pack_weights(q, (w.shape[0], 1, 1, K), 4)
         sc = mld.pack_scales(s, True)
@@ -204,9 +207,14 @@ def build_model(mld, torch, rank, world, n_layers, dev):
         base = 1000 * l
         t = {}
         t["wqkv"], t["sqkv"] = qpack(3 * d, d, base + 1, shd.qkv_shard_rows(heads, hd, rank, world))
-        t["wo"], t["so"] = qpack(d, d, base + 2, shd.column_shard_rows(d, rank, world))
+        if shard_layout == 1:   # o and down: all rows, the input columns of this rank's heads / FFN units
+            import numpy as np
+            t["wo"], t["so"] = qpack(d, d, base + 2, np.arange(d), shd.input_shard_cols(d, rank, world))
+            t["wdown"], t["sdown"] = qpack(d, ffn, base + 4, np.arange(d), shd.input_shard_cols(ffn, rank, world))
+        else:
+            t["wo"], t["so"] = qpack(d, d, base + 2, shd.column_shard_rows(d, rank, world))
+            t["wdown"], t["sdown"] = qpack(d, ffn, base + 4, shd.column_shard_rows(d, rank, world))
         t["wgu"], t["sgu"] = qpack(2 * ffn, d, base + 3, shd.gate_up_shard_rows(ffn, rank, world))
-        t["wdown"], t["sdown"] = qpack(d, ffn, base + 4, shd.column_shard_rows(d, rank, world))
         t["norm1"] = torch.ones(d, dtype=torch.float16, device=dev)
         t["norm2"] = torch.ones(d, dtype=torch.float16, device=dev)
         for name, seed in (("kcache", base + 5), ("vcache", base + 6)):
@@ -218,13 +226,15 @@ def build_model(mld, torch, rank, world, n_layers, dev):
     return layers
 
 
-def gemv_roofline(mld, torch, layers, world, peaks):
+def gemv_roofline(mld, torch, layers, world, peaks, layout=0):
     """Times the decode GEMV (the dominant kernel) alone: every projection of every layer once
     per pass, back to back on the current stream, CUDA events around the passes.  The weights
     of a pass (3.6 GB / world) exceed L2, so every launch streams from HBM."""
     d, ffn, blk = CFG["d_model"], CFG["ffn"], CFG["block"]
     dl, fl = d // world, ffn // world
     shapes = {"qkv": (3 * dl, d), "o": (dl, d), "gu": (2 * fl, d), "down": (dl, ffn)}
+    if layout == 1:
+        shapes["o"], shapes["down"] = (d, dl), (d, fl)
     plans = {k: mld.FullyConnectedPlan(n, kk, 4, scale_mode=mld.SCALE_BLOCK, groups=kk // blk, precision=mld.F32F16)
              for k, (n, kk) in shapes.items()}
     xs = {k: torch.randn(kk, device="cuda").half() for k, (n, kk) in shapes.items()}
@@ -369,10 +379,12 @@ def run_ours(args):
         pass
 
     n_layers = args.layers
-    layers = build_model(mld, torch, rank, world, n_layers, dev)
+    # sharded step kernel: o and down split by input columns (two exchanges per layer instead of four)
+    layout = int(os.environ.get("MLD_SHARD_LAYOUT", "1")) if world > 1 and os.environ.get("MLD_DECODER_MODE") == "mega" else 0
+    layers = build_model(mld, torch, rank, world, n_layers, dev, layout)
     T = CFG["kv_len"] + 1
     dec = mld.Decoder(n_layers, CFG["d_model"], CFG["heads"], CFG["ffn"], T, block=CFG["block"], rank=rank,
-                      world=world, nccl_id=nccl_id)
+                      world=world, nccl_id=nccl_id, shard_layout=layout)
     for l, t in enumerate(layers):
         dec.set_layer(l, **t)
     if exchange == "peer":
@@ -453,7 +465,7 @@ def run_ours(args):
     status = dec.device_status()
     if status != 0:
         raise RuntimeError(f"a device-side wait gave up (code {status}); the timing is void")
-    roof = gemv_roofline(mld, torch, layers, world, peaks) if rank == 0 or world > 1 else None
+    roof = gemv_roofline(mld, torch, layers, world, peaks, layout) if rank == 0 or world > 1 else None
     if single:
         # the step is one kernel: its roofline is the step's own — every weight, scale and cached K/V
         # byte once, over the CUDA-event time of the launch
@@ -498,7 +510,8 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"7B INT4 decode step ({n_layers}L, d{d}, 32h x128, ffn{ffn}, KV 2048, batch 1)",
                        "weights": "INT4 block-32, fp16 scales, random init ~N(0,0.02)",
-                       "parallelism": f"column-sharded x{world}, shard exchange: {exchange}" if world > 1 else "single GPU",
+                       "parallelism": (f"sharded x{world} ({'o/down by input columns, partial sums' if layout == 1 else 'all by output rows'}), "
+                                       f"shard exchange: {exchange}") if world > 1 else "single GPU",
                        "l2": "inputs larger than L2 (3.6 GB of weights per step / world)",
                        "timed_with": "cuda graph replay" if graph is not None else "direct launches",
                        "decoder": "one persistent kernel per step" if single else "kernel chain"},

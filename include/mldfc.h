@@ -231,6 +231,15 @@ typedef struct mld_decoder_desc {
   float rope_max_timescale;      /* 1e6 */
   int32_t rank, world;
   int32_t device;                /* -1 = current */
+  /* How a sharded decoder's matrices are split (world > 1):
+   * 0 = by output rows, all four projections (shard outputs are all-gathered);
+   * 1 = q/k/v and gate/up by output rows, o and down by INPUT columns (wo:
+   *     N = d_model, K = d_model/world, the columns of this rank's heads;
+   *     wdown: N = d_model, K = ffn/world, the columns of this rank's FFN
+   *     units); their outputs are partial sums that every rank adds up, which
+   *     halves the exchanges per layer.  Supported by the single-kernel
+   *     decoder (MLD_DECODER_MODE=mega) only. */
+  int32_t shard_layout;
 } mld_decoder_desc;
 
 /* Device tensors of one layer, in the layouts named at the top of this file.

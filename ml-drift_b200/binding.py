@@ -45,7 +45,7 @@ class DecoderDesc(C.Structure):
     _fields_ = [("layers", C.c_int32), ("d_model", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
                 ("ffn", C.c_int32), ("max_seq", C.c_int32), ("block", C.c_int32), ("rms_eps", C.c_float),
                 ("rope_min_timescale", C.c_float), ("rope_max_timescale", C.c_float), ("rank", C.c_int32),
-                ("world", C.c_int32), ("device", C.c_int32)]
+                ("world", C.c_int32), ("device", C.c_int32), ("shard_layout", C.c_int32)]
 
 
 class LayerWeights(C.Structure):
@@ -211,9 +211,10 @@ class Decoder:
     FullyConnected nodes.  Layer tensors are torch tensors kept alive here."""
 
     def __init__(self, layers, d_model, heads, ffn, max_seq, block=32, head_dim=128, rms_eps=1e-6,
-                 rope_min_timescale=1.0, rope_max_timescale=1.0e6, rank=0, world=1, nccl_id=None, device=-1):
+                 rope_min_timescale=1.0, rope_max_timescale=1.0e6, rank=0, world=1, nccl_id=None, device=-1,
+                 shard_layout=0):
         self.desc = DecoderDesc(layers, d_model, heads, head_dim, ffn, max_seq, block, rms_eps,
-                                rope_min_timescale, rope_max_timescale, rank, world, device)
+                                rope_min_timescale, rope_max_timescale, rank, world, device, shard_layout)
         self._h = C.c_void_p()
         self._keep = []
         idbuf = None if nccl_id is None else C.create_string_buffer(nccl_id, 128)

@@ -92,8 +92,10 @@ struct MegaArgs {
   // and the cross-rank barrier counter live in an exchange block with the same layout on every rank;
   // peers[r] is rank r's block as mapped here (peers[rank] = the local one).
   int world, rank, d_local, ffn_local;
+  int paired;  // 1: o and down are split by INPUT columns; their outputs are partial sums every rank adds up
   uint8_t* peers[8];
   unsigned long long off_attn, off_h, off_act, off_xa, off_xb, off_xbar;  // byte offsets in the exchange block
+  unsigned long long off_ph, off_pd;  // paired: fp32 partial sums of o / down, [world][d_model] each
   const __half* x_in;
   __half* x_out;
   __half *qkv, *attn, *h, *act, *xa, *xb;  // local copies (attn .. xb inside the local exchange block)
@@ -166,8 +168,13 @@ struct ProjShape {
 };
 __device__ __forceinline__ ProjShape proj_shape(const MegaArgs& a, int kind) {
   ProjShape p;
-  p.N = kind == kQkv ? 3 * a.d_local : kind == kGu ? 2 * a.ffn_local : a.d_local;
-  p.K = kind == kDown ? a.ffn : a.d_model;
+  if (a.paired) {
+    p.N = kind == kQkv ? 3 * a.d_local : kind == kGu ? 2 * a.ffn_local : a.d_model;
+    p.K = kind == kDown ? a.ffn_local : kind == kO ? a.d_local : a.d_model;
+  } else {
+    p.N = kind == kQkv ? 3 * a.d_local : kind == kGu ? 2 * a.ffn_local : a.d_local;
+    p.K = kind == kDown ? a.ffn : a.d_model;
+  }
   p.C = p.N / kStripN;
   p.S = (p.K + kBoxK - 1) / kBoxK;
   p.I = p.C * p.S;
@@ -503,6 +510,32 @@ __device__ void digitise_x(Ctx& c, int d) {
   }
 }
 
+// Where a projection's input vector comes from: a plain fp16 vector, or (paired sharding) a residual
+// plus the ranks' fp32 partial sums of the projection before: v = resid + fp16(sum over ranks, in rank
+// order).  CTA 0 also stores the assembled vector (it is the residual of a later sum).
+struct Src {
+  const __half* x;
+  const float* partials;  // [world][stride] or null
+  int world, stride;
+  __half* store;
+};
+__device__ __forceinline__ uint4 fetch8(const Src& s, int i) {
+  uint4 xv = __ldcg(reinterpret_cast<const uint4*>(s.x + i));
+  if (s.partials == nullptr) return xv;
+  float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+  for (int r = 0; r < s.world; ++r) {
+    const float4 p0 = __ldcg(reinterpret_cast<const float4*>(s.partials + (size_t)r * s.stride + i));
+    const float4 p1 = __ldcg(reinterpret_cast<const float4*>(s.partials + (size_t)r * s.stride + i + 4));
+    acc[0] += p0.x; acc[1] += p0.y; acc[2] += p0.z; acc[3] += p0.w;
+    acc[4] += p1.x; acc[5] += p1.y; acc[6] += p1.z; acc[7] += p1.w;
+  }
+  __half2* h = reinterpret_cast<__half2*>(&xv);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __hadd2(__floats2half2_rn(acc[2 * j], acc[2 * j + 1]), h[j]);
+  if (s.store != nullptr && blockIdx.x == 0) *reinterpret_cast<uint4*>(s.store + i) = xv;
+  return xv;
+}
+
 constexpr int kRegChunks = 4;  // chunks of 8 inputs a thread can hold: vectors up to 4 * 8 * 32 * kCW inputs
 
 // Block-wide reduction of one float per thread over the consumer warps (slot: 0 sum, 1 max).
@@ -547,7 +580,7 @@ __device__ __forceinline__ void consumer_reduce2(Ctx& c, float& a, float& b) {
 // NORM: the reference RMSNorm first, xs = fp16(v * rsqrt(mean(v^2) + eps) * gamma), fp32 statistics.
 // Vectors of up to kRegChunks chunks per thread stay in registers between the passes.
 template <bool NORM>
-__device__ void load_x(Ctx& c, const __half* x, const __half* gamma, int d) {
+__device__ void load_x(Ctx& c, const Src& src, const __half* gamma, int d) {
   const int padded = (d + kBoxK - 1) / kBoxK * kBoxK;
   const int chunks = padded / 8;
   if (chunks > kRegChunks * kCW * 32) {
@@ -555,7 +588,7 @@ __device__ void load_x(Ctx& c, const __half* x, const __half* gamma, int d) {
     float ss = 0.0f;
     for (int i = threadIdx.x * 8; i < padded; i += kCW * 32 * 8) {
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (i < d) v = __ldcg(reinterpret_cast<const uint4*>(x + i));
+      if (i < d) v = fetch8(src, i);
       *reinterpret_cast<uint4*>(c.xs + i) = v;
       const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
@@ -599,7 +632,7 @@ __device__ void load_x(Ctx& c, const __half* x, const __half* gamma, int d) {
       v[r] = make_uint4(0u, 0u, 0u, 0u);
       gv[r] = make_uint4(0u, 0u, 0u, 0u);
       if (ci * 8 < d) {
-        v[r] = __ldcg(reinterpret_cast<const uint4*>(x + ci * 8));
+        v[r] = fetch8(src, ci * 8);
         gv[r] = __ldg(reinterpret_cast<const uint4*>(gamma + ci * 8));
       }
       const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
@@ -631,7 +664,7 @@ __device__ void load_x(Ctx& c, const __half* x, const __half* gamma, int d) {
     for (int r = 0; r < kRegChunks; ++r) {
       const int ci = threadIdx.x + r * kCW * 32;
       v[r] = make_uint4(0u, 0u, 0u, 0u);
-      if (ci * 8 < d) v[r] = __ldcg(reinterpret_cast<const uint4*>(x + ci * 8));
+      if (ci * 8 < d) v[r] = fetch8(src, ci * 8);
       const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -726,6 +759,7 @@ struct Dest {
   __half* local;
   unsigned long long off;  // byte offset in the exchange block of output 0 of this rank's shard
   bool all;
+  bool partial;  // the outputs are fp32 partial sums (paired sharding): no rounding, no residual here
 };
 __device__ __forceinline__ void store_out(const MegaArgs& a, const Dest& dst, int idx, __half v) {
   if (dst.all) {
@@ -741,6 +775,11 @@ __device__ __forceinline__ void finish_strip(const MegaArgs& a, int kind, int st
                                              __half resid, const Dest& out) {
   const int lane = threadIdx.x & 31;
   const int n = strip * kStripN + lane;
+  if (out.partial) {
+    if (lane < kStripN)
+      for (int r = 0; r < a.world; ++r) reinterpret_cast<float*>(a.peers[r] + out.off)[n] = v * sx;
+    return;
+  }
   const __half r = __float2half_rn(v * sx);
   if (kind == kGu) {
     // rows interleave gate_i, up_i: even lanes hold the gate, the next lane its up value
@@ -1277,9 +1316,13 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
         pk.x = *reinterpret_cast<uint32_t*>(&r01);
         pk.y = *reinterpret_cast<uint32_t*>(&r23);
         // this rank's heads sit at rank * d_local in the full vector, which every rank needs
-        const size_t at = (size_t)a.rank * a.d_local + (size_t)head * kHeadDim + 4 * lane;
-        for (int r = 0; r < a.world; ++r)
-          *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(a.peers[r] + a.off_attn) + at) = pk;
+        if (a.paired) {  // o is split by input columns: this rank's heads are all it reads
+          *reinterpret_cast<uint2*>(a.attn + (size_t)head * kHeadDim + 4 * lane) = pk;
+        } else {
+          const size_t at = (size_t)a.rank * a.d_local + (size_t)head * kHeadDim + 4 * lane;
+          for (int r = 0; r < a.world; ++r)
+            *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(a.peers[r] + a.off_attn) + at) = pk;
+        }
         if (trs) trs[11] = globaltimer_ns();
       }
     }
@@ -1346,62 +1389,129 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
     const int d = a.d_model;
     const bool sharded = a.world > 1;
     const size_t shard = (size_t)a.rank * a.d_local;  // first output of this rank in h / x
-    for (int l = 0; l < a.n_layers; ++l) {
-      const MegaLayer* ly = a.layers + l;
-      const bool last = l + 1 == a.n_layers;
-      const __half* x_cur = l == 0 ? a.x_in : (((l - 1) & 1) ? a.xb : a.xa);
-      // the last layer writes the caller's vector directly, unless peers have to write it too
-      __half* x_next = (last && !sharded) ? a.x_out : ((l & 1) ? a.xb : a.xa);
-      const Dest d_qkv{a.qkv, 0ull, false};
-      const Dest d_h{a.h + shard, a.off_h + shard * 2, sharded};
-      const Dest d_act{a.act + (size_t)a.rank * a.ffn_local, a.off_act + (size_t)a.rank * a.ffn_local * 2, sharded};
-      const Dest d_x{x_next + shard, ((l & 1) ? a.off_xb : a.off_xa) + shard * 2, sharded};
-      c.op_index = l * kOpsPerLayer;
-      trace_mark(c, 0);
-      load_x<true>(c, x_cur, ly->norm1, d);
-      trace_mark(c, 1);
-      run_projection(c, kQkv, nullptr, d_qkv);
-      trace_mark(c, 2);
-      grid_barrier(c);  // q, k, v stay on this rank
-      trace_mark(c, 3);
+    if (!a.paired) {
+      for (int l = 0; l < a.n_layers; ++l) {
+        const MegaLayer* ly = a.layers + l;
+        const bool last = l + 1 == a.n_layers;
+        const __half* x_cur = l == 0 ? a.x_in : (((l - 1) & 1) ? a.xb : a.xa);
+        // the last layer writes the caller's vector directly, unless peers have to write it too
+        __half* x_next = (last && !sharded) ? a.x_out : ((l & 1) ? a.xb : a.xa);
+        const Dest d_qkv{a.qkv, 0ull, false, false};
+        const Dest d_h{a.h + shard, a.off_h + shard * 2, sharded, false};
+        const Dest d_act{a.act + (size_t)a.rank * a.ffn_local, a.off_act + (size_t)a.rank * a.ffn_local * 2, sharded, false};
+        const Dest d_x{x_next + shard, ((l & 1) ? a.off_xb : a.off_xa) + shard * 2, sharded, false};
+        c.op_index = l * kOpsPerLayer;
+        trace_mark(c, 0);
+        load_x<true>(c, Src{x_cur, nullptr, 0, 0, nullptr}, ly->norm1, d);
+        trace_mark(c, 1);
+        run_projection(c, kQkv, nullptr, d_qkv);
+        trace_mark(c, 2);
+        grid_barrier(c);  // q, k, v stay on this rank
+        trace_mark(c, 3);
 
-      c.op_index += 1;
-      trace_mark(c, 0);
-      run_attention(c, ly);
-      trace_mark(c, 2);
-      grid_barrier(c, true);
-      trace_mark(c, 3);
+        c.op_index += 1;
+        trace_mark(c, 0);
+        run_attention(c, ly);
+        trace_mark(c, 2);
+        grid_barrier(c, true);
+        trace_mark(c, 3);
 
-      c.op_index += 1;
-      trace_mark(c, 0);
-      load_x<false>(c, a.attn, nullptr, d);
-      trace_mark(c, 1);
-      run_projection(c, kO, x_cur + shard, d_h);
-      trace_mark(c, 2);
-      grid_barrier(c, true);
-      trace_mark(c, 3);
+        c.op_index += 1;
+        trace_mark(c, 0);
+        load_x<false>(c, Src{a.attn, nullptr, 0, 0, nullptr}, nullptr, d);
+        trace_mark(c, 1);
+        run_projection(c, kO, x_cur + shard, d_h);
+        trace_mark(c, 2);
+        grid_barrier(c, true);
+        trace_mark(c, 3);
 
-      c.op_index += 1;
-      trace_mark(c, 0);
-      load_x<true>(c, a.h, ly->norm2, d);
-      trace_mark(c, 1);
-      run_projection(c, kGu, nullptr, d_act);
-      trace_mark(c, 2);
-      grid_barrier(c, true);
-      trace_mark(c, 3);
+        c.op_index += 1;
+        trace_mark(c, 0);
+        load_x<true>(c, Src{a.h, nullptr, 0, 0, nullptr}, ly->norm2, d);
+        trace_mark(c, 1);
+        run_projection(c, kGu, nullptr, d_act);
+        trace_mark(c, 2);
+        grid_barrier(c, true);
+        trace_mark(c, 3);
 
-      c.op_index += 1;
-      trace_mark(c, 0);
-      load_x<false>(c, a.act, nullptr, a.ffn);
-      trace_mark(c, 1);
-      run_projection(c, kDown, a.h + shard, d_x);
-      trace_mark(c, 2);
-      grid_barrier(c, true);
-      trace_mark(c, 3);
-      if (last && sharded && blockIdx.x == 0) {
-        // the step's result, assembled from all ranks' shards, goes to the caller's vector
-        for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8)
-          *reinterpret_cast<uint4*>(a.x_out + i) = __ldcg(reinterpret_cast<const uint4*>(x_next + i));
+        c.op_index += 1;
+        trace_mark(c, 0);
+        load_x<false>(c, Src{a.act, nullptr, 0, 0, nullptr}, nullptr, a.ffn);
+        trace_mark(c, 1);
+        run_projection(c, kDown, a.h + shard, d_x);
+        trace_mark(c, 2);
+        grid_barrier(c, true);
+        trace_mark(c, 3);
+        if (last && sharded && blockIdx.x == 0) {
+          // the step's result, assembled from all ranks' shards, goes to the caller's vector
+          for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8)
+            *reinterpret_cast<uint4*>(a.x_out + i) = __ldcg(reinterpret_cast<const uint4*>(x_next + i));
+        }
+      }
+    } else {
+      // Paired sharding: q/k/v and gate/up are split by outputs, o and down by inputs, so attention's
+      // output and the activations never leave the rank; o and down produce fp32 partial sums of the
+      // whole vector, stored on every rank, and the next vector load adds them up (rank order) onto the
+      // residual.  Two barriers of a layer span the ranks instead of four.
+      const float* ph = reinterpret_cast<const float*>(a.peers[a.rank] + a.off_ph);
+      const float* pd = reinterpret_cast<const float*>(a.peers[a.rank] + a.off_pd);
+      const Dest d_qkv{a.qkv, 0ull, false, false};
+      const Dest d_act{a.act, 0ull, false, false};
+      const Dest d_ph{nullptr, a.off_ph + (size_t)a.rank * d * 4, true, true};
+      const Dest d_pd{nullptr, a.off_pd + (size_t)a.rank * d * 4, true, true};
+      for (int l = 0; l < a.n_layers; ++l) {
+        const MegaLayer* ly = a.layers + l;
+        // layer input: the caller's vector, or h of the layer before (a.h) plus its down partials; kept in
+        // a.xa because it is the residual of this layer's h
+        const Src s_x = l == 0 ? Src{a.x_in, nullptr, 0, 0, nullptr} : Src{a.h, pd, a.world, d, a.xa};
+        const __half* x_res = l == 0 ? a.x_in : a.xa;
+        c.op_index = l * kOpsPerLayer;
+        trace_mark(c, 0);
+        load_x<true>(c, s_x, ly->norm1, d);
+        trace_mark(c, 1);
+        run_projection(c, kQkv, nullptr, d_qkv);
+        trace_mark(c, 2);
+        grid_barrier(c);
+        trace_mark(c, 3);
+
+        c.op_index += 1;
+        trace_mark(c, 0);
+        run_attention(c, ly);
+        trace_mark(c, 2);
+        grid_barrier(c);
+        trace_mark(c, 3);
+
+        c.op_index += 1;
+        trace_mark(c, 0);
+        load_x<false>(c, Src{a.attn, nullptr, 0, 0, nullptr}, nullptr, a.d_local);
+        trace_mark(c, 1);
+        run_projection(c, kO, nullptr, d_ph);
+        trace_mark(c, 2);
+        grid_barrier(c, true);
+        trace_mark(c, 3);
+
+        c.op_index += 1;
+        trace_mark(c, 0);
+        load_x<true>(c, Src{x_res, ph, a.world, d, a.h}, ly->norm2, d);  // h = x + o
+        trace_mark(c, 1);
+        run_projection(c, kGu, nullptr, d_act);
+        trace_mark(c, 2);
+        grid_barrier(c);
+        trace_mark(c, 3);
+
+        c.op_index += 1;
+        trace_mark(c, 0);
+        load_x<false>(c, Src{a.act, nullptr, 0, 0, nullptr}, nullptr, a.ffn_local);
+        trace_mark(c, 1);
+        run_projection(c, kDown, nullptr, d_pd);
+        trace_mark(c, 2);
+        grid_barrier(c, true);
+        trace_mark(c, 3);
+      }
+      if (blockIdx.x == 0) {
+        // the step's result: h of the last layer plus its down partials
+        const Src s_out{a.h, pd, a.world, d, a.x_out};
+        for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8) fetch8(s_out, i);
       }
     }
   }
@@ -1486,8 +1596,9 @@ struct MegaDecoder {
   uint8_t* scratch;
   uint8_t* xchg;              // exchange block (vectors every rank needs + the cross-rank barrier counter)
   uint8_t* peers[8];          // every rank's exchange block as mapped here (own entry = xchg)
-  size_t off_attn, off_h, off_act, off_xa, off_xb, off_xbar;
+  size_t off_attn, off_h, off_act, off_xa, off_xb, off_xbar, off_ph, off_pd;
   int heads_local, d_local, ffn_local;
+  bool paired;
   bool peers_ready;
   uint8_t* prepared;          // re-tiled weights of all layers
   size_t proj_bytes[4], layer_bytes;
@@ -1504,6 +1615,7 @@ bool mega_supported(const MegaConfig& c) {
   if (c.d_model != c.heads * kHeadDim) return false;
   if (c.world < 1 || c.world > 8 || c.rank < 0 || c.rank >= c.world) return false;
   if (c.heads % c.world != 0 || c.ffn % (32 * c.world) != 0) return false;
+  if (c.shard_layout == 1 && ((c.d_model / c.world) % c.block != 0 || (c.ffn / c.world) % c.block != 0)) return false;
   if (c.block != 32 && c.block != 64 && c.block != 128 && c.block != 256) return false;
   if (c.d_model % c.block != 0 || c.ffn % c.block != 0) return false;
   return get_encode_tiled() != nullptr;
@@ -1535,6 +1647,7 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   m->heads_local = cfg.heads / cfg.world;
   m->d_local = cfg.d_model / cfg.world;
   m->ffn_local = cfg.ffn / cfg.world;
+  m->paired = cfg.world > 1 && cfg.shard_layout == 1;
   m->sms = sm_count(cfg.device);
   // shared memory: ring + max(input vector padded to whole boxes, per-warp attention scratch) + unit sums +
   // run slots + rope table + barriers
@@ -1608,9 +1721,11 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   m->off_xa = take((size_t)d * 2);
   m->off_xb = take((size_t)d * 2);
   m->off_xbar = take(8);
+  m->off_ph = take(m->paired ? (size_t)cfg.world * d * 4 : 0);
+  m->off_pd = take(m->paired ? (size_t)cfg.world * d * 4 : 0);
   const size_t xchg_bytes = off;
-  const int Ns[4] = {3 * dl, dl, 2 * fl, dl};
-  const int Ks[4] = {d, d, d, ffn};
+  const int Ns[4] = {3 * dl, m->paired ? d : dl, 2 * fl, m->paired ? d : dl};
+  const int Ks[4] = {d, m->paired ? dl : d, d, m->paired ? fl : ffn};
   m->layer_bytes = 0;
   for (int i = 0; i < 4; ++i) {
     m->proj_bytes[i] = (size_t)(Ns[i] / kStripN) * div_up(Ks[i], kBoxK) * kStageBytes;
@@ -1648,8 +1763,8 @@ int mega_set_layer(MegaDecoder* m, int layer, const MegaLayerPtrs& p) {
   MegaLayer& L = m->h_layers[layer];
   memset(&L, 0, sizeof L);
   const int d = c.d_model, ffn = c.ffn;
-  const int Ns[4] = {3 * m->d_local, m->d_local, 2 * m->ffn_local, m->d_local};
-  const int Ks[4] = {d, d, d, ffn};
+  const int Ns[4] = {3 * m->d_local, m->paired ? d : m->d_local, 2 * m->ffn_local, m->paired ? d : m->d_local};
+  const int Ks[4] = {d, m->paired ? m->d_local : d, d, m->paired ? m->ffn_local : ffn};
   const void* ws[4] = {p.wqkv, p.wo, p.wgu, p.wdown};
   const void* ss[4] = {p.sqkv, p.so, p.sgu, p.sdown};
   uint8_t* dst = m->prepared + (size_t)layer * m->layer_bytes;
@@ -1743,6 +1858,9 @@ int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream
   a.rank = c.rank;
   a.d_local = m->d_local;
   a.ffn_local = m->ffn_local;
+  a.paired = m->paired ? 1 : 0;
+  a.off_ph = m->off_ph;
+  a.off_pd = m->off_pd;
   for (int r = 0; r < 8; ++r) a.peers[r] = m->peers[r];
   a.off_attn = m->off_attn;
   a.off_h = m->off_h;

@@ -733,7 +733,8 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
                                        : (mode != nullptr && strcmp(mode, "mega") == 0 && nccl_id128 == nullptr);
   if (want_mega) {
     MegaConfig mc = {d->layers, d->d_model, d->heads, d->head_dim, d->ffn, d->max_seq, d->block,
-                     d->rms_eps, d->rope_min_timescale, d->rope_max_timescale, device, d->rank, d->world};
+                     d->rms_eps, d->rope_min_timescale, d->rope_max_timescale, device, d->rank, d->world,
+                     d->shard_layout};
     if (mega_supported(mc)) {
       const int mrc = mega_create(mc, &dec->mega);
       if (mrc != MLD_OK) {
@@ -744,6 +745,12 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
         }
       }
     }
+  }
+  if (d->world > 1 && d->shard_layout != 0 && dec->mega == nullptr) {
+    set_last_error_text("shard_layout 1 (o and down split by input columns) needs the single-kernel decoder: "
+                        "MLD_DECODER_MODE=mega and no NCCL id");
+    mld_decoder_destroy(dec);
+    return MLD_UNIMPLEMENTED;
   }
   *out = dec;
   return MLD_OK;

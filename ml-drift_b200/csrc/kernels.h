@@ -105,7 +105,8 @@ struct MegaConfig {
   int layers, d_model, heads, head_dim, ffn, max_seq, block;
   float rms_eps, rope_min_timescale, rope_max_timescale;
   int device;
-  int rank, world;  // column sharding: heads, o/down outputs and FFN units are split evenly over the ranks
+  int rank, world;  // sharding: heads, o/down outputs and FFN units are split evenly over the ranks
+  int shard_layout; // 0: every projection split by output rows; 1: o and down split by input columns
 };
 struct MegaLayerPtrs {
   const void *wqkv, *sqkv, *wo, *so, *wgu, *sgu, *wdown, *sdown, *norm1, *norm2;

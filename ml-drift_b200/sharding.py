@@ -52,3 +52,11 @@ def gathered_order(kind: str, rank_outputs):
         return np.concatenate([np.concatenate([o[0::2] for o in outs]), np.concatenate([o[1::2] for o in outs])])
     split = [np.split(np.asarray(o), 3) for o in rank_outputs]
     return np.concatenate([np.concatenate([s[p] for s in split]) for p in range(3)])
+
+
+def input_shard_cols(k: int, rank: int, world: int) -> np.ndarray:
+    """Input columns of a projection split by inputs (shard_layout 1: o takes the columns of the rank's
+    heads, down the columns of the rank's FFN units): a contiguous K / world slice."""
+    assert k % world == 0
+    per = k // world
+    return np.arange(rank * per, (rank + 1) * per, dtype=np.int64)

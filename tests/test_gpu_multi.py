@@ -25,19 +25,28 @@ def _model(rng, L, heads, ffn, T):
     return layers, kc, vc
 
 
-def _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id):
+def _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id, shard_layout=0):
     shd = mld.sharding
     d = heads * 128
     dev = torch.device("cuda", torch.cuda.current_device())
-    dec = mld.Decoder(len(layers), d, heads, ffn, T, rank=rank, world=world, nccl_id=nccl_id)
+    dec = mld.Decoder(len(layers), d, heads, ffn, T, rank=rank, world=world, nccl_id=nccl_id,
+                      shard_layout=shard_layout)
     rows = {"qkv": shd.qkv_shard_rows(heads, 128, rank, world), "o": shd.column_shard_rows(d, rank, world),
             "gu": shd.gate_up_shard_rows(ffn, rank, world), "down": shd.column_shard_rows(d, rank, world)}
+    in_cols = {"qkv": None, "gu": None, "o": None, "down": None}
+    if shard_layout == 1:     # o and down keep all rows and take the input columns of the rank's heads / FFN units
+        rows["o"] = rows["down"] = np.arange(d)
+        in_cols["o"] = shd.input_shard_cols(d, rank, world)
+        in_cols["down"] = shd.input_shard_cols(ffn, rank, world)
     cols = shd.column_shard_rows(d, rank, world)
     keep = []
     for l, layer in enumerate(layers):
         t = {}
         for n in ("qkv", "o", "gu", "down"):
-            w = torch.from_numpy(np.ascontiguousarray(layer[n][rows[n]])).to(dev)
+            wn = layer[n][rows[n]]
+            if in_cols[n] is not None:
+                wn = wn[:, in_cols[n]]
+            w = torch.from_numpy(np.ascontiguousarray(wn)).to(dev)
             q, s = mld.quantize_weights(w, 4, 32)
             t["w" + n], _ = mld.pack_weights(q, (w.shape[0], 1, 1, w.shape[1]), 4)
             t["s" + n] = mld.pack_scales(s, True)
@@ -63,7 +72,8 @@ def _worker(rank, world, port, out_dir, exchange):
     nccl_id = None
     # "mega": every rank runs the whole step as one persistent kernel, shards go to the peers with plain
     # stores and the kernel's barriers span the ranks; "peer" / "nccl": the chain of kernels
-    os.environ["MLD_DECODER_MODE"] = "mega" if exchange == "mega" else "ops"
+    os.environ["MLD_DECODER_MODE"] = "mega" if exchange.startswith("mega") else "ops"
+    layout = 1 if exchange == "mega_paired" else 0
     if exchange == "nccl":
         idt = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:
@@ -74,9 +84,9 @@ def _worker(rank, world, port, out_dir, exchange):
     d = heads * 128
     layers, kc, vc = _model(np.random.default_rng(0), L, heads, ffn, T)
     x = torch.from_numpy(np.random.default_rng(1).standard_normal(d).astype(np.float16)).cuda()
-    dec, keep = _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id)
-    assert dec.single_kernel == (exchange == "mega")
-    if exchange in ("peer", "mega"):         # shards go straight into every rank's exchange block
+    dec, keep = _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id, layout)
+    assert dec.single_kernel == exchange.startswith("mega")
+    if exchange in ("peer", "mega", "mega_paired"):         # shards go straight into every rank's exchange block
         mine = torch.frombuffer(bytearray(dec.ipc_export()), dtype=torch.uint8).clone()
         table = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
         dist.all_gather(table, mine)
@@ -109,10 +119,10 @@ def _worker(rank, world, port, out_dir, exchange):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("exchange", ["nccl", "peer", "mega"])
+@pytest.mark.parametrize("exchange", ["nccl", "peer", "mega", "mega_paired"])
 def test_two_gpu_sharded_decode_equals_single_gpu(tmp_path, exchange):
     import torch.multiprocessing as mp
-    port = 29700 + (os.getpid() % 2000) + {"nccl": 0, "peer": 7, "mega": 13}[exchange]
+    port = 29700 + (os.getpid() % 2000) + {"nccl": 0, "peer": 7, "mega": 13, "mega_paired": 19}[exchange]
     mp.spawn(_worker, args=(2, port, str(tmp_path), exchange), nprocs=2, join=True)
     err, finite, same = open(tmp_path / "result.txt").read().split()
     assert int(finite) == 1
