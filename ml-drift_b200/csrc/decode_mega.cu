@@ -4,39 +4,42 @@
 // projection drains its TMA pipeline, the next one fills it again, and the
 // weights of a projection (8-45 MB) stream for only a few microseconds.  Here
 // one cooperative grid of one CTA per SM runs all layers:
-//   * a producer thread per CTA walks the step's whole list of weight and
-//     KV-cache tiles this CTA will need, in order, and keeps a ~185 KB ring of
-//     TMA boxes full.  Nothing it loads depends on the step's activations, so
-//     it runs ahead across op and layer boundaries: HBM stays busy while the
-//     consumers finish an op, cross the grid barrier and load the next input
-//     vector;
-//   * eight consumer warps per CTA do the arithmetic of every op:
+//   * a producer thread per CTA walks the step's whole list of weight boxes and
+//     KV-cache tiles this CTA will need, in order, and keeps a ring of 9 KB
+//     stages (about 170 KB) full.  Nothing it loads depends on the step's
+//     activations, so it runs ahead across op and layer boundaries;
+//   * the consumer warps do the arithmetic of every op:
 //       qkv  = Wqkv rmsnorm(x) g1                 (RMSNorm fused into the vector load)
 //       attn = softmax(rope(q) K^T) V             (new k/v roped, written to the cache)
 //       h    = x + Wo attn
 //       act  = silu(Wg hn) * (Wu hn), hn = rmsnorm(h) g2
 //       x'   = h + Wdown act
-//     with a grid barrier after each (five per layer);
-//   * work is split in items of one ring stage: a projection's boxes of 16
-//     outputs x 1024 inputs, attention's (head, 32-token tile) pairs.  A CTA owns
-//     whole 16-output strips of a projection (all of K), so projections need
-//     nothing from other CTAs; a head of attention is shared between CTAs and
-//     completed by whichever of them finishes last (a ticket), summing the
-//     partial results in CTA order, so results do not depend on arrival order;
+//     with a grid barrier after each (five per layer), after which every CTA
+//     loads the op's input vector;
+//   * work is split in items of one ring stage, each consumed by one warp: a
+//     projection's boxes of 16 outputs x 1024 inputs, attention's (head,
+//     32-token tile) pairs.  A CTA owns whole 16-output strips of a projection
+//     (all of K), so projections need nothing from other CTAs; a head of
+//     attention is shared by a group of CTAs whose partial results are merged in
+//     a fixed order, so results do not depend on arrival order;
 //   * the decoder keeps its own copy of the projection weights, re-tiled from
 //     the reference layout when a layer is set: box after box, 8 KB of nibbles
 //     in the order the MMA fragments want them followed by the 1 KB of scales
 //     they need, strip after strip.  A box is one contiguous 9 KB bulk copy and a
-//     CTA's share of a projection one contiguous stream.
+//     CTA's share of a projection one contiguous stream;
+//   * sharded over several GPUs, every rank runs this kernel on its shard,
+//     stores what the other ranks need straight into their memory and the
+//     barriers after such an exchange span the ranks.
 //
-// Projection arithmetic is the streaming GEMV's (gemv_stream.cu): weights as
-// the MMA A operand straight from the packed INT4 bytes (fp16 subnormals),
-// fp32 accumulation, one scale multiply per 32-input block.  Restated from
-// GetFullyConnectedKernelCode (ml_drift/common/kernels/fully_connected.cc:623-942)
-// and the decoder graph of samples/llm/qwen3_model_builder.cc:880-1017.
+// Projection arithmetic: the dequantisation of GetFullyConnectedKernelCode
+// (ml_drift/common/kernels/fully_connected.cc:623-942), w = (u - 8) * scale
+// per block of 32 inputs, as sum(u * x) - 8 * sum(x) per block times the scale:
+// the sums are exact integer MMAs over the nibbles and the input vector in
+// 16-bit fixed point (see digitise_x), the scale is applied in fp32.  The
+// decoder graph is that of samples/llm/qwen3_model_builder.cc:880-1017.
 //
-// Every wait (ring barriers, grid barrier) is bounded; when one runs out the
-// CTA records an error code, stops waiting and runs to the end.
+// Every wait (ring barriers, flags, grid barriers) is bounded; when one runs
+// out the CTA records an error code, stops waiting and runs to the end.
 #include <cuda_fp16.h>
 
 #include <cstdlib>

@@ -69,3 +69,13 @@ def test_shard_row_helpers():
     import pytest
     with pytest.raises(ValueError):
         shd.column_shard_rows(10, 0, 4)
+
+
+def test_input_shard_cols_partition_the_inputs():
+    """shard_layout 1: o / down take contiguous input-column slices that tile K exactly."""
+    import __graft_entry__ as g
+    shd = g.import_package().sharding
+    for k, world in ((4096, 2), (11008, 8), (512, 4)):
+        cols = [shd.input_shard_cols(k, r, world) for r in range(world)]
+        assert np.array_equal(np.concatenate(cols), np.arange(k))
+        assert all(len(c) == k // world for c in cols)
