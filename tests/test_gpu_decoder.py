@@ -103,6 +103,63 @@ def test_decode_step_matches_oracle(mld, oracle, monkeypatch, mode, L, heads, ff
     dec.close()
 
 
+# Small grids reach the work splits a full B200 grid does not: fewer CTAs than heads (heads shared out
+# item by item, several heads per CTA, ticketed merge), a handful of CTAs per head, one CTA for everything;
+# and the last row of the cache (its tile is cut off by the end of the tensor).
+@pytest.mark.parametrize("grid,heads,ffn,T,pos", [
+    (3, 4, 512, 200, 130),
+    (2, 2, 256, 96, 95),
+    (8, 2, 384, 160, 159),
+    (37, 4, 1408, 300, 299),
+])
+def test_single_kernel_step_on_small_grids(mld, oracle, monkeypatch, grid, heads, ffn, T, pos):
+    from oracle import decode_ref
+    monkeypatch.setenv("MLD_MEGA_GRID", str(grid))
+    rng = np.random.default_rng(grid)
+    L, d = 2, heads * 128
+    layers_ref, dec_tensors, kc, vc = build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos)
+    x = rng.standard_normal(d).astype(np.float16)
+    kcd, vcd = _dev(kc), _dev(vc)
+    dec = _make(mld, monkeypatch, "mega", L, d, heads, ffn, T, 32, dec_tensors, kcd, vcd)
+    y = torch.empty(d, dtype=torch.float16, device="cuda")
+    dec.step(_dev(x), y, pos)
+    torch.cuda.synchronize()
+    assert dec.device_status() == 0
+    kref, vref = kc.astype(np.float32), vc.astype(np.float32)
+    ref = decode_ref.decode_step(x.astype(np.float32), layers_ref, kref, vref, pos, heads, 128, ffn)
+    got = y.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) < 1e-2
+    assert np.max(np.abs(kcd[:, pos].float().cpu().numpy() - kref[:, pos])) < 2e-2
+    dec.close()
+
+
+def test_single_kernel_step_ignores_uninitialised_cache_rows(mld, oracle, monkeypatch):
+    """Rows of the cache past the current position may hold anything (NaN included): they must not reach
+    the result."""
+    from oracle import decode_ref
+    rng = np.random.default_rng(11)
+    L, heads, ffn, T, pos = 1, 2, 256, 128, 37
+    d = heads * 128
+    layers_ref, dec_tensors, kc, vc = build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos)
+    x = rng.standard_normal(d).astype(np.float16)
+    kbad, vbad = kc.copy(), vc.copy()
+    kbad[:, pos + 1:] = np.nan
+    vbad[:, pos + 1:] = np.nan
+    kcd, vcd = _dev(kbad), _dev(vbad)
+    dec = _make(mld, monkeypatch, "mega", L, d, heads, ffn, T, 32, dec_tensors, kcd, vcd)
+    y = torch.empty(d, dtype=torch.float16, device="cuda")
+    dec.step(_dev(x), y, pos)
+    torch.cuda.synchronize()
+    assert dec.device_status() == 0
+    ref = decode_ref.decode_step(x.astype(np.float32), layers_ref, kc.astype(np.float32), vc.astype(np.float32),
+                                 pos, heads, 128, ffn)
+    got = y.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) < 1e-2
+    dec.close()
+
+
 def test_single_kernel_step_agrees_with_op_chain(mld, oracle, monkeypatch):
     """Both decoders on the same model and cache: same result within fp16 rounding of the partial sums'
     different order, same cache rows."""
