@@ -465,6 +465,16 @@ def run_ours(args):
     status = dec.device_status()
     if status != 0:
         raise RuntimeError(f"a device-side wait gave up (code {status}); the timing is void")
+    ranks_agree = None
+    if world > 1:
+        # every rank assembled the same output vector from the shards (bit for bit), and it is finite
+        dec.step(x, y, pos)
+        torch.cuda.synchronize()
+        ys = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(ys, y)
+        ranks_agree = bool(all(torch.equal(ys[0], t) for t in ys)) and bool(torch.isfinite(y).all())
+        if not ranks_agree:
+            raise RuntimeError("the ranks' outputs differ or are not finite; the timing is void")
     roof = gemv_roofline(mld, torch, layers, world, peaks, layout) if rank == 0 or world > 1 else None
     if single:
         # the step is one kernel: its roofline is the step's own — every weight, scale and cached K/V
@@ -518,7 +528,7 @@ def run_ours(args):
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": d * 2, "d2h_bytes_per_step": d * 2},
             "gpu_launches": int(launches_per_step) * args.steps,
             "launches_per_step": int(launches_per_step),
-            "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "kernels": side,
+            "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "kernels": side, "ranks_agree": ranks_agree,
         }
         print(json.dumps(line), flush=True)
     # Tear down without collective destructors: every rank has printed / finished its work, and a
