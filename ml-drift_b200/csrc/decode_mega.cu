@@ -63,13 +63,12 @@ constexpr int kStageBytes = kBox + kScaleBox;
 constexpr int kHeadDim = 128;
 constexpr int kTile = 32;                    // cached tokens per attention item (K box, V box: 8 KB each)
 constexpr int kAttSlots = 4;                 // heads a CTA's attention range can touch
-constexpr int kProjSlots = 4;                // column runs whose per-warp sums can be pending at once
+constexpr int kProjCounters = 12;            // >= kCW: arrivals of a shared strip are counted at its first warp
 constexpr int kAttnSlots = 2;                // head runs likewise
 constexpr int kAttDump = kHeadDim + 4;       // 128 outputs, then max and sum (padded: rows stay 16-byte aligned)
-constexpr int kDumpFloats = kProjSlots * kCW * kStripN > kAttnSlots * kCW * kAttDump ? kProjSlots * kCW * kStripN
-                                                                                : kAttnSlots * kCW * kAttDump;
+constexpr int kDumpFloats = 2 * kCW * kStripN > kAttnSlots * kCW * kAttDump ? 2 * kCW * kStripN : kAttnSlots * kCW * kAttDump;
 constexpr int kWarpScratch = 3 * kHeadDim;   // attention: rotated q, new k, new v (floats) per warp
-constexpr int kTraceSlots = 12;              // per (CTA, op): 4 timestamps, wait clocks, stages, all-warps-done time
+constexpr int kTraceSlots = 12;              // per (CTA, op): 4 timestamps, warp 0's clocks, all-warps-done, last load issued
 enum { kQkv = 0, kAttn = 1, kO = 2, kGu = 3, kDown = 4, kOpsPerLayer = 5 };
 
 struct alignas(128) MegaLayer {
@@ -343,15 +342,24 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
         const uint8_t* wbase = ly->w[map_index(kind)];
         int pi0, pi1;
         proj_range(p, cta, G, pi0, pi1);
-        // boxes are stored strip after strip: the CTA's items are one contiguous stream
-        for (int i = pi0; i < pi1; ++i) {
-          w.wait(&empty[r.stage], r.phase ^ 1, 11);
-          uint8_t* st = ring + (size_t)r.stage * kStageBytes;
-          mbar_arrive_expect_tx(&full[r.stage], kStageBytes);
-          bulk_load_1d_hint(st, wbase + (size_t)i * kStageBytes, kStageBytes, &full[r.stage], pol);
-          r.advance(a.stages);
+        // boxes are stored strip after strip: the CTA's boxes are one contiguous stream, cut into kCW
+        // chunks (one per consumer warp); ring position kCW j + w takes box j of chunk w
+        const int B = pi1 - pi0, qn = B / kCW, rn = B % kCW;
+        for (int j = 0; j * kCW < B; ++j) {
+          const int nw = B - j * kCW < kCW ? B - j * kCW : kCW;
+          for (int cw = 0; cw < nw; ++cw) {
+            const int i = pi0 + cw * qn + (cw < rn ? cw : rn) + j;
+            w.wait(&empty[r.stage], r.phase ^ 1, 11);
+            uint8_t* st = ring + (size_t)r.stage * kStageBytes;
+            mbar_arrive_expect_tx(&full[r.stage], kStageBytes);
+            bulk_load_1d_hint(st, wbase + (size_t)i * kStageBytes, kStageBytes, &full[r.stage], pol);
+            r.advance(a.stages);
+          }
         }
       }
+      // when this op's last load was issued
+      if (a.trace != nullptr)
+        a.trace[((size_t)blockIdx.x * a.n_layers * kOpsPerLayer + l * kOpsPerLayer + kind) * kTraceSlots + 11] = globaltimer_ns();
     }
   }
 }
@@ -366,22 +374,21 @@ struct Ctx {
   int* isum;           // [box][t][set]: 8 * (sum of the integers of unit 4 set + t of the box), see digitise_x
   float sx;            // scale of the digitised input vector
   const float2* rope;  // [64] (cos, sin) of pos / timescale_i, the rotary embedding of this step
-  float* dump;         // per-warp sums of pending runs: [slot][warp][kStripN] or [slot][warp][kAttDump]
+  float* dump;         // per-warp sums: projections [warp][share (2)][kStripN], attention [slot][warp][kAttDump]
   int* s_int;          // [0] failure flag, [1..] run bookkeeping (see below)
   Waiter w;
   int ring_base;       // stages of this CTA consumed by earlier ops (same in every warp)
-  int proj_runs;       // column runs started so far (selects the dump slot)
   int attn_runs;       // head runs started so far
   unsigned long long bar_target;  // arrival count that completes the barrier this CTA waits for next
   unsigned long long xbar_target; // the same for the barrier across ranks
   unsigned epoch_base;            // unique per launch: op k of this launch has epoch epoch_base + k + 1
   int op_index;
-  __device__ __forceinline__ int* proj_arrived() const { return s_int + 1; }                     // [kProjSlots]
-  __device__ __forceinline__ volatile int* proj_done() const { return s_int + 1 + kProjSlots; }  // [kProjSlots]
-  __device__ __forceinline__ int* attn_arrived() const { return s_int + 1 + 2 * kProjSlots; }    // [kAttnSlots]
-  __device__ __forceinline__ volatile int* attn_done() const { return s_int + 1 + 2 * kProjSlots + kAttnSlots; }
+  __device__ __forceinline__ int* proj_arrived() const { return s_int + 1; }                  // [kProjCounters]
+  __device__ __forceinline__ int* attn_arrived() const { return s_int + 1 + kProjCounters; }  // [kAttnSlots]
+  __device__ __forceinline__ volatile int* attn_done() const { return s_int + 1 + kProjCounters + kAttnSlots; }
 };
-constexpr int kSharedInts = 1 + 2 * kProjSlots + 2 * kAttnSlots;  // (odd) + 5 behind them: pad, two 64-bit barrier bases
+static_assert(kProjCounters >= kCW && kProjCounters % 2 == 0, "one counter per consumer warp, even count");
+constexpr int kSharedInts = 1 + kProjCounters + 2 * kAttnSlots;  // (odd) + 5 behind them: pad, two 64-bit barrier bases
 
 __device__ __forceinline__ void trace_mark(const Ctx& c, int k) {
   if (c.a.trace != nullptr && threadIdx.x == 0)
@@ -695,10 +702,13 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], ui
 }
 
 // One box (16 outputs x 1024 inputs) by one warp.  Lane = 4g + t.  A unit of 32
-// inputs (one scale per output) is exactly one integer MMA m16n8k32: A = the
-// unit's nibbles as bytes (a 32-bit word of the re-tiled weights holds four
-// inputs of row g in its low nibbles and of row g+8 in its high nibbles), B =
-// the digitised inputs, exact in int32.  The 32 units of a box go in eight sets
+// inputs (one scale per output) is exactly one integer MMA m16n8k32.  A 32-bit
+// word of the re-tiled weights holds four inputs of row g in its low nibbles
+// and of row g+8 in its high nibbles; A's rows g take the word as it is (bytes
+// u_g + 16 u_g8) and its rows g+8 the word with the low nibbles cleared (bytes
+// 16 u_g8), so that row g's sum is the difference of the two results and the
+// nibbles are never shifted apart.  B = the digitised inputs; everything is
+// exact in int32.  The 32 units of a box go in eight sets
 // of four; B column 2j holds the high digit and 2j + 1 the low digit of unit j
 // of the set (lane g supplies column g, zero for the other units), so a lane
 // ends a set with both digits of unit t for rows g and g+8, combines them,
@@ -731,7 +741,8 @@ __device__ __forceinline__ void consume_box(const Ctx& c, const uint8_t* st, int
       for (int h = 0; h < 2; ++h) {
         const int us = 2 * (jj & 1) + h;  // unit within the set
         const uint32_t w0 = h ? wv.z : wv.x, w1 = h ? wv.w : wv.y;
-        const uint32_t af[4] = {w0 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu};
+        // rows g: the whole byte (row g's nibble + 16 x row g+8's); rows g+8: 16 x row g+8's nibble
+        const uint32_t af[4] = {w0, w0 & 0xF0F0F0F0u, w1, w1 & 0xF0F0F0F0u};
         const bool mine = (g >> 1) == us;
         mma_u8s8(acc[sidx], af, mine ? xb[sidx].x : 0u, mine ? xb[sidx].y : 0u);
       }
@@ -748,9 +759,10 @@ __device__ __forceinline__ void consume_box(const Ctx& c, const uint8_t* st, int
 #pragma unroll
   for (int sidx = 0; sidx < 8; ++sidx) {
     const float2 sc = __half22float2(sidx < 4 ? sh0[sidx] : sh1[sidx - 4]);
-    // acc: {row g, high digit}, {row g, low digit}, {row g+8, high digit}, {row g+8, low digit}
-    const int r0 = acc[sidx][0] * 256 + acc[sidx][1] - offs[sidx];
-    const int r1 = acc[sidx][2] * 256 + acc[sidx][3] - offs[sidx];
+    // acc: {row g + 16 row g+8, high digit}, {same, low digit}, {16 row g+8, high digit}, {same, low digit};
+    // every term is exact in int32 (|acc| <= 32 * 255 * 128)
+    const int r0 = (acc[sidx][0] - acc[sidx][2]) * 256 + (acc[sidx][1] - acc[sidx][3]) - offs[sidx];
+    const int r1 = ((acc[sidx][2] * 256 + acc[sidx][3]) >> 4) - offs[sidx];
     tot[0] = fmaf(sc.x, static_cast<float>(r0), tot[0]);
     tot[1] = fmaf(sc.y, static_cast<float>(r1), tot[1]);
   }
@@ -794,6 +806,14 @@ __device__ __forceinline__ void finish_strip(const MegaArgs& a, int kind, int st
   }
 }
 
+// Which warp's chunk holds box b of an op whose boxes are cut into kCW chunks: the first rn chunks have
+// qn + 1 boxes, the others qn.
+__device__ __forceinline__ int chunk_owner(int b, int qn, int rn) {
+  const int big = rn * (qn + 1);
+  if (b < big) return static_cast<int>(static_cast<unsigned>(b) / static_cast<unsigned>(qn + 1));
+  return rn + static_cast<int>(static_cast<unsigned>(b - big) / static_cast<unsigned>(qn));  // qn > 0 here
+}
+
 __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest& out) {
   const MegaArgs& a = c.a;
   const ProjShape p = proj_shape(a, kind);
@@ -802,28 +822,34 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
   const int g = lane >> 2, t = lane & 3;
   int i0, i1;
   proj_range(p, cta, G, i0, i1);
-  const int n_runs = (i1 - i0) / p.S;  // whole strips
-  long long waited = 0, boxed = 0;
-  const bool tracing = a.trace != nullptr && threadIdx.x == 0;
-  // this warp takes every kCW-th stage of the op's sequence
-  int q = warp;
+  const int B = i1 - i0;
+  long long waited = 0, boxed = 0, ea = 0, eb = 0, ec = 0;
+  const bool tracing = a.trace != nullptr && lane == 0;  // every warp keeps its own clocks
+  // The op's boxes are cut into kCW contiguous chunks, one per warp (lengths differ by at most one), so
+  // that a warp meets few strips; ring position kCW j + w holds box j of warp w's chunk.
+  const int qn = B / kCW, rn = B % kCW;
+  const int len = qn + (warp < rn ? 1 : 0);
+  const int start = warp * qn + (warp < rn ? warp : rn);
   int pos = c.ring_base + warp;
   int stage = pos % a.stages;
   uint32_t phase = static_cast<uint32_t>(pos / a.stages) & 1u;
-  for (int rr = 0; rr < n_runs; ++rr) {
-    const int strip = i0 / p.S + rr;
-    const int seq_lo = rr * p.S, seq_hi = seq_lo + p.S;
-    if (q >= seq_hi) continue;  // no box of this strip for this warp
+  int b = start;
+  const int b_stop = start + len;
+  while (b < b_stop) {
+    const int sl = b / p.S;  // strip within the CTA's range
+    const int strip = i0 / p.S + sl;
+    const int s_lo = sl * p.S, s_hi = s_lo + p.S;
+    const int b_end = b_stop < s_hi ? b_stop : s_hi;
     // the strip's residual values are fetched now: whichever warp completes the strip has them at hand
     __half rv = __float2half_rn(0.0f);
     if (resid != nullptr && lane < kStripN) rv = __ldcg(resid + strip * kStripN + lane);
     float tot[2] = {0.0f, 0.0f};
-    for (; q < seq_hi; q += kCW) {
+    for (; b < b_end; ++b) {
       const long long w0 = tracing ? clock64() : 0;
       c.w.wait(&c.full[stage], phase, 12);
       if (tracing) waited += clock64() - w0;
       const long long b0 = tracing ? clock64() : 0;
-      consume_box(c, c.ring + (size_t)stage * kStageBytes, q - seq_lo, tot);
+      consume_box(c, c.ring + (size_t)stage * kStageBytes, b - s_lo, tot);
       __syncwarp();
       if (tracing) boxed += clock64() - b0;
       if (lane == 0) mbar_arrive_n(&c.empty[stage], kCW);
@@ -833,22 +859,26 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
         phase ^= 1u;
       }
     }
-    // sum the four unit pairs (lanes t); park this warp's share in the strip's slot
+    const long long e0 = tracing ? clock64() : 0;
+    // sum the four unit pairs (lanes t)
     tot[0] += __shfl_xor_sync(0xffffffffu, tot[0], 1);
     tot[0] += __shfl_xor_sync(0xffffffffu, tot[0], 2);
     tot[1] += __shfl_xor_sync(0xffffffffu, tot[1], 1);
     tot[1] += __shfl_xor_sync(0xffffffffu, tot[1], 2);
-    const int n_part = p.S < kCW ? p.S : kCW;  // warps that have a box of this strip
-    const int run = c.proj_runs + rr, slot = run % kProjSlots, use = run / kProjSlots;
-    if (n_part == 1) {
+    // the warps that hold boxes of this strip: w_lo .. w_hi
+    const int w_lo = chunk_owner(s_lo, qn, rn), w_hi = chunk_owner(s_hi - 1, qn, rn);
+    if (w_lo == w_hi) {
       // the strip is this warp's alone: rows g and g+8 sit in lanes t == 0
       const float lo = __shfl_sync(0xffffffffu, tot[0], (lane & 7) * 4);
       const float hi = __shfl_sync(0xffffffffu, tot[1], (lane & 7) * 4);
       finish_strip(a, kind, strip, (lane & 8) ? hi : lo, c.sx, resid != nullptr, rv, out);
+      if (tracing) ec += clock64() - e0;
       continue;
     }
-    c.w.wait_count(c.proj_done() + slot, use, 15);  // the slot's previous strip has been summed
-    float* mine = c.dump + ((size_t)slot * kCW + warp) * kStripN;
+    // A warp shares at most two strips with others: the one its chunk begins in (share 0) and the one it
+    // ends in (share 1, where it is w_lo).  Each share is written once per op, so nothing waits for a
+    // place; the strip's arrivals are counted at w_lo.
+    float* mine = c.dump + (warp * 2 + (warp == w_lo ? 1 : 0)) * kStripN;
     if (t == 0) {
       mine[g] = tot[0];
       mine[g + 8] = tot[1];
@@ -857,31 +887,31 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
     int last = 0;
     if (lane == 0) {
       __threadfence_block();
-      last = atomicAdd(c.proj_arrived() + slot, 1) == n_part - 1 ? 1 : 0;
+      last = atomicAdd(c.proj_arrived() + w_lo, 1) == w_hi - w_lo ? 1 : 0;
     }
     last = __shfl_sync(0xffffffffu, last, 0);
+    const long long e3 = tracing ? clock64() : 0;
+    if (tracing) ea += e3 - e0;
     if (last) {
-      // the last warp to get here sums the shares in the order of the boxes and completes the strip
+      // the last warp to get here sums the shares in the order of the inputs and completes the strip
       __threadfence_block();
-      const float* all = c.dump + (size_t)slot * kCW * kStripN;
-      float v = 0.0f;
-      for (int k = 0; k < n_part; ++k) v += all[((seq_lo + k) % kCW) * kStripN + (lane & 15)];
-      __syncwarp();
-      if (lane == 0) {
-        c.proj_arrived()[slot] = 0;
-        __threadfence_block();
-        c.proj_done()[slot] = use + 1;
-      }
+      float v = c.dump[(w_lo * 2 + 1) * kStripN + (lane & 15)];
+      for (int w = w_lo + 1; w <= w_hi; ++w) v += c.dump[w * 2 * kStripN + (lane & 15)];
+      if (lane == 0) c.proj_arrived()[w_lo] = 0;  // next used after the op's grid barrier
       finish_strip(a, kind, strip, v, c.sx, resid != nullptr, rv, out);
     }
+    if (tracing) eb += clock64() - e3;
   }
-  if (p.S > 1) c.proj_runs += n_runs;  // single-box strips never use a slot
-  c.ring_base += i1 - i0;
-  if (tracing) {
+  c.ring_base += B;
+  if (tracing && warp == 0) {
     unsigned long long* tr = a.trace + ((size_t)blockIdx.x * a.n_layers * kOpsPerLayer + c.op_index) * kTraceSlots;
     tr[4] = static_cast<unsigned long long>(waited);
-    tr[5] = static_cast<unsigned long long>(i1 - i0);
+    tr[5] = static_cast<unsigned long long>(B);
     tr[7] = static_cast<unsigned long long>(boxed);
+    // warp 0's clocks after its boxes: up to the arrival, after it (the sum, when it is the last), own strips
+    tr[8] = static_cast<unsigned long long>(ea);
+    tr[9] = static_cast<unsigned long long>(eb);
+    tr[10] = static_cast<unsigned long long>(ec);
   }
 }
 
@@ -1384,7 +1414,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
   if (warp == kCW) {
     if (lane == 0) producer_loop(a, ring, full, empty, w);
   } else {
-    Ctx c{a, ring, full, empty, xs, reinterpret_cast<int*>(us), 1.0f, rope, dump, s_int, w, 0, 0, 0, 0ull, 0ull, 0u, 0};
+    Ctx c{a, ring, full, empty, xs, reinterpret_cast<int*>(us), 1.0f, rope, dump, s_int, w, 0, 0, 0ull, 0ull, 0u, 0};
     c.bar_target = *reinterpret_cast<const unsigned long long*>(s_int + kSharedInts + 1);
     c.xbar_target = *reinterpret_cast<const unsigned long long*>(s_int + kSharedInts + 3);
     // every launch completes at least one local barrier, so five epochs per barrier keep launches apart
