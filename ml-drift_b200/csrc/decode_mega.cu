@@ -101,6 +101,11 @@ struct MegaArgs {
   const __half* x_in;
   __half* x_out;
   __half *qkv, *attn, *h, *act, *xa, *xb;  // local copies (attn .. xb inside the local exchange block)
+  // Single GPU: the vectors that pass from op to op are arrays of 32-bit words, fp16 value in the low half
+  // and the writing op's tag in the high half; a reader polls a word until it carries the tag it expects,
+  // so no barrier separates the ops (tagged != 0).
+  int tagged;
+  uint32_t *tq, *tattn, *th, *tact, *txa, *txb;
   float* att_part;     // [grid][kAttSlots][kAttDump]
   int* att_tickets;    // [heads]
   unsigned* att_flags; // [heads][grid / heads]: epoch of the attention whose partial the part has published
@@ -155,6 +160,64 @@ struct Waiter {
     }
   }
 };
+
+// Tag of op number `epoch` (unique over launches): 1 .. 65535, never the 0 of untouched memory.
+__device__ __forceinline__ uint32_t op_tag(unsigned epoch) { return epoch % 65535u + 1u; }
+__device__ __forceinline__ void st_tagged(uint32_t* p, __half v, uint32_t tag) {
+  const uint32_t w = (tag << 16) | static_cast<uint32_t>(__half_as_ushort(v));
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(w) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_word(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_word4(const uint32_t* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// One tagged value, waited for (bounded; code 22).
+__device__ __forceinline__ __half ld_tagged(const Waiter& w, const uint32_t* p, uint32_t tag) {
+  uint32_t v = ld_word(p);
+  if ((v >> 16) != tag && !*w.s_fail) {
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+      v = ld_word(p);
+      if ((v >> 16) == tag || *w.s_fail) break;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *w.s_fail = 1;
+        atomicExch(w.error, 22);
+        break;
+      }
+    }
+  }
+  return __ushort_as_half(static_cast<unsigned short>(v & 0xFFFFu));
+}
+// Eight consecutive tagged values (32-byte aligned), packed as eight halves.
+__device__ __forceinline__ uint4 ld_tagged8(const Waiter& w, const uint32_t* p, uint32_t tag) {
+  uint4 a = ld_word4(p), b = ld_word4(p + 4);
+  const uint32_t want = tag * 0x00010001u;  // the tag in both halves of a word
+  auto ok = [&](const uint4& u, const uint4& v) {
+    return __byte_perm(u.x, u.y, 0x7632) == want && __byte_perm(u.z, u.w, 0x7632) == want &&
+           __byte_perm(v.x, v.y, 0x7632) == want && __byte_perm(v.z, v.w, 0x7632) == want;
+  };
+  if (!ok(a, b) && !*w.s_fail) {
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+      a = ld_word4(p);
+      b = ld_word4(p + 4);
+      if (ok(a, b) || *w.s_fail) break;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *w.s_fail = 1;
+        atomicExch(w.error, 22);
+        break;
+      }
+    }
+  }
+  return make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(b.x, b.y, 0x5410),
+                    __byte_perm(b.z, b.w, 0x5410));
+}
 
 // Balanced contiguous split of `items` over the grid (32-bit: the host checks items * grid < 2^31).
 __device__ __forceinline__ int range_start(int cta, int items, int grid) {
@@ -358,7 +421,7 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
         }
       }
       // when this op's last load was issued
-      if (a.trace != nullptr)
+      if (a.trace != nullptr && kind != kAttn)
         a.trace[((size_t)blockIdx.x * a.n_layers * kOpsPerLayer + l * kOpsPerLayer + kind) * kTraceSlots + 11] = globaltimer_ns();
     }
   }
@@ -440,6 +503,17 @@ __device__ void grid_barrier(Ctx& c, bool cross = false) {
   else
     c.bar_target += gridDim.x;
   consumer_bar();
+}
+
+// Between two ops: the grid barrier, or (tagged vectors) only this CTA's consumer warps, whose shared
+// buffers the next op reuses.
+__device__ __forceinline__ void op_boundary(Ctx& c, bool tagged, bool cross) {
+  if (tagged) {
+    consumer_bar();
+    if (threadIdx.x == 0) trace_mark(c, 6);
+  } else {
+    grid_barrier(c, cross);
+  }
 }
 
 // Eight inputs (chunk ci = inputs 8 ci .. 8 ci + 7, fp16 in v) become digits in place; the four lanes
@@ -528,8 +602,11 @@ struct Src {
   const float* partials;  // [world][stride] or null
   int world, stride;
   __half* store;
+  const uint32_t* tx = nullptr;  // the vector as tagged words (then x is unused), written by the op with tag `tag`
+  uint32_t tag = 0;
 };
-__device__ __forceinline__ uint4 fetch8(const Src& s, int i) {
+__device__ __forceinline__ uint4 fetch8(const Waiter& w, const Src& s, int i) {
+  if (s.tx != nullptr) return ld_tagged8(w, s.tx + i, s.tag);
   uint4 xv = __ldcg(reinterpret_cast<const uint4*>(s.x + i));
   if (s.partials == nullptr) return xv;
   float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
@@ -598,7 +675,7 @@ __device__ void load_x(Ctx& c, const Src& src, const __half* gamma, int d) {
     float ss = 0.0f;
     for (int i = threadIdx.x * 8; i < padded; i += kCW * 32 * 8) {
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (i < d) v = fetch8(src, i);
+      if (i < d) v = fetch8(c.w, src, i);
       *reinterpret_cast<uint4*>(c.xs + i) = v;
       const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
@@ -642,7 +719,7 @@ __device__ void load_x(Ctx& c, const Src& src, const __half* gamma, int d) {
       v[r] = make_uint4(0u, 0u, 0u, 0u);
       gv[r] = make_uint4(0u, 0u, 0u, 0u);
       if (ci * 8 < d) {
-        v[r] = fetch8(src, ci * 8);
+        v[r] = fetch8(c.w, src, ci * 8);
         gv[r] = __ldg(reinterpret_cast<const uint4*>(gamma + ci * 8));
       }
       const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
@@ -674,7 +751,7 @@ __device__ void load_x(Ctx& c, const Src& src, const __half* gamma, int d) {
     for (int r = 0; r < kRegChunks; ++r) {
       const int ci = threadIdx.x + r * kCW * 32;
       v[r] = make_uint4(0u, 0u, 0u, 0u);
-      if (ci * 8 < d) v[r] = fetch8(src, ci * 8);
+      if (ci * 8 < d) v[r] = fetch8(c.w, src, ci * 8);
       const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -775,9 +852,13 @@ struct Dest {
   unsigned long long off;  // byte offset in the exchange block of output 0 of this rank's shard
   bool all;
   bool partial;  // the outputs are fp32 partial sums (paired sharding): no rounding, no residual here
+  uint32_t* tagged = nullptr;  // single GPU: the outputs go here as tagged words instead
+  uint32_t tag = 0;
 };
 __device__ __forceinline__ void store_out(const MegaArgs& a, const Dest& dst, int idx, __half v) {
-  if (dst.all) {
+  if (dst.tagged != nullptr) {
+    st_tagged(dst.tagged + idx, v, dst.tag);
+  } else if (dst.all) {
     for (int r = 0; r < a.world; ++r) reinterpret_cast<__half*>(a.peers[r] + dst.off)[idx] = v;
   } else {
     dst.local[idx] = v;
@@ -814,7 +895,9 @@ __device__ __forceinline__ int chunk_owner(int b, int qn, int rn) {
   return rn + static_cast<int>(static_cast<unsigned>(b - big) / static_cast<unsigned>(qn));  // qn > 0 here
 }
 
-__device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest& out) {
+// resid / tresid: the vector added to the outputs, as halves or (single GPU) as tagged words this CTA has
+// already waited for when it loaded the vector as an input.
+__device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest& out, const uint32_t* tresid = nullptr) {
   const MegaArgs& a = c.a;
   const ProjShape p = proj_shape(a, kind);
   const int cta = blockIdx.x, G = gridDim.x;
@@ -842,7 +925,11 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
     const int b_end = b_stop < s_hi ? b_stop : s_hi;
     // the strip's residual values are fetched now: whichever warp completes the strip has them at hand
     __half rv = __float2half_rn(0.0f);
-    if (resid != nullptr && lane < kStripN) rv = __ldcg(resid + strip * kStripN + lane);
+    if (tresid != nullptr) {
+      if (lane < kStripN) rv = __ushort_as_half(static_cast<unsigned short>(ld_word(tresid + strip * kStripN + lane) & 0xFFFFu));
+    } else if (resid != nullptr && lane < kStripN) {
+      rv = __ldcg(resid + strip * kStripN + lane);
+    }
     float tot[2] = {0.0f, 0.0f};
     for (; b < b_end; ++b) {
       const long long w0 = tracing ? clock64() : 0;
@@ -871,7 +958,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
       // the strip is this warp's alone: rows g and g+8 sit in lanes t == 0
       const float lo = __shfl_sync(0xffffffffu, tot[0], (lane & 7) * 4);
       const float hi = __shfl_sync(0xffffffffu, tot[1], (lane & 7) * 4);
-      finish_strip(a, kind, strip, (lane & 8) ? hi : lo, c.sx, resid != nullptr, rv, out);
+      finish_strip(a, kind, strip, (lane & 8) ? hi : lo, c.sx, resid != nullptr || tresid != nullptr, rv, out);
       if (tracing) ec += clock64() - e0;
       continue;
     }
@@ -898,7 +985,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
       float v = c.dump[(w_lo * 2 + 1) * kStripN + (lane & 15)];
       for (int w = w_lo + 1; w <= w_hi; ++w) v += c.dump[w * 2 * kStripN + (lane & 15)];
       if (lane == 0) c.proj_arrived()[w_lo] = 0;  // next used after the op's grid barrier
-      finish_strip(a, kind, strip, v, c.sx, resid != nullptr, rv, out);
+      finish_strip(a, kind, strip, v, c.sx, resid != nullptr || tresid != nullptr, rv, out);
     }
     if (tracing) eb += clock64() - e3;
   }
@@ -952,6 +1039,7 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
   split.range(cta, i0, i1);
   const Runs runs(i0, i1, nt);
   __half* sq = reinterpret_cast<__half*>(reinterpret_cast<float*>(c.xs) + warp * kWarpScratch);  // rotated, scaled q
+  const uint32_t qtag = op_tag(c.epoch_base + c.op_index - 1);  // q, k, v come from the op before this one
   long long awaited = 0;
   const bool atracing = a.trace != nullptr && threadIdx.x == 0;
   // this warp takes every kCW-th item of the op's sequence; an item is two ring stages
@@ -975,8 +1063,16 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
       for (int rep = 0; rep < 2; ++rep) {
         const int e = lane + 32 * rep, half = kHeadDim / 2;
         const float2 rot = c.rope[e];
-        const __half* qp = a.qkv + (size_t)head * kHeadDim;
-        const float q0 = __half2float(__ldcg(qp + e)), q1 = __half2float(__ldcg(qp + e + half));
+        float q0, q1;
+        if (a.tagged) {
+          const uint32_t* qp = a.tq + (size_t)head * kHeadDim;
+          q0 = __half2float(ld_tagged(c.w, qp + e, qtag));
+          q1 = __half2float(ld_tagged(c.w, qp + e + half, qtag));
+        } else {
+          const __half* qp = a.qkv + (size_t)head * kHeadDim;
+          q0 = __half2float(__ldcg(qp + e));
+          q1 = __half2float(__ldcg(qp + e + half));
+        }
         sq[e] = __float2half_rn((q0 * rot.x - q1 * rot.y) * a.q_scale);
         sq[e + half] = __float2half_rn((q1 * rot.x + q0 * rot.y) * a.q_scale);
       }
@@ -1014,9 +1110,22 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
           for (int rep = 0; rep < 2; ++rep) {
             const int e = lane + 32 * rep, half = kHeadDim / 2;
             const float2 rot = c.rope[e];
-            const float k0 = __half2float(__ldcg(kp + e)), k1 = __half2float(__ldcg(kp + e + half));
+            float k0, k1;
+            __half v0, v1;
+            if (a.tagged) {
+              const uint32_t* tk = a.tq + (size_t)(a.heads + head) * kHeadDim;
+              const uint32_t* tv = a.tq + (size_t)(2 * a.heads + head) * kHeadDim;
+              k0 = __half2float(ld_tagged(c.w, tk + e, qtag));
+              k1 = __half2float(ld_tagged(c.w, tk + e + half, qtag));
+              v0 = ld_tagged(c.w, tv + e, qtag);
+              v1 = ld_tagged(c.w, tv + e + half, qtag);
+            } else {
+              k0 = __half2float(__ldcg(kp + e));
+              k1 = __half2float(__ldcg(kp + e + half));
+              v0 = __ldcg(vp + e);
+              v1 = __ldcg(vp + e + half);
+            }
             const __half r0 = __float2half_rn(k0 * rot.x - k1 * rot.y), r1 = __float2half_rn(k1 * rot.x + k0 * rot.y);
-            const __half v0 = __ldcg(vp + e), v1 = __ldcg(vp + e + half);
             kc[e] = r0;
             kc[e + half] = r1;
             vc[e] = v0;
@@ -1349,7 +1458,13 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
         pk.x = *reinterpret_cast<uint32_t*>(&r01);
         pk.y = *reinterpret_cast<uint32_t*>(&r23);
         // this rank's heads sit at rank * d_local in the full vector, which every rank needs
-        if (a.paired) {  // o is split by input columns: this rank's heads are all it reads
+        if (a.tagged) {
+          const uint32_t tg = op_tag(c.epoch_base + c.op_index) << 16;
+          uint32_t* dst = a.tattn + (size_t)head * kHeadDim + 4 * lane;
+          asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(tg | (pk.x & 0xFFFFu)),
+                       "r"(tg | (pk.x >> 16)), "r"(tg | (pk.y & 0xFFFFu)), "r"(tg | (pk.y >> 16))
+                       : "memory");
+        } else if (a.paired) {  // o is split by input columns: this rank's heads are all it reads
           *reinterpret_cast<uint2*>(a.attn + (size_t)head * kHeadDim + 4 * lane) = pk;
         } else {
           const size_t at = (size_t)a.rank * a.d_local + (size_t)head * kHeadDim + 4 * lane;
@@ -1418,7 +1533,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
     c.bar_target = *reinterpret_cast<const unsigned long long*>(s_int + kSharedInts + 1);
     c.xbar_target = *reinterpret_cast<const unsigned long long*>(s_int + kSharedInts + 3);
     // every launch completes at least one local barrier, so five epochs per barrier keep launches apart
-    c.epoch_base = static_cast<unsigned>(c.bar_target / gridDim.x) * kOpsPerLayer;
+    c.epoch_base = static_cast<unsigned>(c.bar_target / gridDim.x) * kOpsPerLayer * (a.tagged ? a.n_layers : 1);
     const int d = a.d_model;
     const bool sharded = a.world > 1;
     const size_t shard = (size_t)a.rank * a.d_local;  // first output of this rank in h / x
@@ -1429,51 +1544,75 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
         const __half* x_cur = l == 0 ? a.x_in : (((l - 1) & 1) ? a.xb : a.xa);
         // the last layer writes the caller's vector directly, unless peers have to write it too
         __half* x_next = (last && !sharded) ? a.x_out : ((l & 1) ? a.xb : a.xa);
-        const Dest d_qkv{a.qkv, 0ull, false, false};
-        const Dest d_h{a.h + shard, a.off_h + shard * 2, sharded, false};
-        const Dest d_act{a.act + (size_t)a.rank * a.ffn_local, a.off_act + (size_t)a.rank * a.ffn_local * 2, sharded, false};
-        const Dest d_x{x_next + shard, ((l & 1) ? a.off_xb : a.off_xa) + shard * 2, sharded, false};
+        Dest d_qkv{a.qkv, 0ull, false, false};
+        Dest d_h{a.h + shard, a.off_h + shard * 2, sharded, false};
+        Dest d_act{a.act + (size_t)a.rank * a.ffn_local, a.off_act + (size_t)a.rank * a.ffn_local * 2, sharded, false};
+        Dest d_x{x_next + shard, ((l & 1) ? a.off_xb : a.off_xa) + shard * 2, sharded, false};
+        Src s_x{x_cur, nullptr, 0, 0, nullptr}, s_attn{a.attn, nullptr, 0, 0, nullptr}, s_h{a.h, nullptr, 0, 0, nullptr},
+            s_act{a.act, nullptr, 0, 0, nullptr};
+        const uint32_t* tres_o = nullptr;
+        const uint32_t* tres_down = nullptr;
+        const bool tg = a.tagged != 0;
+        if (tg) {
+          // tagged vectors: every op's outputs carry the op's number, readers wait word by word
+          const unsigned e0 = c.epoch_base + l * kOpsPerLayer;
+          d_qkv.tagged = a.tq, d_qkv.tag = op_tag(e0 + kQkv);
+          d_h.tagged = a.th, d_h.tag = op_tag(e0 + kO);
+          d_act.tagged = a.tact, d_act.tag = op_tag(e0 + kGu);
+          if (!last) d_x.tagged = (l & 1) ? a.txb : a.txa, d_x.tag = op_tag(e0 + kDown);
+          if (l > 0) {
+            s_x.tx = ((l - 1) & 1) ? a.txb : a.txa, s_x.tag = op_tag(e0 - 1);  // down of the layer before
+            tres_o = s_x.tx;
+          }
+          s_attn.tx = a.tattn, s_attn.tag = op_tag(e0 + kAttn);
+          s_h.tx = a.th, s_h.tag = op_tag(e0 + kO);
+          s_act.tx = a.tact, s_act.tag = op_tag(e0 + kGu);
+          tres_down = a.th;
+        }
         c.op_index = l * kOpsPerLayer;
         trace_mark(c, 0);
-        load_x<true>(c, Src{x_cur, nullptr, 0, 0, nullptr}, ly->norm1, d);
+        load_x<true>(c, s_x, ly->norm1, d);
         trace_mark(c, 1);
         run_projection(c, kQkv, nullptr, d_qkv);
         trace_mark(c, 2);
-        grid_barrier(c);  // q, k, v stay on this rank
+        op_boundary(c, tg, false);  // q, k, v stay on this rank
         trace_mark(c, 3);
 
         c.op_index += 1;
         trace_mark(c, 0);
         run_attention(c, ly);
         trace_mark(c, 2);
-        grid_barrier(c, true);
+        op_boundary(c, tg, true);
         trace_mark(c, 3);
 
         c.op_index += 1;
         trace_mark(c, 0);
-        load_x<false>(c, Src{a.attn, nullptr, 0, 0, nullptr}, nullptr, d);
+        load_x<false>(c, s_attn, nullptr, d);
         trace_mark(c, 1);
-        run_projection(c, kO, x_cur + shard, d_h);
+        run_projection(c, kO, tres_o != nullptr ? nullptr : x_cur + shard, d_h, tres_o);
         trace_mark(c, 2);
-        grid_barrier(c, true);
+        op_boundary(c, tg, true);
         trace_mark(c, 3);
 
         c.op_index += 1;
         trace_mark(c, 0);
-        load_x<true>(c, Src{a.h, nullptr, 0, 0, nullptr}, ly->norm2, d);
+        load_x<true>(c, s_h, ly->norm2, d);
         trace_mark(c, 1);
         run_projection(c, kGu, nullptr, d_act);
         trace_mark(c, 2);
-        grid_barrier(c, true);
+        op_boundary(c, tg, true);
         trace_mark(c, 3);
 
         c.op_index += 1;
         trace_mark(c, 0);
-        load_x<false>(c, Src{a.act, nullptr, 0, 0, nullptr}, nullptr, a.ffn);
+        load_x<false>(c, s_act, nullptr, a.ffn);
         trace_mark(c, 1);
-        run_projection(c, kDown, a.h + shard, d_x);
+        run_projection(c, kDown, tg ? nullptr : a.h + shard, d_x, tres_down);
         trace_mark(c, 2);
-        grid_barrier(c, true);
+        if (tg && last)
+          grid_barrier(c);  // one barrier per launch keeps the launches' op numbers apart
+        else
+          op_boundary(c, tg, true);
         trace_mark(c, 3);
         if (last && sharded && blockIdx.x == 0) {
           // the step's result, assembled from all ranks' shards, goes to the caller's vector
@@ -1544,7 +1683,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
       if (blockIdx.x == 0) {
         // the step's result: h of the last layer plus its down partials
         const Src s_out{a.h, pd, a.world, d, a.x_out};
-        for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8) fetch8(s_out, i);
+        for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8) fetch8(c.w, s_out, i);
       }
     }
   }
@@ -1627,6 +1766,8 @@ struct MegaDecoder {
   std::vector<MegaLayer> h_layers;
   std::vector<char> layer_set;
   uint8_t* scratch;
+  int tagged;
+  uint32_t *tq, *tattn, *th, *tact, *txa, *txb;  // tagged-word vectors (inside scratch)
   uint8_t* xchg;              // exchange block (vectors every rank needs + the cross-rank barrier counter)
   uint8_t* peers[8];          // every rank's exchange block as mapped here (own entry = xchg)
   size_t off_attn, off_h, off_act, off_xa, off_xb, off_xbar, off_ph, off_pd;
@@ -1746,6 +1887,12 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   const size_t o_qkv = take((size_t)3 * dl * 2), o_ap = take((size_t)m->grid * kAttSlots * kAttDump * 4),
                o_at = take((size_t)m->heads_local * 4), o_af = take((size_t)(m->grid + m->heads_local) * 4),
                o_bar = take(8), o_err = take(4);
+  // one GPU: the op-to-op vectors as tagged words (MLD_MEGA_TAGGED=0 keeps the barriers instead)
+  m->tagged = cfg.world == 1 ? 1 : 0;
+  if (const char* et = getenv("MLD_MEGA_TAGGED")) m->tagged = m->tagged && atoi(et) != 0;
+  const size_t o_tq = take(m->tagged ? (size_t)3 * d * 4 : 0), o_ta = take(m->tagged ? (size_t)d * 4 : 0),
+               o_th = take(m->tagged ? (size_t)d * 4 : 0), o_tact = take(m->tagged ? (size_t)ffn * 4 : 0),
+               o_txa = take(m->tagged ? (size_t)d * 4 : 0), o_txb = take(m->tagged ? (size_t)d * 4 : 0);
   const size_t scratch_bytes = off;
   off = 0;  // the exchange block: same layout on every rank
   m->off_attn = take((size_t)d * 2);
@@ -1780,6 +1927,12 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   m->act = reinterpret_cast<__half*>(m->xchg + m->off_act);
   m->xa = reinterpret_cast<__half*>(m->xchg + m->off_xa);
   m->xb = reinterpret_cast<__half*>(m->xchg + m->off_xb);
+  m->tq = reinterpret_cast<uint32_t*>(m->scratch + o_tq);
+  m->tattn = reinterpret_cast<uint32_t*>(m->scratch + o_ta);
+  m->th = reinterpret_cast<uint32_t*>(m->scratch + o_th);
+  m->tact = reinterpret_cast<uint32_t*>(m->scratch + o_tact);
+  m->txa = reinterpret_cast<uint32_t*>(m->scratch + o_txa);
+  m->txb = reinterpret_cast<uint32_t*>(m->scratch + o_txb);
   m->att_part = reinterpret_cast<float*>(m->scratch + o_ap);
   m->att_tickets = reinterpret_cast<int*>(m->scratch + o_at);
   m->att_flags = reinterpret_cast<unsigned*>(m->scratch + o_af);
@@ -1912,6 +2065,13 @@ int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream
   a.q_scale = 1.0f / sqrtf(static_cast<float>(kHeadDim));
   a.x_in = static_cast<const __half*>(x_in);
   a.x_out = static_cast<__half*>(x_out);
+  a.tagged = m->tagged;
+  a.tq = m->tq;
+  a.tattn = m->tattn;
+  a.th = m->th;
+  a.tact = m->tact;
+  a.txa = m->txa;
+  a.txb = m->txb;
   a.qkv = m->qkv;
   a.attn = m->attn;
   a.h = m->h;
