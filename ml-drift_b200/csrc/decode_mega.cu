@@ -194,6 +194,12 @@ __device__ __forceinline__ __half ld_tagged(const Waiter& w, const uint32_t* p, 
   }
   return __ushort_as_half(static_cast<unsigned short>(v & 0xFFFFu));
 }
+// The same for a word already asked for: callers load all their words first, so that the loads overlap,
+// and then call this for each.
+__device__ __forceinline__ __half tagged_value(const Waiter& w, const uint32_t* p, uint32_t tag, uint32_t v) {
+  if ((v >> 16) != tag) return ld_tagged(w, p, tag);
+  return __ushort_as_half(static_cast<unsigned short>(v & 0xFFFFu));
+}
 // Eight consecutive tagged values (32-byte aligned), packed as eight halves.
 __device__ __forceinline__ uint4 ld_tagged8(const Waiter& w, const uint32_t* p, uint32_t tag) {
   uint4 a = ld_word4(p), b = ld_word4(p + 4);
@@ -1059,6 +1065,12 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
     if (q < seq_hi) {
       // rotary embedding of q (rope.cc:70-89), scaled and rounded to fp16 as the unfused graph stores it
       __syncwarp();
+      uint32_t qw[4] = {0u, 0u, 0u, 0u};
+      if (a.tagged) {  // all four words are asked for before any is looked at
+        const uint32_t* qp = a.tq + (size_t)head * kHeadDim;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qw[i] = ld_word(qp + lane + 32 * (i >> 1) + (i & 1) * (kHeadDim / 2));
+      }
 #pragma unroll
       for (int rep = 0; rep < 2; ++rep) {
         const int e = lane + 32 * rep, half = kHeadDim / 2;
@@ -1066,8 +1078,8 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
         float q0, q1;
         if (a.tagged) {
           const uint32_t* qp = a.tq + (size_t)head * kHeadDim;
-          q0 = __half2float(ld_tagged(c.w, qp + e, qtag));
-          q1 = __half2float(ld_tagged(c.w, qp + e + half, qtag));
+          q0 = __half2float(tagged_value(c.w, qp + e, qtag, qw[2 * rep]));
+          q1 = __half2float(tagged_value(c.w, qp + e + half, qtag, qw[2 * rep + 1]));
         } else {
           const __half* qp = a.qkv + (size_t)head * kHeadDim;
           q0 = __half2float(__ldcg(qp + e));
@@ -1106,6 +1118,16 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
           const __half* vp = a.qkv + (size_t)(2 * a.heads + head) * kHeadDim;
           __half* kc = ly->kcache + (size_t)a.pos * width + head * kHeadDim;
           __half* vc = ly->vcache + (size_t)a.pos * width + head * kHeadDim;
+          uint32_t kw[4] = {0u, 0u, 0u, 0u}, vw[4] = {0u, 0u, 0u, 0u};
+          if (a.tagged) {
+            const uint32_t* tk = a.tq + (size_t)(a.heads + head) * kHeadDim;
+            const uint32_t* tv = a.tq + (size_t)(2 * a.heads + head) * kHeadDim;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              kw[i] = ld_word(tk + lane + 32 * (i >> 1) + (i & 1) * (kHeadDim / 2));
+              vw[i] = ld_word(tv + lane + 32 * (i >> 1) + (i & 1) * (kHeadDim / 2));
+            }
+          }
 #pragma unroll
           for (int rep = 0; rep < 2; ++rep) {
             const int e = lane + 32 * rep, half = kHeadDim / 2;
@@ -1115,10 +1137,10 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
             if (a.tagged) {
               const uint32_t* tk = a.tq + (size_t)(a.heads + head) * kHeadDim;
               const uint32_t* tv = a.tq + (size_t)(2 * a.heads + head) * kHeadDim;
-              k0 = __half2float(ld_tagged(c.w, tk + e, qtag));
-              k1 = __half2float(ld_tagged(c.w, tk + e + half, qtag));
-              v0 = ld_tagged(c.w, tv + e, qtag);
-              v1 = ld_tagged(c.w, tv + e + half, qtag);
+              k0 = __half2float(tagged_value(c.w, tk + e, qtag, kw[2 * rep]));
+              k1 = __half2float(tagged_value(c.w, tk + e + half, qtag, kw[2 * rep + 1]));
+              v0 = tagged_value(c.w, tv + e, qtag, vw[2 * rep]);
+              v1 = tagged_value(c.w, tv + e + half, qtag, vw[2 * rep + 1]);
             } else {
               k0 = __half2float(__ldcg(kp + e));
               k1 = __half2float(__ldcg(kp + e + half));
