@@ -225,6 +225,16 @@ __device__ __forceinline__ uint4 ld_tagged8(const Waiter& w, const uint32_t* p, 
                     __byte_perm(b.z, b.w, 0x5410));
 }
 
+// The rare path of a wait that is nearly always over already, kept out of line so that the loops that
+// make it stay small.
+__device__ __noinline__ void wait_out_of_line(volatile int* s_fail, int* error, uint64_t* bar, uint32_t parity, int code) {
+  const Waiter w{s_fail, error};
+  w.wait(bar, parity, code);
+}
+__device__ __forceinline__ void wait_released(const Waiter& w, uint64_t* bar, uint32_t parity, int code) {
+  if (!mbar_try_wait(bar, parity)) wait_out_of_line(w.s_fail, w.error, bar, parity, code);
+}
+
 // Balanced contiguous split of `items` over the grid (32-bit: the host checks items * grid < 2^31).
 __device__ __forceinline__ int range_start(int cta, int items, int grid) {
   return static_cast<int>(static_cast<unsigned>(cta) * static_cast<unsigned>(items) / static_cast<unsigned>(grid));
@@ -939,6 +949,12 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
     float tot[2] = {0.0f, 0.0f};
     for (; b < b_end; ++b) {
       const long long w0 = tracing ? clock64() : 0;
+      // A parity wait is only right while the barrier is at most one phase behind: the stage's previous
+      // use must have been filled before its next filling is waited for.  Its having been released (what
+      // the producer also waits for) says so, and that wait cannot itself be a phase off, because
+      // everything up to a ring's length before this warp's previous box has been released.  The first
+      // ring's length of an op needs none of this: what came before it was used up before the op began.
+      if ((b - start) * kCW + warp >= a.stages) wait_released(c.w, &c.empty[stage], phase ^ 1u, 17);
       c.w.wait(&c.full[stage], phase, 12);
       if (tracing) waited += clock64() - w0;
       const long long b0 = tracing ? clock64() : 0;
@@ -1048,9 +1064,12 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
   const uint32_t qtag = op_tag(c.epoch_base + c.op_index - 1);  // q, k, v come from the op before this one
   long long awaited = 0;
   const bool atracing = a.trace != nullptr && threadIdx.x == 0;
-  // this warp takes every kCW-th item of the op's sequence; an item is two ring stages
-  int q = warp;
-  int pos = c.ring_base + 2 * warp;
+  // The first aw warps take every aw-th item of the op's sequence; an item is two ring stages.  A warp's
+  // items lie 2 aw stages apart, which must not exceed the ring (2 kCW - 1 stages do for kCW warps: the
+  // later stage of an item is waited for after the earlier one): shorter rings put fewer warps to work.
+  const int aw = a.stages >= 2 * kCW - 1 ? kCW : a.stages / 2;
+  int q = warp < aw ? warp : (1 << 30);
+  int pos = c.ring_base + 2 * (warp < aw ? warp : 0);
   int stage = pos % a.stages;
   uint32_t phase = static_cast<uint32_t>(pos / a.stages) & 1u;
   int seq_lo = 0;
@@ -1096,7 +1115,7 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
         qb[ks][0] = *reinterpret_cast<const uint32_t*>(sq + 16 * ks + 2 * t);
         qb[ks][1] = *reinterpret_cast<const uint32_t*>(sq + 16 * ks + 2 * t + 8);
       }
-      for (; q < seq_hi; q += kCW) {
+      for (; q < seq_hi; q += aw) {
         const int j = j0 + (q - seq_lo);
         int vstage = stage + 1;
         uint32_t vphase = phase;
@@ -1105,7 +1124,10 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
           vphase ^= 1u;
         }
         const long long w0 = atracing ? clock64() : 0;
+        // (the stages' previous uses released first: see run_projection)
+        if (2 * q >= a.stages) wait_released(c.w, &c.empty[stage], phase ^ 1u, 18);
         c.w.wait(&c.full[stage], phase, 13);
+        if (2 * q + 1 >= a.stages) wait_released(c.w, &c.empty[vstage], vphase ^ 1u, 18);
         c.w.wait(&c.full[vstage], vphase, 14);
         if (atracing) awaited += clock64() - w0;
         uint8_t* kt = c.ring + (size_t)stage * kStageBytes;
@@ -1245,7 +1267,7 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
           mbar_arrive_n(&c.empty[stage], kCW);
           mbar_arrive_n(&c.empty[vstage], kCW);
         }
-        stage += 2 * kCW;
+        stage += 2 * aw;
         while (stage >= a.stages) {
           stage -= a.stages;
           phase ^= 1u;
@@ -1861,7 +1883,7 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
     if (v >= 2 && v < stages) stages = v;
   }
   if (stages > 64) stages = 64;
-  if (stages < 4) {
+  if (stages < kCW + 1) {  // every consumer warp needs a stage of its own in a round
     set_last_error_text("not enough shared memory for the persistent step kernel");
     mega_destroy(m);
     return MLD_UNIMPLEMENTED;

@@ -134,6 +134,37 @@ def test_single_kernel_step_on_small_grids(mld, oracle, monkeypatch, grid, heads
     dec.close()
 
 
+@pytest.mark.parametrize("stages", [12, 16, 20])
+def test_single_kernel_step_with_a_short_ring(mld, oracle, monkeypatch, stages):
+    """Rings shorter than two stages per consumer warp (large vectors leave that little shared memory)
+    put fewer warps on attention and must give the same step; the step is run several times so that
+    consecutive launches, whose vectors carry different tags, are covered too."""
+    from oracle import decode_ref
+    monkeypatch.setenv("MLD_MEGA_STAGES", str(stages))
+    rng = np.random.default_rng(stages)
+    L, heads, ffn, T, pos = 2, 4, 1408, 1024, 1000
+    d = heads * 128
+    layers_ref, dec_tensors, kc, vc = build_small_decoder(mld, oracle, rng, L, heads, ffn, T, pos)
+    x = rng.standard_normal(d).astype(np.float16)
+    kcd, vcd = _dev(kc), _dev(vc)
+    dec = _make(mld, monkeypatch, "mega", L, d, heads, ffn, T, 32, dec_tensors, kcd, vcd)
+    y = torch.empty(d, dtype=torch.float16, device="cuda")
+    xd = _dev(x)
+    outs = []
+    for _ in range(3):
+        dec.step(xd, y, pos)
+        torch.cuda.synchronize()
+        assert dec.device_status() == 0
+        outs.append(y.float().cpu().numpy().copy())
+    kref, vref = kc.astype(np.float32), vc.astype(np.float32)
+    ref = decode_ref.decode_step(x.astype(np.float32), layers_ref, kref, vref, pos, heads, 128, ffn)
+    for got in outs:
+        assert np.isfinite(got).all()
+        assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) < 1e-2
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
+    dec.close()
+
+
 def test_single_kernel_step_ignores_uninitialised_cache_rows(mld, oracle, monkeypatch):
     """Rows of the cache past the current position may hold anything (NaN included): they must not reach
     the result."""
