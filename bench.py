@@ -492,7 +492,7 @@ def run_ours(args):
                 "frac": step_bytes / sec / 1e9 / gemv_alone["peak"], "peak_source": gemv_alone["peak_source"],
                 # dram__bytes_read + write of one launch: ncu capture of the same kernel on 2 layers
                 # (296.3 + 6.2 MB against 294.9 MB algorithmic), scaled by the layer count
-                "traffic": step_bytes * 1.026,
+                "traffic": step_bytes * 1.018,
                 "traffic_source": "ncu capture on 2 layers, scaled by layers (profiles/decode_mega_kernel_2_layers_ncu_full.md)",
                 "launches_timed": args.steps, "avg_launch_us": sec * 1e6,
                 "algorithmic_bytes_per_launch": step_bytes,
