@@ -178,6 +178,13 @@ typedef struct mld_fc_desc {
                                 scale pointers stay the same (the caller
                                 promises not to modify them in between) */
   int32_t epilogue;          /* mld_epilogue */
+  /* Tuning of the streaming decode kernel; 0 everywhere = the defaults. */
+  int32_t exact_operands;    /* 1: dequantise to exact fp16 integers before the MMA
+                                instead of feeding the raw nibbles / bytes as fp16
+                                subnormals (same results up to fp32 summation order) */
+  int32_t no_overlap;        /* 1: do not let consecutive launches overlap
+                                (programmatic dependent launch off) */
+  int32_t smem_limit_kb;     /* > 0: shared-memory budget of the stage ring */
 } mld_fc_desc;
 
 typedef struct mld_fc_plan mld_fc_plan;
@@ -193,6 +200,11 @@ MLD_API int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out);
 MLD_API int mld_fc_plan_destroy(mld_fc_plan* plan);
 /* Bytes of device workspace the plan holds. */
 MLD_API size_t mld_fc_plan_workspace_bytes(const mld_fc_plan* plan);
+/* Synchronous read of the plan's device-side status: *code = 0, or the code of
+ * a bounded device-side wait that gave up during an earlier mld_fc_run (then
+ * cleared); the function then returns MLD_TIMEOUT.  The kernels never spin
+ * without a limit: a wait that runs out makes its CTA stop and record the code. */
+MLD_API int mld_fc_plan_device_status(mld_fc_plan* plan, int32_t* code);
 
 /* Optional hint for the next mld_fc_run on this plan: once that call's decode
  * kernel has requested all of its own data it also asks for `bytes` of
@@ -238,9 +250,30 @@ typedef struct mld_decoder_desc {
    *     wdown: N = d_model, K = ffn/world, the columns of this rank's FFN
    *     units); their outputs are partial sums that every rank adds up, which
    *     halves the exchanges per layer.  Supported by the single-kernel
-   *     decoder (MLD_DECODER_MODE=mega) only. */
+   *     decoder only. */
   int32_t shard_layout;
+  int32_t mode;                  /* mld_decoder_mode */
+  /* Single-kernel decoder, 0 everywhere = the defaults: */
+  int32_t handover;              /* how a vector passes from one op to the next:
+                                    0 = every value travels with the number of the
+                                    op that wrote it and readers poll the words they
+                                    need (no barrier; sharded: the writer stores the
+                                    words into every rank's copy over NVLink);
+                                    1 = grid barriers between ops */
+  int32_t grid_limit;            /* > 0: use at most this many CTAs */
+  int32_t ring_stages;           /* > 0: use at most this many ring stages */
+  int32_t wait_limit_us;         /* > 0: bound, in microseconds, on every device-side
+                                    wait of a step (default 2 000 000) */
 } mld_decoder_desc;
+
+typedef enum mld_decoder_mode {
+  MLD_DECODER_AUTO = 0,          /* one GPU: single kernel when the shape allows it;
+                                    sharded: op chain */
+  MLD_DECODER_OP_CHAIN = 1,      /* a chain of mld_fc_run / attention kernels */
+  MLD_DECODER_SINGLE_KERNEL = 2  /* the whole step as one persistent kernel; sharded
+                                    ranks exchange shards with peer stores
+                                    (mld_decoder_ipc_export / _import, no NCCL id) */
+} mld_decoder_mode;
 
 /* Device tensors of one layer, in the layouts named at the top of this file.
  * Shard-local: wqkv packs the rows [q heads | k heads | v heads] of this rank
@@ -297,14 +330,27 @@ MLD_API int mld_decoder_destroy(mld_decoder* dec);
 /* 1 when this decoder runs a step as ONE persistent kernel (single GPU, INT4
  * block scales, head_dim 128): a producer thread per SM streams every weight
  * and KV-cache tile of the step through a shared-memory ring while the other
- * warps compute, with a grid barrier between dependent ops.  0: the step is a
- * chain of mld_fc_run / attention kernels.  The environment variable
- * MLD_DECODER_MODE=ops|mega, read at creation, forces one or the other. */
+ * warps compute.  0: the step is a chain of mld_fc_run / attention kernels.
+ * mld_decoder_desc.mode chooses. */
 MLD_API int mld_decoder_is_single_kernel(const mld_decoder* dec);
-/* Synchronous read of the device-side status of the steps run so far: 0, or
- * the code of the bounded wait that gave up (then cleared, with the kernel's
- * barrier state reset so that the decoder can be used again). */
+/* Synchronous read of the device-side status of the steps run so far: *code =
+ * 0, or the code of the bounded wait that gave up (then cleared, with the
+ * decoder's hand-over state made consistent so that it can be used again; the
+ * ranks of a sharded decoder must all call this before any of them steps
+ * again); the function then returns MLD_TIMEOUT. */
 MLD_API int mld_decoder_device_status(mld_decoder* dec, int32_t* code);
+/* Puts the decoder's hand-over state (launch counters, step counters, the tagged
+ * words and completion flags of the vectors that pass between ops and ranks)
+ * back to what it was after creation; weights and KV caches are untouched.
+ * mld_decoder_device_status does this by itself on the rank that saw a failure.
+ * The ranks of a sharded decoder number their steps alike, so after a failure on
+ * any rank ALL ranks call this, with no step in flight anywhere, and none steps
+ * again before all have returned (the caller synchronises them).  Synchronous.
+ * No counterpart in the reference. */
+MLD_API int mld_decoder_reset(mld_decoder* dec);
+/* Changes the bound on device-side waits (see mld_decoder_desc.wait_limit_us)
+ * for the steps enqueued after this call. */
+MLD_API int mld_decoder_set_wait_limit(mld_decoder* dec, int32_t wait_limit_us);
 /* Direct shard exchange between the ranks of one node, without a collective
  * library: every kernel that produces a shard stores it straight into each
  * rank's copy of the gathered vector (peer stores over NVLink) and raises a
@@ -325,7 +371,9 @@ MLD_API int mld_decoder_set_layer(mld_decoder* dec, int32_t layer, const mld_lay
 MLD_API int mld_decoder_step(mld_decoder* dec, const void* x_in, void* x_out, int32_t pos, void* stream);
 /* The same step with host vectors: copies x_host to the device, runs the step,
  * copies the result back and synchronises `stream` (the shape of the
- * reference runner's per-token host round trip, llm_opencl.cc:503-596). */
+ * reference runner's per-token host round trip, llm_opencl.cc:503-596).
+ * Returns MLD_TIMEOUT when a device-side wait of the step gave up (the result
+ * is then not valid; call mld_decoder_device_status before stepping again). */
 MLD_API int mld_decoder_step_host(mld_decoder* dec, const void* x_host, void* y_host, int32_t pos, void* stream);
 
 #ifdef __cplusplus

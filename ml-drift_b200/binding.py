@@ -16,6 +16,8 @@ SCALE_SCALAR, SCALE_PER_CHANNEL, SCALE_BLOCK = 0, 1, 2
 LAYOUT_SLICED, LAYOUT_ROW_MAJOR = 0, 1
 SRC_INT8, SRC_UINT4_PACKED = 0, 1
 PATH_AUTO, PATH_GEMV, PATH_GEMM = 0, 1, 2
+DECODER_AUTO, DECODER_OP_CHAIN, DECODER_SINGLE_KERNEL = 0, 1, 2
+HANDOVER_TAGGED, HANDOVER_BARRIERS = 0, 1
 EPILOGUE_NONE, EPILOGUE_SWIGLU_PAIRS = 0, 1
 
 
@@ -38,14 +40,18 @@ class FcDesc(C.Structure):
                 ("scalar_zero_point", C.c_float), ("has_zero_point", C.c_int32),
                 ("has_bias", C.c_int32), ("precision", C.c_int32), ("src_layout", C.c_int32),
                 ("dst_layout", C.c_int32), ("max_tokens", C.c_int32), ("force_path", C.c_int32),
-                ("device", C.c_int32), ("prefill_act_quant", C.c_int32), ("cache_prepared_weights", C.c_int32), ("epilogue", C.c_int32)]
+                ("device", C.c_int32), ("prefill_act_quant", C.c_int32), ("cache_prepared_weights", C.c_int32),
+                ("epilogue", C.c_int32), ("exact_operands", C.c_int32), ("no_overlap", C.c_int32),
+                ("smem_limit_kb", C.c_int32)]
 
 
 class DecoderDesc(C.Structure):
     _fields_ = [("layers", C.c_int32), ("d_model", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
                 ("ffn", C.c_int32), ("max_seq", C.c_int32), ("block", C.c_int32), ("rms_eps", C.c_float),
                 ("rope_min_timescale", C.c_float), ("rope_max_timescale", C.c_float), ("rank", C.c_int32),
-                ("world", C.c_int32), ("device", C.c_int32), ("shard_layout", C.c_int32)]
+                ("world", C.c_int32), ("device", C.c_int32), ("shard_layout", C.c_int32), ("mode", C.c_int32),
+                ("handover", C.c_int32), ("grid_limit", C.c_int32), ("ring_stages", C.c_int32),
+                ("wait_limit_us", C.c_int32)]
 
 
 class LayerWeights(C.Structure):
@@ -162,15 +168,25 @@ class FullyConnectedPlan:
     def __init__(self, n, k, weight_bits, scale_mode=SCALE_PER_CHANNEL, groups=1, scalar_scale=0.0,
                  scalar_zero_point=0.0, has_zero_point=False, has_bias=False, precision=F32F16,
                  src_layout=LAYOUT_SLICED, dst_layout=LAYOUT_SLICED, max_tokens=1, force_path=PATH_AUTO,
-                 device=-1, prefill_act_quant=0, cache_prepared_weights=False, epilogue=0):
+                 device=-1, prefill_act_quant=0, cache_prepared_weights=False, epilogue=0, exact_operands=False,
+                 no_overlap=False, smem_limit_kb=0):
         self.desc = FcDesc(n, k, weight_bits, scale_mode, groups, scalar_scale, scalar_zero_point,
                            int(has_zero_point), int(has_bias), precision, src_layout, dst_layout,
-                           max_tokens, force_path, device, prefill_act_quant, int(cache_prepared_weights), epilogue)
+                           max_tokens, force_path, device, prefill_act_quant, int(cache_prepared_weights), epilogue,
+                           int(exact_operands), int(no_overlap), smem_limit_kb)
         self._h = C.c_void_p()
         _check(lib().mld_fc_plan_create(C.byref(self.desc), C.byref(self._h)), "mld_fc_plan_create")
 
     def workspace_bytes(self) -> int:
         return int(lib().mld_fc_plan_workspace_bytes(self._h))
+
+    def device_status(self) -> int:
+        """0, or the code of a bounded device-side wait that gave up (then cleared)."""
+        code = C.c_int32(0)
+        rc = lib().mld_fc_plan_device_status(self._h, C.byref(code))
+        if rc not in (OK, TIMEOUT):
+            raise MldError(rc, "mld_fc_plan_device_status")
+        return code.value
 
     def run(self, src, weights, scale, dst, tokens, zero_point=None, bias=None, stream=None):
         _check(lib().mld_fc_run(self._h, _ptr(src), _ptr(weights), _ptr(scale), _ptr(zero_point), _ptr(bias),
@@ -212,9 +228,11 @@ class Decoder:
 
     def __init__(self, layers, d_model, heads, ffn, max_seq, block=32, head_dim=128, rms_eps=1e-6,
                  rope_min_timescale=1.0, rope_max_timescale=1.0e6, rank=0, world=1, nccl_id=None, device=-1,
-                 shard_layout=0):
+                 shard_layout=0, mode=DECODER_AUTO, handover=HANDOVER_TAGGED, grid_limit=0, ring_stages=0,
+                 wait_limit_us=0):
         self.desc = DecoderDesc(layers, d_model, heads, head_dim, ffn, max_seq, block, rms_eps,
-                                rope_min_timescale, rope_max_timescale, rank, world, device, shard_layout)
+                                rope_min_timescale, rope_max_timescale, rank, world, device, shard_layout, mode,
+                                handover, grid_limit, ring_stages, wait_limit_us)
         self._h = C.c_void_p()
         self._keep = []
         idbuf = None if nccl_id is None else C.create_string_buffer(nccl_id, 128)
@@ -230,9 +248,18 @@ class Decoder:
         return bool(lib().mld_decoder_is_single_kernel(self._h))
 
     def device_status(self) -> int:
+        """0, or the code of the bounded device-side wait that gave up (then cleared)."""
         code = C.c_int32(0)
-        _check(lib().mld_decoder_device_status(self._h, C.byref(code)), "mld_decoder_device_status")
+        rc = lib().mld_decoder_device_status(self._h, C.byref(code))
+        if rc not in (OK, TIMEOUT):
+            raise MldError(rc, "mld_decoder_device_status")
         return code.value
+
+    def reset(self):
+        _check(lib().mld_decoder_reset(self._h), "mld_decoder_reset")
+
+    def set_wait_limit(self, wait_limit_us: int):
+        _check(lib().mld_decoder_set_wait_limit(self._h, int(wait_limit_us)), "mld_decoder_set_wait_limit")
 
     def ipc_export(self) -> bytes:
         buf = C.create_string_buffer(64)

@@ -1,5 +1,8 @@
 """Builds libmldfc.so (the CUDA kernels and their C ABI) in-tree with nvcc for
-sm_100a.  Usage: python build.py [--force] [--verbose]"""
+sm_100a.  Usage: python build.py [--force] [--verbose] [--trace]
+--trace compiles the kernels' tuning instrumentation (per-CTA timestamps and the
+mld_debug_* entry points that read them) into the library; the default build has
+neither."""
 import os
 import subprocess
 import sys
@@ -36,9 +39,9 @@ def _stale():
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, trace=False):
     """Compiles every CUDA source of the package into one shared library."""
-    if not force and not _stale():
+    if not force and not trace and not _stale():
         return OUT
     objs = []
     procs = []
@@ -48,6 +51,8 @@ def build(force=False, verbose=False):
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, s), "-o", obj]
         if verbose:
             cmd += ["-Xptxas", "-v"]
+        if trace:
+            cmd += ["-DMLD_TRACE"]
         procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objs.append(obj)
     failed = False
@@ -83,4 +88,4 @@ def build_host_test(force=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv))

@@ -100,8 +100,9 @@ struct mld_fc_plan {
   int group_slices;
   StripGeometry gm;
   int* error;            // device error word written by kernels whose bounded waits ran out
+  int* error_shared;     // when set (a decoder's word), the kernels report there instead
   size_t ws_bytes;
-  // prefill GEMM workspace (allocated on first use)
+  // prefill GEMM workspace (allocated with the plan)
   void* w_kmajor;        // dequantised fp16 / re-biased s8 weights, [N4][kp]
   void* x_kmajor;        // activations, [max_tokens][kp]
   float* a_params;       // per-token {inv_scale, offset, sum}
@@ -113,14 +114,21 @@ struct mld_fc_plan {
   std::mutex mu;
 };
 
-// Tuning aid: when set (mld_debug_set_trace), the streaming GEMV records per-CTA timestamps.
+// Tuning aid, compiled only with -DMLD_TRACE: when set (mld_debug_set_trace), the streaming GEMV records
+// per-CTA timestamps.
 static unsigned long long* g_trace_buffer = nullptr;
+
+void mld::fc_plan_share_error(mld_fc_plan* plan, int* word) {
+  if (plan != nullptr) plan->error_shared = word;
+}
 
 extern "C" {
 
+#ifdef MLD_TRACE
 __attribute__((visibility("default"))) void mld_debug_set_trace(void* dev_buffer) {
   g_trace_buffer = static_cast<unsigned long long*>(dev_buffer);
 }
+#endif
 
 const char* mld_status_string(int status) {
   switch (status) {
@@ -214,6 +222,7 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   MLD_REQUIRE(d->max_tokens >= 1, "max_tokens must be at least 1");
   MLD_REQUIRE(d->prefill_act_quant == 0 || d->prefill_act_quant == 1, "bad prefill_act_quant");
   MLD_REQUIRE(d->epilogue == MLD_EPILOGUE_NONE || d->epilogue == MLD_EPILOGUE_SWIGLU_PAIRS, "bad epilogue");
+  MLD_REQUIRE((d->exact_operands | 1) == 1 && (d->no_overlap | 1) == 1 && d->smem_limit_kb >= 0, "bad tuning field");
   if (d->epilogue == MLD_EPILOGUE_SWIGLU_PAIRS)
     MLD_REQUIRE(d->n % 8 == 0 && !d->has_bias, "the SiLU*mul write needs an even row count (n % 8 == 0) and no bias");
   if (d->prefill_act_quant == 1)
@@ -235,16 +244,15 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   p->sms = sm_count(device);
   p->group_slices = group_slices;
   p->error = nullptr;
+  p->error_shared = nullptr;
   p->ws_bytes = 0;
   p->w_kmajor = p->x_kmajor = nullptr;
   p->a_params = nullptr;
   p->prepared_w = p->prepared_s = nullptr;
   p->next_w = nullptr;
   p->next_w_bytes = 0;
-  const char* enc = getenv("MLD_GEMV_OPERANDS");  // "exact" or "subnormal"
-  p->subnormal = !(enc != nullptr && strcmp(enc, "exact") == 0);
-  const char* pdl = getenv("MLD_GEMV_PDL");        // "0" disables programmatic dependent launch
-  p->pdl = !(pdl != nullptr && strcmp(pdl, "0") == 0);
+  p->subnormal = d->exact_operands == 0;
+  p->pdl = d->no_overlap == 0;
 
   const int N4 = align_n(d->n, 4);
   bool ok = d->precision != MLD_PRECISION_F32 && !d->has_zero_point && (N4 % 8 == 0) && (d->k % 8 == 0) &&
@@ -257,7 +265,8 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   p->stream_ok = ok;
   if (ok) {
     const int max_m = d->max_tokens < 16 ? d->max_tokens : 16;
-    p->gm = strip_geometry(d->weight_bits, d->n, d->k, max_m, group_slices, d->scale_mode, p->sms, p->pdl);
+    p->gm = strip_geometry(d->weight_bits, d->n, d->k, max_m, group_slices, d->scale_mode, p->sms, p->pdl,
+                           d->smem_limit_kb);
     if (p->gm.stages < 2) p->stream_ok = false;
   }
   {
@@ -271,6 +280,26 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
       return MLD_CUDA_ERROR;
     }
     p->ws_bytes = sizeof(int);
+  }
+  // An operator that may run as the prefill GEMM gets its operand workspace now, so that mld_fc_run never
+  // allocates: the K-major copy of the weights, the K-major (optionally quantised) activations and the
+  // per-token quantisation parameters.
+  const bool may_gemm = d->force_path == 2 || (d->force_path == 0 && !mld_fc_is_gemv_recommended(d->precision, d->max_tokens));
+  if (may_gemm && d->precision != MLD_PRECISION_F32 && !d->has_zero_point) {
+    const bool i8 = d->prefill_act_quant == 1;
+    const size_t esz = i8 ? 1 : 2;
+    const GemmGeometry gmax = gemm_geometry(d->max_tokens, d->n, d->k, i8, p->sms);
+    const size_t wb = (size_t)N4 * gmax.kp * esz, xb = (size_t)d->max_tokens * gmax.kp * esz,
+                 pb = (size_t)d->max_tokens * 3 * sizeof(float);
+    cudaError_t e = cudaMalloc(&p->w_kmajor, wb);
+    if (e == cudaSuccess) e = cudaMalloc(&p->x_kmajor, xb);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&p->a_params), pb);
+    if (e != cudaSuccess) {
+      set_last_error("prefill workspace", e);
+      mld_fc_plan_destroy(p);
+      return MLD_CUDA_ERROR;
+    }
+    p->ws_bytes += wb + xb + pb;
   }
   *out = p;
   return MLD_OK;
@@ -287,6 +316,20 @@ int mld_fc_plan_destroy(mld_fc_plan* plan) {
 }
 
 size_t mld_fc_plan_workspace_bytes(const mld_fc_plan* plan) { return plan ? plan->ws_bytes : 0; }
+
+int mld_fc_plan_device_status(mld_fc_plan* plan, int32_t* code) {
+  MLD_REQUIRE(plan != nullptr && code != nullptr, "null argument");
+  int c = 0;
+  int* word = plan->error_shared != nullptr ? plan->error_shared : plan->error;
+  MLD_CUDA_CHECK(cudaMemcpy(&c, word, sizeof(int), cudaMemcpyDeviceToHost));
+  *code = c;
+  if (c != 0) {
+    MLD_CUDA_CHECK(cudaMemset(word, 0, sizeof(int)));
+    set_last_error_text("a bounded device-side wait of a FullyConnected kernel gave up");
+    return MLD_TIMEOUT;
+  }
+  return MLD_OK;
+}
 
 int mld_fc_plan_prefetch_next(mld_fc_plan* plan, const void* next_weights, size_t bytes) {
   MLD_REQUIRE(plan != nullptr, "null plan");
@@ -362,7 +405,7 @@ static int run_stream(mld_fc_plan* p, const void* src, const void* weights, cons
   a.x = src;
   a.bias = bias;
   a.y = dst;
-  a.error = p->error;
+  a.error = p->error_shared != nullptr ? p->error_shared : p->error;
   a.M_total = tokens;
   a.N = d.n;
   a.N4 = N4;
@@ -408,12 +451,11 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
   const GemmGeometry g = gemm_geometry(tokens, d.n, d.k, i8, p->sms);
   const int N4 = align_n(d.n, 4);
   const size_t esz = i8 ? 1 : 2;
+  (void)N4;
+  (void)esz;
   if (p->w_kmajor == nullptr) {
-    const GemmGeometry gmax = gemm_geometry(d.max_tokens, d.n, d.k, i8, p->sms);
-    MLD_CUDA_CHECK(cudaMalloc(&p->w_kmajor, (size_t)N4 * gmax.kp * esz));
-    MLD_CUDA_CHECK(cudaMalloc(&p->x_kmajor, (size_t)d.max_tokens * gmax.kp * esz));
-    MLD_CUDA_CHECK(cudaMalloc(&p->a_params, (size_t)d.max_tokens * 3 * sizeof(float)));
-    p->ws_bytes += (size_t)N4 * gmax.kp * esz + (size_t)d.max_tokens * gmax.kp * esz + (size_t)d.max_tokens * 12;
+    set_last_error_text("this operator was not planned for the prefill route (force_path / max_tokens at creation)");
+    return MLD_INVALID_ARGUMENT;
   }
   int rc;
   const bool reuse = d.cache_prepared_weights && p->prepared_w == weights && p->prepared_s == scale;
@@ -431,7 +473,7 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
     rc = launch_transpose_x(src, d.src_layout, tokens, d.k, g.kp, p->x_kmajor, stream);
   if (rc != MLD_OK) return rc;
   return launch_gemm_umma(i8, p->x_kmajor, p->w_kmajor, g, tokens, d.n, d.k, bias, scale, p->a_params, dst,
-                          d.dst_layout, p->error, stream);
+                          d.dst_layout, p->error_shared != nullptr ? p->error_shared : p->error, stream);
 }
 
 int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const void* scale, const void* zero_point,

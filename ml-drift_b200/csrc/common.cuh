@@ -47,6 +47,20 @@ static inline int align_n(int a, int n) { return div_up(a, n) * n; }
 
 int sm_count(int device);
 
+// Function attributes such as the dynamic shared-memory limit are per device: a kernel is configured
+// once on every device it is launched on.  `done` is a zero-initialised table owned by the caller (one
+// per kernel instantiation); returns true when the current device still needs the attribute set.
+constexpr int kMaxDevices = 64;
+inline bool needs_configure(bool (&done)[kMaxDevices], int* device_out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    *device_out = -1;
+    return true;  // unknown device: set the attribute every time
+  }
+  *device_out = dev;
+  return !done[dev];
+}
+
 // cuTensorMapEncodeTiled fetched through the runtime (no libcuda link).
 typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                     const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -185,11 +199,12 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
   return v;
 }
 // Waits until every rank's flag has reached `seq`; false when the time limit ran out.
-__device__ __forceinline__ bool wait_peer_flags(const unsigned* flags, int world, unsigned seq) {
+__device__ __forceinline__ bool wait_peer_flags(const unsigned* flags, int world, unsigned seq,
+                                                unsigned long long limit_ns) {
   const unsigned long long t0 = globaltimer_ns();
   for (int r = 0; r < world; ++r) {
     while (static_cast<int>(ld_acquire_sys(flags + r) - seq) < 0) {
-      if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+      if (globaltimer_ns() - t0 > limit_ns) return false;
     }
   }
   return true;

@@ -53,6 +53,13 @@ namespace mld {
 
 namespace {
 
+// Per-CTA timestamps for tuning are compiled in only with -DMLD_TRACE (build.py --trace).
+#ifdef MLD_TRACE
+#define MLD_TRACING(a) ((a).trace != nullptr)
+#else
+#define MLD_TRACING(a) false
+#endif
+
 constexpr int kCW = 11;                      // consumer warps; every ring stage is consumed by ONE warp
 constexpr int kThreads = (kCW + 1) * 32;     // + one producer warp
 constexpr int kStripN = 16;                  // outputs per strip (the MMA's M)
@@ -104,8 +111,12 @@ struct MegaArgs {
   // Single GPU: the vectors that pass from op to op are arrays of 32-bit words, fp16 value in the low half
   // and the writing op's tag in the high half; a reader polls a word until it carries the tag it expects,
   // so no barrier separates the ops (tagged != 0).
+  // Sharded with tagged vectors: tattn .. txb live in the exchange block (same layout on every rank) and a
+  // writer stores each word into every rank's copy (plain peer stores; a word carries its own validity, so no
+  // fence, flag or barrier orders the exchange); xoff[i] = byte offset of tattn, th, tact, txa, txb there.
   int tagged;
   uint32_t *tq, *tattn, *th, *tact, *txa, *txb;
+  unsigned long long wait_limit_ns;  // bound on every wait of this launch
   float* att_part;     // [grid][kAttSlots][kAttDump]
   int* att_tickets;    // [heads]
   unsigned* att_flags; // [heads][grid / heads]: epoch of the attention whose partial the part has published
@@ -130,6 +141,8 @@ __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" 
 struct Waiter {
   volatile int* s_fail;
   int* error;
+  unsigned long long limit;  // ns
+  bool sys;                  // tagged words may be written by other GPUs: poll them at system scope
   __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, int code) const {
     if (mbar_try_wait(bar, parity)) return true;
     if (*s_fail) return false;
@@ -139,7 +152,7 @@ struct Waiter {
       for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
       if (*s_fail) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit) {
         *s_fail = 1;
         atomicExch(error, code);
         return false;
@@ -152,7 +165,7 @@ struct Waiter {
     const unsigned long long t0 = globaltimer_ns();
     while (*counter - want < 0) {
       if (*s_fail) return;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit) {
         *s_fail = 1;
         atomicExch(error, code);
         return;
@@ -167,25 +180,35 @@ __device__ __forceinline__ void st_tagged(uint32_t* p, __half v, uint32_t tag) {
   const uint32_t w = (tag << 16) | static_cast<uint32_t>(__half_as_ushort(v));
   asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(w) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_word(const uint32_t* p) {
+__device__ __forceinline__ void st_tagged_sys(uint32_t* p, __half v, uint32_t tag) {
+  const uint32_t w = (tag << 16) | static_cast<uint32_t>(__half_as_ushort(v));
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(w) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_word(const uint32_t* p, bool sys) {
   uint32_t v;
-  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  if (sys)
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  else
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ uint4 ld_word4(const uint32_t* p) {
+__device__ __forceinline__ uint4 ld_word4(const uint32_t* p, bool sys) {
   uint4 v;
-  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  if (sys)
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  else
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
 // One tagged value, waited for (bounded; code 22).
 __device__ __forceinline__ __half ld_tagged(const Waiter& w, const uint32_t* p, uint32_t tag) {
-  uint32_t v = ld_word(p);
+  uint32_t v = ld_word(p, w.sys);
   if ((v >> 16) != tag && !*w.s_fail) {
     const unsigned long long t0 = globaltimer_ns();
     for (;;) {
-      v = ld_word(p);
+      v = ld_word(p, w.sys);
       if ((v >> 16) == tag || *w.s_fail) break;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > w.limit) {
         *w.s_fail = 1;
         atomicExch(w.error, 22);
         break;
@@ -202,7 +225,7 @@ __device__ __forceinline__ __half tagged_value(const Waiter& w, const uint32_t* 
 }
 // Eight consecutive tagged values (32-byte aligned), packed as eight halves.
 __device__ __forceinline__ uint4 ld_tagged8(const Waiter& w, const uint32_t* p, uint32_t tag) {
-  uint4 a = ld_word4(p), b = ld_word4(p + 4);
+  uint4 a = ld_word4(p, w.sys), b = ld_word4(p + 4, w.sys);
   const uint32_t want = tag * 0x00010001u;  // the tag in both halves of a word
   auto ok = [&](const uint4& u, const uint4& v) {
     return __byte_perm(u.x, u.y, 0x7632) == want && __byte_perm(u.z, u.w, 0x7632) == want &&
@@ -211,10 +234,10 @@ __device__ __forceinline__ uint4 ld_tagged8(const Waiter& w, const uint32_t* p, 
   if (!ok(a, b) && !*w.s_fail) {
     const unsigned long long t0 = globaltimer_ns();
     for (;;) {
-      a = ld_word4(p);
-      b = ld_word4(p + 4);
+      a = ld_word4(p, w.sys);
+      b = ld_word4(p + 4, w.sys);
       if (ok(a, b) || *w.s_fail) break;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > w.limit) {
         *w.s_fail = 1;
         atomicExch(w.error, 22);
         break;
@@ -227,12 +250,13 @@ __device__ __forceinline__ uint4 ld_tagged8(const Waiter& w, const uint32_t* p, 
 
 // The rare path of a wait that is nearly always over already, kept out of line so that the loops that
 // make it stay small.
-__device__ __noinline__ void wait_out_of_line(volatile int* s_fail, int* error, uint64_t* bar, uint32_t parity, int code) {
-  const Waiter w{s_fail, error};
+__device__ __noinline__ void wait_out_of_line(volatile int* s_fail, int* error, unsigned long long limit, uint64_t* bar,
+                                              uint32_t parity, int code) {
+  const Waiter w{s_fail, error, limit, false};
   w.wait(bar, parity, code);
 }
 __device__ __forceinline__ void wait_released(const Waiter& w, uint64_t* bar, uint32_t parity, int code) {
-  if (!mbar_try_wait(bar, parity)) wait_out_of_line(w.s_fail, w.error, bar, parity, code);
+  if (!mbar_try_wait(bar, parity)) wait_out_of_line(w.s_fail, w.error, w.limit, bar, parity, code);
 }
 
 // Balanced contiguous split of `items` over the grid (32-bit: the host checks items * grid < 2^31).
@@ -406,7 +430,9 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
           for (int i = lo; i < hi; ++i) {
             const int j = i - head * nt;
             for (int kv = 0; kv < 2; ++kv) {
-              w.wait(&empty[r.stage], r.phase ^ 1, 10);
+              // a producer whose wait ran out requests nothing more: stages it cannot know to be free stay
+              // untouched, and no barrier sees an arrival its phase does not expect
+              if (!w.wait(&empty[r.stage], r.phase ^ 1, 10)) return;
               uint8_t* st = ring + (size_t)r.stage * kStageBytes;
               mbar_arrive_expect_tx(&full[r.stage], kBox);
               const CUtensorMap* map = kv == 0 ? &ly->kc : &ly->vc;
@@ -428,7 +454,7 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
           const int nw = B - j * kCW < kCW ? B - j * kCW : kCW;
           for (int cw = 0; cw < nw; ++cw) {
             const int i = pi0 + cw * qn + (cw < rn ? cw : rn) + j;
-            w.wait(&empty[r.stage], r.phase ^ 1, 11);
+            if (!w.wait(&empty[r.stage], r.phase ^ 1, 11)) return;
             uint8_t* st = ring + (size_t)r.stage * kStageBytes;
             mbar_arrive_expect_tx(&full[r.stage], kStageBytes);
             bulk_load_1d_hint(st, wbase + (size_t)i * kStageBytes, kStageBytes, &full[r.stage], pol);
@@ -437,7 +463,7 @@ __device__ void producer_loop(const MegaArgs& a, uint8_t* ring, uint64_t* full, 
         }
       }
       // when this op's last load was issued
-      if (a.trace != nullptr && kind != kAttn)
+      if (MLD_TRACING(a) && kind != kAttn)
         a.trace[((size_t)blockIdx.x * a.n_layers * kOpsPerLayer + l * kOpsPerLayer + kind) * kTraceSlots + 11] = globaltimer_ns();
     }
   }
@@ -450,8 +476,7 @@ struct Ctx {
   uint64_t* full;
   uint64_t* empty;
   __half* xs;          // input vector of the running projection / per-warp attention scratch
-  int* isum;           // [box][t][set]: 8 * (sum of the integers of unit 4 set + t of the box), see digitise_x
-  float sx;            // scale of the digitised input vector
+  int* isum;           // [box][t][set]: scale exponent | 8 * (sum of the integers) of unit 4 set + t of the box, see digitise_x
   const float2* rope;  // [64] (cos, sin) of pos / timescale_i, the rotary embedding of this step
   float* dump;         // per-warp sums: projections [warp][share (2)][kStripN], attention [slot][warp][kAttDump]
   int* s_int;          // [0] failure flag, [1..] run bookkeeping (see below)
@@ -470,7 +495,7 @@ static_assert(kProjCounters >= kCW && kProjCounters % 2 == 0, "one counter per c
 constexpr int kSharedInts = 1 + kProjCounters + 2 * kAttnSlots;  // (odd) + 5 behind them: pad, two 64-bit barrier bases
 
 __device__ __forceinline__ void trace_mark(const Ctx& c, int k) {
-  if (c.a.trace != nullptr && threadIdx.x == 0)
+  if (MLD_TRACING(c.a) && threadIdx.x == 0)
     c.a.trace[((size_t)blockIdx.x * c.a.n_layers * kOpsPerLayer + c.op_index) * kTraceSlots + k] = globaltimer_ns();
 }
 
@@ -506,7 +531,7 @@ __device__ void grid_barrier(Ctx& c, bool cross = false) {
         else
           asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cnt) : "memory");
         if (static_cast<long long>(v - target) >= 0) break;
-        if (globaltimer_ns() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(c.a.error) != 0) {
+        if (globaltimer_ns() - t0 > c.w.limit || *reinterpret_cast<volatile int*>(c.a.error) != 0) {
           *c.w.s_fail = 1;
           atomicCAS(c.a.error, 0, 20);
           break;
@@ -532,17 +557,38 @@ __device__ __forceinline__ void op_boundary(Ctx& c, bool tagged, bool cross) {
   }
 }
 
-// Eight inputs (chunk ci = inputs 8 ci .. 8 ci + 7, fp16 in v) become digits in place; the four lanes
-// of a unit (consecutive chunks, one warp) also add up the unit's integers.  All lanes of the warp call.
-__device__ __forceinline__ void digitise_chunk(Ctx& c, int ci, const uint4& v, float inv) {
+// The digit scale of a unit of 32 inputs whose largest magnitude is amax: the smallest power of two s with
+// amax / s <= 32512, so that round(x / s) fits 16 bits with head-room and 1 / s is exact.  Returns the bits
+// of s (a float with an empty mantissa).
+__device__ __forceinline__ uint32_t unit_scale_bits(float amax) {
+  const float t = amax * (1.0f / 32512.0f);
+  uint32_t b = (__float_as_uint(t) + 0x007FFFFFu) & 0x7F800000u;  // next power of two >= t
+  if (b < (16u << 23)) b = 16u << 23;                              // an all-zero (or vanishing) unit: any scale does
+  return b;
+}
+
+// Eight inputs (chunk ci = inputs 8 ci .. 8 ci + 7, fp16 in v) become digits in place.  The four lanes of a
+// unit (consecutive chunks, one warp) agree on the unit's scale and add up the unit's integers.  All lanes
+// of the warp call.
+__device__ __forceinline__ void digitise_chunk(Ctx& c, int ci, const uint4& v) {
   const __half2* h = reinterpret_cast<const __half2*>(&v);
-  // z = round(x / sx) + 128 in the low 16 bits of the float's mantissa: high byte = hi digit, low byte ^ 0x80 = lo digit
+  float2 f[4];
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    f[j] = __half22float2(h[j]);
+    amax = fmaxf(amax, fmaxf(fabsf(f[j].x), fabsf(f[j].y)));
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  const uint32_t sbits = unit_scale_bits(amax);
+  const float inv = __uint_as_float((254u << 23) - sbits);  // 1 / s, exact
+  // z = round(x / s) + 128 in the low 16 bits of the float's mantissa: high byte = hi digit, low byte ^ 0x80 = lo digit
   uint32_t z[8];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float2 f = __half22float2(h[j]);
-    z[2 * j] = __float_as_uint(fmaf(f.x, inv, 12583040.0f));
-    z[2 * j + 1] = __float_as_uint(fmaf(f.y, inv, 12583040.0f));
+    z[2 * j] = __float_as_uint(fmaf(f[j].x, inv, 12583040.0f));
+    z[2 * j + 1] = __float_as_uint(fmaf(f[j].y, inv, 12583040.0f));
   }
   uint32_t hiw[2], low[2];
 #pragma unroll
@@ -567,46 +613,29 @@ __device__ __forceinline__ void digitise_chunk(Ctx& c, int ci, const uint4& v, f
   ub[8 + w0] = low[0];
   ub[8 + w0 + 2] = low[1];
   if (q == 0) {
+    // |8 sum| <= 8 * 32 * 32512 < 2^23: the offset term and the scale's exponent share one word
     const int m = unit & 31;
-    c.isum[(unit >> 5) * 32 + (m & 3) * 8 + (m >> 2)] = 8 * sum;
+    c.isum[(unit >> 5) * 32 + (m & 3) * 8 + (m >> 2)] = static_cast<int>(sbits | (static_cast<uint32_t>(8 * sum) & 0x007FFFFFu));
   }
 }
 
-// Turns the fp16 vector in xs into what the integer MMAs read, in place.  The
-// vector becomes 16-bit fixed point with one scale for the whole vector,
-// x ~ sx * (256 hi + lo) with hi, lo in [-128, 127] (sx = max|x| / 32512: the
-// error is at most 1.6e-5 of the largest element, far below the fp16 rounding
-// of the outputs), and every unit of 32 inputs (64 bytes either way) is
-// rewritten as [hi: 32 bytes][lo: 32 bytes], each in the order the B fragments
-// take them (8 bytes per lane t: inputs 4t..4t+3 and 16+4t..16+4t+3).
-// isum[box][t][set] = 8 * sum of the unit's integers: the nibble offset's share.
+// Turns the fp16 vector in xs into what the integer MMAs read, in place.  Every
+// unit of 32 inputs (the span of one weight scale) becomes 16-bit fixed point
+// with a scale of its own, x ~ s * (256 hi + lo) with hi, lo in [-128, 127] and
+// s a power of two with max|x| / s in (16256, 32512]: 15 significant bits
+// against fp16's 11, relative to the unit's own largest element, so an outlier
+// channel costs its 31 neighbours nothing worth naming and the rest of the
+// vector nothing at all.  The unit (64 bytes either way) is rewritten as
+// [hi: 32 bytes][lo: 32 bytes], each in the order the B fragments take them
+// (8 bytes per lane t: inputs 4t..4t+3 and 16+4t..16+4t+3).
+// isum[box][t][set] = the scale's exponent bits | 23 bits of 8 * (sum of the
+// unit's integers), the nibble offset's share.
 __device__ void digitise_x(Ctx& c, int d) {
   const int chunks = (d + kBoxK - 1) / kBoxK * kBoxK / 8;  // 8 inputs (16 bytes) per thread and round
-  float amax = 0.0f;
-  for (int ci = threadIdx.x; ci < chunks; ci += kCW * 32) {
-    const uint4 v = *reinterpret_cast<const uint4*>(c.xs + ci * 8);
-    const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __half22float2(__habs2(h[j]));
-      amax = fmaxf(amax, fmaxf(f.x, f.y));
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  float* part = c.dump + 32;  // free between ops (the first entries serve the RMSNorm sum)
-  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = amax;
-  consumer_bar();
-  amax = 0.0f;
-#pragma unroll
-  for (int wi = 0; wi < kCW; ++wi) amax = fmaxf(amax, part[wi]);
-  const float sx = amax > 0.0f ? amax / 32512.0f : 1.0f;
-  const float inv = 1.0f / sx;
-  c.sx = sx;
   for (int ci = threadIdx.x; ci < chunks; ci += kCW * 32) {
     const uint4 v = *reinterpret_cast<const uint4*>(c.xs + ci * 8);
     __syncwarp();  // rounds are warp-uniform (whole boxes): the unit's four lanes have read before any rewrites
-    digitise_chunk(c, ci, v, inv);
+    digitise_chunk(c, ci, v);
   }
 }
 
@@ -641,42 +670,17 @@ __device__ __forceinline__ uint4 fetch8(const Waiter& w, const Src& s, int i) {
 
 constexpr int kRegChunks = 4;  // chunks of 8 inputs a thread can hold: vectors up to 4 * 8 * 32 * kCW inputs
 
-// Block-wide reduction of one float per thread over the consumer warps (slot: 0 sum, 1 max).
-__device__ __forceinline__ float consumer_reduce(Ctx& c, float v, int slot) {
+// Block-wide sum of one float per thread over the consumer warps.
+__device__ __forceinline__ float consumer_sum(Ctx& c, float v) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float w = __shfl_xor_sync(0xffffffffu, v, o);
-    v = slot == 0 ? v + w : fmaxf(v, w);
-  }
-  float* part = c.dump + 32 * slot;  // free between ops
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  float* part = c.dump;  // free between ops
   if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
   consumer_bar();
-  float r = slot == 0 ? 0.0f : 0.0f;
+  float r = 0.0f;
 #pragma unroll
-  for (int wi = 0; wi < kCW; ++wi) r = slot == 0 ? r + part[wi] : fmaxf(r, part[wi]);
+  for (int wi = 0; wi < kCW; ++wi) r += part[wi];
   return r;
-}
-
-// Sum of `a` and maximum of `b` over the consumer warps with one barrier.
-__device__ __forceinline__ void consumer_reduce2(Ctx& c, float& a, float& b) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    a += __shfl_xor_sync(0xffffffffu, a, o);
-    b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, o));
-  }
-  float* part = c.dump + 64;  // free between ops
-  if ((threadIdx.x & 31) == 0) {
-    part[threadIdx.x >> 5] = a;
-    part[32 + (threadIdx.x >> 5)] = b;
-  }
-  consumer_bar();
-  a = 0.0f;
-  b = 0.0f;
-#pragma unroll
-  for (int wi = 0; wi < kCW; ++wi) {
-    a += part[wi];
-    b = fmaxf(b, part[32 + wi]);
-  }
 }
 
 // Loads the d-element input vector of a projection and leaves it digitised in xs (digitise_x).
@@ -701,7 +705,7 @@ __device__ void load_x(Ctx& c, const Src& src, const __half* gamma, int d) {
       }
     }
     if (NORM) {
-      const float inv = rsqrtf(consumer_reduce(c, ss, 0) / static_cast<float>(d) + c.a.rms_eps);
+      const float inv = rsqrtf(consumer_sum(c, ss) / static_cast<float>(d) + c.a.rms_eps);
       for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8) {
         uint4 v = *reinterpret_cast<uint4*>(c.xs + i);
         const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gamma + i));
@@ -722,13 +726,9 @@ __device__ void load_x(Ctx& c, const Src& src, const __half* gamma, int d) {
     return;
   }
   uint4 v[kRegChunks];
-  float amax = 0.0f;
   if (NORM) {
-    // one pass: sum of squares for the statistics and max |v * gamma| for the digit scale; the largest
-    // normalised element is that maximum times the inverse RMS (up to fp16 rounding, for which the digit
-    // range keeps head-room)
     uint4 gv[kRegChunks];
-    float ss = 0.0f, gmax = 0.0f;
+    float ss = 0.0f;
 #pragma unroll
     for (int r = 0; r < kRegChunks; ++r) {
       const int ci = threadIdx.x + r * kCW * 32;
@@ -739,18 +739,13 @@ __device__ void load_x(Ctx& c, const Src& src, const __half* gamma, int d) {
         gv[r] = __ldg(reinterpret_cast<const uint4*>(gamma + ci * 8));
       }
       const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
-      const __half2* gh = reinterpret_cast<const __half2*>(&gv[r]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 f = __half22float2(h[j]);
-        const float2 g = __half22float2(gh[j]);
         ss += f.x * f.x + f.y * f.y;
-        gmax = fmaxf(gmax, fmaxf(fabsf(f.x * g.x), fabsf(f.y * g.y)));
       }
     }
-    consumer_reduce2(c, ss, gmax);
-    const float inv = rsqrtf(ss / static_cast<float>(d) + c.a.rms_eps);
-    amax = gmax * inv * 1.001f;
+    const float inv = rsqrtf(consumer_sum(c, ss) / static_cast<float>(d) + c.a.rms_eps);
 #pragma unroll
     for (int r = 0; r < kRegChunks; ++r) {
       __half2* h = reinterpret_cast<__half2*>(&v[r]);
@@ -768,22 +763,13 @@ __device__ void load_x(Ctx& c, const Src& src, const __half* gamma, int d) {
       const int ci = threadIdx.x + r * kCW * 32;
       v[r] = make_uint4(0u, 0u, 0u, 0u);
       if (ci * 8 < d) v[r] = fetch8(c.w, src, ci * 8);
-      const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(__habs2(h[j]));
-        amax = fmaxf(amax, fmaxf(f.x, f.y));
-      }
     }
-    amax = consumer_reduce(c, amax, 1);
   }
-  const float sx = amax > 0.0f ? amax / 32512.0f : 1.0f;
-  const float inv_sx = 1.0f / sx;
-  c.sx = sx;
+  // the digit scale is per unit of 32 inputs, found by the unit's own four lanes: no block-wide maximum
 #pragma unroll
   for (int r = 0; r < kRegChunks; ++r) {
     const int ci = threadIdx.x + r * kCW * 32;
-    if (ci < chunks) digitise_chunk(c, ci, v[r], inv_sx);  // warp-uniform: chunks is a multiple of 32
+    if (ci < chunks) digitise_chunk(c, ci, v[r]);  // warp-uniform: chunks is a multiple of 32
   }
   consumer_bar();
 }
@@ -852,12 +838,15 @@ __device__ __forceinline__ void consume_box(const Ctx& c, const uint8_t* st, int
 #pragma unroll
   for (int sidx = 0; sidx < 8; ++sidx) {
     const float2 sc = __half22float2(sidx < 4 ? sh0[sidx] : sh1[sidx - 4]);
+    // the unit's digit scale (a power of two: the exponent bits) and its offset term (signed, 23 bits)
+    const float sxu = __int_as_float(offs[sidx] & 0x7F800000);
+    const int off = (offs[sidx] << 9) >> 9;
     // acc: {row g + 16 row g+8, high digit}, {same, low digit}, {16 row g+8, high digit}, {same, low digit};
     // every term is exact in int32 (|acc| <= 32 * 255 * 128)
-    const int r0 = (acc[sidx][0] - acc[sidx][2]) * 256 + (acc[sidx][1] - acc[sidx][3]) - offs[sidx];
-    const int r1 = ((acc[sidx][2] * 256 + acc[sidx][3]) >> 4) - offs[sidx];
-    tot[0] = fmaf(sc.x, static_cast<float>(r0), tot[0]);
-    tot[1] = fmaf(sc.y, static_cast<float>(r1), tot[1]);
+    const int r0 = (acc[sidx][0] - acc[sidx][2]) * 256 + (acc[sidx][1] - acc[sidx][3]) - off;
+    const int r1 = ((acc[sidx][2] * 256 + acc[sidx][3]) >> 4) - off;
+    tot[0] = fmaf(sc.x * sxu, static_cast<float>(r0), tot[0]);
+    tot[1] = fmaf(sc.y * sxu, static_cast<float>(r1), tot[1]);
   }
 }
 
@@ -868,12 +857,20 @@ struct Dest {
   unsigned long long off;  // byte offset in the exchange block of output 0 of this rank's shard
   bool all;
   bool partial;  // the outputs are fp32 partial sums (paired sharding): no rounding, no residual here
-  uint32_t* tagged = nullptr;  // single GPU: the outputs go here as tagged words instead
-  uint32_t tag = 0;
+  uint32_t* tagged = nullptr;  // tagged vectors: the outputs go here as tagged words instead (output 0 of this
+  uint32_t tag = 0;            // rank's shard); with `all`, also to the same place in every other rank's block
 };
+// The place in rank r's exchange block that corresponds to p in this rank's.
+template <typename T>
+__device__ __forceinline__ T* peer_ptr(const MegaArgs& a, T* p, int r) {
+  return reinterpret_cast<T*>(a.peers[r] + (reinterpret_cast<uint8_t*>(p) - a.peers[a.rank]));
+}
 __device__ __forceinline__ void store_out(const MegaArgs& a, const Dest& dst, int idx, __half v) {
   if (dst.tagged != nullptr) {
     st_tagged(dst.tagged + idx, v, dst.tag);
+    if (dst.all)
+      for (int r = 0; r < a.world; ++r)
+        if (r != a.rank) st_tagged_sys(peer_ptr(a, dst.tagged, r) + idx, v, dst.tag);
   } else if (dst.all) {
     for (int r = 0; r < a.world; ++r) reinterpret_cast<__half*>(a.peers[r] + dst.off)[idx] = v;
   } else {
@@ -883,16 +880,16 @@ __device__ __forceinline__ void store_out(const MegaArgs& a, const Dest& dst, in
 
 // Lanes 0..15 of one warp: output strip * 16 + lane, summed over all of K, gets its
 // epilogue and is written.
-__device__ __forceinline__ void finish_strip(const MegaArgs& a, int kind, int strip, float v, float sx, bool has_resid,
+__device__ __forceinline__ void finish_strip(const MegaArgs& a, int kind, int strip, float v, bool has_resid,
                                              __half resid, const Dest& out) {
   const int lane = threadIdx.x & 31;
   const int n = strip * kStripN + lane;
   if (out.partial) {
     if (lane < kStripN)
-      for (int r = 0; r < a.world; ++r) reinterpret_cast<float*>(a.peers[r] + out.off)[n] = v * sx;
+      for (int r = 0; r < a.world; ++r) reinterpret_cast<float*>(a.peers[r] + out.off)[n] = v;
     return;
   }
-  const __half r = __float2half_rn(v * sx);
+  const __half r = __float2half_rn(v);
   if (kind == kGu) {
     // rows interleave gate_i, up_i: even lanes hold the gate, the next lane its up value
     const float gf = __half2float(r);
@@ -911,9 +908,10 @@ __device__ __forceinline__ int chunk_owner(int b, int qn, int rn) {
   return rn + static_cast<int>(static_cast<unsigned>(b - big) / static_cast<unsigned>(qn));  // qn > 0 here
 }
 
-// resid / tresid: the vector added to the outputs, as halves or (single GPU) as tagged words this CTA has
-// already waited for when it loaded the vector as an input.
-__device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest& out, const uint32_t* tresid = nullptr) {
+// resid / tresid: the vector added to the outputs (element 0 = output 0 of this rank's shard), as halves or as
+// tagged words written by the op with tag tresid_tag.
+__device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest& out, const uint32_t* tresid = nullptr,
+                               uint32_t tresid_tag = 0) {
   const MegaArgs& a = c.a;
   const ProjShape p = proj_shape(a, kind);
   const int cta = blockIdx.x, G = gridDim.x;
@@ -923,7 +921,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
   proj_range(p, cta, G, i0, i1);
   const int B = i1 - i0;
   long long waited = 0, boxed = 0, ea = 0, eb = 0, ec = 0;
-  const bool tracing = a.trace != nullptr && lane == 0;  // every warp keeps its own clocks
+  const bool tracing = MLD_TRACING(a) && lane == 0;  // every warp keeps its own clocks
   // The op's boxes are cut into kCW contiguous chunks, one per warp (lengths differ by at most one), so
   // that a warp meets few strips; ring position kCW j + w holds box j of warp w's chunk.
   const int qn = B / kCW, rn = B % kCW;
@@ -942,7 +940,10 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
     // the strip's residual values are fetched now: whichever warp completes the strip has them at hand
     __half rv = __float2half_rn(0.0f);
     if (tresid != nullptr) {
-      if (lane < kStripN) rv = __ushort_as_half(static_cast<unsigned short>(ld_word(tresid + strip * kStripN + lane) & 0xFFFFu));
+      if (lane < kStripN) {
+        const uint32_t* rp = tresid + strip * kStripN + lane;
+        rv = tagged_value(c.w, rp, tresid_tag, ld_word(rp, c.w.sys));
+      }
     } else if (resid != nullptr && lane < kStripN) {
       rv = __ldcg(resid + strip * kStripN + lane);
     }
@@ -980,7 +981,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
       // the strip is this warp's alone: rows g and g+8 sit in lanes t == 0
       const float lo = __shfl_sync(0xffffffffu, tot[0], (lane & 7) * 4);
       const float hi = __shfl_sync(0xffffffffu, tot[1], (lane & 7) * 4);
-      finish_strip(a, kind, strip, (lane & 8) ? hi : lo, c.sx, resid != nullptr || tresid != nullptr, rv, out);
+      finish_strip(a, kind, strip, (lane & 8) ? hi : lo, resid != nullptr || tresid != nullptr, rv, out);
       if (tracing) ec += clock64() - e0;
       continue;
     }
@@ -1007,7 +1008,7 @@ __device__ void run_projection(Ctx& c, int kind, const __half* resid, const Dest
       float v = c.dump[(w_lo * 2 + 1) * kStripN + (lane & 15)];
       for (int w = w_lo + 1; w <= w_hi; ++w) v += c.dump[w * 2 * kStripN + (lane & 15)];
       if (lane == 0) c.proj_arrived()[w_lo] = 0;  // next used after the op's grid barrier
-      finish_strip(a, kind, strip, v, c.sx, resid != nullptr || tresid != nullptr, rv, out);
+      finish_strip(a, kind, strip, v, resid != nullptr || tresid != nullptr, rv, out);
     }
     if (tracing) eb += clock64() - e3;
   }
@@ -1063,7 +1064,7 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
   __half* sq = reinterpret_cast<__half*>(reinterpret_cast<float*>(c.xs) + warp * kWarpScratch);  // rotated, scaled q
   const uint32_t qtag = op_tag(c.epoch_base + c.op_index - 1);  // q, k, v come from the op before this one
   long long awaited = 0;
-  const bool atracing = a.trace != nullptr && threadIdx.x == 0;
+  const bool atracing = MLD_TRACING(a) && threadIdx.x == 0;
   // The first aw warps take every aw-th item of the op's sequence; an item is two ring stages.  A warp's
   // items lie 2 aw stages apart, which must not exceed the ring (2 kCW - 1 stages do for kCW warps: the
   // later stage of an item is waited for after the earlier one): shorter rings put fewer warps to work.
@@ -1088,7 +1089,7 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
       if (a.tagged) {  // all four words are asked for before any is looked at
         const uint32_t* qp = a.tq + (size_t)head * kHeadDim;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) qw[i] = ld_word(qp + lane + 32 * (i >> 1) + (i & 1) * (kHeadDim / 2));
+        for (int i = 0; i < 4; ++i) qw[i] = ld_word(qp + lane + 32 * (i >> 1) + (i & 1) * (kHeadDim / 2), false);
       }
 #pragma unroll
       for (int rep = 0; rep < 2; ++rep) {
@@ -1146,8 +1147,8 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
             const uint32_t* tv = a.tq + (size_t)(2 * a.heads + head) * kHeadDim;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              kw[i] = ld_word(tk + lane + 32 * (i >> 1) + (i & 1) * (kHeadDim / 2));
-              vw[i] = ld_word(tv + lane + 32 * (i >> 1) + (i & 1) * (kHeadDim / 2));
+              kw[i] = ld_word(tk + lane + 32 * (i >> 1) + (i & 1) * (kHeadDim / 2), false);
+              vw[i] = ld_word(tv + lane + 32 * (i >> 1) + (i & 1) * (kHeadDim / 2), false);
             }
           }
 #pragma unroll
@@ -1295,7 +1296,7 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
       last = atomicAdd(c.attn_arrived() + slot, 1) == kCW - 1 ? 1 : 0;
     }
     last = __shfl_sync(0xffffffffu, last, 0);
-    unsigned long long* trs = a.trace != nullptr && lane == 0
+    unsigned long long* trs = MLD_TRACING(a) && lane == 0
                                   ? a.trace + ((size_t)blockIdx.x * a.n_layers * kOpsPerLayer + c.op_index) * kTraceSlots
                                   : nullptr;
     if (last) {
@@ -1352,7 +1353,7 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
                 unsigned fv;
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(fv) : "l"(flags + u) : "memory");
                 if (fv == epoch) break;
-                if (globaltimer_ns() - t0 > kWaitLimitNs || *c.w.s_fail) {
+                if (globaltimer_ns() - t0 > c.w.limit || *c.w.s_fail) {
                   *c.w.s_fail = 1;
                   atomicCAS(a.error, 0, 21);
                   break;
@@ -1504,10 +1505,16 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
         // this rank's heads sit at rank * d_local in the full vector, which every rank needs
         if (a.tagged) {
           const uint32_t tg = op_tag(c.epoch_base + c.op_index) << 16;
-          uint32_t* dst = a.tattn + (size_t)head * kHeadDim + 4 * lane;
+          uint32_t* dst = a.tattn + (size_t)a.rank * a.d_local + (size_t)head * kHeadDim + 4 * lane;
           asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(tg | (pk.x & 0xFFFFu)),
                        "r"(tg | (pk.x >> 16)), "r"(tg | (pk.y & 0xFFFFu)), "r"(tg | (pk.y >> 16))
                        : "memory");
+          for (int r = 0; r < a.world; ++r)
+            if (r != a.rank)
+              asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(peer_ptr(a, dst, r)),
+                           "r"(tg | (pk.x & 0xFFFFu)), "r"(tg | (pk.x >> 16)), "r"(tg | (pk.y & 0xFFFFu)),
+                           "r"(tg | (pk.y >> 16))
+                           : "memory");
         } else if (a.paired) {  // o is split by input columns: this rank's heads are all it reads
           *reinterpret_cast<uint2*>(a.attn + (size_t)head * kHeadDim + 4 * lane) = pk;
         } else {
@@ -1568,12 +1575,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
     rope[e] = make_float2(cs, sn);
   }
   __syncthreads();
-  Waiter w{s_int, a.error};
+  Waiter w{s_int, a.error, a.wait_limit_ns, a.world > 1};
 
   if (warp == kCW) {
     if (lane == 0) producer_loop(a, ring, full, empty, w);
   } else {
-    Ctx c{a, ring, full, empty, xs, reinterpret_cast<int*>(us), 1.0f, rope, dump, s_int, w, 0, 0, 0ull, 0ull, 0u, 0};
+    Ctx c{a, ring, full, empty, xs, reinterpret_cast<int*>(us), rope, dump, s_int, w, 0, 0, 0ull, 0ull, 0u, 0};
     c.bar_target = *reinterpret_cast<const unsigned long long*>(s_int + kSharedInts + 1);
     c.xbar_target = *reinterpret_cast<const unsigned long long*>(s_int + kSharedInts + 3);
     // every launch completes at least one local barrier, so five epochs per barrier keep launches apart
@@ -1596,28 +1603,41 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
             s_act{a.act, nullptr, 0, 0, nullptr};
         const uint32_t* tres_o = nullptr;
         const uint32_t* tres_down = nullptr;
+        uint32_t tres_o_tag = 0, tres_down_tag = 0;
         const bool tg = a.tagged != 0;
+        uint32_t* tx_next = (l & 1) ? a.txb : a.txa;
         if (tg) {
           // tagged vectors: every op's outputs carry the op's number, readers wait word by word
           const unsigned e0 = c.epoch_base + l * kOpsPerLayer;
           d_qkv.tagged = a.tq, d_qkv.tag = op_tag(e0 + kQkv);
-          d_h.tagged = a.th, d_h.tag = op_tag(e0 + kO);
-          d_act.tagged = a.tact, d_act.tag = op_tag(e0 + kGu);
-          if (!last) d_x.tagged = (l & 1) ? a.txb : a.txa, d_x.tag = op_tag(e0 + kDown);
+          d_h.tagged = a.th + shard, d_h.tag = op_tag(e0 + kO);
+          d_act.tagged = a.tact + (size_t)a.rank * a.ffn_local, d_act.tag = op_tag(e0 + kGu);
+          // (one GPU: the last layer writes the caller's vector directly)
+          if (!last || sharded) d_x.tagged = tx_next + shard, d_x.tag = op_tag(e0 + kDown);
           if (l > 0) {
             s_x.tx = ((l - 1) & 1) ? a.txb : a.txa, s_x.tag = op_tag(e0 - 1);  // down of the layer before
-            tres_o = s_x.tx;
+            tres_o = s_x.tx + shard, tres_o_tag = s_x.tag;
           }
           s_attn.tx = a.tattn, s_attn.tag = op_tag(e0 + kAttn);
           s_h.tx = a.th, s_h.tag = op_tag(e0 + kO);
           s_act.tx = a.tact, s_act.tag = op_tag(e0 + kGu);
-          tres_down = a.th;
+          tres_down = a.th + shard, tres_down_tag = s_h.tag;
         }
+        // With tagged vectors a CTA without strips of a projection has no business with its input vector
+        // (with barriers every CTA keeps the same sequence of block-wide steps).
+        auto has_items = [&](int kind) {
+          if (!tg) return true;
+          int j0, j1;
+          proj_range(proj_shape(a, kind), blockIdx.x, gridDim.x, j0, j1);
+          return j1 > j0;
+        };
         c.op_index = l * kOpsPerLayer;
         trace_mark(c, 0);
-        load_x<true>(c, s_x, ly->norm1, d);
-        trace_mark(c, 1);
-        run_projection(c, kQkv, nullptr, d_qkv);
+        if (has_items(kQkv)) {
+          load_x<true>(c, s_x, ly->norm1, d);
+          trace_mark(c, 1);
+          run_projection(c, kQkv, nullptr, d_qkv);
+        }
         trace_mark(c, 2);
         op_boundary(c, tg, false);  // q, k, v stay on this rank
         trace_mark(c, 3);
@@ -1631,27 +1651,33 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
 
         c.op_index += 1;
         trace_mark(c, 0);
-        load_x<false>(c, s_attn, nullptr, d);
-        trace_mark(c, 1);
-        run_projection(c, kO, tres_o != nullptr ? nullptr : x_cur + shard, d_h, tres_o);
+        if (has_items(kO)) {
+          load_x<false>(c, s_attn, nullptr, d);
+          trace_mark(c, 1);
+          run_projection(c, kO, tres_o != nullptr ? nullptr : x_cur + shard, d_h, tres_o, tres_o_tag);
+        }
         trace_mark(c, 2);
         op_boundary(c, tg, true);
         trace_mark(c, 3);
 
         c.op_index += 1;
         trace_mark(c, 0);
-        load_x<true>(c, s_h, ly->norm2, d);
-        trace_mark(c, 1);
-        run_projection(c, kGu, nullptr, d_act);
+        if (has_items(kGu)) {
+          load_x<true>(c, s_h, ly->norm2, d);
+          trace_mark(c, 1);
+          run_projection(c, kGu, nullptr, d_act);
+        }
         trace_mark(c, 2);
         op_boundary(c, tg, true);
         trace_mark(c, 3);
 
         c.op_index += 1;
         trace_mark(c, 0);
-        load_x<false>(c, s_act, nullptr, a.ffn);
-        trace_mark(c, 1);
-        run_projection(c, kDown, tg ? nullptr : a.h + shard, d_x, tres_down);
+        if (has_items(kDown)) {
+          load_x<false>(c, s_act, nullptr, a.ffn);
+          trace_mark(c, 1);
+          run_projection(c, kDown, tg ? nullptr : a.h + shard, d_x, tres_down, tres_down_tag);
+        }
         trace_mark(c, 2);
         if (tg && last)
           grid_barrier(c);  // one barrier per launch keeps the launches' op numbers apart
@@ -1660,8 +1686,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
         trace_mark(c, 3);
         if (last && sharded && blockIdx.x == 0) {
           // the step's result, assembled from all ranks' shards, goes to the caller's vector
-          for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8)
-            *reinterpret_cast<uint4*>(a.x_out + i) = __ldcg(reinterpret_cast<const uint4*>(x_next + i));
+          for (int i = threadIdx.x * 8; i < d; i += kCW * 32 * 8) {
+            if (tg)
+              *reinterpret_cast<uint4*>(a.x_out + i) = ld_tagged8(c.w, tx_next + i, d_x.tag);
+            else
+              *reinterpret_cast<uint4*>(a.x_out + i) = __ldcg(reinterpret_cast<const uint4*>(x_next + i));
+          }
         }
       }
     } else {
@@ -1811,7 +1841,8 @@ struct MegaDecoder {
   std::vector<char> layer_set;
   uint8_t* scratch;
   int tagged;
-  uint32_t *tq, *tattn, *th, *tact, *txa, *txb;  // tagged-word vectors (inside scratch)
+  uint32_t *tq, *tattn, *th, *tact, *txa, *txb;  // tagged-word vectors (tq in scratch, the others in xchg)
+  size_t off_tagged, tagged_bytes, tq_bytes, flags_bytes;
   uint8_t* xchg;              // exchange block (vectors every rank needs + the cross-rank barrier counter)
   uint8_t* peers[8];          // every rank's exchange block as mapped here (own entry = xchg)
   size_t off_attn, off_h, off_act, off_xa, off_xb, off_xbar, off_ph, off_pd;
@@ -1878,10 +1909,7 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   int max_smem = 0;
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, cfg.device);
   int stages = (max_smem - fixed) / (kStageBytes + 16);
-  if (const char* e = getenv("MLD_MEGA_STAGES")) {
-    const int v = atoi(e);
-    if (v >= 2 && v < stages) stages = v;
-  }
+  if (cfg.ring_stages >= 2 && cfg.ring_stages < stages) stages = cfg.ring_stages;
   if (stages > 64) stages = 64;
   if (stages < kCW + 1) {  // every consumer warp needs a stage of its own in a round
     set_last_error_text("not enough shared memory for the persistent step kernel");
@@ -1890,7 +1918,6 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   }
   m->stages = stages;
   m->l2_ahead = 0;  // measured: asking L2 for the next op ahead of the ring's loads slows the step down
-  if (const char* e2 = getenv("MLD_MEGA_L2_AHEAD")) m->l2_ahead = atoi(e2) < 0 ? 0 : atoi(e2);
   m->smem_bytes = (size_t)fixed + (size_t)stages * (kStageBytes + 16);
   cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(m->smem_bytes));
@@ -1903,10 +1930,7 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
     return MLD_CUDA_ERROR;
   }
   m->grid = m->sms;
-  if (const char* g = getenv("MLD_MEGA_GRID")) {
-    const int v = atoi(g);
-    if (v >= 1 && v < m->grid) m->grid = v;
-  }
+  if (cfg.grid_limit >= 1 && cfg.grid_limit < m->grid) m->grid = cfg.grid_limit;
   // an attention range must not touch more than kAttSlots heads: ceil(n/nt)+1 with n = ceil(heads*nt/grid)
   // is at most ceil(heads/grid + 1/nt) + 1 <= heads/grid + 3
   if ((int64_t)m->heads_local * (cfg.max_seq / kTile + 1) * m->grid >= (int64_t(1) << 31) ||
@@ -1931,12 +1955,10 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   const size_t o_qkv = take((size_t)3 * dl * 2), o_ap = take((size_t)m->grid * kAttSlots * kAttDump * 4),
                o_at = take((size_t)m->heads_local * 4), o_af = take((size_t)(m->grid + m->heads_local) * 4),
                o_bar = take(8), o_err = take(4);
-  // one GPU: the op-to-op vectors as tagged words (MLD_MEGA_TAGGED=0 keeps the barriers instead)
-  m->tagged = cfg.world == 1 ? 1 : 0;
-  if (const char* et = getenv("MLD_MEGA_TAGGED")) m->tagged = m->tagged && atoi(et) != 0;
-  const size_t o_tq = take(m->tagged ? (size_t)3 * d * 4 : 0), o_ta = take(m->tagged ? (size_t)d * 4 : 0),
-               o_th = take(m->tagged ? (size_t)d * 4 : 0), o_tact = take(m->tagged ? (size_t)ffn * 4 : 0),
-               o_txa = take(m->tagged ? (size_t)d * 4 : 0), o_txb = take(m->tagged ? (size_t)d * 4 : 0);
+  // the op-to-op vectors as tagged words unless the descriptor asks for grid barriers (the split of o and down
+  // by input columns exchanges fp32 partial sums and keeps the barriers)
+  m->tagged = (cfg.handover == 0 && !m->paired) ? 1 : 0;
+  const size_t o_tq = take(m->tagged ? (size_t)3 * dl * 4 : 0);
   const size_t scratch_bytes = off;
   off = 0;  // the exchange block: same layout on every rank
   m->off_attn = take((size_t)d * 2);
@@ -1947,6 +1969,12 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   m->off_xbar = take(8);
   m->off_ph = take(m->paired ? (size_t)cfg.world * d * 4 : 0);
   m->off_pd = take(m->paired ? (size_t)cfg.world * d * 4 : 0);
+  // the vectors every rank reads in full, as tagged words (peers write their shards into them)
+  m->off_tagged = off;
+  const size_t o_ta = take(m->tagged ? (size_t)d * 4 : 0), o_th = take(m->tagged ? (size_t)d * 4 : 0),
+               o_tact = take(m->tagged ? (size_t)ffn * 4 : 0), o_txa = take(m->tagged ? (size_t)d * 4 : 0),
+               o_txb = take(m->tagged ? (size_t)d * 4 : 0);
+  m->tagged_bytes = off - m->off_tagged;
   const size_t xchg_bytes = off;
   const int Ns[4] = {3 * dl, m->paired ? d : dl, 2 * fl, m->paired ? d : dl};
   const int Ks[4] = {d, m->paired ? dl : d, d, m->paired ? fl : ffn};
@@ -1972,11 +2000,13 @@ int mega_create(const MegaConfig& cfg, MegaDecoder** out) {
   m->xa = reinterpret_cast<__half*>(m->xchg + m->off_xa);
   m->xb = reinterpret_cast<__half*>(m->xchg + m->off_xb);
   m->tq = reinterpret_cast<uint32_t*>(m->scratch + o_tq);
-  m->tattn = reinterpret_cast<uint32_t*>(m->scratch + o_ta);
-  m->th = reinterpret_cast<uint32_t*>(m->scratch + o_th);
-  m->tact = reinterpret_cast<uint32_t*>(m->scratch + o_tact);
-  m->txa = reinterpret_cast<uint32_t*>(m->scratch + o_txa);
-  m->txb = reinterpret_cast<uint32_t*>(m->scratch + o_txb);
+  m->tq_bytes = m->tagged ? (size_t)3 * dl * 4 : 0;
+  m->tattn = reinterpret_cast<uint32_t*>(m->xchg + o_ta);
+  m->th = reinterpret_cast<uint32_t*>(m->xchg + o_th);
+  m->tact = reinterpret_cast<uint32_t*>(m->xchg + o_tact);
+  m->txa = reinterpret_cast<uint32_t*>(m->xchg + o_txa);
+  m->txb = reinterpret_cast<uint32_t*>(m->xchg + o_txb);
+  m->flags_bytes = (size_t)(m->grid + m->heads_local) * 4;
   m->att_part = reinterpret_cast<float*>(m->scratch + o_ap);
   m->att_tickets = reinterpret_cast<int*>(m->scratch + o_at);
   m->att_flags = reinterpret_cast<unsigned*>(m->scratch + o_af);
@@ -2040,6 +2070,7 @@ int mega_ipc_import(MegaDecoder* m, const void* handles) {
   return MLD_OK;
 }
 
+#ifdef MLD_TRACE
 int mega_enable_trace(MegaDecoder* m, bool on) {
   if (on && m->trace == nullptr) {
     const size_t bytes = (size_t)m->grid * m->cfg.layers * kOpsPerLayer * kTraceSlots * sizeof(unsigned long long);
@@ -2058,18 +2089,32 @@ int mega_read_trace(MegaDecoder* m, unsigned long long* out, size_t count) {
                             cudaMemcpyDeviceToHost));
   return MLD_OK;
 }
+#endif
 int mega_grid(const MegaDecoder* m) { return m->grid; }
+
+const int* mega_error_word(const MegaDecoder* m) { return m->error; }
+
+// Back to the state after creation: counters zero, no tagged word or flag valid.  (Tags and flag epochs
+// derive from the launch counter; restarting it is safe only because everything that carries a tag or an
+// epoch is cleared with it.)
+int mega_reset(MegaDecoder* m) {
+  MLD_CUDA_CHECK(cudaMemset(m->error, 0, sizeof(int)));
+  MLD_CUDA_CHECK(cudaMemset(m->bar, 0, 8));
+  MLD_CUDA_CHECK(cudaMemset(m->xchg + m->off_xbar, 0, 8));
+  MLD_CUDA_CHECK(cudaMemset(m->att_tickets, 0, (size_t)m->heads_local * 4));
+  MLD_CUDA_CHECK(cudaMemset(m->att_flags, 0, m->flags_bytes));
+  if (m->tagged) {
+    MLD_CUDA_CHECK(cudaMemset(m->tq, 0, m->tq_bytes));
+    MLD_CUDA_CHECK(cudaMemset(m->xchg + m->off_tagged, 0, m->tagged_bytes));
+  }
+  MLD_CUDA_CHECK(cudaDeviceSynchronize());
+  return MLD_OK;
+}
+void mega_set_wait_limit(MegaDecoder* m, int us) { m->cfg.wait_limit_us = us; }
 
 int mega_device_status(MegaDecoder* m, int* code) {
   MLD_CUDA_CHECK(cudaMemcpy(code, m->error, sizeof(int), cudaMemcpyDeviceToHost));
-  if (*code != 0) {
-    // leave the barrier and tickets consistent for the next step
-    const int zero = 0;
-    cudaMemcpy(m->error, &zero, sizeof zero, cudaMemcpyHostToDevice);
-    cudaMemset(m->bar, 0, 8);
-    cudaMemset(m->att_tickets, 0, (size_t)m->heads_local * 4);
-    cudaMemset(m->xchg + m->off_xbar, 0, 8);  // ranks must reset together (after a failed step on any rank)
-  }
+  if (*code != 0) return mega_reset(m);
   return MLD_OK;
 }
 
@@ -2110,6 +2155,7 @@ int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream
   a.x_in = static_cast<const __half*>(x_in);
   a.x_out = static_cast<__half*>(x_out);
   a.tagged = m->tagged;
+  a.wait_limit_ns = static_cast<unsigned long long>(m->cfg.wait_limit_us > 0 ? m->cfg.wait_limit_us : 2000000) * 1000ull;
   a.tq = m->tq;
   a.tattn = m->tattn;
   a.th = m->th;

@@ -41,8 +41,10 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __half* __restr
   pdl_wait();
   pdl_launch_dependents();
   if (wait.world > 1) {  // x is a vector other ranks contribute to: wait for all of its shards
-    if (threadIdx.x == 0)
-      wait_peer_flags(wait.flags, wait.world, static_cast<unsigned>(*wait.step * wait.seq_per_step + wait.seq_off));
+    if (threadIdx.x == 0 &&
+        !wait_peer_flags(wait.flags, wait.world, static_cast<unsigned>(*wait.step * wait.seq_per_step + wait.seq_off),
+                         wait.limit_ns))
+      atomicExch(wait.error, kErrPeerWait);  // the step goes on with what has arrived; the host sees the code
     __syncthreads();
   }
   float ss = 0.0f;
@@ -349,8 +351,10 @@ __global__ void __launch_bounds__(256) copy_after_wait_kernel(const __half* __re
   pdl_wait();
   pdl_launch_dependents();
   if (wait.world > 1) {
-    if (threadIdx.x == 0)
-      wait_peer_flags(wait.flags, wait.world, static_cast<unsigned>(*wait.step * wait.seq_per_step + wait.seq_off));
+    if (threadIdx.x == 0 &&
+        !wait_peer_flags(wait.flags, wait.world, static_cast<unsigned>(*wait.step * wait.seq_per_step + wait.seq_off),
+                         wait.limit_ns))
+      atomicExch(wait.error, kErrPeerWait);
     __syncthreads();
   }
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = src[i];
@@ -454,13 +458,16 @@ struct mld_decoder {
   bool peer_mode;
   size_t off_attn, off_h, off_act, off_xa, off_xb, off_flags, xchg_bytes;
   int* peer_tickets;             // local: [4] CTA counters + [1] step counter
+  int* error;                    // device error word of the op chain (shared with its four plans)
+  int* error_host;               // pinned copy read back by mld_decoder_step_host
+  unsigned long long wait_limit_ns;
   // single GPU: the whole step as one persistent kernel (null = op-by-op path)
   mld::MegaDecoder* mega;
 };
 
 namespace {
 
-int make_plan(int n, int k, int block, int device, bool residual, int epilogue, mld_fc_plan** out) {
+int make_plan(int n, int k, int block, int device, bool residual, int epilogue, int* error_word, mld_fc_plan** out) {
   mld_fc_desc fd;
   memset(&fd, 0, sizeof fd);
   fd.n = n;
@@ -476,7 +483,9 @@ int make_plan(int n, int k, int block, int device, bool residual, int epilogue, 
   fd.device = device;
   fd.has_bias = residual ? 1 : 0;  // the residual vector rides in the bias slot of the dst write
   fd.epilogue = epilogue;
-  return mld_fc_plan_create(&fd, out);
+  const int rc = mld_fc_plan_create(&fd, out);
+  if (rc == MLD_OK) fc_plan_share_error(*out, error_word);
+  return rc;
 }
 
 int gather(mld_decoder* dec, const __half* send, __half* recv, int count, cudaStream_t stream) {
@@ -599,10 +608,9 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   if (device < 0) MLD_CUDA_CHECK(cudaGetDevice(&device));
   MLD_CUDA_CHECK(cudaSetDevice(device));
 
-  {
-    const char* pdl = getenv("MLD_GEMV_PDL");  // "0" disables programmatic dependent launch everywhere
-    g_glue_pdl = !(pdl != nullptr && strcmp(pdl, "0") == 0);
-  }
+  MLD_REQUIRE(d->mode >= MLD_DECODER_AUTO && d->mode <= MLD_DECODER_SINGLE_KERNEL, "bad decoder mode");
+  MLD_REQUIRE(d->handover == 0 || d->handover == 1, "bad handover");
+  MLD_REQUIRE(d->grid_limit >= 0 && d->ring_stages >= 0 && d->wait_limit_us >= 0, "bad tuning field");
   mld_decoder* dec = new mld_decoder();
   dec->d = *d;
   dec->d.device = device;
@@ -615,20 +623,29 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   dec->scratch = nullptr;
   dec->xchg = nullptr;
   dec->peer_tickets = nullptr;
+  dec->error = nullptr;
+  dec->error_host = nullptr;
+  dec->wait_limit_ns = static_cast<unsigned long long>(d->wait_limit_us > 0 ? d->wait_limit_us : 2000000) * 1000ull;
   dec->peer_mode = false;
   dec->mega = nullptr;
   for (int r = 0; r < 8; ++r) dec->xchg_peers[r] = nullptr;
   dec->p_qkv = dec->p_o = dec->p_gu = dec->p_down = nullptr;
-  int rc = make_plan(3 * dec->d_local, d->d_model, d->block, device, false, MLD_EPILOGUE_NONE, &dec->p_qkv);
-  if (rc == MLD_OK) rc = make_plan(dec->d_local, d->d_model, d->block, device, true, MLD_EPILOGUE_NONE, &dec->p_o);
+  int rc = MLD_OK;
+  if (cudaMalloc(&dec->error, sizeof(int)) != cudaSuccess || cudaMemset(dec->error, 0, sizeof(int)) != cudaSuccess ||
+      cudaHostAlloc(&dec->error_host, sizeof(int), cudaHostAllocDefault) != cudaSuccess) {
+    set_last_error_text("decoder status word allocation failed");
+    rc = MLD_CUDA_ERROR;
+  }
+  int* ew = dec->error;
+  if (rc == MLD_OK) rc = make_plan(3 * dec->d_local, d->d_model, d->block, device, false, MLD_EPILOGUE_NONE, ew, &dec->p_qkv);
+  if (rc == MLD_OK) rc = make_plan(dec->d_local, d->d_model, d->block, device, true, MLD_EPILOGUE_NONE, ew, &dec->p_o);
   if (rc == MLD_OK)
-    rc = make_plan(2 * dec->ffn_local, d->d_model, d->block, device, false, MLD_EPILOGUE_SWIGLU_PAIRS, &dec->p_gu);
-  if (rc == MLD_OK) rc = make_plan(dec->d_local, d->ffn, d->block, device, true, MLD_EPILOGUE_NONE, &dec->p_down);
+    rc = make_plan(2 * dec->ffn_local, d->d_model, d->block, device, false, MLD_EPILOGUE_SWIGLU_PAIRS, ew, &dec->p_gu);
+  if (rc == MLD_OK) rc = make_plan(dec->d_local, d->ffn, d->block, device, true, MLD_EPILOGUE_NONE, ew, &dec->p_down);
   // split count: fill the GPU about four CTAs deep
   int sms = sm_count(device);
   {
-    const char* pf = getenv("MLD_DECODER_PREFETCH");  // "0" disables the next-projection L2 prefetch
-    dec->prefetch = !(pf != nullptr && strcmp(pf, "0") == 0);
+    dec->prefetch = true;  // every projection asks L2 for the next one's weights behind its own
     dec->bytes_qkv = (size_t)3 * dec->d_local * d->d_model / 2;
     dec->bytes_o = (size_t)dec->d_local * d->d_model / 2;
     dec->bytes_gu = (size_t)2 * dec->ffn_local * d->d_model / 2;
@@ -724,31 +741,33 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
       return MLD_NCCL_ERROR;
     }
   }
-  // One GPU: run the step as one persistent kernel when the shape allows it
-  // (MLD_DECODER_MODE=ops keeps the op-by-op path).
-  const char* mode = getenv("MLD_DECODER_MODE");
-  // (a sharded decoder does so when asked with MLD_DECODER_MODE=mega and created without an NCCL id: its
-  // ranks exchange shards with peer stores, see mld_decoder_ipc_export).
-  const bool want_mega = d->world == 1 ? !(mode != nullptr && strcmp(mode, "ops") == 0)
-                                       : (mode != nullptr && strcmp(mode, "mega") == 0 && nccl_id128 == nullptr);
+  // One GPU: run the step as one persistent kernel when the shape allows it, unless the descriptor asks
+  // for the op chain.  A sharded decoder does so when asked to (mode MLD_DECODER_SINGLE_KERNEL) and created
+  // without an NCCL id: its ranks exchange shards with peer stores, see mld_decoder_ipc_export.
+  const bool forced = d->mode == MLD_DECODER_SINGLE_KERNEL;
+  const bool want_mega = d->world == 1 ? d->mode != MLD_DECODER_OP_CHAIN : (forced && nccl_id128 == nullptr);
   if (want_mega) {
     MegaConfig mc = {d->layers, d->d_model, d->heads, d->head_dim, d->ffn, d->max_seq, d->block,
                      d->rms_eps, d->rope_min_timescale, d->rope_max_timescale, device, d->rank, d->world,
-                     d->shard_layout};
+                     d->shard_layout, d->handover, d->grid_limit, d->ring_stages, d->wait_limit_us};
     if (mega_supported(mc)) {
       const int mrc = mega_create(mc, &dec->mega);
       if (mrc != MLD_OK) {
         dec->mega = nullptr;
-        if (mode != nullptr && strcmp(mode, "mega") == 0) {
+        if (forced) {
           mld_decoder_destroy(dec);
           return mrc;
         }
       }
+    } else if (forced) {
+      set_last_error_text("decoder shape not supported by the single-kernel decoder");
+      mld_decoder_destroy(dec);
+      return MLD_UNIMPLEMENTED;
     }
   }
   if (d->world > 1 && d->shard_layout != 0 && dec->mega == nullptr) {
     set_last_error_text("shard_layout 1 (o and down split by input columns) needs the single-kernel decoder: "
-                        "MLD_DECODER_MODE=mega and no NCCL id");
+                        "mode MLD_DECODER_SINGLE_KERNEL and no NCCL id");
     mld_decoder_destroy(dec);
     return MLD_UNIMPLEMENTED;
   }
@@ -769,6 +788,8 @@ int mld_decoder_destroy(mld_decoder* dec) {
     if (dec->xchg_peers[r] != nullptr && dec->xchg_peers[r] != dec->xchg) cudaIpcCloseMemHandle(dec->xchg_peers[r]);
   if (dec->xchg != nullptr) cudaFree(dec->xchg);
   if (dec->peer_tickets != nullptr) cudaFree(dec->peer_tickets);
+  if (dec->error != nullptr) cudaFree(dec->error);
+  if (dec->error_host != nullptr) cudaFreeHost(dec->error_host);
   delete dec;
   return MLD_OK;
 }
@@ -819,7 +840,8 @@ int mld_decoder_set_layer(mld_decoder* dec, int32_t layer, const mld_layer_weigh
 
 int mld_decoder_is_single_kernel(const mld_decoder* dec) { return dec != nullptr && dec->mega != nullptr ? 1 : 0; }
 
-// Tuning aids (not part of the public header): per-CTA timestamps of the persistent step kernel.
+#ifdef MLD_TRACE
+// Tuning aids, compiled only with -DMLD_TRACE: per-CTA timestamps of the persistent step kernel.
 __attribute__((visibility("default"))) int mld_debug_decoder_trace(mld_decoder* dec, int on) {
   if (dec == nullptr || dec->mega == nullptr) return MLD_INVALID_ARGUMENT;
   return mega_enable_trace(dec->mega, on != 0);
@@ -832,16 +854,48 @@ __attribute__((visibility("default"))) int mld_debug_decoder_read_trace(mld_deco
 __attribute__((visibility("default"))) int mld_debug_decoder_grid(mld_decoder* dec) {
   return dec != nullptr && dec->mega != nullptr ? mega_grid(dec->mega) : 0;
 }
+#endif
 
 int mld_decoder_device_status(mld_decoder* dec, int32_t* code) {
   MLD_REQUIRE(dec != nullptr && code != nullptr, "null argument");
   *code = 0;
+  int c = 0;
   if (dec->mega != nullptr) {
-    int c = 0;
     const int rc = mega_device_status(dec->mega, &c);
-    *code = c;
-    return rc;
+    if (rc != MLD_OK) return rc;
+  } else {
+    // the op chain: one word shared by its FullyConnected plans and glue kernels
+    MLD_CUDA_CHECK(cudaMemcpy(&c, dec->error, sizeof(int), cudaMemcpyDeviceToHost));
+    if (c != 0) {
+      const int rc = mld_decoder_reset(dec);
+      if (rc != MLD_OK) return rc;
+    }
   }
+  *code = c;
+  if (c != 0) {
+    set_last_error_text("a bounded device-side wait of the decode step gave up");
+    return MLD_TIMEOUT;
+  }
+  return MLD_OK;
+}
+
+int mld_decoder_reset(mld_decoder* dec) {
+  MLD_REQUIRE(dec != nullptr, "null argument");
+  MLD_CUDA_CHECK(cudaSetDevice(dec->d.device));
+  if (dec->mega != nullptr) return mega_reset(dec->mega);
+  MLD_CUDA_CHECK(cudaMemset(dec->error, 0, sizeof(int)));
+  MLD_CUDA_CHECK(cudaMemset(dec->tickets, 0, (size_t)dec->heads_local * 4));
+  if (dec->peer_tickets != nullptr) MLD_CUDA_CHECK(cudaMemset(dec->peer_tickets, 0, 5 * sizeof(int)));
+  if (dec->xchg != nullptr) MLD_CUDA_CHECK(cudaMemset(dec->xchg + dec->off_flags, 0, 4 * 8 * sizeof(unsigned)));
+  MLD_CUDA_CHECK(cudaDeviceSynchronize());
+  return MLD_OK;
+}
+
+int mld_decoder_set_wait_limit(mld_decoder* dec, int32_t wait_limit_us) {
+  MLD_REQUIRE(dec != nullptr && wait_limit_us >= 0, "bad argument");
+  dec->d.wait_limit_us = wait_limit_us;
+  dec->wait_limit_ns = static_cast<unsigned long long>(wait_limit_us > 0 ? wait_limit_us : 2000000) * 1000ull;
+  if (dec->mega != nullptr) mega_set_wait_limit(dec->mega, wait_limit_us);
   return MLD_OK;
 }
 
@@ -887,6 +941,8 @@ int mld_decoder_step(mld_decoder* dec, const void* x_in, void* x_out, int32_t po
     pw.step = dec->peer_tickets + 4;
     pw.seq_off = 4 * layer + kind + 1;
     pw.seq_per_step = 4 * d.layers;
+    pw.error = dec->error;
+    pw.limit_ns = dec->wait_limit_ns;
     return pw;
   };
   const __half* x = static_cast<const __half*>(x_in);
@@ -981,7 +1037,14 @@ int mld_decoder_step_host(mld_decoder* dec, const void* x_host, void* y_host, in
   const int rc = mld_decoder_step(dec, dec->x_stage, dec->y_stage, pos, stream);
   if (rc != MLD_OK) return rc;
   MLD_CUDA_CHECK(cudaMemcpyAsync(y_host, dec->y_stage, bytes, cudaMemcpyDeviceToHost, stream));
+  // the step's status word travels behind the result in the same stream
+  const int* status = dec->mega != nullptr ? mega_error_word(dec->mega) : dec->error;
+  MLD_CUDA_CHECK(cudaMemcpyAsync(dec->error_host, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
   MLD_CUDA_CHECK(cudaStreamSynchronize(stream));
+  if (*dec->error_host != 0) {
+    set_last_error_text("a bounded device-side wait of the decode step gave up");
+    return MLD_TIMEOUT;
+  }
   return MLD_OK;
 }
 

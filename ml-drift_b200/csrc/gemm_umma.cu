@@ -591,17 +591,18 @@ int launch_gemm_umma(bool i8, const void* a_mat, const void* b_mat, const GemmGe
   a.y = y;
   a.dst_layout = dst_layout;
   a.error = error;
-  static bool configured[2] = {false, false};
+  static bool configured[2][kMaxDevices];
+  int dev;
   if (i8) {
-    if (!configured[1]) {
+    if (needs_configure(configured[1], &dev)) {
       MLD_CUDA_CHECK(cudaFuncSetAttribute(gemm_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-      configured[1] = true;
+      if (dev >= 0) configured[1][dev] = true;
     }
     gemm_umma_kernel<true><<<g.grid, kGemmThreads, g.smem_bytes, stream>>>(ta, tb, a);
   } else {
-    if (!configured[0]) {
+    if (needs_configure(configured[0], &dev)) {
       MLD_CUDA_CHECK(cudaFuncSetAttribute(gemm_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-      configured[0] = true;
+      if (dev >= 0) configured[0][dev] = true;
     }
     gemm_umma_kernel<false><<<g.grid, kGemmThreads, g.smem_bytes, stream>>>(ta, tb, a);
   }

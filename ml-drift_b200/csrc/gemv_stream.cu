@@ -208,7 +208,11 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
   const int r_hi = min(a.src_slices, r_lo + a.rows_per_split);
   const int n_st = (r_hi - r_lo + kStageRows - 1) / kStageRows;
 
+#ifdef MLD_TRACE  // per-CTA timestamps for tuning, compiled in only on request
   unsigned long long* tr = a.trace != nullptr ? a.trace + (size_t)blockIdx.x * 8 : nullptr;
+#else
+  constexpr unsigned long long* tr = nullptr;
+#endif
   // The producer thread initialises the barriers and goes straight on to issue
   // its first loads; the consumers wait for the initialisation on a named
   // barrier the producer warp only arrives at.
@@ -269,7 +273,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
       if (a.pdl) pdl_wait();
       if (a.wait.world > 1) {
         const unsigned seq = static_cast<unsigned>(*a.wait.step * a.wait.seq_per_step + a.wait.seq_off);
-        if (!wait_peer_flags(a.wait.flags, a.wait.world, seq)) atomicExch(a.error, 4);
+        if (!wait_peer_flags(a.wait.flags, a.wait.world, seq, a.wait.limit_ns)) atomicExch(a.error, kErrPeerWait);
       }
       if (tr) tr[2] = globaltimer_ns();
       for (int it = 0; it < head; ++it) issue_x(it, it);
@@ -531,10 +535,11 @@ template <int BITS, int W, bool SUBNORMAL, bool MONE>
 int launch_strip_t(const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a, const StripGeometry& gm,
                    cudaStream_t stream) {
   auto kern = fc_strip_kernel<BITS, W, SUBNORMAL, MONE>;
-  static bool configured = false;  // per instantiation
-  if (!configured) {
+  static bool configured[kMaxDevices];  // per instantiation and device
+  int dev;
+  if (needs_configure(configured, &dev)) {
     MLD_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    configured = true;
+    if (dev >= 0) configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(gm.grid, 1, 1);
@@ -576,7 +581,7 @@ int launch_strip_w(bool subnormal, bool mone, const CUtensorMap& tw, const CUten
 }  // namespace
 
 StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slices, int scale_mode, int sms,
-                             bool pdl) {
+                             bool pdl, int smem_limit_kb) {
   StripGeometry gm;
   memset(&gm, 0, sizeof gm);
   const int N4 = align_n(N, 4), SS = div_up(K, 4);
@@ -626,10 +631,7 @@ StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slic
   // With programmatic dependent launch two consecutive GEMVs share an SM while
   // one drains and the next prefetches, so each takes at most half of it.
   int budget = pdl ? 112 * 1024 : 224 * 1024;
-  if (const char* kb = getenv("MLD_GEMV_SMEM_KB")) {  // tuning override
-    const int v = atoi(kb);
-    if (v >= 32 && v <= 224) budget = v * 1024;
-  }
+  if (smem_limit_kb >= 32 && smem_limit_kb <= 224) budget = smem_limit_kb * 1024;
   int stages = (budget - fixed) / gm.stage_bytes;
   if (stages > 16) stages = 16;
   if (stages < 2) stages = (227 * 1024 - fixed) / gm.stage_bytes;

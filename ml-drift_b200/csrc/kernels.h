@@ -53,7 +53,10 @@ struct PeerWait {
   const unsigned* flags;     // local flags, one per rank
   const int* step;
   int seq_off, seq_per_step;
+  int* error;                // device error word: receives code 4 when the wait runs out
+  unsigned long long limit_ns;
 };
+enum { kErrPeerWait = 4 };
 
 struct StripArgs {
   const void* x;      // fp16, sliced [K/4][M_total][4] (for one token a plain vector)
@@ -92,7 +95,10 @@ struct StripGeometry {
   size_t smem_bytes;
 };
 StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slices, int scale_mode, int sms,
-                             bool pdl);
+                             bool pdl, int smem_limit_kb = 0);
+// Makes the plan's kernels report their bounded waits that ran out in `word` (a device int the caller
+// owns and reads) instead of the plan's own word.
+void fc_plan_share_error(mld_fc_plan* plan, int* word);
 // mld_fc_run with the sharded-decoder hooks (null = none); not part of the C ABI.
 int fc_run_internal(mld_fc_plan* plan, const void* src, const void* weights, const void* scale, const void* zero_point,
                     const void* bias, void* dst, int32_t tokens, void* stream, const PeerScatter* scatter,
@@ -107,6 +113,10 @@ struct MegaConfig {
   int device;
   int rank, world;  // sharding: heads, o/down outputs and FFN units are split evenly over the ranks
   int shard_layout; // 0: every projection split by output rows; 1: o and down split by input columns
+  int handover;     // 0: op-to-op vectors as tagged words; 1: grid barriers between ops
+  int grid_limit;   // > 0: at most this many CTAs
+  int ring_stages;  // > 0: at most this many ring stages
+  int wait_limit_us;  // > 0: bound on every device-side wait, microseconds (default 2 000 000)
 };
 struct MegaLayerPtrs {
   const void *wqkv, *sqkv, *wo, *so, *wgu, *sgu, *wdown, *sdown, *norm1, *norm2;
@@ -120,11 +130,16 @@ int mega_set_layer(MegaDecoder* m, int layer, const MegaLayerPtrs& p);
 int mega_step(MegaDecoder* m, const void* x_in, void* x_out, int pos, cudaStream_t stream);
 // Reads (and clears) the kernel's error word: 0 = every wait of the last steps was satisfied.
 int mega_device_status(MegaDecoder* m, int* code);
+const int* mega_error_word(const MegaDecoder* m);
+int mega_reset(MegaDecoder* m);
+void mega_set_wait_limit(MegaDecoder* m, int us);
 // Sharded: every rank exports its exchange block (64-byte IPC handle) and imports all of them (rank order).
 int mega_ipc_export(MegaDecoder* m, void* handle64);
 int mega_ipc_import(MegaDecoder* m, const void* handles);
+#ifdef MLD_TRACE
 int mega_enable_trace(MegaDecoder* m, bool on);
 int mega_read_trace(MegaDecoder* m, unsigned long long* out, size_t count);
+#endif
 int mega_grid(const MegaDecoder* m);
 
 // ----------------------------------------------------------------- prefill GEMM

@@ -766,6 +766,14 @@ ORC_API void orc_gemv_f32_fast(int bits, int K, int N, const float* x,
   }
 }
 
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -292,3 +292,17 @@ def gemv_f32_fast(bits, x, packed, N, scale_gn, bias=None):
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """Thread count of the OpenMP loops (launchers such as torchrun export OMP_NUM_THREADS=1)."""
+    lib().orc_set_num_threads(int(n))
+
+
+def host_cores() -> int:
+    """Cores this process may run on."""
+    import os
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1

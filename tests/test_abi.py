@@ -37,6 +37,13 @@ def test_library_exports_every_declared_symbol(mld):
         assert hasattr(lib, name), f"{name} is declared in include/ but not exported"
 
 
+def test_library_exports_nothing_the_header_does_not_declare(mld):
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", mld.binding.LIB_PATH], capture_output=True, text=True, check=True)
+    exported = {ln.split()[-1] for ln in out.stdout.splitlines() if " T " in ln}
+    assert exported == set(_declared()), exported ^ set(_declared())
+
+
 def test_status_strings_and_sizes(mld):
     lib = mld.binding.lib()
     assert lib.mld_status_string(0) == b"OK"

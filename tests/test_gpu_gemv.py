@@ -32,7 +32,7 @@ def _dev(a):
 
 
 def _run(mld, oracle, precision, bits, x, packed, N, K, scale=None, zp=None, bias=None, mode=None, G=1,
-         scalar_scale=0.0, scalar_zp=None, layout="sliced", force_generic=False):
+         scalar_scale=0.0, scalar_zp=None, layout="sliced", force_generic=False, exact_operands=False):
     """Runs mld_fc_run on logical float inputs; returns [M][N] float32."""
     prec = getattr(mld, precision)
     half = precision != "F32"
@@ -57,7 +57,7 @@ def _run(mld, oracle, precision, bits, x, packed, N, K, scale=None, zp=None, bia
                                   scalar_zero_point=0.0 if scalar_zp is None else scalar_zp,
                                   has_zero_point=(zp is not None or scalar_zp is not None),
                                   has_bias=bias is not None, precision=prec, src_layout=lay, dst_layout=lay,
-                                  max_tokens=M, force_path=mld.PATH_GEMV)
+                                  max_tokens=M, force_path=mld.PATH_GEMV, exact_operands=exact_operands)
     if force_generic:
         plan_ws = plan.workspace_bytes()
     S = (N + 3) // 4
@@ -178,15 +178,15 @@ STREAM_CASES = [
 
 @pytest.mark.parametrize("operands", ["subnormal", "exact"])
 @pytest.mark.parametrize("bits,K,N,block,M", STREAM_CASES)
-def test_streaming_gemv_vs_oracle(mld, oracle, monkeypatch, operands, bits, K, N, block, M):
-    monkeypatch.setenv("MLD_GEMV_OPERANDS", operands)
+def test_streaming_gemv_vs_oracle(mld, oracle, operands, bits, K, N, block, M):
     rng = np.random.default_rng(bits + K + N + block + M)
     q, s, packed = _quantised_case(oracle, rng, bits, K, N, block)
     G = s.shape[1]
     x = rng.standard_normal((M, K)).astype(np.float16).astype(np.float32)
     bias = (rng.standard_normal(N) * 0.01).astype(np.float32) if (N % 3 == 0) else None
     mode = mld.SCALE_BLOCK if G > 1 else mld.SCALE_PER_CHANNEL
-    y = _run(mld, oracle, "F32F16", bits, x, packed, N, K, scale=s, bias=bias, mode=mode, G=G)
+    y = _run(mld, oracle, "F32F16", bits, x, packed, N, K, scale=s, bias=bias, mode=mode, G=G,
+             exact_operands=operands == "exact")
     assert not np.isnan(y).any()
     plain = oracle.fc_plain_reference(q, oracle.f16_bits_to_f32(oracle.f32_to_f16_bits(s)), x,
                                       bias=None if bias is None else bias.astype(np.float16).astype(np.float32))
@@ -239,7 +239,7 @@ def test_row_major_single_token(mld, oracle):
 
 
 def test_config1_f32_int8(mld, oracle):
-    # BASELINE config 1: N=2048, K=2048, INT8 per-channel, fp32 activations and bias, seed 0
+    # the W8 per-channel CPU-runnable case: N=2048, K=2048, INT8, fp32 activations and bias, seed 0
     rng = np.random.default_rng(0)
     K = N = 2048
     w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)

@@ -25,12 +25,12 @@ def _model(rng, L, heads, ffn, T):
     return layers, kc, vc
 
 
-def _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id, shard_layout=0):
+def _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id, shard_layout=0, **kw):
     shd = mld.sharding
     d = heads * 128
     dev = torch.device("cuda", torch.cuda.current_device())
     dec = mld.Decoder(len(layers), d, heads, ffn, T, rank=rank, world=world, nccl_id=nccl_id,
-                      shard_layout=shard_layout)
+                      shard_layout=shard_layout, **kw)
     rows = {"qkv": shd.qkv_shard_rows(heads, 128, rank, world), "o": shd.column_shard_rows(d, rank, world),
             "gu": shd.gate_up_shard_rows(ffn, rank, world), "down": shd.column_shard_rows(d, rank, world)}
     in_cols = {"qkv": None, "gu": None, "o": None, "down": None}
@@ -59,7 +59,18 @@ def _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id, shar
     return dec, keep
 
 
-def _worker(rank, world, port, out_dir, exchange):
+EXCHANGES = {
+    # name: (decoder mode, shard layout, extra descriptor fields, how shards travel)
+    "nccl": ("op_chain", 0, {}, "nccl"),                 # chain of kernels, ncclAllGather after each producer
+    "peer": ("op_chain", 0, {}, "ipc"),                  # chain of kernels storing shards into every rank's memory
+    "mega": ("single", 0, {}, "ipc"),                    # one persistent kernel per rank, tagged words over NVLink
+    "mega_barriers": ("single", 0, {"handover": 1}, "ipc"),   # the same with cross-rank grid barriers
+    "mega_paired": ("single", 1, {}, "ipc"),             # o / down split by input columns, fp32 partial sums
+}
+SHAPES = {"small": (2, 4, 512, 64, 40), "wide": (2, 8, 2816, 300, 257)}   # L, heads, ffn, T, pos
+
+
+def _setup(rank, world, port):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     import __graft_entry__ as g
@@ -69,29 +80,39 @@ def _worker(rank, world, port, out_dir, exchange):
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("gloo", rank=rank, world_size=world)
+    return mld, dist
+
+
+def _sharded_decoder(mld, dist, exchange, model, heads, ffn, T, rank, world, **kw):
+    mode_name, layout, extra, travel = EXCHANGES[exchange]
+    mode = mld.DECODER_SINGLE_KERNEL if mode_name == "single" else mld.DECODER_OP_CHAIN
     nccl_id = None
-    # "mega": every rank runs the whole step as one persistent kernel, shards go to the peers with plain
-    # stores and the kernel's barriers span the ranks; "peer" / "nccl": the chain of kernels
-    os.environ["MLD_DECODER_MODE"] = "mega" if exchange.startswith("mega") else "ops"
-    layout = 1 if exchange == "mega_paired" else 0
-    if exchange == "nccl":
+    if travel == "nccl":
         idt = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:
             idt = torch.frombuffer(bytearray(mld.comm_unique_id()), dtype=torch.uint8).clone()
         dist.broadcast(idt, 0)
         nccl_id = idt.numpy().tobytes()
-    L, heads, ffn, T, pos = 2, 4, 512, 64, 40
-    d = heads * 128
-    layers, kc, vc = _model(np.random.default_rng(0), L, heads, ffn, T)
-    x = torch.from_numpy(np.random.default_rng(1).standard_normal(d).astype(np.float16)).cuda()
-    dec, keep = _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id, layout)
-    assert dec.single_kernel == exchange.startswith("mega")
-    if exchange in ("peer", "mega", "mega_paired"):         # shards go straight into every rank's exchange block
+    layers, kc, vc = model
+    dec, keep = _make_decoder(mld, layers, kc, vc, heads, ffn, T, rank, world, nccl_id, layout, mode=mode,
+                              **dict(extra, **kw))
+    assert dec.single_kernel == (mode_name == "single")
+    if travel == "ipc":         # shards go straight into every rank's exchange block
         mine = torch.frombuffer(bytearray(dec.ipc_export()), dtype=torch.uint8).clone()
         table = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
         dist.all_gather(table, mine)
         dec.ipc_import(b"".join(t.numpy().tobytes() for t in table))
         dist.barrier()
+    return dec, keep
+
+
+def _worker(rank, world, port, out_dir, exchange, shape):
+    mld, dist = _setup(rank, world, port)
+    L, heads, ffn, T, pos = SHAPES[shape]
+    d = heads * 128
+    model = _model(np.random.default_rng(0), L, heads, ffn, T)
+    x = torch.from_numpy(np.random.default_rng(1).standard_normal(d).astype(np.float16)).cuda()
+    dec, keep = _sharded_decoder(mld, dist, exchange, model, heads, ffn, T, rank, world)
     y = torch.empty(d, dtype=torch.float16, device="cuda")
     for _ in range(3):                       # repeated steps reuse the gather buffers
         dec.step(x, y, pos)
@@ -104,8 +125,8 @@ def _worker(rank, world, port, out_dir, exchange):
     dist.barrier()
     assert dec.device_status() == 0
     if rank == 0:
-        os.environ["MLD_DECODER_MODE"] = "ops"
-        single, keep1 = _make_decoder(mld, layers, kc, vc, heads, ffn, T, 0, 1, None)
+        layers, kc, vc = model
+        single, keep1 = _make_decoder(mld, layers, kc, vc, heads, ffn, T, 0, 1, None, mode=mld.DECODER_OP_CHAIN)
         y1 = torch.empty_like(y)
         single.step(x, y1, pos)
         torch.cuda.synchronize()
@@ -118,13 +139,84 @@ def _worker(rank, world, port, out_dir, exchange):
     dist.destroy_process_group()
 
 
+def _port(offset):
+    return 29700 + (os.getpid() % 2000) + offset
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("exchange", ["nccl", "peer", "mega", "mega_paired"])
-def test_two_gpu_sharded_decode_equals_single_gpu(tmp_path, exchange):
+@pytest.mark.parametrize("exchange,shape", [("nccl", "small"), ("peer", "small"), ("mega", "small"), ("mega", "wide"),
+                                            ("mega_barriers", "small"), ("mega_paired", "small")])
+def test_two_gpu_sharded_decode_equals_single_gpu(tmp_path, exchange, shape):
     import torch.multiprocessing as mp
-    port = 29700 + (os.getpid() % 2000) + {"nccl": 0, "peer": 7, "mega": 13, "mega_paired": 19}[exchange]
-    mp.spawn(_worker, args=(2, port, str(tmp_path), exchange), nprocs=2, join=True)
+    port = _port(list(EXCHANGES).index(exchange) * 7 + (3 if shape == "wide" else 0))
+    mp.spawn(_worker, args=(2, port, str(tmp_path), exchange, shape), nprocs=2, join=True)
     err, finite, same = open(tmp_path / "result.txt").read().split()
     assert int(finite) == 1
     assert int(same) == 1                    # every rank holds the same gathered output
+    assert float(err) < 1e-2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+@pytest.mark.parametrize("exchange", ["mega", "peer"])
+def test_four_gpu_sharded_decode_equals_single_gpu(tmp_path, exchange):
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(4, _port(61 + list(EXCHANGES).index(exchange)), str(tmp_path), exchange, "wide"),
+             nprocs=4, join=True)
+    err, finite, same = open(tmp_path / "result.txt").read().split()
+    assert int(finite) == 1 and int(same) == 1
+    assert float(err) < 1e-2
+
+
+def _late_rank_worker(rank, world, port, out_dir, exchange):
+    """Rank 1 sits out one step (it stays alive and launches nothing): rank 0's step must give up within
+    its wait limit, tell the host, and leave both GPUs usable; after both ranks have reset their
+    decoders the next step, taken together, is right."""
+    mld, dist = _setup(rank, world, port)
+    L, heads, ffn, T, pos = SHAPES["small"]
+    d = heads * 128
+    model = _model(np.random.default_rng(0), L, heads, ffn, T)
+    x = np.random.default_rng(1).standard_normal(d).astype(np.float16)
+    dec, keep = _sharded_decoder(mld, dist, exchange, model, heads, ffn, T, rank, world, wait_limit_us=200000)
+    xh = torch.from_numpy(x).pin_memory()
+    yh = torch.empty(d, dtype=torch.float16).pin_memory()
+    dec.step_host(xh, yh, pos)                 # a good step together
+    dist.barrier()
+    status = 0
+    if rank == 0:
+        try:
+            dec.step_host(xh, yh, pos)             # alone: the other rank's shards never come
+        except mld.MldError as e:
+            status = e.status
+    dist.barrier()                             # rank 1 waited here, on the host
+    code = dec.device_status() if rank == 0 else 0
+    dec.reset()                                # both ranks, nothing in flight
+    dist.barrier()
+    dec.step_host(xh, yh, pos)
+    dist.barrier()
+    ok = dec.device_status() == 0
+    if rank == 0:
+        layers, kc, vc = model
+        single, keep1 = _make_decoder(mld, layers, kc, vc, heads, ffn, T, 0, 1, None, mode=mld.DECODER_OP_CHAIN)
+        y1 = torch.empty(d, dtype=torch.float16, device="cuda")
+        single.step(torch.from_numpy(x).cuda(), y1, pos)
+        torch.cuda.synchronize()
+        err = (yh.float() - y1.float().cpu()).abs().max().item() / y1.float().abs().max().item()
+        with open(os.path.join(out_dir, "result.txt"), "w") as f:
+            f.write(f"{status}\n{code}\n{int(ok)}\n{err}")
+        single.close()
+    dist.barrier()
+    dec.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("exchange", ["peer", "mega"])
+def test_two_gpu_step_without_the_other_rank_times_out_and_recovers(tmp_path, exchange):
+    import torch.multiprocessing as mp
+    mp.spawn(_late_rank_worker, args=(2, _port(90 + list(EXCHANGES).index(exchange)), str(tmp_path), exchange),
+             nprocs=2, join=True)
+    status, code, ok, err = open(tmp_path / "result.txt").read().split()
+    assert int(status) == 5                   # MLD_TIMEOUT from mld_decoder_step_host
+    assert int(code) != 0
+    assert int(ok) == 1
     assert float(err) < 1e-2
