@@ -765,10 +765,12 @@ def run_ours(args):
                                                                        "algorithmic_bytes_per_launch")}}
     if world == 1:
         parity = parity_vs_oracle(mld, torch, layers, x)
-    dec.close()
-    del layers
-    torch.cuda.empty_cache()
-    if world > 1:
+        dec.close()
+        del layers
+        torch.cuda.empty_cache()
+    else:
+        # (the sharded decoder stays open until the process exits: tearing a communicator down is a
+        # collective matter, and the other ranks are waiting at the barrier below)
         if rank == 0:
             parity = parity_vs_single_gpu(mld, torch, dev, n_layers, x, y)
         barrier()

@@ -166,17 +166,26 @@ typedef struct mld_fc_desc {
   int32_t force_path;        /* 0 = IsFullyConnectedRecommended rule,
                                 1 = decode GEMV kernel, 2 = prefill GEMM */
   int32_t device;            /* CUDA device ordinal, -1 = current */
-  int32_t prefill_act_quant; /* prefill GEMM only: 0 = float activations
-                                (WeightsConverter + float conv route,
-                                gpu_model_builder.cc:1110-1276); 1 = per-token
-                                symmetric int8 activations x int8 weights
+  int32_t prefill_act_quant; /* prefill GEMM only: 0 = float activations (the
+                                convolution that dequantises inline,
+                                gpu_model_builder.cc:1128-1173,
+                                conv_generic.cc:1553-1640); 1 / 2 = per-token
+                                int8 activations x int8 weights
                                 (FullyConnectedInt8QuantizedWithSrcQuantization,
                                 gpu_model_builder.cc:1325-1431; per-channel
-                                INT8 weights only) */
-  int32_t cache_prepared_weights; /* prefill GEMM only: keep the K-major copy of
-                                the weights between calls while the weights and
-                                scale pointers stay the same (the caller
-                                promises not to modify them in between) */
+                                INT8 weights only), 1 with the symmetric and 2
+                                with the asymmetric quantisation rule
+                                (quantize_and_dequantize.cc:355-441; 2 is the
+                                builder's default and needs
+                                mld_fc_plan_set_weights_sum) */
+  int32_t cache_prepared_weights; /* prefill GEMM only: instead of dequantising
+                                inside the GEMM, expand the weights to a K-major
+                                fp16 (s8) copy in a pass of its own
+                                (WeightsConverter + float conv route,
+                                gpu_model_builder.cc:1110-1276) and keep the
+                                copy between calls while the weights and scale
+                                pointers stay the same (the caller promises not
+                                to modify them in between) */
   int32_t epilogue;          /* mld_epilogue */
   /* Tuning of the streaming decode kernel; 0 everywhere = the defaults. */
   int32_t exact_operands;    /* 1: dequantise to exact fp16 integers before the MMA
@@ -205,6 +214,14 @@ MLD_API size_t mld_fc_plan_workspace_bytes(const mld_fc_plan* plan);
  * cleared); the function then returns MLD_TIMEOUT.  The kernels never spin
  * without a limit: a wait that runs out makes its CTA stop and record the code. */
 MLD_API int mld_fc_plan_device_status(mld_fc_plan* plan, int32_t* code);
+
+/* The weights_sum input of the fused dequantisation of the int8-activation
+ * route (CreateDequantization, quantize_and_dequantize.cc:867-964;
+ * GetWeightsAccumulatedInputChannels, weights_conversion.cc:1584-1602):
+ * sum_i[o] = sum over the inputs of the signed weights of output o, a device
+ * array of at least n entries as mld_pack_weights / mld_weights_sum_i produce
+ * it.  Borrowed: it must stay valid while the plan runs. */
+MLD_API int mld_fc_plan_set_weights_sum(mld_fc_plan* plan, const int32_t* sum_i);
 
 /* Optional hint for the next mld_fc_run on this plan: once that call's decode
  * kernel has requested all of its own data it also asks for `bytes` of

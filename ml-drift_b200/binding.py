@@ -177,6 +177,11 @@ class FullyConnectedPlan:
         self._h = C.c_void_p()
         _check(lib().mld_fc_plan_create(C.byref(self.desc), C.byref(self._h)), "mld_fc_plan_create")
 
+    def set_weights_sum(self, sum_i):
+        """sum_i: device int32 tensor [n] (kept alive here)."""
+        self._w_sum = sum_i
+        _check(lib().mld_fc_plan_set_weights_sum(self._h, _ptr(sum_i)), "mld_fc_plan_set_weights_sum")
+
     def workspace_bytes(self) -> int:
         return int(lib().mld_fc_plan_workspace_bytes(self._h))
 

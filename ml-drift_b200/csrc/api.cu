@@ -108,6 +108,8 @@ struct mld_fc_plan {
   float* a_params;       // per-token {inv_scale, offset, sum}
   const void* prepared_w;
   const void* prepared_s;
+  const int32_t* w_sum;  // per-output sums of the signed weights (asymmetric int8 activations), caller-owned
+  bool pair_ok;          // the prefill GEMM can read the packed weights directly (tensor-map pitch rule)
   const void* next_w;    // one-shot L2 prefetch hint for the next mld_fc_run on this plan
   size_t next_w_bytes;
   std::vector<TmapEntry> tmaps;  // tensor maps keyed by the (weights, scale) pointers last seen
@@ -220,12 +222,12 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   MLD_REQUIRE(d->src_layout == MLD_LAYOUT_SLICED || d->src_layout == MLD_LAYOUT_ROW_MAJOR, "bad src layout");
   MLD_REQUIRE(d->dst_layout == MLD_LAYOUT_SLICED || d->dst_layout == MLD_LAYOUT_ROW_MAJOR, "bad dst layout");
   MLD_REQUIRE(d->max_tokens >= 1, "max_tokens must be at least 1");
-  MLD_REQUIRE(d->prefill_act_quant == 0 || d->prefill_act_quant == 1, "bad prefill_act_quant");
+  MLD_REQUIRE(d->prefill_act_quant >= 0 && d->prefill_act_quant <= 2, "bad prefill_act_quant");
   MLD_REQUIRE(d->epilogue == MLD_EPILOGUE_NONE || d->epilogue == MLD_EPILOGUE_SWIGLU_PAIRS, "bad epilogue");
   MLD_REQUIRE((d->exact_operands | 1) == 1 && (d->no_overlap | 1) == 1 && d->smem_limit_kb >= 0, "bad tuning field");
   if (d->epilogue == MLD_EPILOGUE_SWIGLU_PAIRS)
     MLD_REQUIRE(d->n % 8 == 0 && !d->has_bias, "the SiLU*mul write needs an even row count (n % 8 == 0) and no bias");
-  if (d->prefill_act_quant == 1)
+  if (d->prefill_act_quant != 0)
     MLD_REQUIRE(d->weight_bits == 8 && d->scale_mode == MLD_SCALE_PER_CHANNEL && !d->has_zero_point,
                 "int8-activation prefill needs per-channel INT8 weights without zero points");
   const int src_slices = div_up(d->k, 4);
@@ -249,6 +251,9 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   p->w_kmajor = p->x_kmajor = nullptr;
   p->a_params = nullptr;
   p->prepared_w = p->prepared_s = nullptr;
+  p->w_sum = nullptr;
+  // the packed weight matrix as a TMA tensor: rows of N4 / 4 blocks, pitch a multiple of 16 bytes
+  p->pair_ok = ((align_n(d->n, 4) / 4) * (d->weight_bits == 4 ? 8 : 16)) % 16 == 0 && get_encode_tiled() != nullptr;
   p->next_w = nullptr;
   p->next_w_bytes = 0;
   p->subnormal = d->exact_operands == 0;
@@ -286,12 +291,14 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   // per-token quantisation parameters.
   const bool may_gemm = d->force_path == 2 || (d->force_path == 0 && !mld_fc_is_gemv_recommended(d->precision, d->max_tokens));
   if (may_gemm && d->precision != MLD_PRECISION_F32 && !d->has_zero_point) {
-    const bool i8 = d->prefill_act_quant == 1;
+    const bool i8 = d->prefill_act_quant != 0;
     const size_t esz = i8 ? 1 : 2;
     const GemmGeometry gmax = gemm_geometry(d->max_tokens, d->n, d->k, i8, p->sms);
-    const size_t wb = (size_t)N4 * gmax.kp * esz, xb = (size_t)d->max_tokens * gmax.kp * esz,
+    // the K-major copy of the weights is needed only by the route that prepares them in a pass of its own
+    const bool need_w = d->cache_prepared_weights != 0 || !p->pair_ok;
+    const size_t wb = need_w ? (size_t)N4 * gmax.kp * esz : 0, xb = (size_t)d->max_tokens * gmax.kp * esz,
                  pb = (size_t)d->max_tokens * 3 * sizeof(float);
-    cudaError_t e = cudaMalloc(&p->w_kmajor, wb);
+    cudaError_t e = need_w ? cudaMalloc(&p->w_kmajor, wb) : cudaSuccess;
     if (e == cudaSuccess) e = cudaMalloc(&p->x_kmajor, xb);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&p->a_params), pb);
     if (e != cudaSuccess) {
@@ -328,6 +335,12 @@ int mld_fc_plan_device_status(mld_fc_plan* plan, int32_t* code) {
     set_last_error_text("a bounded device-side wait of a FullyConnected kernel gave up");
     return MLD_TIMEOUT;
   }
+  return MLD_OK;
+}
+
+int mld_fc_plan_set_weights_sum(mld_fc_plan* plan, const int32_t* sum_i) {
+  MLD_REQUIRE(plan != nullptr, "null plan");
+  plan->w_sum = sum_i;
   return MLD_OK;
 }
 
@@ -443,21 +456,43 @@ static int run_stream(mld_fc_plan* p, const void* src, const void* weights, cons
   return MLD_OK;
 }
 
-// Prefill: operand preparation + tcgen05 GEMM.
+// Prefill: the activations are brought into K-major order (and quantised per token for the int8 route),
+// then one tcgen05 GEMM.  By default the GEMM reads the packed weights as they are and dequantises them in
+// shared memory (gemm_pair_kernel); with cache_prepared_weights, or for a weight matrix whose row pitch a
+// tensor map cannot express, the weights are first expanded to a K-major copy (kept between calls when
+// cached) and a plain GEMM runs on that.
 static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const void* scale, const void* bias,
                     void* dst, int tokens, cudaStream_t stream) {
   const mld_fc_desc& d = p->d;
-  const bool i8 = d.prefill_act_quant == 1;
-  const GemmGeometry g = gemm_geometry(tokens, d.n, d.k, i8, p->sms);
-  const int N4 = align_n(d.n, 4);
-  const size_t esz = i8 ? 1 : 2;
-  (void)N4;
-  (void)esz;
-  if (p->w_kmajor == nullptr) {
+  const bool i8 = d.prefill_act_quant != 0;
+  int* err = p->error_shared != nullptr ? p->error_shared : p->error;
+  if (p->x_kmajor == nullptr) {
     set_last_error_text("this operator was not planned for the prefill route (force_path / max_tokens at creation)");
     return MLD_INVALID_ARGUMENT;
   }
+  if (d.prefill_act_quant == 2 && p->w_sum == nullptr) {
+    set_last_error_text("asymmetric int8 activations need the weights' per-output sums (mld_fc_plan_set_weights_sum)");
+    return MLD_INVALID_ARGUMENT;
+  }
   int rc;
+  if (p->pair_ok && d.cache_prepared_weights == 0) {
+    const int mode = i8 ? 2 : (d.weight_bits == 4 ? 0 : 1);
+    const PairGeometry pg = pair_geometry(tokens, d.n, d.k, mode, p->sms);
+    if (i8)
+      rc = launch_quantize_act(src, d.src_layout, tokens, d.k, pg.kp, d.prefill_act_quant == 1, p->x_kmajor, p->a_params,
+                               stream);
+    else
+      rc = launch_transpose_x(src, d.src_layout, tokens, d.k, pg.kp, p->x_kmajor, stream);
+    if (rc != MLD_OK) return rc;
+    return launch_gemm_pair(mode, p->x_kmajor, weights, pg, tokens, d.n, d.k, scale, d.scale_mode,
+                            d.scale_mode == MLD_SCALE_BLOCK ? d.groups : 1, p->group_slices, d.scalar_scale, bias,
+                            p->a_params, d.prefill_act_quant == 2 ? p->w_sum : nullptr, dst, d.dst_layout, err, stream);
+  }
+  if (d.prefill_act_quant == 2) {
+    set_last_error_text("asymmetric int8 activations are served by the inline-dequantisation GEMM only");
+    return MLD_UNIMPLEMENTED;
+  }
+  const GemmGeometry g = gemm_geometry(tokens, d.n, d.k, i8, p->sms);
   const bool reuse = d.cache_prepared_weights && p->prepared_w == weights && p->prepared_s == scale;
   if (!reuse) {
     rc = launch_dequant_weights(d.weight_bits, i8, weights, scale, d.scale_mode,
@@ -468,12 +503,12 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
     p->prepared_s = scale;
   }
   if (i8)
-    rc = launch_quantize_act(src, d.src_layout, tokens, d.k, g.kp, p->x_kmajor, p->a_params, stream);
+    rc = launch_quantize_act(src, d.src_layout, tokens, d.k, g.kp, true, p->x_kmajor, p->a_params, stream);
   else
     rc = launch_transpose_x(src, d.src_layout, tokens, d.k, g.kp, p->x_kmajor, stream);
   if (rc != MLD_OK) return rc;
   return launch_gemm_umma(i8, p->x_kmajor, p->w_kmajor, g, tokens, d.n, d.k, bias, scale, p->a_params, dst,
-                          d.dst_layout, p->error_shared != nullptr ? p->error_shared : p->error, stream);
+                          d.dst_layout, err, stream);
 }
 
 int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const void* scale, const void* zero_point,

@@ -431,40 +431,76 @@ __global__ void __launch_bounds__(256) transpose_x_kernel(const __half* __restri
   *reinterpret_cast<uint2*>(out + (size_t)m * Kp + ks * 4) = v;
 }
 
-// Per-token symmetric quantisation to s8 (CreateQuantization, symmetric form:
-// ml_drift/common/kernels/quantize_and_dequantize.cc:355-378, 421-441, constants
-// :757-784): inv_scale = max(min_scale, absmax / 127), scale = 1 / inv_scale,
-// q = clamp(floor(x * scale + 128.5), 0, 255) - 128.  One CTA per token.
-// Output xq row-major [M][Kp] s8 (zero padded), params [M][3] = {inv_scale, 0, sum}.
+// Per-token quantisation to s8 (CreateQuantization,
+// ml_drift/common/kernels/quantize_and_dequantize.cc:355-441, constants :757-784).
+// One CTA per token; x ~ q * inv_scale + offset.
+//   symmetric   inv_scale = max(min_scale, absmax / 127), scale = 1 / inv_scale, offset = 0,
+//               q = clamp(floor(x * scale + 128.5), 0, 255) - 128
+//   asymmetric  (the reference builder's default, common/gpu_model_builder.h:236-240)
+//               range = max - min, scale = 255 / range, inv_scale = range / 255,
+//               offset = min + range * (128 / 255), q = clamp(int((x - min) * scale + 0.5), 0, 255) - 128
+//               (a constant token, range 0, gets inv_scale 0: every x equals the offset)
+// Output xq row-major [M][Kp] s8 (zero padded), params [M][3] = {inv_scale, offset, sum of the codes}.
 __global__ void __launch_bounds__(256) quantize_act_kernel(const __half* __restrict__ x, int layout, int M, int K, int Kp,
-                                                           int8_t* __restrict__ xq, float* __restrict__ params) {
+                                                           int symmetric, int8_t* __restrict__ xq,
+                                                           float* __restrict__ params) {
   const int m = blockIdx.x;
-  __shared__ float red[8];
+  __shared__ float red[8], red2[8];
   __shared__ int redi[8];
   auto load = [&](int k) -> float {
     const size_t idx = layout == MLD_LAYOUT_SLICED ? (((size_t)(k >> 2) * M + m) * 4 + (k & 3)) : ((size_t)m * K + k);
     return __half2float(x[idx]);
   };
-  float amax = 0.0f;
-  for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(load(k)));
+  float vmin = INFINITY, vmax = -INFINITY;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    const float v = load(k);
+    vmin = fminf(vmin, v);
+    vmax = fmaxf(vmax, v);
+  }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  for (int off = 16; off > 0; off >>= 1) {
+    vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, off));
+    vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    red[threadIdx.x >> 5] = vmin;
+    red2[threadIdx.x >> 5] = vmax;
+  }
   __syncthreads();
-  amax = 0.0f;
-  for (int w = 0; w < 8; ++w) amax = fmaxf(amax, red[w]);
-  float inv_scale = 0.0f, scale = 0.0f;
-  if (amax > 0.0f) {
-    inv_scale = fmaxf(6.103515625e-05f, __fdiv_rn(amax, 127.0f));
-    scale = __fdiv_rn(1.0f, inv_scale);
+  vmin = INFINITY;
+  vmax = -INFINITY;
+  for (int w = 0; w < 8; ++w) {
+    vmin = fminf(vmin, red[w]);
+    vmax = fmaxf(vmax, red2[w]);
+  }
+  float inv_scale = 0.0f, scale = 0.0f, offset = 0.0f;
+  if (symmetric) {
+    const float amax = fmaxf(fabsf(vmin), fabsf(vmax));
+    if (amax > 0.0f) {
+      inv_scale = fmaxf(6.103515625e-05f, __fdiv_rn(amax, 127.0f));
+      scale = __fdiv_rn(1.0f, inv_scale);
+    }
+  } else {
+    const float range = __fsub_rn(vmax, vmin);
+    offset = vmin;
+    if (range > 0.0f) {
+      scale = __fdiv_rn(255.0f, range);
+      inv_scale = __fdiv_rn(range, 255.0f);
+      offset = __fadd_rn(offset, __fmul_rn(range, __fdiv_rn(128.0f, 255.0f)));
+    }
   }
   int sum = 0;
   for (int k = threadIdx.x; k < Kp; k += blockDim.x) {
     int q = 0;
     if (k < K) {
-      float r = floorf(__fadd_rn(__fmul_rn(load(k), scale), 128.5f));
-      r = fminf(255.0f, fmaxf(0.0f, r));
-      q = static_cast<int>(r) - 128;
+      if (symmetric) {
+        float r = floorf(__fadd_rn(__fmul_rn(load(k), scale), 128.5f));
+        r = fminf(255.0f, fmaxf(0.0f, r));
+        q = static_cast<int>(r) - 128;
+      } else {
+        const float r = __fadd_rn(__fmul_rn(__fsub_rn(load(k), vmin), scale), 0.5f);
+        q = min(255, max(0, static_cast<int>(r))) - 128;
+      }
     }
     xq[(size_t)m * Kp + k] = static_cast<int8_t>(q);
     sum += q;
@@ -477,7 +513,7 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const __half* __restr
     int t = 0;
     for (int w = 0; w < 8; ++w) t += redi[w];
     params[m * 3 + 0] = inv_scale;
-    params[m * 3 + 1] = 0.0f;
+    params[m * 3 + 1] = offset;
     params[m * 3 + 2] = static_cast<float>(t);
   }
 }
@@ -550,9 +586,10 @@ int launch_transpose_x(const void* x, int layout, int M, int K, int Kp, void* ou
   return MLD_OK;
 }
 
-int launch_quantize_act(const void* x, int layout, int M, int K, int Kp, void* xq, float* params, cudaStream_t stream) {
-  quantize_act_kernel<<<M, 256, 0, stream>>>(static_cast<const __half*>(x), layout, M, K, Kp, static_cast<int8_t*>(xq),
-                                             params);
+int launch_quantize_act(const void* x, int layout, int M, int K, int Kp, bool symmetric, void* xq, float* params,
+                        cudaStream_t stream) {
+  quantize_act_kernel<<<M, 256, 0, stream>>>(static_cast<const __half*>(x), layout, M, K, Kp, symmetric ? 1 : 0,
+                                             static_cast<int8_t*>(xq), params);
   MLD_LAUNCH_CHECK();
   return MLD_OK;
 }

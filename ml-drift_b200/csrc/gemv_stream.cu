@@ -182,7 +182,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 // W: weight boxes per stage (strip width up to W * 128 bytes per pass).
 // MONE: single-token launch (only token column 0 is kept).
 template <int BITS, int W, bool SUBNORMAL, bool MONE>
-__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
+__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
     fc_strip_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
                     StripArgs a) {
   using F = Frag<BITS>;
@@ -600,14 +600,17 @@ StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slic
   gm.grid = strips * gm.ksplit;
   const int max_width = div_up(gm.units, strips) * gm.gran;  // chunks
   int w = div_up(max_width, 8);
-  if (gm.ksplit > 1 && w > 4) {  // a cluster pair runs a single pass
+  // Overlapping launches need two CTAs per SM, which the register file grants to the instantiations of up
+  // to two boxes per stage: wider strips take more column passes instead.
+  const int w_max = pdl ? 2 : 4;
+  if (gm.ksplit > 1 && w > w_max) {  // a cluster pair runs a single pass
     gm.ksplit = 1;
     strips = sms < gm.units ? sms : gm.units;
     gm.strips = strips;
     gm.grid = strips;
     w = div_up(div_up(gm.units, strips) * gm.gran, 8);
   }
-  gm.w = w > 4 ? 4 : w;
+  gm.w = w > w_max ? w_max : w;
   gm.rows_per_split = gm.ksplit == 1 ? align_n(SS, kStageRows) : align_n(div_up(SS, 2), kStageRows);
   if (scale_mode == MLD_SCALE_SCALAR) {
     gm.scale_rows = 0;

@@ -155,9 +155,22 @@ GemmGeometry gemm_geometry(int M, int N, int K, bool i8, int sms);
 int launch_dequant_weights(int bits, bool to_s8, const void* packed, const void* scale, int scale_mode, int G,
                            int group_slices, float scalar_scale, int N, int K, int Kp, void* out, cudaStream_t stream);
 int launch_transpose_x(const void* x, int layout, int M, int K, int Kp, void* out, cudaStream_t stream);
-int launch_quantize_act(const void* x, int layout, int M, int K, int Kp, void* xq, float* params, cudaStream_t stream);
+int launch_quantize_act(const void* x, int layout, int M, int K, int Kp, bool symmetric, void* xq, float* params,
+                        cudaStream_t stream);
 int launch_gemm_umma(bool i8, const void* a_mat, const void* b_mat, const GemmGeometry& g, int M, int N, int K,
                      const void* bias, const void* w_scale, const float* a_params, void* y, int dst_layout, int* error,
+                     cudaStream_t stream);
+
+// ------------------------------------------- prefill GEMM, dequantisation inside (SM pairs)
+struct PairGeometry {
+  int kp, tile_n, m_tiles, n_tiles, k_blocks, stages, w_box_bytes, grid;
+  size_t smem_bytes;
+};
+// mode: 0 = INT4 weights -> fp16 MMA, 1 = INT8 weights -> fp16 MMA, 2 = INT8 weights x int8 activations
+PairGeometry pair_geometry(int M, int N, int K, int mode, int sms);
+int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const PairGeometry& g, int M, int N, int K,
+                     const void* scale, int scale_mode, int G, int group_slices, float scalar_scale, const void* bias,
+                     const float* a_params, const int32_t* w_sum, void* y, int dst_layout, int* error,
                      cudaStream_t stream);
 
 }  // namespace mld
