@@ -545,9 +545,15 @@ def side_benchmarks(mld, torch, peaks):
     yy = torch.empty((N // 4, M, 4), dtype=torch.float16, device="cuda")
     flops = 2.0 * M * K * N
     res = {}
-    for label, cache in (("with_weight_conversion", False), ("weights_prepared_once", True)):
+    # the three ways the operator serves a prefill call: the weights dequantised inside the GEMM (route 1),
+    # a conversion pass before a plain GEMM on every call (route 0: what the conversion-cost rule picks at
+    # this M), and the converted copy kept between calls
+    ROUTES = (("dequantised_inside_gemm", 1, False), ("with_weight_conversion", 0, False),
+              ("weights_prepared_once", 0, True))
+    for label, route, cache in ROUTES:
         plan = mld.FullyConnectedPlan(N, K, 4, scale_mode=mld.SCALE_BLOCK, groups=K // blk, precision=mld.F32F16,
-                                      max_tokens=M, force_path=mld.PATH_GEMM, cache_prepared_weights=cache)
+                                      max_tokens=M, force_path=mld.PATH_GEMM, cache_prepared_weights=cache,
+                                      prefill_route=route)
         for _ in range(3):
             plan.run(xs, packed, sc, yy, M)
         torch.cuda.synchronize()
@@ -576,16 +582,18 @@ def side_benchmarks(mld, torch, peaks):
     M, K, N = 2048, 8192, 3584
     w = torch.randn((N, K), generator=g, device="cuda") * 0.02
     q, s = mld.quantize_weights(w, 8)
-    packed, _ = mld.pack_weights(q, (N, 1, 1, K), 8)
+    packed, w_sum = mld.pack_weights(q, (N, 1, 1, K), 8, want_sum=True)
     sc = mld.pack_scales(s, True)
     del w, q, s
     xs = torch.randn((K // 4, M, 4), generator=g, device="cuda").half()
     yy = torch.empty((N // 4, M, 4), dtype=torch.float16, device="cuda")
     ops = 2.0 * M * K * N
     res = {}
-    for label, cache in (("with_weight_conversion", False), ("weights_prepared_once", True)):
+    for label, route, cache in ROUTES:
         plan = mld.FullyConnectedPlan(N, K, 8, scale_mode=mld.SCALE_PER_CHANNEL, precision=mld.F32F16, max_tokens=M,
-                                      force_path=mld.PATH_GEMM, prefill_act_quant=1, cache_prepared_weights=cache)
+                                      force_path=mld.PATH_GEMM, prefill_act_quant=2, cache_prepared_weights=cache,
+                                      prefill_route=route)
+        plan.set_weights_sum(w_sum)
         for _ in range(3):
             plan.run(xs, packed, sc, yy, M)
         torch.cuda.synchronize()
@@ -598,12 +606,88 @@ def side_benchmarks(mld, torch, peaks):
         res[label] = {"us": us, "TOPs": ops / us / 1e6}
         plan.close()
     out["prefill_gemm_w8a8_shard"] = {
-        "workload": "W8A8 GEMM M=2048 K=8192 N=3584 (one rank's eighth of N=28672): per-token int8 activations "
-                    "(quantised inside the call), int32 accumulate, fp16 out", **res,
+        "workload": "W8A8 GEMM M=2048 K=8192 N=3584 (one rank's eighth of N=28672): asymmetric per-token int8 "
+                    "activations (quantised inside the call), int32 accumulate, fp16 out", **res,
         "nominal_int8_dense_peak_TOPs": 4500.0,
         "frac_of_nominal_int8_peak": res["weights_prepared_once"]["TOPs"] / 4500.0,
         "vs_measured_bf16_burst_TFLOPs": res["weights_prepared_once"]["TOPs"] / pk}
     return out
+
+
+def sharded_prefill_benchmark(mld, torch, dist, rank, world, dev, nccl_id):
+    """The W8A8 prefill case split over the ranks by output rows: M=2048, K=8192, N=28672 (N / world rows
+    per rank), asymmetric per-token int8 activations, gather of Y on every rank.  Reports the GEMM alone,
+    GEMM + ncclAllGather, and the GEMM whose epilogue stores into every rank's tensor (max over ranks)."""
+    M, K, N = 2048, 8192, 28672
+    n = N // world
+
+    def all_ok(flag):   # the ranks agree on whether to go on, so that no rank enters a collective alone
+        t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t[0])
+
+    failure = None
+    try:
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        w = torch.randn((n, K), generator=g, device=dev) * 0.02
+        q, s = mld.quantize_weights(w, 8)
+        packed, w_sum = mld.pack_weights(q, (n, 1, 1, K), 8, want_sum=True)
+        sc = mld.pack_scales(s, True)
+        del w, q, s
+        gx = torch.Generator(device=dev).manual_seed(99)
+        xs = (torch.randn((K // 4, M, 4), generator=gx, device=dev) + 0.2).half()
+        plan = mld.FullyConnectedPlan(n, K, 8, scale_mode=mld.SCALE_PER_CHANNEL, precision=mld.F32F16, max_tokens=M,
+                                      force_path=mld.PATH_GEMM, prefill_act_quant=2)
+        plan.set_weights_sum(w_sum)
+        y_local = torch.empty((n // 4, M, 4), dtype=torch.float16, device=dev)
+    except Exception as exc:  # noqa: BLE001
+        failure = f"{type(exc).__name__}: {exc}"
+    if not all_ok(failure is None):
+        return {"error": failure or "another rank failed to set up"}
+    group = mld.ShardGroup(rank, world, N * M * 2, nccl_id=nccl_id)      # collective (NCCL communicator)
+    mine = torch.frombuffer(bytearray(group.ipc_export()), dtype=torch.uint8).to(dev)
+    table = [torch.zeros(64, dtype=torch.uint8, device=dev) for _ in range(world)]
+    dist.all_gather(table, mine)
+    try:
+        group.ipc_import(b"".join(t.cpu().numpy().tobytes() for t in table))
+    except Exception as exc:  # noqa: BLE001
+        failure = f"{type(exc).__name__}: {exc}"
+    if not all_ok(failure is None):
+        return {"error": failure or "another rank failed to import the exchange blocks"}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    us_gemm = timed(lambda: plan.run(xs, packed, sc, y_local, M))
+    us_nccl = timed(lambda: group.run(plan, xs, packed, sc, M, mld.GATHER_NCCL))
+    y_nccl = group.output(N * M, dev).clone()
+    us_peer = timed(lambda: group.run(plan, xs, packed, sc, M, mld.GATHER_PEER_STORES))
+    y_peer = group.output(N * M, dev)
+    status = group.device_status()
+    same = bool(torch.equal(y_nccl, y_peer)) and status == 0
+    own = y_peer.view(N // 4, M, 4)[rank * (n // 4):(rank + 1) * (n // 4)]
+    own_ok = bool(torch.equal(own, y_local))
+    ops = 2.0 * M * K * N
+    plan.close()
+    return {"workload": f"W8A8 GEMM M={M} K={K} N={N} split {world} ways by output rows ({n} per rank), asymmetric "
+                        "per-token int8 activations, Y gathered on every rank (fp16, 117 MB)",
+            "gemm_only_us": us_gemm, "gemm_plus_nccl_allgather_us": us_nccl, "gemm_storing_into_every_rank_us": us_peer,
+            "whole_job_TOPs_nccl": ops / us_nccl / 1e6, "whole_job_TOPs_peer_stores": ops / us_peer / 1e6,
+            "gather_bytes_per_rank_out": (world - 1) * n * M * 2,
+            "peer_stores_equal_nccl": same, "own_block_equals_unsharded_kernel_output": own_ok,
+            "timing": "10 runs after 3 warm-ups, CUDA events, max over ranks"}
 
 
 def run_ours(args):
@@ -623,13 +707,16 @@ def run_ours(args):
     layout = 1 if exchange == "paired" else 0
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(minutes=10))
+        ids = torch.zeros(2, 128, dtype=torch.uint8, device=dev)   # one for the decoder, one for the operator group
+        if rank == 0:
+            for i in range(2):
+                ids[i].copy_(torch.frombuffer(bytearray(mld.comm_unique_id()), dtype=torch.uint8))
+        dist.broadcast(ids, 0)
         if exchange == "nccl":
-            idt = torch.zeros(128, dtype=torch.uint8, device=dev)
-            if rank == 0:
-                idt.copy_(torch.frombuffer(bytearray(mld.comm_unique_id()), dtype=torch.uint8))
-            dist.broadcast(idt, 0)
-            nccl_id = bytes(idt.cpu().numpy().tobytes())
+            nccl_id = bytes(ids[0].cpu().numpy().tobytes())
+        group_id = bytes(ids[1].cpu().numpy().tobytes())
 
     def barrier():
         if world > 1:
@@ -731,6 +818,7 @@ def run_ours(args):
         raise RuntimeError(f"a device-side wait gave up (code {status}); the timing is void")
     ranks_agree = None
     parity = None
+    sharded_side = None
     if world > 1:
         # every rank assembled the same output vector from the shards (bit for bit), and it is finite
         dec.step(x, y, pos)
@@ -774,9 +862,16 @@ def run_ours(args):
         if rank == 0:
             parity = parity_vs_single_gpu(mld, torch, dev, n_layers, x, y)
         barrier()
+        if not args.no_kernels:
+            del layers
+            torch.cuda.empty_cache()
+            try:
+                sharded_side = sharded_prefill_benchmark(mld, torch, dist, rank, world, dev, group_id)
+            except Exception as exc:  # noqa: BLE001
+                sharded_side = {"error": f"{type(exc).__name__}: {exc}"}
     if parity is not None and not parity["ok"]:
         raise RuntimeError(f"parity check failed: {parity}")
-    side = None
+    side = None if world == 1 else ({"prefill_gemm_w8a8_sharded": sharded_side} if sharded_side is not None else None)
     cpu = None
     if rank == 0 and world == 1:
         if not args.no_kernels:

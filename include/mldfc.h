@@ -149,6 +149,12 @@ MLD_API int mld_quantize_weights(const float* w, int32_t o, int32_t i,
 /* What CreateFullyConnectedExternalWeights receives
  * (common/kernels/fully_connected.h:155-161; ExternalWeights,
  * common/task/gpu_operation.h:354-363). */
+enum mld_prefill_route {
+  MLD_PREFILL_ROUTE_AUTO = 0,
+  MLD_PREFILL_ROUTE_INLINE = 1,
+  MLD_PREFILL_ROUTE_CONVERT = 2
+};
+
 typedef struct mld_fc_desc {
   int32_t n;                 /* weights.shape.o */
   int32_t k;                 /* weights.shape.i */
@@ -187,6 +193,14 @@ typedef struct mld_fc_desc {
                                 pointers stay the same (the caller promises not
                                 to modify them in between) */
   int32_t epilogue;          /* mld_epilogue */
+  int32_t prefill_route;     /* prefill GEMM only, mld_prefill_route: 0 = the
+                                builder's conversion-cost rule
+                                (gpu_model_builder.cc:1132-1173: convert the
+                                weights in a pass of their own when
+                                100 * 2.5 / (2 * tokens) * 32 <= 20, i.e. from
+                                200 tokens up, and dequantise inside the GEMM
+                                below that), 1 = always inside the GEMM, 2 =
+                                always the separate pass */
   /* Tuning of the streaming decode kernel; 0 everywhere = the defaults. */
   int32_t exact_operands;    /* 1: dequantise to exact fp16 integers before the MMA
                                 instead of feeding the raw nibbles / bytes as fp16
@@ -243,6 +257,87 @@ MLD_API int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights,
                        const void* scale, const void* zero_point,
                        const void* bias, void* dst, int32_t tokens,
                        void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Embedding lookup over the same packed table                               */
+/* ------------------------------------------------------------------------ */
+
+/* EmbeddingLookupAttributes (common/operations.h) for a quantised table that
+ * is stored as FullyConnected weights, O = vocabulary, I = embedding width
+ * (common/kernels/embedding_lookup.cc:200-216 builds it with
+ * GetFullyConnectedInt{8,4}WeightsDesc), so that one packed tensor serves the
+ * lookup and the lm_head projection. */
+typedef struct mld_embed_desc {
+  int32_t vocab;             /* original_weights_shape.o */
+  int32_t dim;               /* original_weights_shape.i */
+  int32_t weight_bits;       /* 4 or 8 */
+  int32_t scale_mode;        /* MLD_SCALE_PER_CHANNEL or MLD_SCALE_BLOCK */
+  int32_t groups;            /* scale groups along dim (block-wise only) */
+  int32_t has_zero_point;
+  int32_t f16;               /* 1: scales, zero points and dst are fp16; 0: fp32 */
+  int32_t dst_layout;        /* mld_act_layout: [dim/4][tokens][4] or [tokens][dim] */
+} mld_embed_desc;
+
+/* The generated kernel of EmbeddingLookup (embedding_lookup.cc:44-196): for
+ * every token, column ids[token] % 4 of the 4x4 blocks of output slice
+ * ids[token] / 4, dequantised in fp32 as u * scale - scale * (shift +
+ * zero_point) and converted to the dst type.  Ids are clamped to [0, vocab - 1]
+ * as in the reference.  ids: int32 device array [tokens]; weights / scale /
+ * zero_point: as for mld_fc_run with n = vocab, k = dim. */
+MLD_API int mld_embedding_lookup(const mld_embed_desc* d, const int32_t* ids, const void* weights, const void* scale,
+                                 const void* zero_point, void* dst, int32_t tokens, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* A FullyConnected node split over the GPUs of one node                      */
+/* ------------------------------------------------------------------------ */
+
+/* The reference is single-device; nothing below has a counterpart in it.
+ * Output channels are independent dot products (FullyConnectedReference,
+ * common/task/testing_ref_ops.cc:961-988), so rank r of `world` computes the
+ * rows [r n, (r+1) n) of a node with world * n outputs from its own packed
+ * sub-matrix (a plan with n outputs), and the gathered result is the
+ * concatenation of the ranks' blocks.  A shard group owns that gathered tensor
+ * on every rank: fp16 in the sliced layout [world * n / 4][tokens][4], where a
+ * rank's block is one contiguous range. */
+typedef struct mld_shard_group mld_shard_group;
+
+typedef enum mld_gather {
+  MLD_GATHER_NCCL = 0,        /* compute into the own range, then one in-place
+                                 ncclAllGather (the group needs an NCCL id) */
+  MLD_GATHER_PEER_STORES = 1  /* the producing kernel stores its block into every
+                                 rank's tensor over NVLink while it computes (the
+                                 prefill GEMM does so tile by tile; other kernels
+                                 are followed by a copy), then the ranks exchange
+                                 completion flags (bounded waits; see
+                                 mld_shard_group_device_status).  Needs
+                                 mld_shard_group_ipc_export / _import. */
+} mld_gather;
+
+/* output_bytes: capacity of the gathered tensor (a multiple of 16).
+ * nccl_id128: the 128-byte id from mld_comm_unique_id, distributed by the
+ * caller, or NULL when only peer stores will be used.  Collective when an id
+ * is given.  Synchronous. */
+MLD_API int mld_shard_group_create(int32_t rank, int32_t world, int32_t device, size_t output_bytes,
+                                   const void* nccl_id128, mld_shard_group** out);
+MLD_API int mld_shard_group_destroy(mld_shard_group* group);
+/* Every rank exports a 64-byte handle of its tensor, the caller distributes
+ * them (rank order, world x 64 bytes) and every rank imports the table; all
+ * ranks must have imported before any of them runs with peer stores. */
+MLD_API int mld_shard_group_ipc_export(mld_shard_group* group, void* handle64);
+MLD_API int mld_shard_group_ipc_import(mld_shard_group* group, const void* handles);
+/* Device pointer of this rank's copy of the gathered tensor. */
+MLD_API void* mld_shard_group_output(mld_shard_group* group);
+/* mld_fc_run for one rank's shard, followed by the gather: after the work this
+ * call enqueues on `stream` has completed, the group's tensor on this rank
+ * holds all ranks' blocks.  Every rank calls it with the same `tokens` and
+ * `gather`.  With peer stores a run begins with a handshake, so a rank's
+ * tensor is not overwritten before that rank's own stream has reached the run. */
+MLD_API int mld_fc_run_sharded(mld_fc_plan* plan, mld_shard_group* group, const void* src, const void* weights,
+                               const void* scale, const void* zero_point, const void* bias, int32_t tokens,
+                               int32_t gather, void* stream);
+/* Synchronous: *code = 0, or non-zero when a wait for another rank's flag ran
+ * out during an earlier peer-store run (then cleared); returns MLD_TIMEOUT then. */
+MLD_API int mld_shard_group_device_status(mld_shard_group* group, int32_t* code);
 
 /* ------------------------------------------------------------------------ */
 /* Decode step: the callers of the FullyConnected path                       */

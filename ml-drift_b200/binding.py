@@ -41,7 +41,7 @@ class FcDesc(C.Structure):
                 ("has_bias", C.c_int32), ("precision", C.c_int32), ("src_layout", C.c_int32),
                 ("dst_layout", C.c_int32), ("max_tokens", C.c_int32), ("force_path", C.c_int32),
                 ("device", C.c_int32), ("prefill_act_quant", C.c_int32), ("cache_prepared_weights", C.c_int32),
-                ("epilogue", C.c_int32), ("exact_operands", C.c_int32), ("no_overlap", C.c_int32),
+                ("epilogue", C.c_int32), ("prefill_route", C.c_int32), ("exact_operands", C.c_int32), ("no_overlap", C.c_int32),
                 ("smem_limit_kb", C.c_int32)]
 
 
@@ -169,11 +169,11 @@ class FullyConnectedPlan:
                  scalar_zero_point=0.0, has_zero_point=False, has_bias=False, precision=F32F16,
                  src_layout=LAYOUT_SLICED, dst_layout=LAYOUT_SLICED, max_tokens=1, force_path=PATH_AUTO,
                  device=-1, prefill_act_quant=0, cache_prepared_weights=False, epilogue=0, exact_operands=False,
-                 no_overlap=False, smem_limit_kb=0):
+                 no_overlap=False, smem_limit_kb=0, prefill_route=0):
         self.desc = FcDesc(n, k, weight_bits, scale_mode, groups, scalar_scale, scalar_zero_point,
                            int(has_zero_point), int(has_bias), precision, src_layout, dst_layout,
                            max_tokens, force_path, device, prefill_act_quant, int(cache_prepared_weights), epilogue,
-                           int(exact_operands), int(no_overlap), smem_limit_kb)
+                           prefill_route, int(exact_operands), int(no_overlap), smem_limit_kb)
         self._h = C.c_void_p()
         _check(lib().mld_fc_plan_create(C.byref(self.desc), C.byref(self._h)), "mld_fc_plan_create")
 
@@ -207,6 +207,72 @@ class FullyConnectedPlan:
             self.close()
         except Exception:
             pass
+
+
+class EmbedDesc(C.Structure):
+    _fields_ = [("vocab", C.c_int32), ("dim", C.c_int32), ("weight_bits", C.c_int32), ("scale_mode", C.c_int32),
+                ("groups", C.c_int32), ("has_zero_point", C.c_int32), ("f16", C.c_int32), ("dst_layout", C.c_int32)]
+
+
+def embedding_lookup(ids, weights, scale, dst, vocab, dim, bits, scale_mode=SCALE_PER_CHANNEL, groups=1,
+                     zero_point=None, f16=True, dst_layout=LAYOUT_ROW_MAJOR, stream=None):
+    """ids: int32 device tensor [tokens]; weights / scale: the packed table as for the FullyConnected operator."""
+    d = EmbedDesc(vocab, dim, bits, scale_mode, groups, int(zero_point is not None), int(f16), dst_layout)
+    _check(lib().mld_embedding_lookup(C.byref(d), _ptr(ids), _ptr(weights), _ptr(scale), _ptr(zero_point), _ptr(dst),
+                                      ids.numel(), _stream(stream)), "mld_embedding_lookup")
+
+
+# ------------------------------------------------------- operator split over GPUs
+GATHER_NCCL, GATHER_PEER_STORES = 0, 1
+
+
+class ShardGroup:
+    """Owns one mld_shard_group: this rank's copy of a gathered output tensor."""
+
+    def __init__(self, rank, world, output_bytes, nccl_id=None, device=-1):
+        self._h = C.c_void_p()
+        idbuf = None if nccl_id is None else C.create_string_buffer(nccl_id, 128)
+        _check(lib().mld_shard_group_create(rank, world, device, C.c_size_t(output_bytes), idbuf, C.byref(self._h)),
+               "mld_shard_group_create")
+        self.output_bytes = output_bytes
+
+    def ipc_export(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        _check(lib().mld_shard_group_ipc_export(self._h, buf), "mld_shard_group_ipc_export")
+        return buf.raw
+
+    def ipc_import(self, handles: bytes):
+        _check(lib().mld_shard_group_ipc_import(self._h, C.create_string_buffer(handles, len(handles))),
+               "mld_shard_group_ipc_import")
+
+    def output(self, elems, device):
+        """The gathered tensor as a flat fp16 torch tensor of `elems` elements (a view of library memory)."""
+        lib().mld_shard_group_output.restype = C.c_void_p
+        ptr = lib().mld_shard_group_output(self._h)
+        assert elems * 2 <= self.output_bytes
+
+        class _Mem:
+            __cuda_array_interface__ = {"shape": (elems,), "typestr": "<f2", "data": (ptr, False), "version": 2}
+        keep = self
+        t = torch.as_tensor(_Mem(), device=device)
+        t._mld_keep = keep
+        return t
+
+    def run(self, plan, src, weights, scale, tokens, gather, zero_point=None, bias=None, stream=None):
+        _check(lib().mld_fc_run_sharded(plan._h, self._h, _ptr(src), _ptr(weights), _ptr(scale), _ptr(zero_point),
+                                        _ptr(bias), tokens, gather, _stream(stream)), "mld_fc_run_sharded")
+
+    def device_status(self) -> int:
+        code = C.c_int32(0)
+        rc = lib().mld_shard_group_device_status(self._h, C.byref(code))
+        if rc not in (OK, TIMEOUT):
+            raise MldError(rc, "mld_shard_group_device_status")
+        return code.value
+
+    def close(self):
+        if self._h:
+            lib().mld_shard_group_destroy(self._h)
+            self._h = C.c_void_p()
 
 
 # ---------------------------------------------------------------- decode step

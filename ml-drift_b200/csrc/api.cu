@@ -212,6 +212,10 @@ int mld_fc_is_gemv_recommended(int32_t precision, int32_t tokens) {
   return tokens <= limit ? 1 : 0;
 }
 
+// The builder's conversion-cost rule (gpu_model_builder.cc:1132-1173): 100 * (bytes read + written by the
+// conversion) / flops * 32 = 4000 / tokens for 4-bit weights; the separate pass is taken when that is <= 20.
+static bool convert_pays(int tokens) { return tokens >= 200; }
+
 int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   MLD_REQUIRE(d != nullptr && out != nullptr, "null argument");
   *out = nullptr;
@@ -289,15 +293,18 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   // An operator that may run as the prefill GEMM gets its operand workspace now, so that mld_fc_run never
   // allocates: the K-major copy of the weights, the K-major (optionally quantised) activations and the
   // per-token quantisation parameters.
+  MLD_REQUIRE(d->prefill_route >= MLD_PREFILL_ROUTE_AUTO && d->prefill_route <= MLD_PREFILL_ROUTE_CONVERT,
+              "prefill_route out of range");
   const bool may_gemm = d->force_path == 2 || (d->force_path == 0 && !mld_fc_is_gemv_recommended(d->precision, d->max_tokens));
   if (may_gemm && d->precision != MLD_PRECISION_F32 && !d->has_zero_point) {
     const bool i8 = d->prefill_act_quant != 0;
     const size_t esz = i8 ? 1 : 2;
     const GemmGeometry gmax = gemm_geometry(d->max_tokens, d->n, d->k, i8, p->sms);
     // the K-major copy of the weights is needed only by the route that prepares them in a pass of its own
-    const bool need_w = d->cache_prepared_weights != 0 || !p->pair_ok;
+    const bool need_w = d->cache_prepared_weights != 0 || !p->pair_ok || d->prefill_route == MLD_PREFILL_ROUTE_CONVERT ||
+                        (d->prefill_route == MLD_PREFILL_ROUTE_AUTO && convert_pays(d->max_tokens));
     const size_t wb = need_w ? (size_t)N4 * gmax.kp * esz : 0, xb = (size_t)d->max_tokens * gmax.kp * esz,
-                 pb = (size_t)d->max_tokens * 3 * sizeof(float);
+                 pb = (size_t)d->max_tokens * kActParamFloats * sizeof(float);
     cudaError_t e = need_w ? cudaMalloc(&p->w_kmajor, wb) : cudaSuccess;
     if (e == cudaSuccess) e = cudaMalloc(&p->x_kmajor, xb);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&p->a_params), pb);
@@ -462,7 +469,7 @@ static int run_stream(mld_fc_plan* p, const void* src, const void* weights, cons
 // tensor map cannot express, the weights are first expanded to a K-major copy (kept between calls when
 // cached) and a plain GEMM runs on that.
 static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const void* scale, const void* bias,
-                    void* dst, int tokens, cudaStream_t stream) {
+                    void* dst, int tokens, cudaStream_t stream, const PeerOutputs* outs, bool* outs_used) {
   const mld_fc_desc& d = p->d;
   const bool i8 = d.prefill_act_quant != 0;
   int* err = p->error_shared != nullptr ? p->error_shared : p->error;
@@ -475,7 +482,9 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
     return MLD_INVALID_ARGUMENT;
   }
   int rc;
-  if (p->pair_ok && d.cache_prepared_weights == 0) {
+  const bool convert = d.cache_prepared_weights != 0 || !p->pair_ok || d.prefill_route == MLD_PREFILL_ROUTE_CONVERT ||
+                       (d.prefill_route == MLD_PREFILL_ROUTE_AUTO && convert_pays(tokens));
+  if (!convert) {
     const int mode = i8 ? 2 : (d.weight_bits == 4 ? 0 : 1);
     const PairGeometry pg = pair_geometry(tokens, d.n, d.k, mode, p->sms);
     if (i8)
@@ -486,12 +495,10 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
     if (rc != MLD_OK) return rc;
     return launch_gemm_pair(mode, p->x_kmajor, weights, pg, tokens, d.n, d.k, scale, d.scale_mode,
                             d.scale_mode == MLD_SCALE_BLOCK ? d.groups : 1, p->group_slices, d.scalar_scale, bias,
-                            p->a_params, d.prefill_act_quant == 2 ? p->w_sum : nullptr, dst, d.dst_layout, err, stream);
+                            p->a_params, d.prefill_act_quant == 2 ? p->w_sum : nullptr, dst, d.dst_layout, err, stream,
+                            outs);
   }
-  if (d.prefill_act_quant == 2) {
-    set_last_error_text("asymmetric int8 activations are served by the inline-dequantisation GEMM only");
-    return MLD_UNIMPLEMENTED;
-  }
+
   const GemmGeometry g = gemm_geometry(tokens, d.n, d.k, i8, p->sms);
   const bool reuse = d.cache_prepared_weights && p->prepared_w == weights && p->prepared_s == scale;
   if (!reuse) {
@@ -503,10 +510,25 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
     p->prepared_s = scale;
   }
   if (i8)
-    rc = launch_quantize_act(src, d.src_layout, tokens, d.k, g.kp, true, p->x_kmajor, p->a_params, stream);
+    rc = launch_quantize_act(src, d.src_layout, tokens, d.k, g.kp, d.prefill_act_quant == 1, p->x_kmajor, p->a_params,
+                             stream);
   else
     rc = launch_transpose_x(src, d.src_layout, tokens, d.k, g.kp, p->x_kmajor, stream);
   if (rc != MLD_OK) return rc;
+  {
+    // the multiplication itself: the SM-pair kernel with both operands loaded by TMA
+    const int mode = i8 ? 4 : 3;
+    const PairGeometry pg = pair_geometry(tokens, d.n, d.k, mode, p->sms);
+    if (pg.kp == g.kp)
+      return launch_gemm_pair(mode, p->x_kmajor, p->w_kmajor, pg, tokens, d.n, d.k, scale, d.scale_mode, 1, 1, 0.0f,
+                              bias, p->a_params, d.prefill_act_quant == 2 ? p->w_sum : nullptr, dst, d.dst_layout, err,
+                              stream, outs);
+  }
+  if (d.prefill_act_quant == 2) {
+    set_last_error_text("asymmetric int8 activations are served by the SM-pair GEMM only");
+    return MLD_UNIMPLEMENTED;
+  }
+  if (outs_used != nullptr) *outs_used = false;  // this kernel writes dst only
   return launch_gemm_umma(i8, p->x_kmajor, p->w_kmajor, g, tokens, d.n, d.k, bias, scale, p->a_params, dst,
                           d.dst_layout, err, stream);
 }
@@ -518,10 +540,20 @@ int mld_fc_run(mld_fc_plan* plan, const void* src, const void* weights, const vo
 
 }  // extern "C"
 
+void mld::fc_plan_shape(const mld_fc_plan* plan, int* n, int* dst_layout, int* max_tokens, int* device) {
+  *n = plan->d.n;
+  *dst_layout = plan->d.dst_layout;
+  *max_tokens = plan->d.max_tokens;
+  *device = plan->device;
+}
+
 int mld::fc_run_internal(mld_fc_plan* plan, const void* src, const void* weights, const void* scale,
                          const void* zero_point, const void* bias, void* dst, int32_t tokens, void* stream_v,
-                         const PeerScatter* scatter, const PeerWait* wait) {
+                         const PeerScatter* scatter, const PeerWait* wait, const PeerOutputs* outs, bool* outs_used) {
   MLD_REQUIRE(plan != nullptr, "null plan");
+  // outs_used: whether the kernel that ran stored into the peers' tensors itself (only the inline-dequant
+  // prefill GEMM does; after any other route the caller distributes dst)
+  if (outs_used != nullptr) *outs_used = false;
   const mld_fc_desc& d = plan->d;
   MLD_REQUIRE(tokens >= 0 && tokens <= d.max_tokens, "tokens exceeds the plan's max_tokens");
   if (tokens == 0) return MLD_OK;
@@ -540,7 +572,10 @@ int mld::fc_run_internal(mld_fc_plan* plan, const void* src, const void* weights
     // else is served, correctly but slowly, by the general kernel below
     const bool gemm_ok = d.precision != MLD_PRECISION_F32 && !d.has_zero_point && get_encode_tiled() != nullptr &&
                          (reinterpret_cast<uintptr_t>(src) & 7) == 0;
-    if (gemm_ok) return run_gemm(plan, src, weights, scale, b, dst, tokens, stream);
+    if (gemm_ok) {
+      if (outs_used != nullptr) *outs_used = outs != nullptr && outs->world > 1 && d.dst_layout == MLD_LAYOUT_SLICED;
+      return run_gemm(plan, src, weights, scale, b, dst, tokens, stream, outs, outs_used);
+    }
     if (d.prefill_act_quant != 0) {
       set_last_error_text("quantised-activation prefill needs fp16 tensors and no zero points");
       return MLD_UNIMPLEMENTED;

@@ -10,7 +10,6 @@
 // output shard; shard outputs are concatenated by an all-gather before the next
 // full-width consumer (after attention, o_proj, SiLU*mul and down_proj).
 #include <cuda_fp16.h>
-#include <dlfcn.h>
 
 #include <cmath>
 #include <cstdio>
@@ -21,6 +20,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "nccl_lazy.h"
 
 namespace mld {
 namespace {
@@ -406,32 +406,13 @@ struct AttnScratch {
 AttnScratch g_attn_scratch[64];
 std::mutex g_attn_mu;
 
-// ---------------------------------------------------------------- NCCL (lazy)
-typedef struct ncclComm* ncclComm_t;
-typedef struct { char internal[128]; } ncclUniqueId;
-struct Nccl {
-  void* lib = nullptr;
-  int (*GetUniqueId)(ncclUniqueId*) = nullptr;
-  int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
-  int (*CommDestroy)(ncclComm_t) = nullptr;
-  int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
-  const char* (*GetErrorString)(int) = nullptr;
-  bool load() {
-    if (lib != nullptr) return true;
-    lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-    if (lib == nullptr) return false;
-    GetUniqueId = reinterpret_cast<decltype(GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
-    CommInitRank = reinterpret_cast<decltype(CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
-    CommDestroy = reinterpret_cast<decltype(CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
-    AllGather = reinterpret_cast<decltype(AllGather)>(dlsym(lib, "ncclAllGather"));
-    GetErrorString = reinterpret_cast<decltype(GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
-    return GetUniqueId && CommInitRank && CommDestroy && AllGather;
-  }
-};
-Nccl g_nccl;
-constexpr int kNcclHalf = 6;  // ncclFloat16
-
 }  // namespace
+
+Nccl& nccl() {
+  static Nccl instance;
+  return instance;
+}
+
 }  // namespace mld
 
 using namespace mld;
@@ -490,9 +471,9 @@ int make_plan(int n, int k, int block, int device, bool residual, int epilogue, 
 
 int gather(mld_decoder* dec, const __half* send, __half* recv, int count, cudaStream_t stream) {
   if (dec->d.world == 1) return MLD_OK;  // callers alias send == recv
-  const int rc = g_nccl.AllGather(send, recv, static_cast<size_t>(count), kNcclHalf, dec->comm, stream);
+  const int rc = nccl().AllGather(send, recv, static_cast<size_t>(count), kNcclHalf, dec->comm, stream);
   if (rc != 0) {
-    set_last_error_text(g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "ncclAllGather failed");
+    set_last_error_text(nccl().GetErrorString ? nccl().GetErrorString(rc) : "ncclAllGather failed");
     return MLD_NCCL_ERROR;
   }
   return MLD_OK;
@@ -504,12 +485,12 @@ extern "C" {
 
 int mld_comm_unique_id(void* id128) {
   MLD_REQUIRE(id128 != nullptr, "null id buffer");
-  if (!g_nccl.load()) {
+  if (!nccl().load()) {
     set_last_error_text("libnccl.so.2 could not be loaded");
     return MLD_NCCL_ERROR;
   }
   ncclUniqueId id;
-  if (g_nccl.GetUniqueId(&id) != 0) return MLD_NCCL_ERROR;
+  if (nccl().GetUniqueId(&id) != 0) return MLD_NCCL_ERROR;
   memcpy(id128, &id, sizeof id);
   return MLD_OK;
 }
@@ -726,16 +707,16 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
   dec->o_local = dec->o_full + (size_t)d->rank * dec->d_local;
   dec->act_local = dec->act_full + (size_t)d->rank * dec->ffn_local;
   if (d->world > 1 && nccl_id128 != nullptr) {
-    if (!g_nccl.load()) {
+    if (!nccl().load()) {
       set_last_error_text("libnccl.so.2 could not be loaded");
       mld_decoder_destroy(dec);
       return MLD_NCCL_ERROR;
     }
     ncclUniqueId id;
     memcpy(&id, nccl_id128, sizeof id);
-    const int nrc = g_nccl.CommInitRank(&dec->comm, d->world, id, d->rank);
+    const int nrc = nccl().CommInitRank(&dec->comm, d->world, id, d->rank);
     if (nrc != 0) {
-      set_last_error_text(g_nccl.GetErrorString ? g_nccl.GetErrorString(nrc) : "ncclCommInitRank failed");
+      set_last_error_text(nccl().GetErrorString ? nccl().GetErrorString(nrc) : "ncclCommInitRank failed");
       dec->comm = nullptr;
       mld_decoder_destroy(dec);
       return MLD_NCCL_ERROR;
@@ -777,7 +758,7 @@ int mld_decoder_create(const mld_decoder_desc* d, const void* nccl_id128, mld_de
 
 int mld_decoder_destroy(mld_decoder* dec) {
   if (dec == nullptr) return MLD_OK;
-  if (dec->comm != nullptr && g_nccl.CommDestroy) g_nccl.CommDestroy(dec->comm);
+  if (dec->comm != nullptr && nccl().CommDestroy) nccl().CommDestroy(dec->comm);
   mld_fc_plan_destroy(dec->p_qkv);
   mld_fc_plan_destroy(dec->p_o);
   mld_fc_plan_destroy(dec->p_gu);

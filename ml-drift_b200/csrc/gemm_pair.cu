@@ -17,12 +17,24 @@
 // the tile's weights, and one thread of the pair's first CTA issues
 // tcgen05.mma.cta_group::2, which reads both halves (so every byte of an operand
 // crosses L2 -> shared memory once per pair, not once per SM).  Per CTA:
-//   warp 0      TMA producer: the activation tile (K-major, 128-byte swizzle) and
-//               the packed weight box of the stage ([K/4] rows of 4x4 blocks)
+//   warp 0      TMA producer of the activation tiles (K-major, 128-byte swizzle)
+//   warp 24     TMA producer of the packed weight boxes ([K/4] rows of 4x4 blocks),
+//               in a ring of its own that is deeper than the operand ring: the
+//               boxes are small, and a box that is already in shared memory when
+//               its operand stage comes free takes the load's latency off the
+//               path stage free -> transformed -> multiplied
 //   warp 1      tensor-memory owner; in the first CTA also the MMA issuer
 //   warps 2..5  epilogue: tcgen05.ld -> convert (-> dequantise) -> global stores
 //               in the reference's sliced output layout
-//   warps 6..9  transform: one thread per weight row of the CTA's half turns the
+//   warps 22,23 forwarders: a thread each tells the pair's first CTA that this
+//               CTA's half of a stage has been transformed (the arrival on
+//               another SM's barrier takes several hundred cycles to return,
+//               so it is kept off the transform warps' path; the two threads
+//               take alternate stages)
+//   warps 6..21 transform, two groups of eight warps that take alternate stages
+//               (a stage is a chain of dependent steps - wait, load, convert,
+//               store, fence, signal - and two chains in flight hide each
+//               other's latencies): two threads per weight row of the CTA's half turn the
 //               packed nibbles / bytes of the stage into the K-major,
 //               128-byte-swizzled operand tile the MMA reads:
 //                 fp16 route  w = half(half(u * scale) + half(-scale * shift)),
@@ -32,20 +44,24 @@
 // tile overlaps the main loop of the next.  Every wait is bounded.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
 namespace mld {
 namespace {
 
-enum { kModeInt4F16 = 0, kModeInt8F16 = 1, kModeInt8I8 = 2 };
+// 0..2: the weights arrive packed and are transformed in shared memory; 3, 4: the weight operand was prepared
+// by a pass of its own (K-major fp16 / s8 rows) and is loaded by TMA like the activations.
+enum { kModeInt4F16 = 0, kModeInt8F16 = 1, kModeInt8I8 = 2, kModePreparedF16 = 3, kModePreparedI8 = 4 };
 
-constexpr int kPairThreads = 320;
+constexpr int kPairThreads = 800;
 constexpr int kRowsPerCta = 128;        // tokens per CTA (UMMA M = 256 over the pair)
 constexpr int kKBytes = 128;            // one swizzle atom of K per stage
 constexpr int kABytes = kRowsPerCta * kKBytes;
 constexpr int kBBytes = 128 * kKBytes;  // up to 128 weight rows per CTA
-constexpr int kTransformWarps = 4;
+constexpr int kTransformWarps = 8;       // two threads per weight row: chunks 0..3 and 4..7 of its 128 bytes
 constexpr int kErrPairBase = 30;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -159,14 +175,16 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
 
 struct PairArgs {
   int M, N, N4;
-  int tile_n;                 // UMMA N of the pair (multiple of 32, <= 256); each CTA transforms tile_n / 2 rows
+  int tile_n;                 // UMMA N of the pair (multiple of 16, <= 256); each CTA transforms tile_n / 2 rows
   int m_tiles, n_tiles, k_blocks;
-  int stages;
+  int stages;                 // operand ring: activation tile + transformed weight tile
+  int w_stages;               // packed-weight ring
   int w_box_bytes;            // bytes of one packed-weight box (rows_per_block slices x (tile_n / 2 / 4) blocks)
   int src_slices;             // K / 4 (rounded up)
   // fp16 routes: scales of the weights
   const __half* scale;        // [G][N4] fp16 (null: scalar_scale)
   int scale_mode, G, group_slices;
+  int gs_shift;               // log2(group_slices) when it is a power of two, else -1
   float scalar_scale;
   const void* bias;           // fp16 [N4] or null
   // int8 route
@@ -175,7 +193,16 @@ struct PairArgs {
   void* y;                    // fp16
   int dst_layout;
   int* error;
+  PeerOutputs outs;           // world > 1: the block is stored into every rank's tensor instead of y
+  long long* trace;           // tuning builds only: [grid][8] cycle counts per role (waiting / working)
+  int skip_transform;         // tuning builds only: leave the operand tiles unwritten (timing of the rest)
 };
+
+#ifdef MLD_TRACE
+#define MLD_PAIR_CLOCK() clock64()
+#else
+#define MLD_PAIR_CLOCK() 0ll
+#endif
 
 // (1024 + u) - 1024 = u exactly, then u * s + b with separate roundings (the WeightsConverter arithmetic).
 __device__ __forceinline__ uint32_t dq2(uint32_t biased, __half2 s2, __half2 b2) {
@@ -187,7 +214,8 @@ __device__ __forceinline__ uint32_t dq2(uint32_t biased, __half2 s2, __half2 b2)
 template <int MODE>
 __global__ void __launch_bounds__(kPairThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, PairArgs a) {
-  constexpr bool I8 = MODE == kModeInt8I8;
+  constexpr bool I8 = MODE == kModeInt8I8 || MODE == kModePreparedI8;
+  constexpr bool PREPARED = MODE >= kModePreparedF16;
   constexpr int BLK = MODE == kModeInt4F16 ? 8 : 16;            // bytes of a packed 4x4 block
   constexpr int K_PER_STAGE = I8 ? 128 : 64;                      // elements of K in a 128-byte row
   constexpr int SLICES = K_PER_STAGE / 4;                         // packed rows per stage
@@ -199,12 +227,14 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   uint8_t* sB = sA + (size_t)a.stages * kABytes;
   uint8_t* sW = sB + (size_t)a.stages * kBBytes;
   const int w_stage = (a.w_box_bytes + 127) & ~127;
-  uint64_t* full_w = reinterpret_cast<uint64_t*>(sW + (size_t)a.stages * w_stage);
-  uint64_t* full_ab = full_w + a.stages;     // used in the pair's first CTA: A of both CTAs landed, B of both transformed
+  uint64_t* full_w = reinterpret_cast<uint64_t*>(sW + (size_t)a.w_stages * w_stage);  // [w_stages]: the box has landed
+  uint64_t* w_empty = full_w + a.w_stages;   // [w_stages]: the transform warps have read the box
+  uint64_t* full_ab = w_empty + a.w_stages;  // used in the pair's first CTA: A of both CTAs landed, B of both transformed
   uint64_t* empty = full_ab + a.stages;      // the stage's MMAs have completed (arrives in both CTAs)
   uint64_t* tmem_full = empty + a.stages;    // [2], arrives in both CTAs
   uint64_t* tmem_empty = tmem_full + 2;      // [2], used in the first CTA: the epilogue warps of both CTAs have drained it
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* xf_done = tmem_empty + 2;        // [stages]: this CTA's transform warps have written their half of the stage
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xf_done + a.stages);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
@@ -212,10 +242,15 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   const int total_tiles = a.m_tiles * a.n_tiles;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < a.stages; ++s) {
+    for (int s = 0; s < a.w_stages; ++s) {
       mbar_init(&full_w[s], 1);
-      mbar_init(&full_ab[s], 1 + 2 * kTransformWarps);
+      mbar_init(&w_empty[s], kTransformWarps);
+    }
+    for (int s = 0; s < a.stages; ++s) {
+      // the producer's expect_tx, + one arrival per CTA for its transformed half
+      mbar_init(&full_ab[s], PREPARED ? 1 : 1 + 2);
       mbar_init(&empty[s], 1);
+      mbar_init(&xf_done[s], kTransformWarps);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
@@ -239,24 +274,30 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     // --------------------------------------------------------------- producer
     if (lane == 0) {
       prefetch_tmap(&tmap_a);
-      prefetch_tmap(&tmap_w);
+      if constexpr (PREPARED) prefetch_tmap(&tmap_w);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long tr_wait = 0;
+      [[maybe_unused]] const long long tr_start = MLD_PAIR_CLOCK();
       for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
         const int mi = tile % a.m_tiles, ni = tile / a.m_tiles;
         const int m0 = mi * 2 * kRowsPerCta + static_cast<int>(rank) * kRowsPerCta;
-        const int nb0 = (ni * a.tile_n + static_cast<int>(rank) * half_n) / 4 * BLK;  // byte column of the box
+        (void)ni;
         for (int kb = 0; kb < a.k_blocks; ++kb) {
+          const long long t0 = MLD_PAIR_CLOCK();
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             atomicExch(a.error, kErrPairBase + 1);
             ok = false;
             break;
           }
-          if (rank == 0) mbar_arrive_expect_tx(&full_ab[stage], 2 * kABytes);
+          tr_wait += MLD_PAIR_CLOCK() - t0;
+          const uint32_t b_bytes = PREPARED ? static_cast<uint32_t>(half_n) * kKBytes : 0u;
+          if (rank == 0) mbar_arrive_expect_tx(&full_ab[stage], 2 * (kABytes + b_bytes));
           tma_load_2d_pair(sA + (size_t)stage * kABytes, &tmap_a, full_ab_lead + stage * 8, kb * K_PER_STAGE, m0);
-          mbar_arrive_expect_tx(&full_w[stage], static_cast<uint32_t>(a.w_box_bytes));
-          tma_load_2d(sW + (size_t)stage * w_stage, &tmap_w, &full_w[stage], nb0 / 4, kb * SLICES);  // 32-bit elements
+          if constexpr (PREPARED)  // this CTA's half of the tile's weight rows, K-major like the activations
+            tma_load_2d_pair(sB + (size_t)stage * kBBytes, &tmap_w, full_ab_lead + stage * 8, kb * K_PER_STAGE,
+                             ni * a.tile_n + static_cast<int>(rank) * half_n);
           if (++stage == a.stages) {
             stage = 0;
             phase ^= 1;
@@ -274,25 +315,31 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         idesc = (1u << 4) | (static_cast<uint32_t>(a.tile_n >> 3) << 17) | (16u << 24);
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t acc_phase[2] = {0, 0};
+      uint32_t acc_phase0 = 0, acc_phase1 = 0;  // (scalars: a run-time index would put an array in local memory)
       int local = 0;
       bool ok = true;
+      long long tr_wait_acc = 0, tr_wait_ab = 0;
+      [[maybe_unused]] const long long tr_start = MLD_PAIR_CLOCK();
       for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
         const int acc = local & 1;
-        if (!wait_cluster(&tmem_empty[acc], acc_phase[acc] ^ 1)) {
+        const long long t0 = MLD_PAIR_CLOCK();
+        if (!wait_cluster(&tmem_empty[acc], (acc ? acc_phase1 : acc_phase0) ^ 1)) {
           atomicExch(a.error, kErrPairBase + 2);
           ok = false;
           break;
         }
-        acc_phase[acc] ^= 1;
+        if (acc) acc_phase1 ^= 1; else acc_phase0 ^= 1;
+        tr_wait_acc += MLD_PAIR_CLOCK() - t0;
         tc_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * 256);
         for (int kb = 0; kb < a.k_blocks; ++kb) {
+          const long long t1 = MLD_PAIR_CLOCK();
           if (!wait_cluster(&full_ab[stage], phase)) {
             atomicExch(a.error, kErrPairBase + 3);
             ok = false;
             break;
           }
+          tr_wait_ab += MLD_PAIR_CLOCK() - t1;
           tc_after();
           const uint64_t da = make_desc(smem_u32(sA + (size_t)stage * kABytes));
           const uint64_t db = make_desc(smem_u32(sB + (size_t)stage * kBBytes));
@@ -309,22 +356,29 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         }
         if (ok) commit_pair(&tmem_full[acc]);
       }
+#ifdef MLD_TRACE
+      if (a.trace != nullptr) {
+        a.trace[blockIdx.x * 8 + 2] = tr_wait_acc;
+        a.trace[blockIdx.x * 8 + 3] = tr_wait_ab;
+        a.trace[blockIdx.x * 8 + 4] = MLD_PAIR_CLOCK() - tr_start;
+      }
+#endif
     }
   } else if (warp < 6) {
     // --------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
-    uint32_t acc_phase[2] = {0, 0};
+    uint32_t acc_phase0 = 0, acc_phase1 = 0;
     int local = 0;
     bool ok = true;
     for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
       const int acc = local & 1;
       const int mi = tile % a.m_tiles, ni = tile / a.m_tiles;
-      if (!mbar_wait(&tmem_full[acc], acc_phase[acc])) {
+      if (!mbar_wait(&tmem_full[acc], acc ? acc_phase1 : acc_phase0)) {
         atomicExch(a.error, kErrPairBase + 4);
         ok = false;
         break;
       }
-      acc_phase[acc] ^= 1;
+      if (acc) acc_phase1 ^= 1; else acc_phase0 ^= 1;
       tc_after();
       const int m = mi * 2 * kRowsPerCta + static_cast<int>(rank) * kRowsPerCta + quad * 32 + lane;
       const int n0 = ni * a.tile_n;
@@ -367,7 +421,12 @@ __global__ void __launch_bounds__(kPairThreads, 1)
               uint2 pk;
               pk.x = static_cast<uint32_t>(__half_as_ushort(h[0])) | (static_cast<uint32_t>(__half_as_ushort(h[1])) << 16);
               pk.y = static_cast<uint32_t>(__half_as_ushort(h[2])) | (static_cast<uint32_t>(__half_as_ushort(h[3])) << 16);
-              *reinterpret_cast<uint2*>(static_cast<__half*>(a.y) + ((size_t)(n >> 2) * a.M + m) * 4) = pk;
+              const size_t at = ((size_t)(n >> 2) * a.M + m) * 4;
+              if (a.outs.world > 1) {
+                for (int pr = 0; pr < a.outs.world; ++pr) *reinterpret_cast<uint2*>(static_cast<__half*>(a.outs.y[pr]) + at) = pk;
+              } else {
+                *reinterpret_cast<uint2*>(static_cast<__half*>(a.y) + at) = pk;
+              }
             } else {
 #pragma unroll
               for (int e = 0; e < 4; ++e)
@@ -380,87 +439,230 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       __syncwarp();
       if (lane == 0) arrive_remote(tmem_empty_lead + acc * 8);
     }
+    if (a.outs.world > 1) __threadfence_system();  // the peer stores are performed before the kernel ends
+  } else if (PREPARED) {
+    // nothing to transform: the remaining warps only take part in the barriers at both ends
+  } else if (warp == 24) {
+    // ------------------------------------------------- producer of the packed weight boxes
+    if (lane == 0) {
+      prefetch_tmap(&tmap_w);
+      int ws = 0;
+      uint32_t wphase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        const int ni = tile / a.m_tiles;
+        const int nb0 = (ni * a.tile_n + static_cast<int>(rank) * half_n) / 4 * BLK;  // byte column of the box
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          if (!mbar_wait(&w_empty[ws], wphase ^ 1)) {
+            atomicExch(a.error, kErrPairBase + 7);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&full_w[ws], static_cast<uint32_t>(a.w_box_bytes));
+          tma_load_2d(sW + (size_t)ws * w_stage, &tmap_w, &full_w[ws], nb0 / 4, kb * SLICES);  // 32-bit elements
+          if (++ws == a.w_stages) {
+            ws = 0;
+            wphase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp >= 22) {
+    // -------------------------------------------------------------- forwarders
+    if (lane == 0) {
+      const int parity_of_mine = warp - 22;  // stages of even / odd iterations
+      int stage = 0, iter = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        for (int kb = 0; kb < a.k_blocks; ++kb, ++iter) {
+          if ((iter & 1) == parity_of_mine) {
+            if (!mbar_wait(&xf_done[stage], phase)) {
+              atomicExch(a.error, kErrPairBase + 6);
+              ok = false;
+              break;
+            }
+            arrive_remote(full_ab_lead + stage * 8);
+          }
+          if (++stage == a.stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
   } else {
     // -------------------------------------------------------------- transform
-    const int row = (warp - 6) * 32 + lane;          // weight row of this CTA's half of the tile
+    const int group = (warp - 6) >> 3;                // this group takes the iterations of its parity
+    const int tt = (threadIdx.x - 6 * 32) & 255;      // 0..255 inside the group
+    const int row = tt & 127;                         // weight row of this CTA's half of the tile
+    const int half = tt >> 7;                         // which four of the row's eight 16-byte chunks
     const bool active = row < half_n;
     const int col4 = row & 3;                         // column of the row inside its 4x4 blocks
     uint8_t* const b_row = sB + (row >> 3) * 1024 + (row & 7) * 128;
     const int sw = row & 7;                           // 16-byte chunk c of the row sits at chunk c ^ sw
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-      const int ni = tile / a.m_tiles;
-      const int n = ni * a.tile_n + static_cast<int>(rank) * half_n + row;
-      const bool has_n = active && n < a.N4;
-      for (int kb = 0; kb < a.k_blocks; ++kb) {
-        if (!mbar_wait(&full_w[stage], phase)) {
-          atomicExch(a.error, kErrPairBase + 5);
-          ok = false;
-          break;
-        }
-        if (active) {
-          const uint8_t* wp = sW + (size_t)stage * w_stage + (row >> 2) * BLK;
-          uint8_t* bp = b_row + (size_t)stage * kBBytes;
-          if constexpr (I8) {
-            // bytes (k % 4) * 4 + col4 of each block, re-biased u8 -> s8; 8 slices = 32 bytes of K per two chunks
-#pragma unroll 4
-            for (int c = 0; c < 8; ++c) {       // chunk c: K elements 16 c .. 16 c + 15 = slices 4 c .. 4 c + 3
-              uint32_t o[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint4 blk = *reinterpret_cast<const uint4*>(wp + (size_t)(4 * c + q) * w_pitch);
-                const uint32_t b0 = (blk.x >> (8 * col4)) & 0xFFu, b1 = (blk.y >> (8 * col4)) & 0xFFu;
-                const uint32_t b2 = (blk.z >> (8 * col4)) & 0xFFu, b3 = (blk.w >> (8 * col4)) & 0xFFu;
-                o[q] = (b0 | (b1 << 8) | (b2 << 16) | (b3 << 24)) ^ 0x80808080u;
-              }
-              *reinterpret_cast<uint4*>(bp + ((c ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          } else {
-            // scales of this row for the groups the stage touches
-            const int k_slice0 = kb * SLICES;
-#pragma unroll 2
-            for (int c = 0; c < 8; ++c) {       // chunk c: K elements 8 c .. 8 c + 7 = slices 2 c, 2 c + 1
-              __half sc = __float2half_rn(a.scalar_scale);
-              if (a.scale != nullptr && has_n) {
-                int g = a.scale_mode == MLD_SCALE_BLOCK ? (k_slice0 + 2 * c) / a.group_slices : 0;
-                if (g >= a.G) g = a.G - 1;
-                sc = __ldg(a.scale + (size_t)g * a.N4 + n);
-              }
-              const __half2 s2 = __half2half2(sc);
-              const __half shift = __ushort2half_rn(static_cast<unsigned short>(MODE == kModeInt4F16 ? 8 : 128));
-              const __half2 b2 = __half2half2(__hmul(__hneg(sc), shift));
-              uint32_t o[4];
-#pragma unroll
-              for (int q = 0; q < 2; ++q) {
-                if constexpr (MODE == kModeInt4F16) {
-                  const uint2 blk = *reinterpret_cast<const uint2*>(wp + (size_t)(2 * c + q) * w_pitch);
-                  // nibble (k % 4) * 4 + col4: k0, k1 in the halves of blk.x, k2, k3 in those of blk.y
-                  o[2 * q] = dq2(((blk.x >> (4 * col4)) & 0x000F000Fu) | 0x64006400u, s2, b2);
-                  o[2 * q + 1] = dq2(((blk.y >> (4 * col4)) & 0x000F000Fu) | 0x64006400u, s2, b2);
-                } else {
-                  const uint4 blk = *reinterpret_cast<const uint4*>(wp + (size_t)(2 * c + q) * w_pitch);
-                  const uint32_t b0 = (blk.x >> (8 * col4)) & 0xFFu, b1 = (blk.y >> (8 * col4)) & 0xFFu;
-                  const uint32_t b2b = (blk.z >> (8 * col4)) & 0xFFu, b3 = (blk.w >> (8 * col4)) & 0xFFu;
-                  o[2 * q] = dq2(b0 | (b1 << 16) | 0x64006400u, s2, b2);
-                  o[2 * q + 1] = dq2(b2b | (b3 << 16) | 0x64006400u, s2, b2);
-                }
-              }
-              *reinterpret_cast<uint4*>(bp + ((c ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        }
-        // the tile was written through the generic proxy; the MMA reads it through the async proxy
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) arrive_remote(full_ab_lead + stage * 8);
+    // prmt selector: byte col4 of two words -> the low bytes of the two 16-bit halves (bytes 1 and 3 are masked
+    // off by the user)
+    const uint32_t sel8 = static_cast<uint32_t>(col4) | (static_cast<uint32_t>(4 + col4) << 8);
+    int stage = 0, ws = 0;       // positions in the operand ring and in the packed-weight ring
+    uint32_t phase = 0, wphase = 0;
+    auto advance = [&](int n) {
+      for (int i = 0; i < n; ++i) {
         if (++stage == a.stages) {
           stage = 0;
           phase ^= 1;
         }
+        if (++ws == a.w_stages) {
+          ws = 0;
+          wphase ^= 1;
+        }
       }
+    };
+    bool ok = true;
+    long long tr_wait = 0;
+    int xf_iter = 0;  // stages of earlier tiles (parity decides which group starts a tile)
+    [[maybe_unused]] long long tr_work = 0, tr_fence = 0, tr_arrive = 0;
+    [[maybe_unused]] const long long tr_start = MLD_PAIR_CLOCK();
+    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+      const int ni = tile / a.m_tiles;
+      const int n = ni * a.tile_n + static_cast<int>(rank) * half_n + row;
+      const bool has_n = active && n < a.N4;
+      // fp16 routes: this row's scale for the group the first k-block's chunks fall in, fetched a k-block ahead
+      // (a thread's four chunks are 32 consecutive inputs: one scale group whenever groups are whole
+      // multiples of 32 inputs, the usual case; then one load per stage, issued a stage ahead, serves all four.
+      // Scalars, not arrays: anything indexed here would end up in local memory.)
+      const bool one_group = a.scale_mode != MLD_SCALE_BLOCK || (a.group_slices & 7) == 0;
+      auto scale_at = [&](int slice) -> __half {
+        if (a.scale == nullptr || !has_n) return __float2half_rn(a.scalar_scale);
+        int g = a.scale_mode != MLD_SCALE_BLOCK ? 0 : (a.gs_shift >= 0 ? slice >> a.gs_shift : slice / a.group_slices);
+        if (g >= a.G) g = a.G - 1;
+        return __ldg(a.scale + (size_t)g * a.N4 + n);
+      };
+      // the group's first stage of this tile, and from there every second one
+      int kb = (xf_iter ^ group) & 1;
+      if (kb == 1) advance(1);  // skip the other group's stage
+      __half sc_next = __float2half_rn(0.0f);
+      if constexpr (!I8) {
+        if (kb < a.k_blocks) sc_next = scale_at(kb * SLICES + 8 * half);
+      }
+      for (; kb < a.k_blocks; kb += 2) {
+        const __half sc_cur = sc_next;
+        if constexpr (!I8) {
+          if (kb + 2 < a.k_blocks) sc_next = scale_at((kb + 2) * SLICES + 8 * half);
+        }
+        const long long t0 = MLD_PAIR_CLOCK();
+        // the packed box has landed, and the operand stage it is transformed into is free again
+        if (!mbar_wait(&full_w[ws], wphase) || !mbar_wait(&empty[stage], phase ^ 1)) {
+          atomicExch(a.error, kErrPairBase + 5);
+          ok = false;
+          break;
+        }
+        tr_wait += MLD_PAIR_CLOCK() - t0;
+        const long long tw0 = MLD_PAIR_CLOCK();
+#ifdef MLD_TRACE
+        const bool do_work = a.skip_transform == 0;
+#else
+        constexpr bool do_work = true;
+#endif
+        if ((active || I8) && do_work) {
+          const uint8_t* wp = sW + (size_t)ws * w_stage + (row >> 2) * BLK;
+          uint8_t* bp = b_row + (size_t)stage * kBBytes;
+          if constexpr (I8) {
+            // A thread takes one 4x4-block column of four weight rows and ONE 16-byte chunk of K (four packed
+            // rows): four 16-byte blocks in, transposed byte-wise and re-biased u8 -> s8, four 16-byte pieces
+            // out (rows 4 blk .. 4 blk + 3, chunk c).  Lane = (blk & 7) + 8 * (chunk & 3): both the loads
+            // and the swizzled stores then spread evenly over the banks.
+            const int blk_i = ((tt >> 5) & 3) * 8 + (lane & 7);   // 4x4-block column of this CTA's half: rows 4 blk_i ..
+            const int c = (tt >> 7) * 4 + (lane >> 3);             // chunk of the 128-byte row
+            if (4 * blk_i < half_n) {
+              const uint8_t* wq = sW + (size_t)ws * w_stage + blk_i * 16;
+              uint32_t t[4][4];  // t[slice][row] = bytes k0..k3 of that packed row for weight row `row`
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 v = *reinterpret_cast<const uint4*>(wq + (size_t)(4 * c + q) * w_pitch);
+                const uint32_t p0 = __byte_perm(v.x, v.y, 0x5140), p1 = __byte_perm(v.x, v.y, 0x7362);
+                const uint32_t q0 = __byte_perm(v.z, v.w, 0x5140), q1 = __byte_perm(v.z, v.w, 0x7362);
+                t[q][0] = __byte_perm(p0, q0, 0x5410) ^ 0x80808080u;
+                t[q][1] = __byte_perm(p0, q0, 0x7632) ^ 0x80808080u;
+                t[q][2] = __byte_perm(p1, q1, 0x5410) ^ 0x80808080u;
+                t[q][3] = __byte_perm(p1, q1, 0x7632) ^ 0x80808080u;
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int r = 4 * blk_i + j;
+                uint8_t* dst = sB + (size_t)stage * kBBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) = make_uint4(t[0][j], t[1][j], t[2][j], t[3][j]);
+              }
+            }
+          } else {
+            // chunk c: K elements 8 c .. 8 c + 7 = packed rows 2 c, 2 c + 1
+            const __half shift = __ushort2half_rn(static_cast<unsigned short>(MODE == kModeInt4F16 ? 8 : 128));
+            if constexpr (MODE == kModeInt4F16) {
+              uint2 blk[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) blk[i] = *reinterpret_cast<const uint2*>(wp + (size_t)(8 * half + i) * w_pitch);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                const __half scc = one_group ? sc_cur : scale_at(kb * SLICES + 2 * (4 * half + c));
+                const __half2 s2 = __half2half2(scc);
+                const __half2 b2 = __half2half2(__hmul(__hneg(scc), shift));
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  // nibble (k % 4) * 4 + col4: k0, k1 in the halves of .x, k2, k3 in those of .y
+                  o[2 * q] = dq2(((blk[2 * c + q].x >> (4 * col4)) & 0x000F000Fu) | 0x64006400u, s2, b2);
+                  o[2 * q + 1] = dq2(((blk[2 * c + q].y >> (4 * col4)) & 0x000F000Fu) | 0x64006400u, s2, b2);
+                }
+                *reinterpret_cast<uint4*>(bp + (((4 * half + c) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            } else {
+              uint4 blk[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) blk[i] = *reinterpret_cast<const uint4*>(wp + (size_t)(8 * half + i) * w_pitch);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                const __half scc = one_group ? sc_cur : scale_at(kb * SLICES + 2 * (4 * half + c));
+                const __half2 s2 = __half2half2(scc);
+                const __half2 b2 = __half2half2(__hmul(__hneg(scc), shift));
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  const uint4 v = blk[2 * c + q];
+                  // bytes col4 of k0, k1 -> the low bytes of the two halves
+                  o[2 * q] = dq2((__byte_perm(v.x, v.y, sel8) & 0x00FF00FFu) | 0x64006400u, s2, b2);
+                  o[2 * q + 1] = dq2((__byte_perm(v.z, v.w, sel8) & 0x00FF00FFu) | 0x64006400u, s2, b2);
+                }
+                *reinterpret_cast<uint4*>(bp + (((4 * half + c) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            }
+          }
+        }
+        // the tile was written through the generic proxy; the MMA reads it through the async proxy
+        const long long tw1 = MLD_PAIR_CLOCK();
+        fence_proxy_async();
+        const long long tw2 = MLD_PAIR_CLOCK();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&w_empty[ws]);    // the box may be overwritten
+          mbar_arrive(&xf_done[stage]);  // local; a forwarder passes it on to the pair's first CTA
+        }
+        tr_work += tw1 - tw0;
+        tr_fence += tw2 - tw1;
+        tr_arrive += MLD_PAIR_CLOCK() - tw2;
+        // on to this group's next stage: past its own and, unless the tile ends first, the other group's
+        advance(kb + 1 < a.k_blocks ? 2 : 1);
+      }
+      xf_iter += a.k_blocks;
     }
+#ifdef MLD_TRACE
+    if (a.trace != nullptr && tt == 0 && group == 0) {
+      a.trace[blockIdx.x * 8 + 5] = tr_wait;
+      a.trace[blockIdx.x * 8 + 6] = MLD_PAIR_CLOCK() - tr_start;
+      a.trace[blockIdx.x * 8 + 7] = tr_work;
+      a.trace[blockIdx.x * 8 + 0] = tr_fence;     // (overwrites the producer's slots: the transform split is what is wanted now)
+      a.trace[blockIdx.x * 8 + 1] = tr_arrive;
+    }
+#endif
   }
   // Tear-down: nobody leaves while the partner may still arrive on this CTA's barriers or the pair's MMAs
   // may still write this CTA's tensor memory.
@@ -481,39 +683,65 @@ __global__ void __launch_bounds__(kPairThreads, 1)
 }  // namespace
 
 // ------------------------------------------------------------------ host side
+#ifdef MLD_TRACE
+static long long* g_pair_trace = nullptr;
+extern "C" __attribute__((visibility("default"))) void mld_debug_set_pair_trace(void* p) {
+  g_pair_trace = static_cast<long long*>(p);
+}
+#endif
+
 PairGeometry pair_geometry(int M, int N, int K, int mode, int sms) {
   PairGeometry g;
   const int N4 = align_n(N, 4);
-  const bool i8 = mode == kModeInt8I8;
+  const bool i8 = mode == kModeInt8I8 || mode == kModePreparedI8;
   g.kp = align_n(K, i8 ? 16 : 8);
   g.m_tiles = div_up(M, 2 * kRowsPerCta);
   const int pairs = sms / 2 > 0 ? sms / 2 : 1;
-  // UMMA N of the pair: the widest tile whose wave count wastes least (a tile of width tn costs tn tensor-pipe
-  // time units; the last wave is paid in full whether or not it is full).
+  // UMMA N of the pair.  Measured: a stage takes the same time for every width up to 256 (each MMA re-reads its
+  // 128 x 16 activation fragment from shared memory, which takes as long as the arithmetic of 256 columns), so
+  // what counts is the number of tile waves over the SM pairs; among the widths with the fewest waves the
+  // narrowest wastes least on columns past N.
   int best_n = 256;
-  long best_cost = -1;
-  for (int tn = 256; tn >= 64; tn -= 32) {
+  long best_waves = -1;
+  for (int tn = 256; tn >= 128; tn -= 16) {
     const long tiles = (long)g.m_tiles * div_up(N4, tn);
     const long waves = (tiles + pairs - 1) / pairs;
-    const long cost = waves * tn;
-    if (best_cost < 0 || cost < best_cost) {
-      best_cost = cost;
+    if (best_waves < 0 || waves < best_waves || (waves == best_waves && div_up(N4, tn) == div_up(N4, best_n))) {
+      best_waves = waves;
       best_n = tn;
     }
   }
+  if (N4 < 128) best_n = align_n(N4, 16);  // one narrow tile
   g.tile_n = best_n;
+#ifdef MLD_TRACE
+  if (const char* e = getenv("MLD_PAIR_TN")) g.tile_n = atoi(e);
+#endif
   g.n_tiles = div_up(N4, g.tile_n);
   const int k_per_stage = i8 ? 128 : 64;
   g.k_blocks = div_up(g.kp, k_per_stage);
   const int blk = mode == kModeInt4F16 ? 8 : 16;
   g.w_box_bytes = (k_per_stage / 4) * (g.tile_n / 2 / 4) * blk;
   const int w_stage = (g.w_box_bytes + 127) & ~127;
-  const int per_stage = kABytes + kBBytes + w_stage;
-  const int fixed = 1024 + (3 * 16 + 4) * 8 + 64;
-  int stages = (220 * 1024 - fixed) / per_stage;
-  if (stages > 8) stages = 8;
+  const int fixed = 1024 + (5 * 16 + 4) * 8 + 64;
+  // operand stages of 32 KB, as many as leave room for a packed-weight ring at least one stage deeper
+  const int budget = 226 * 1024 - fixed;
+  int stages = 2, w_stages = 3;
+  for (int st = 6; st >= 2; --st) {
+    int ws = (budget - st * (kABytes + kBBytes)) / w_stage;
+    if (ws > 2 * st) ws = 2 * st;
+    if (ws > 16) ws = 16;
+    if (ws >= st + 1) {
+      stages = st;
+      w_stages = ws;
+      break;
+    }
+  }
+#ifdef MLD_TRACE
+  if (const char* e = getenv("MLD_PAIR_STAGES")) stages = atoi(e) < stages ? atoi(e) : stages;
+#endif
   g.stages = stages;
-  g.smem_bytes = (size_t)stages * per_stage + fixed;
+  g.w_stages = w_stages;
+  g.smem_bytes = (size_t)stages * (kABytes + kBBytes) + (size_t)w_stages * w_stage + fixed;
   const long tiles = (long)g.m_tiles * g.n_tiles;
   g.grid = 2 * static_cast<int>(tiles < pairs ? tiles : pairs);
   return g;
@@ -522,9 +750,10 @@ PairGeometry pair_geometry(int M, int N, int K, int mode, int sms) {
 int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const PairGeometry& g, int M, int N, int K,
                      const void* scale, int scale_mode, int G, int group_slices, float scalar_scale, const void* bias,
                      const float* a_params, const int32_t* w_sum, void* y, int dst_layout, int* error,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const PeerOutputs* outs) {
   const int N4 = align_n(N, 4);
-  const bool i8 = mode == kModeInt8I8;
+  const bool i8 = mode == kModeInt8I8 || mode == kModePreparedI8;
+  const bool prepared = mode >= kModePreparedF16;
   const int esz = i8 ? 1 : 2;
   const int blk = mode == kModeInt4F16 ? 8 : 16;
   const int SS = div_up(K, 4), DS = N4 / 4;
@@ -534,8 +763,13 @@ int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const Pair
                         true);
   if (rc != MLD_OK) return rc;
   // packed weights: [K/4] rows of N4/4 blocks; the box is one stage's rows of the CTA's half of the tile
-  rc = make_tmap_2d(&tw, packed, (uint64_t)DS * blk, SS, (uint64_t)DS * blk, (g.tile_n / 2 / 4) * blk,
-                    (i8 ? 128 : 64) / 4, 4, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (prepared)  // K-major rows [N4][kp], boxes of one swizzle atom of K x the CTA's half of the tile's rows
+    rc = make_tmap_2d(&tw, packed, (uint64_t)g.kp * esz, N4, (uint64_t)g.kp * esz, kKBytes, g.tile_n / 2, esz,
+                      CU_TENSOR_MAP_SWIZZLE_128B,
+                      i8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, true);
+  else
+    rc = make_tmap_2d(&tw, packed, (uint64_t)DS * blk, SS, (uint64_t)DS * blk, (g.tile_n / 2 / 4) * blk,
+                      (i8 ? 128 : 64) / 4, 4, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != MLD_OK) return rc;
   PairArgs a;
   memset(&a, 0, sizeof a);
@@ -547,12 +781,16 @@ int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const Pair
   a.n_tiles = g.n_tiles;
   a.k_blocks = g.k_blocks;
   a.stages = g.stages;
+  a.w_stages = g.w_stages;
   a.w_box_bytes = g.w_box_bytes;
   a.src_slices = SS;
   a.scale = scale_mode == MLD_SCALE_SCALAR ? nullptr : static_cast<const __half*>(scale);
   a.scale_mode = scale_mode;
   a.G = G;
   a.group_slices = group_slices;
+  a.gs_shift = -1;
+  for (int sh = 0; sh < 24; ++sh)
+    if ((1 << sh) == group_slices) a.gs_shift = sh;
   a.scalar_scale = scalar_scale;
   a.bias = bias;
   a.a_params = a_params;
@@ -560,10 +798,21 @@ int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const Pair
   a.y = y;
   a.dst_layout = dst_layout;
   a.error = error;
-  void (*kern)(CUtensorMap, CUtensorMap, PairArgs) =
-      mode == kModeInt4F16 ? gemm_pair_kernel<kModeInt4F16>
-                           : (mode == kModeInt8F16 ? gemm_pair_kernel<kModeInt8F16> : gemm_pair_kernel<kModeInt8I8>);
-  static bool configured[3][kMaxDevices];
+  if (outs != nullptr && outs->world > 1 && dst_layout == MLD_LAYOUT_SLICED) a.outs = *outs;
+#ifdef MLD_TRACE
+  a.trace = g_pair_trace;
+  a.skip_transform = getenv("MLD_PAIR_SKIP_XF") != nullptr ? 1 : 0;
+#endif
+  void (*kern)(CUtensorMap, CUtensorMap, PairArgs) = nullptr;
+  switch (mode) {
+    case kModeInt4F16: kern = gemm_pair_kernel<kModeInt4F16>; break;
+    case kModeInt8F16: kern = gemm_pair_kernel<kModeInt8F16>; break;
+    case kModeInt8I8: kern = gemm_pair_kernel<kModeInt8I8>; break;
+    case kModePreparedF16: kern = gemm_pair_kernel<kModePreparedF16>; break;
+    case kModePreparedI8: kern = gemm_pair_kernel<kModePreparedI8>; break;
+    default: set_last_error_text("bad GEMM mode"); return MLD_INVALID_ARGUMENT;
+  }
+  static bool configured[5][kMaxDevices];
   int dev;
   if (needs_configure(configured[mode], &dev)) {
     MLD_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));

@@ -411,23 +411,48 @@ __global__ void __launch_bounds__(256) dequant_weights_kernel(const uint8_t* __r
 }
 
 // Activations: sliced [K/4][M][4] (or row-major [M][K]) fp16 -> row-major [M][Kp] fp16.
+// Sliced source: a 32-token x 32-slice tile goes through shared memory, read with lanes along the tokens
+// (8 bytes each, contiguous in the source) and written with lanes along K (contiguous in the destination).
 __global__ void __launch_bounds__(256) transpose_x_kernel(const __half* __restrict__ x, int layout, int M, int K, int Kp,
                                                           __half* __restrict__ out) {
-  const int ks = blockIdx.x * blockDim.x + threadIdx.x;  // k-slice
-  const int m = blockIdx.y;
-  if (ks * 4 >= Kp) return;
-  uint2 v = make_uint2(0, 0);
-  if (ks * 4 < K) {
-    if (layout == MLD_LAYOUT_SLICED) {
-      v = *reinterpret_cast<const uint2*>(x + ((size_t)ks * M + m) * 4);
-    } else {
-      __half h[4];
+  const int S = (K + 3) / 4, Sp = Kp / 4;
+  if (layout == MLD_LAYOUT_SLICED) {
+    __shared__ uint2 tile[32][33];
+    const int m0 = blockIdx.y * 32, s0 = blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 8 rows of the tile per pass
 #pragma unroll
-      for (int i = 0; i < 4; ++i) h[i] = ks * 4 + i < K ? x[(size_t)m * K + ks * 4 + i] : __float2half(0.0f);
-      v.x = static_cast<uint32_t>(__half_as_ushort(h[0])) | (static_cast<uint32_t>(__half_as_ushort(h[1])) << 16);
-      v.y = static_cast<uint32_t>(__half_as_ushort(h[2])) | (static_cast<uint32_t>(__half_as_ushort(h[3])) << 16);
+    for (int r = 0; r < 4; ++r) {
+      const int sl = s0 + ty + 8 * r, m = m0 + tx;
+      uint2 v = make_uint2(0u, 0u);
+      if (sl < S && m < M) v = *reinterpret_cast<const uint2*>(x + ((size_t)sl * M + m) * 4);
+      tile[ty + 8 * r][tx] = v;  // [slice][token]
     }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int m = m0 + ty + 8 * r, sl = s0 + tx;
+      if (m < M && sl < Sp) {
+        uint2 v = tile[tx][ty + 8 * r];
+        // a ragged K: the channels past K inside the last slice must read as zero
+        if (sl * 4 + 3 >= K) {
+          __half* h = reinterpret_cast<__half*>(&v);
+          for (int i = 0; i < 4; ++i)
+            if (sl * 4 + i >= K) h[i] = __float2half(0.0f);
+        }
+        *reinterpret_cast<uint2*>(out + (size_t)m * Kp + sl * 4) = v;
+      }
+    }
+    return;
   }
+  const int ks = blockIdx.x * 32 * 8 + threadIdx.x;  // one token row per blockIdx.y, 256 slices per block
+  const int m = blockIdx.y;
+  if (ks >= Sp || m >= M) return;
+  __half h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = ks * 4 + i < K ? x[(size_t)m * K + ks * 4 + i] : __float2half(0.0f);
+  uint2 v;
+  v.x = static_cast<uint32_t>(__half_as_ushort(h[0])) | (static_cast<uint32_t>(__half_as_ushort(h[1])) << 16);
+  v.y = static_cast<uint32_t>(__half_as_ushort(h[2])) | (static_cast<uint32_t>(__half_as_ushort(h[3])) << 16);
   *reinterpret_cast<uint2*>(out + (size_t)m * Kp + ks * 4) = v;
 }
 
@@ -518,6 +543,125 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const __half* __restr
   }
 }
 
+// The same quantisation for the sliced source layout [K/4][M][4], where a token's channels lie M * 8 bytes
+// apart: two passes with lanes along the tokens (contiguous 8-byte pieces), the second one turning a
+// 32-token x 32-slice tile through shared memory so that the K-major rows are written in 128-byte runs.
+//   pass 1: per-token minimum / maximum over one of kStatSplits ranges of the slices -> part [split][M][2]
+//   pass 2: folds the partial extremes, derives the token's parameters (params [M][3] = {inv_scale, offset, 0},
+//           written by the first column of blocks) and the codes (the arithmetic of quantize_act_kernel, bit
+//           for bit)
+// The sum of a token's codes (params[2]) is not produced: only a weight zero point would use it
+// (quantize_and_dequantize.cc:927-936), and that route takes none.
+__global__ void __launch_bounds__(256) act_stats_sliced_kernel(const __half* __restrict__ x, int M, int K,
+                                                               float* __restrict__ part) {
+  __shared__ float smin[8][33], smax[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int m = blockIdx.x * 32 + tx;
+  const int S = (K + 3) / 4;
+  const int per = (S + kStatSplits - 1) / kStatSplits;
+  const int s_begin = blockIdx.y * per, s_end = min(S, s_begin + per);
+  float vmin = INFINITY, vmax = -INFINITY;
+  if (m < M) {
+#pragma unroll 4
+    for (int sl = s_begin + ty; sl < s_end; sl += 8) {
+      const uint2 v = *reinterpret_cast<const uint2*>(x + ((size_t)sl * M + m) * 4);
+      const __half* h = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (sl * 4 + i < K) {
+          const float f = __half2float(h[i]);
+          vmin = fminf(vmin, f);
+          vmax = fmaxf(vmax, f);
+        }
+      }
+    }
+  }
+  smin[ty][tx] = vmin;
+  smax[ty][tx] = vmax;
+  __syncthreads();
+  if (ty == 0 && m < M) {
+#pragma unroll
+    for (int r = 1; r < 8; ++r) {
+      vmin = fminf(vmin, smin[r][tx]);
+      vmax = fmaxf(vmax, smax[r][tx]);
+    }
+    part[((size_t)blockIdx.y * M + m) * 2 + 0] = vmin;
+    part[((size_t)blockIdx.y * M + m) * 2 + 1] = vmax;
+  }
+}
+
+__global__ void __launch_bounds__(256) act_quantize_sliced_kernel(const __half* __restrict__ x, int M, int K, int Kp,
+                                                                  int symmetric, const float* __restrict__ part,
+                                                                  float* __restrict__ params,
+                                                                  int8_t* __restrict__ xq) {
+  __shared__ uint32_t tile[32][33];
+  const int S = (K + 3) / 4, Sp = Kp / 4;
+  const int m0 = blockIdx.y * 32, s0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int m = m0 + tx;
+  float scale = 0.0f, vmin = 0.0f;
+  if (m < M) {
+    float vmax = -INFINITY;
+    vmin = INFINITY;
+#pragma unroll
+    for (int y = 0; y < kStatSplits; ++y) {
+      vmin = fminf(vmin, part[((size_t)y * M + m) * 2 + 0]);
+      vmax = fmaxf(vmax, part[((size_t)y * M + m) * 2 + 1]);
+    }
+    float inv_scale = 0.0f, offset = 0.0f;
+    if (symmetric) {
+      const float amax = fmaxf(fabsf(vmin), fabsf(vmax));
+      if (amax > 0.0f) inv_scale = fmaxf(6.103515625e-05f, __fdiv_rn(amax, 127.0f));
+      if (inv_scale > 0.0f) scale = __fdiv_rn(1.0f, inv_scale);
+    } else {
+      const float range = __fsub_rn(vmax, vmin);
+      offset = vmin;
+      if (range > 0.0f) {
+        inv_scale = __fdiv_rn(range, 255.0f);
+        offset = __fadd_rn(offset, __fmul_rn(range, __fdiv_rn(128.0f, 255.0f)));
+        scale = __fdiv_rn(255.0f, range);
+      }
+    }
+    if (blockIdx.x == 0 && ty == 0) {
+      params[m * 3 + 0] = inv_scale;
+      params[m * 3 + 1] = offset;
+      params[m * 3 + 2] = 0.0f;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int sl = s0 + ty + 8 * r;
+    uint32_t packed = 0;
+    if (sl < S && m < M) {
+      const uint2 v = *reinterpret_cast<const uint2*>(x + ((size_t)sl * M + m) * 4);
+      const __half* h = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int q = 0;
+        if (sl * 4 + i < K) {
+          const float f = __half2float(h[i]);
+          if (symmetric) {
+            float t = floorf(__fadd_rn(__fmul_rn(f, scale), 128.5f));
+            t = fminf(255.0f, fmaxf(0.0f, t));
+            q = static_cast<int>(t) - 128;
+          } else {
+            const float t = __fadd_rn(__fmul_rn(__fsub_rn(f, vmin), scale), 0.5f);
+            q = min(255, max(0, static_cast<int>(t))) - 128;
+          }
+        }
+        packed |= static_cast<uint32_t>(q & 0xFF) << (8 * i);
+      }
+    }
+    tile[ty + 8 * r][tx] = packed;  // [slice][token]
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int mm = m0 + ty + 8 * r, sl = s0 + tx;
+    if (mm < M && sl < Sp) *reinterpret_cast<uint32_t*>(xq + (size_t)mm * Kp + sl * 4) = tile[tx][ty + 8 * r];
+  }
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------ host side
@@ -580,6 +724,7 @@ int launch_dequant_weights(int bits, bool to_s8, const void* packed, const void*
 
 int launch_transpose_x(const void* x, int layout, int M, int K, int Kp, void* out, cudaStream_t stream) {
   dim3 grid(div_up(div_up(Kp, 4), 256), M);
+  if (layout == MLD_LAYOUT_SLICED) grid = dim3(div_up(div_up(Kp, 4), 32), div_up(M, 32));
   transpose_x_kernel<<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), layout, M, K, Kp,
                                                static_cast<__half*>(out));
   MLD_LAUNCH_CHECK();
@@ -588,6 +733,19 @@ int launch_transpose_x(const void* x, int layout, int M, int K, int Kp, void* ou
 
 int launch_quantize_act(const void* x, int layout, int M, int K, int Kp, bool symmetric, void* xq, float* params,
                         cudaStream_t stream) {
+  if (layout == MLD_LAYOUT_SLICED) {
+    // params holds [M][3] parameters followed by the partial extremes [kStatSplits][M][2]
+    // (kActParamFloats floats per token in all)
+    float* part = params + (size_t)M * 3;
+    act_stats_sliced_kernel<<<dim3(div_up(M, 32), kStatSplits), 256, 0, stream>>>(static_cast<const __half*>(x), M, K,
+                                                                                  part);
+    MLD_LAUNCH_CHECK();
+    dim3 grid(div_up(Kp / 4, 32), div_up(M, 32));
+    act_quantize_sliced_kernel<<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), M, K, Kp, symmetric ? 1 : 0,
+                                                         part, params, static_cast<int8_t*>(xq));
+    MLD_LAUNCH_CHECK();
+    return MLD_OK;
+  }
   quantize_act_kernel<<<M, 256, 0, stream>>>(static_cast<const __half*>(x), layout, M, K, Kp, symmetric ? 1 : 0,
                                              static_cast<int8_t*>(xq), params);
   MLD_LAUNCH_CHECK();

@@ -58,6 +58,13 @@ struct PeerWait {
 };
 enum { kErrPeerWait = 4 };
 
+// A sharded operator whose output block goes straight into every rank's copy of the gathered tensor:
+// y[r] = where this rank's block starts in rank r's tensor (plain peer stores; y[rank] is local).
+struct PeerOutputs {
+  int world;
+  void* y[8];
+};
+
 struct StripArgs {
   const void* x;      // fp16, sliced [K/4][M_total][4] (for one token a plain vector)
   const void* bias;   // fp16 [N4] or null
@@ -102,7 +109,9 @@ void fc_plan_share_error(mld_fc_plan* plan, int* word);
 // mld_fc_run with the sharded-decoder hooks (null = none); not part of the C ABI.
 int fc_run_internal(mld_fc_plan* plan, const void* src, const void* weights, const void* scale, const void* zero_point,
                     const void* bias, void* dst, int32_t tokens, void* stream, const PeerScatter* scatter,
-                    const PeerWait* wait);
+                    const PeerWait* wait, const PeerOutputs* outs = nullptr, bool* outs_used = nullptr);
+// Shape facts of a plan the sharded entry points need.
+void fc_plan_shape(const mld_fc_plan* plan, int* n, int* dst_layout, int* max_tokens, int* device);
 int launch_fc_strip(int bits, bool subnormal, const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a,
                     const StripGeometry& gm, cudaStream_t stream);
 
@@ -155,6 +164,10 @@ GemmGeometry gemm_geometry(int M, int N, int K, bool i8, int sms);
 int launch_dequant_weights(int bits, bool to_s8, const void* packed, const void* scale, int scale_mode, int G,
                            int group_slices, float scalar_scale, int N, int K, int Kp, void* out, cudaStream_t stream);
 int launch_transpose_x(const void* x, int layout, int M, int K, int Kp, void* out, cudaStream_t stream);
+// Per-token workspace of launch_quantize_act: {inv_scale, offset, sum} followed by the partial extremes of
+// kStatSplits ranges of the input channels.
+constexpr int kStatSplits = 16;
+constexpr int kActParamFloats = 3 + 2 * kStatSplits;
 int launch_quantize_act(const void* x, int layout, int M, int K, int Kp, bool symmetric, void* xq, float* params,
                         cudaStream_t stream);
 int launch_gemm_umma(bool i8, const void* a_mat, const void* b_mat, const GemmGeometry& g, int M, int N, int K,
@@ -163,14 +176,16 @@ int launch_gemm_umma(bool i8, const void* a_mat, const void* b_mat, const GemmGe
 
 // ------------------------------------------- prefill GEMM, dequantisation inside (SM pairs)
 struct PairGeometry {
-  int kp, tile_n, m_tiles, n_tiles, k_blocks, stages, w_box_bytes, grid;
+  int kp, tile_n, m_tiles, n_tiles, k_blocks, stages, w_stages, w_box_bytes, grid;
   size_t smem_bytes;
 };
-// mode: 0 = INT4 weights -> fp16 MMA, 1 = INT8 weights -> fp16 MMA, 2 = INT8 weights x int8 activations
+// mode: 0 = INT4 weights -> fp16 MMA, 1 = INT8 weights -> fp16 MMA, 2 = INT8 weights x int8 activations (packed
+// weights, transformed in shared memory); 3 / 4 = weights prepared as K-major fp16 / s8 rows [N4][kp] by
+// launch_dequant_weights (then `packed` is that matrix)
 PairGeometry pair_geometry(int M, int N, int K, int mode, int sms);
 int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const PairGeometry& g, int M, int N, int K,
                      const void* scale, int scale_mode, int G, int group_slices, float scalar_scale, const void* bias,
                      const float* a_params, const int32_t* w_sum, void* y, int dst_layout, int* error,
-                     cudaStream_t stream);
+                     cudaStream_t stream, const PeerOutputs* outs = nullptr);
 
 }  // namespace mld

@@ -585,6 +585,56 @@ ORC_API void orc_quantize_act_sym(const void* x, int src_f16, int M, int K,
   }
 }
 
+/* Asymmetric per-token quantisation to signed int8, the other branch of the
+ * same generated kernel (quantize_and_dequantize.cc:379-437; it is the model
+ * builder's default, common/gpu_model_builder.h:236-240): src_range = max - min,
+ * offset = min, scale = dst_range / src_range, inv_scale = src_range / dst_range,
+ * and for a signed destination offset += src_range * src_range_middle with
+ * src_range_middle = (range / 2) / (range - 1) = 128 / 255 (:778-781);
+ * q = clamp(int((x - min) * scale + 0.5), 0, 255) - 128.  A constant token
+ * (src_range 0) is given scale = inv_scale = 0 here (the generated kernel would
+ * divide by zero): every x then equals the offset.  Same outputs as the
+ * symmetric form. */
+ORC_API void orc_quantize_act_asym(const void* x, int src_f16, int M, int K,
+                                   int8_t* q, float* params) {
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    float vmin = INFINITY, vmax = -INFINITY;
+    for (int k = 0; k < K; ++k) {
+      const float v = src_f16 ? orc_h2f(((const uint16_t*)x)[(size_t)m * K + k])
+                              : ((const float*)x)[(size_t)m * K + k];
+      vmin = fminf(vmin, v);
+      vmax = fmaxf(vmax, v);
+    }
+    const float src_range = vmax - vmin;
+    float offset = vmin, scale = 0.0f, inv_scale = 0.0f;
+    if (src_range > 0.0f) {
+      scale = 255.0f / src_range;
+      inv_scale = src_range / 255.0f;
+      const float middle = 128.0f / 255.0f;
+      const float t = src_range * middle;
+      offset = offset + t;
+    }
+    int sum = 0;
+    for (int k = 0; k < K; ++k) {
+      const float v = src_f16 ? orc_h2f(((const uint16_t*)x)[(size_t)m * K + k])
+                              : ((const float*)x)[(size_t)m * K + k];
+      float t = v - vmin;
+      t = t * scale;
+      t = t + 0.5f;
+      int qi = (int)t;
+      qi = qi > 255 ? 255 : qi;
+      qi = qi < 0 ? 0 : qi;
+      qi -= 128;
+      q[(size_t)m * K + k] = (int8_t)qi;
+      sum += qi;
+    }
+    params[m * 3 + 0] = inv_scale;
+    params[m * 3 + 1] = offset;
+    params[m * 3 + 2] = (float)sum;
+  }
+}
+
 /* int8 x int8 -> int32 GEMM, the exact reference the Si8Wi8 tests use
  * (common/task/testing_ref_ops.cc:1069-1098).  xq [M][K], wq [N][K]. */
 ORC_API void orc_gemm_s8s8_s32(const int8_t* xq, const int8_t* wq, int M, int K,

@@ -235,6 +235,15 @@ def quantize_act_sym(x_bits_or_f32: np.ndarray, src_f16: bool):
     return q, params
 
 
+def quantize_act_asym(x_bits_or_f32: np.ndarray, src_f16: bool):
+    x = _c(x_bits_or_f32, np.uint16 if src_f16 else np.float32)
+    M, K = x.shape
+    q = np.empty((M, K), np.int8)
+    params = np.empty((M, 3), np.float32)
+    lib().orc_quantize_act_asym(_p(x), int(src_f16), M, K, _p(q), _p(params))
+    return q, params
+
+
 def gemm_s8s8_s32(xq, wq):
     xq = _c(xq, np.int8)
     wq = _c(wq, np.int8)
@@ -288,6 +297,39 @@ def gemv_f32_fast(bits, x, packed, N, scale_gn, bias=None):
     lib().orc_gemv_f32_fast(bits, K, N, _p(x), _p(_c(packed, np.uint8)), G, _p(scale_gn),
                             _p(None if bias is None else _c(bias, np.float32)), _p(y))
     return y[:N]
+
+
+def embedding_lookup(ids, packed, vocab, dim, bits, scale, zp=None):
+    """The generated kernel of EmbeddingLookup (ml_drift/common/kernels/embedding_lookup.cc:44-196) over the
+    FullyConnected weight layout (O = vocab, I = dim): for token id `index` (clamped to [0, vocab - 1]) and
+    input slice S, column index % 4 of block (S, index / 4), dequantised in fp32 as
+    value * scale + (-scale * (shift + zero_point)).  scale / zp: [vocab] or [vocab][G] float32 (already
+    rounded to the storage type).  Returns float32 [tokens][dim]."""
+    ids = np.clip(np.asarray(ids, np.int64), 0, vocab - 1)
+    scale = np.asarray(scale, np.float32).reshape(vocab, -1)
+    G = scale.shape[1]
+    zpa = None if zp is None else np.asarray(zp, np.float32).reshape(vocab, -1)
+    S = div_up(dim, 4)
+    OS = div_up(vocab, 4)
+    blk = 16 if bits == 8 else 8
+    pk = np.asarray(packed, np.uint8).reshape(S, OS, blk)
+    shift = np.float32(128.0 if bits == 8 else 8.0)
+    group_slices = (dim // G) // 4
+    out = np.zeros((len(ids), S * 4), np.float32)
+    for t, index in enumerate(ids):
+        b = pk[:, index // 4, :]                                   # [S][blk]
+        sub = int(index % 4)
+        if bits == 8:
+            vals = b.reshape(S, 4, 4)[:, :, sub].astype(np.float32)   # byte (k % 4) * 4 + sub
+        else:
+            nib = np.stack([b & 15, b >> 4], axis=-1).reshape(S, 16)  # nibble e = 2 * byte + (high)
+            vals = nib.reshape(S, 4, 4)[:, :, sub].astype(np.float32)
+        g = np.minimum(np.arange(S) // max(group_slices, 1), G - 1)
+        sc = scale[index, g].astype(np.float32)[:, None]
+        z = np.float32(0.0) if zpa is None else zpa[index, g].astype(np.float32)[:, None]
+        bias = (-sc) * (shift + z)
+        out[t] = (vals * sc + bias).astype(np.float32).reshape(-1)
+    return out[:, :dim]
 
 
 def num_threads() -> int:

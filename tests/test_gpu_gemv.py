@@ -156,7 +156,7 @@ def _quantised_case(oracle, rng, bits, K, N, block):
 
 STREAM_CASES = [
     # bits, K, N, block, M
-    (4, 2048, 16384, 32, 1),     # BASELINE config 2
+    (4, 2048, 16384, 32, 1),     # the decode GEMV benchmark case (FFN up-projection)
     (4, 4096, 4096, 32, 1),      # 7B attention projection
     (4, 11008, 4096, 32, 1),     # 7B down projection: ragged last K chunk, split-K
     (4, 4096, 11008, 32, 1),     # 7B up projection: ragged last tile
@@ -166,11 +166,11 @@ STREAM_CASES = [
     (4, 2048, 1024, 32, 9), (4, 2048, 1024, 32, 16),
     (4, 2048, 1024, 64, 1), (4, 2048, 1024, 128, 3), (4, 2048, 1024, 256, 1), (4, 2048, 1024, 512, 1),
     (4, 2048, 1024, 1024, 1), (4, 2048, 1024, 0, 1),
-    (8, 2048, 2048, 0, 1),       # config-1 geometry with fp16 tensors
+    (8, 2048, 2048, 0, 1),       # the W8 per-channel case with fp16 tensors
     (8, 4096, 1000, 0, 4), (8, 1024, 3584, 0, 16),
     (4, 512, 65536, 32, 1),      # strips wider than four boxes: several column passes per CTA
     (4, 1024, 40000, 128, 2),    # multi-pass with ragged last strip
-    (8, 8192, 3584, 0, 1),       # config-5 shard geometry, one token
+    (8, 8192, 3584, 0, 1),       # one rank's shard of the W8A8 prefill case, one token
     (4, 256, 4096, 32, 1),       # K too short to split: narrow strips, one CTA each
     (4, 1024, 8, 32, 1), (4, 1024, 16, 32, 3), (8, 1024, 8, 0, 1),   # a single chunk / unit
 ]

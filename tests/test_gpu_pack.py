@@ -117,7 +117,7 @@ def test_quantiser_matches_reference_vectors(mld):
 
 
 def test_full_size_packing_roundtrip(mld):
-    # config-2 size: unpacking the packed bytes on the host recovers every weight
+    # the decode GEMV benchmark size: unpacking the packed bytes on the host recovers every weight
     O, I = 16384, 2048
     g = torch.Generator(device="cuda").manual_seed(0)
     q = torch.randint(-8, 8, (O, I), dtype=torch.int8, device="cuda", generator=g)
