@@ -105,6 +105,7 @@ struct mld_fc_plan {
   // prefill GEMM workspace (allocated with the plan)
   void* w_kmajor;        // dequantised fp16 / re-biased s8 weights, [N4][kp]
   void* x_kmajor;        // activations, [max_tokens][kp]
+  PairSplit split;       // where SM pairs that share a tile of the prefill GEMM combine their partial sums
   float* a_params;       // per-token {inv_scale, offset, sum}
   const void* prepared_w;
   const void* prepared_s;
@@ -253,6 +254,7 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   p->error_shared = nullptr;
   p->ws_bytes = 0;
   p->w_kmajor = p->x_kmajor = nullptr;
+  p->split = PairSplit{nullptr, nullptr, 0};
   p->a_params = nullptr;
   p->prepared_w = p->prepared_s = nullptr;
   p->w_sum = nullptr;
@@ -308,12 +310,16 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
     cudaError_t e = need_w ? cudaMalloc(&p->w_kmajor, wb) : cudaSuccess;
     if (e == cudaSuccess) e = cudaMalloc(&p->x_kmajor, xb);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&p->a_params), pb);
+    const size_t sb = pair_split_bytes(p->sms), fb = pair_split_flags(p->sms) * sizeof(uint32_t);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&p->split.ws), sb);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&p->split.flags), fb);
+    if (e == cudaSuccess) e = cudaMemset(p->split.flags, 0, fb);
     if (e != cudaSuccess) {
       set_last_error("prefill workspace", e);
       mld_fc_plan_destroy(p);
       return MLD_CUDA_ERROR;
     }
-    p->ws_bytes += wb + xb + pb;
+    p->ws_bytes += wb + xb + pb + sb + fb;
   }
   *out = p;
   return MLD_OK;
@@ -324,6 +330,8 @@ int mld_fc_plan_destroy(mld_fc_plan* plan) {
   if (plan->error) cudaFree(plan->error);
   if (plan->w_kmajor) cudaFree(plan->w_kmajor);
   if (plan->x_kmajor) cudaFree(plan->x_kmajor);
+  if (plan->split.ws) cudaFree(plan->split.ws);
+  if (plan->split.flags) cudaFree(plan->split.flags);
   if (plan->a_params) cudaFree(plan->a_params);
   delete plan;
   return MLD_OK;
@@ -477,6 +485,7 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
     set_last_error_text("this operator was not planned for the prefill route (force_path / max_tokens at creation)");
     return MLD_INVALID_ARGUMENT;
   }
+  MLD_REQUIRE((reinterpret_cast<uintptr_t>(bias) & 7) == 0, "biases must be 8-byte aligned");
   if (d.prefill_act_quant == 2 && p->w_sum == nullptr) {
     set_last_error_text("asymmetric int8 activations need the weights' per-output sums (mld_fc_plan_set_weights_sum)");
     return MLD_INVALID_ARGUMENT;
@@ -486,7 +495,8 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
                        (d.prefill_route == MLD_PREFILL_ROUTE_AUTO && convert_pays(tokens));
   if (!convert) {
     const int mode = i8 ? 2 : (d.weight_bits == 4 ? 0 : 1);
-    const PairGeometry pg = pair_geometry(tokens, d.n, d.k, mode, p->sms);
+    const PairGeometry pg = pair_geometry(tokens, d.n, d.k, mode, p->sms, true);
+    if (++p->split.epoch == 0) p->split.epoch = 1;
     if (i8)
       rc = launch_quantize_act(src, d.src_layout, tokens, d.k, pg.kp, d.prefill_act_quant == 1, p->x_kmajor, p->a_params,
                                stream);
@@ -496,7 +506,7 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
     return launch_gemm_pair(mode, p->x_kmajor, weights, pg, tokens, d.n, d.k, scale, d.scale_mode,
                             d.scale_mode == MLD_SCALE_BLOCK ? d.groups : 1, p->group_slices, d.scalar_scale, bias,
                             p->a_params, d.prefill_act_quant == 2 ? p->w_sum : nullptr, dst, d.dst_layout, err, stream,
-                            outs);
+                            outs, &p->split);
   }
 
   const GemmGeometry g = gemm_geometry(tokens, d.n, d.k, i8, p->sms);
@@ -518,11 +528,12 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
   {
     // the multiplication itself: the SM-pair kernel with both operands loaded by TMA
     const int mode = i8 ? 4 : 3;
-    const PairGeometry pg = pair_geometry(tokens, d.n, d.k, mode, p->sms);
+    const PairGeometry pg = pair_geometry(tokens, d.n, d.k, mode, p->sms, true);
+    if (++p->split.epoch == 0) p->split.epoch = 1;
     if (pg.kp == g.kp)
       return launch_gemm_pair(mode, p->x_kmajor, p->w_kmajor, pg, tokens, d.n, d.k, scale, d.scale_mode, 1, 1, 0.0f,
                               bias, p->a_params, d.prefill_act_quant == 2 ? p->w_sum : nullptr, dst, d.dst_layout, err,
-                              stream, outs);
+                              stream, outs, &p->split);
   }
   if (d.prefill_act_quant == 2) {
     set_last_error_text("asymmetric int8 activations are served by the SM-pair GEMM only");

@@ -194,6 +194,16 @@ struct PairArgs {
   int dst_layout;
   int* error;
   PeerOutputs outs;           // world > 1: the block is stored into every rank's tensor instead of y
+  // Work split.  The first shared_tiles tiles are cut into k-block units, in the order (tile 0, k-block 0),
+  // (tile 0, k-block 1), ..., and SM pair p takes the units [p * units_per_pair, (p + 1) * units_per_pair): a
+  // range that is not a whole number of tiles makes the pair share its first and / or last tile with a
+  // neighbour (each tile with at most one: a range is never shorter than a tile); the partial sums meet
+  // through split_ws.  After that the pair takes whole tiles shared_tiles + p, + p + pairs, ...
+  // (shared_tiles = 0: whole tiles only.)
+  int shared_tiles, units_per_pair;
+  float* split_ws;            // [pairs][2 CTAs][4 warps][8 chunks][8][32 lanes] x 16 bytes of raw accumulators
+  uint32_t* split_flags;      // [pairs][2 CTAs][4 warps]: = epoch once that warp's share of the slot is written
+  uint32_t epoch;             // differs from launch to launch, so the flags never need clearing
   long long* trace;           // tuning builds only: [grid][8] cycle counts per role (waiting / working)
   int skip_transform;         // tuning builds only: leave the operand tiles unwritten (timing of the rest)
 };
@@ -211,11 +221,52 @@ __device__ __forceinline__ uint32_t dq2(uint32_t biased, __half2 s2, __half2 b2)
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+// A pair's work in order: runs of k-blocks of the shared tiles inside [u, u_end), then whole tiles.
+struct Segment {
+  int tile, kb0, kb1;
+};
+struct WorkList {
+  int u, u_end, tile, tile_end, tile_step, k_blocks;
+  __device__ __forceinline__ bool next(Segment& sg) {
+    if (u < u_end) {
+      sg.tile = u / k_blocks;
+      sg.kb0 = u - sg.tile * k_blocks;
+      sg.kb1 = min(k_blocks, sg.kb0 + (u_end - u));
+      u += sg.kb1 - sg.kb0;
+      return true;
+    }
+    if (tile < tile_end) {
+      sg.tile = tile;
+      sg.kb0 = 0;
+      sg.kb1 = k_blocks;
+      tile += tile_step;
+      return true;
+    }
+    return false;
+  }
+  __device__ __forceinline__ int stages_in_all() const {
+    return (u_end - u) + (tile < tile_end ? (tile_end - tile + tile_step - 1) / tile_step : 0) * k_blocks;
+  }
+};
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kPairThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, PairArgs a) {
   constexpr bool I8 = MODE == kModeInt8I8 || MODE == kModePreparedI8;
   constexpr bool PREPARED = MODE >= kModePreparedF16;
+  // Epilogue warps: four (one per quarter of the TMEM lanes) while the transform warps are at work; with
+  // prepared weights those warps are free, and sixteen share a tile, four taking every fourth 32-column chunk
+  // of each lane quarter.
+  constexpr int EPI_PARTS = PREPARED ? 4 : 1;
+  constexpr int EPI_WARPS = 4 * EPI_PARTS;
   constexpr int BLK = MODE == kModeInt4F16 ? 8 : 16;            // bytes of a packed 4x4 block
   constexpr int K_PER_STAGE = I8 ? 128 : 64;                      // elements of K in a 128-byte row
   constexpr int SLICES = K_PER_STAGE / 4;                         // packed rows per stage
@@ -239,8 +290,18 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int total_tiles = a.m_tiles * a.n_tiles;
+  WorkList work0;
+  {
+    const int shared_units = a.shared_tiles * a.k_blocks;
+    work0.u = min(shared_units, pair * a.units_per_pair);
+    work0.u_end = min(shared_units, work0.u + a.units_per_pair);
+    work0.tile = a.shared_tiles + pair;
+    work0.tile_end = a.m_tiles * a.n_tiles;
+    work0.tile_step = n_pairs;
+    work0.k_blocks = a.k_blocks;
+  }
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.w_stages; ++s) {
       mbar_init(&full_w[s], 1);
@@ -254,7 +315,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 2 * 4);
+      mbar_init(&tmem_empty[b], 2 * EPI_WARPS);
     }
     fence_barrier_init();
   }
@@ -266,6 +327,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   __syncthreads();
   cluster_sync_all();  // the partner's barriers are initialised before anything arrives on them
   tc_after();
+  pdl_wait();  // everything above overlapped the tail of the kernel before; the operands are its outputs
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t full_ab_lead = map_shared(smem_u32(full_ab), 0);      // the first CTA's barriers, as cluster addresses
   const uint32_t tmem_empty_lead = map_shared(smem_u32(tmem_empty), 0);
@@ -280,11 +342,13 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       bool ok = true;
       long long tr_wait = 0;
       [[maybe_unused]] const long long tr_start = MLD_PAIR_CLOCK();
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-        const int mi = tile % a.m_tiles, ni = tile / a.m_tiles;
+      WorkList work = work0;
+      Segment sg;
+      while (ok && work.next(sg)) {
+        const int mi = sg.tile % a.m_tiles, ni = sg.tile / a.m_tiles;
         const int m0 = mi * 2 * kRowsPerCta + static_cast<int>(rank) * kRowsPerCta;
         (void)ni;
-        for (int kb = 0; kb < a.k_blocks; ++kb) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           const long long t0 = MLD_PAIR_CLOCK();
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             atomicExch(a.error, kErrPairBase + 1);
@@ -320,7 +384,9 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       bool ok = true;
       long long tr_wait_acc = 0, tr_wait_ab = 0;
       [[maybe_unused]] const long long tr_start = MLD_PAIR_CLOCK();
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
+      WorkList work = work0;
+      Segment sg;
+      for (; ok && work.next(sg); ++local) {
         const int acc = local & 1;
         const long long t0 = MLD_PAIR_CLOCK();
         if (!wait_cluster(&tmem_empty[acc], (acc ? acc_phase1 : acc_phase0) ^ 1)) {
@@ -332,7 +398,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         tr_wait_acc += MLD_PAIR_CLOCK() - t0;
         tc_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * 256);
-        for (int kb = 0; kb < a.k_blocks; ++kb) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           const long long t1 = MLD_PAIR_CLOCK();
           if (!wait_cluster(&full_ab[stage], phase)) {
             atomicExch(a.error, kErrPairBase + 3);
@@ -346,7 +412,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint64_t adv = static_cast<uint64_t>((k * 32) >> 4);  // 32 bytes of K per MMA inside the swizzle atom
-            umma_pair<I8>(tmem_d, da + adv, db + adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_pair<I8>(tmem_d, da + adv, db + adv, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
           }
           commit_pair(&empty[stage]);
           if (++stage == a.stages) {
@@ -364,15 +430,21 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       }
 #endif
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + EPI_WARPS) {
     // --------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+    const int part = (warp - 2) >> 2;  // this warp's chunks: part, part + EPI_PARTS, ...
     uint32_t acc_phase0 = 0, acc_phase1 = 0;
     int local = 0;
     bool ok = true;
-    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
+    WorkList work = work0;
+    Segment sg;
+    [[maybe_unused]] long long tr_full = 0, tr_flag = 0;
+    [[maybe_unused]] const long long tr_start = MLD_PAIR_CLOCK();
+    for (; ok && work.next(sg); ++local) {
       const int acc = local & 1;
-      const int mi = tile % a.m_tiles, ni = tile / a.m_tiles;
+      const int mi = sg.tile % a.m_tiles, ni = sg.tile / a.m_tiles;
+      [[maybe_unused]] const long long tf0 = MLD_PAIR_CLOCK();
       if (!mbar_wait(&tmem_full[acc], acc ? acc_phase1 : acc_phase0)) {
         atomicExch(a.error, kErrPairBase + 4);
         ok = false;
@@ -380,6 +452,49 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       }
       if (acc) acc_phase1 ^= 1; else acc_phase0 ^= 1;
       tc_after();
+      tr_full += MLD_PAIR_CLOCK() - tf0;
+      // A tile shared with a neighbour: the pair that holds the tile's LAST k-blocks meets it first in its range
+      // and leaves its raw accumulators in the slot of the pair before it; the pair that holds the tile's FIRST
+      // k-blocks meets it last in its range, adds what it finds in its own slot and writes the outputs.  Each of
+      // the eight epilogue warps of a pair hands over its own 32 rows.
+      const bool hands_over = sg.kb0 > 0, takes_over = sg.kb1 < a.k_blocks;
+      const int slot = hands_over ? pair - 1 : pair;
+      uint4* const slot_rows =
+          reinterpret_cast<uint4*>(a.split_ws) + ((size_t)(slot * 2 + static_cast<int>(rank)) * 4 + quad) * (8 * 8 * 32) + lane;
+      uint32_t* const slot_flag = a.split_flags + ((slot * 2 + static_cast<int>(rank)) * 4 + quad) * 4 + part;
+      if (hands_over) {
+        for (int c0 = part * 32; c0 < a.tile_n; c0 += 32 * EPI_PARTS) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * 256 + c0), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            slot_rows[((c0 >> 5) * 8 + j) * 32] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+        __threadfence();
+        tc_before();
+        __syncwarp();
+        if (lane == 0) {
+          st_release_gpu(slot_flag, a.epoch);
+          arrive_remote(tmem_empty_lead + acc * 8);
+        }
+        continue;
+      }
+      if (takes_over) {
+        [[maybe_unused]] const long long tg0 = MLD_PAIR_CLOCK();
+        uint32_t seen = 0;
+        if (lane == 0) {
+          const unsigned long long t0 = globaltimer_ns();
+          while ((seen = ld_acquire_gpu(slot_flag)) != a.epoch && globaltimer_ns() - t0 <= kWaitLimitNs) __nanosleep(64);
+        }
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+        if (seen != a.epoch) {
+          atomicExch(a.error, kErrPairBase + 8);
+          ok = false;
+          break;
+        }
+        tr_flag += MLD_PAIR_CLOCK() - tg0;
+      }
       const int m = mi * 2 * kRowsPerCta + static_cast<int>(rank) * kRowsPerCta + quad * 32 + lane;
       const int n0 = ni * a.tile_n;
       float a_scale = 1.0f, a_off = 0.0f;
@@ -391,36 +506,63 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           a_scale = 0.0f;
         }
       }
-      for (int c0 = 0; c0 < a.tile_n; c0 += 32) {
+      for (int c0 = part * 32; c0 < a.tile_n; c0 += 32 * EPI_PARTS) {
         uint32_t r[32];
+        // int8 route: lane l holds the constants of column c0 + l, handed round by shuffles below
+        float col_scale = 0.0f, col_offset = 0.0f;  // w_scale and weights_sum of the column
+        if constexpr (I8) {
+          const int nl = n0 + c0 + lane;
+          if (c0 + lane < a.tile_n && nl < a.N) {
+            col_scale = __half2float(a.scale[nl]);
+            if (a.w_sum != nullptr) col_offset = static_cast<float>(a.w_sum[nl]);
+          }
+        }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * 256 + c0);
         tmem_ld32(taddr, r);
         tmem_ld_wait();
+        if (takes_over) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 o = __ldcg(&slot_rows[((c0 >> 5) * 8 + j) * 32]);
+            if constexpr (I8) {
+              r[4 * j] += o.x, r[4 * j + 1] += o.y, r[4 * j + 2] += o.z, r[4 * j + 3] += o.w;
+            } else {
+              r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + __uint_as_float(o.x));
+              r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + __uint_as_float(o.y));
+              r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + __uint_as_float(o.z));
+              r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + __uint_as_float(o.w));
+            }
+          }
+        }
+        if constexpr (I8) {
+          // CreateDequantization (quantize_and_dequantize.cc:867-964):
+          //   res = float(acc) * (w_scale * src_scale) + w_scale * src_zero_point * weights_sum
+          // (every lane takes part in the shuffles, rows past M included)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float ws = __shfl_sync(0xffffffffu, col_scale, j), wo = __shfl_sync(0xffffffffu, col_offset, j);
+            float v = static_cast<float>(static_cast<int32_t>(r[j])) * (ws * a_scale);
+            if (a.w_sum != nullptr) v += ws * a_off * wo;
+            r[j] = __float_as_uint(v);
+          }
+        }
         if (m < a.M) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             const int n = n0 + c0 + j;
             if (c0 + j >= a.tile_n || n >= a.N4) break;
-            __half h[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float v;
-              if constexpr (I8) {
-                // CreateDequantization (quantize_and_dequantize.cc:867-964):
-                //   res = float(acc) * (w_scale * src_scale) + w_scale * src_zero_point * weights_sum
-                const float ws = (n + e) < a.N ? __half2float(a.scale[n + e]) : 0.0f;
-                v = static_cast<float>(static_cast<int32_t>(r[j + e])) * (ws * a_scale);
-                if (a.w_sum != nullptr && (n + e) < a.N) v += ws * a_off * static_cast<float>(a.w_sum[n + e]);
-              } else {
-                v = __uint_as_float(r[j + e]);
-              }
-              h[e] = __float2half_rn(v);
-              if (a.bias != nullptr) h[e] = __hadd(h[e], static_cast<const __half*>(a.bias)[n + e]);
+            __half2 h01 = __floats2half2_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            __half2 h23 = __floats2half2_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            if (a.bias != nullptr) {  // [N4] halves: the four of this column block in one load
+              const uint2 bv = __ldg(reinterpret_cast<const uint2*>(static_cast<const __half*>(a.bias) + n));
+              h01 = __hadd2(h01, *reinterpret_cast<const __half2*>(&bv.x));
+              h23 = __hadd2(h23, *reinterpret_cast<const __half2*>(&bv.y));
             }
+            const __half h[4] = {__low2half(h01), __high2half(h01), __low2half(h23), __high2half(h23)};
             if (a.dst_layout == MLD_LAYOUT_SLICED) {
               uint2 pk;
-              pk.x = static_cast<uint32_t>(__half_as_ushort(h[0])) | (static_cast<uint32_t>(__half_as_ushort(h[1])) << 16);
-              pk.y = static_cast<uint32_t>(__half_as_ushort(h[2])) | (static_cast<uint32_t>(__half_as_ushort(h[3])) << 16);
+              pk.x = *reinterpret_cast<const uint32_t*>(&h01);
+              pk.y = *reinterpret_cast<const uint32_t*>(&h23);
               const size_t at = ((size_t)(n >> 2) * a.M + m) * 4;
               if (a.outs.world > 1) {
                 for (int pr = 0; pr < a.outs.world; ++pr) *reinterpret_cast<uint2*>(static_cast<__half*>(a.outs.y[pr]) + at) = pk;
@@ -439,6 +581,13 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       __syncwarp();
       if (lane == 0) arrive_remote(tmem_empty_lead + acc * 8);
     }
+#ifdef MLD_TRACE
+    if (a.trace != nullptr && PREPARED && warp == 2 && lane == 0) {
+      a.trace[blockIdx.x * 8 + 0] = tr_full;
+      a.trace[blockIdx.x * 8 + 1] = tr_flag;
+      a.trace[blockIdx.x * 8 + 5] = MLD_PAIR_CLOCK() - tr_start;
+    }
+#endif
     if (a.outs.world > 1) __threadfence_system();  // the peer stores are performed before the kernel ends
   } else if (PREPARED) {
     // nothing to transform: the remaining warps only take part in the barriers at both ends
@@ -449,10 +598,12 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       int ws = 0;
       uint32_t wphase = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-        const int ni = tile / a.m_tiles;
+      WorkList work = work0;
+      Segment sg;
+      while (ok && work.next(sg)) {
+        const int ni = sg.tile / a.m_tiles;
         const int nb0 = (ni * a.tile_n + static_cast<int>(rank) * half_n) / 4 * BLK;  // byte column of the box
-        for (int kb = 0; kb < a.k_blocks; ++kb) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(&w_empty[ws], wphase ^ 1)) {
             atomicExch(a.error, kErrPairBase + 7);
             ok = false;
@@ -474,20 +625,19 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       int stage = 0, iter = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-        for (int kb = 0; kb < a.k_blocks; ++kb, ++iter) {
-          if ((iter & 1) == parity_of_mine) {
-            if (!mbar_wait(&xf_done[stage], phase)) {
-              atomicExch(a.error, kErrPairBase + 6);
-              ok = false;
-              break;
-            }
-            arrive_remote(full_ab_lead + stage * 8);
+      const int n_iter = work0.stages_in_all();
+      for (; iter < n_iter && ok; ++iter) {
+        if ((iter & 1) == parity_of_mine) {
+          if (!mbar_wait(&xf_done[stage], phase)) {
+            atomicExch(a.error, kErrPairBase + 6);
+            ok = false;
+            break;
           }
-          if (++stage == a.stages) {
-            stage = 0;
-            phase ^= 1;
-          }
+          arrive_remote(full_ab_lead + stage * 8);
+        }
+        if (++stage == a.stages) {
+          stage = 0;
+          phase ^= 1;
         }
       }
     }
@@ -523,8 +673,10 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     int xf_iter = 0;  // stages of earlier tiles (parity decides which group starts a tile)
     [[maybe_unused]] long long tr_work = 0, tr_fence = 0, tr_arrive = 0;
     [[maybe_unused]] const long long tr_start = MLD_PAIR_CLOCK();
-    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-      const int ni = tile / a.m_tiles;
+    WorkList work = work0;
+    Segment sg;
+    while (ok && work.next(sg)) {
+      const int ni = sg.tile / a.m_tiles;
       const int n = ni * a.tile_n + static_cast<int>(rank) * half_n + row;
       const bool has_n = active && n < a.N4;
       // fp16 routes: this row's scale for the group the first k-block's chunks fall in, fetched a k-block ahead
@@ -539,16 +691,16 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         return __ldg(a.scale + (size_t)g * a.N4 + n);
       };
       // the group's first stage of this tile, and from there every second one
-      int kb = (xf_iter ^ group) & 1;
-      if (kb == 1) advance(1);  // skip the other group's stage
+      int kb = sg.kb0 + ((xf_iter ^ group) & 1);
+      if (kb != sg.kb0) advance(1);  // skip the other group's stage
       __half sc_next = __float2half_rn(0.0f);
       if constexpr (!I8) {
-        if (kb < a.k_blocks) sc_next = scale_at(kb * SLICES + 8 * half);
+        if (kb < sg.kb1) sc_next = scale_at(kb * SLICES + 8 * half);
       }
-      for (; kb < a.k_blocks; kb += 2) {
+      for (; kb < sg.kb1; kb += 2) {
         const __half sc_cur = sc_next;
         if constexpr (!I8) {
-          if (kb + 2 < a.k_blocks) sc_next = scale_at((kb + 2) * SLICES + 8 * half);
+          if (kb + 2 < sg.kb1) sc_next = scale_at((kb + 2) * SLICES + 8 * half);
         }
         const long long t0 = MLD_PAIR_CLOCK();
         // the packed box has landed, and the operand stage it is transformed into is free again
@@ -650,9 +802,9 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         tr_fence += tw2 - tw1;
         tr_arrive += MLD_PAIR_CLOCK() - tw2;
         // on to this group's next stage: past its own and, unless the tile ends first, the other group's
-        advance(kb + 1 < a.k_blocks ? 2 : 1);
+        advance(kb + 1 < sg.kb1 ? 2 : 1);
       }
-      xf_iter += a.k_blocks;
+      xf_iter += sg.kb1 - sg.kb0;
     }
 #ifdef MLD_TRACE
     if (a.trace != nullptr && tt == 0 && group == 0) {
@@ -690,24 +842,33 @@ extern "C" __attribute__((visibility("default"))) void mld_debug_set_pair_trace(
 }
 #endif
 
-PairGeometry pair_geometry(int M, int N, int K, int mode, int sms) {
+PairGeometry pair_geometry(int M, int N, int K, int mode, int sms, bool may_share) {
   PairGeometry g;
   const int N4 = align_n(N, 4);
   const bool i8 = mode == kModeInt8I8 || mode == kModePreparedI8;
   g.kp = align_n(K, i8 ? 16 : 8);
   g.m_tiles = div_up(M, 2 * kRowsPerCta);
+  const int k_per_stage = i8 ? 128 : 64;
+  g.k_blocks = div_up(g.kp, k_per_stage);
   const int pairs = sms / 2 > 0 ? sms / 2 : 1;
   // UMMA N of the pair.  Measured: a stage takes the same time for every width up to 256 (each MMA re-reads its
   // 128 x 16 activation fragment from shared memory, which takes as long as the arithmetic of 256 columns), so
-  // what counts is the number of tile waves over the SM pairs; among the widths with the fewest waves the
-  // narrowest wastes least on columns past N.
-  int best_n = 256;
-  long best_waves = -1;
-  for (int tn = 256; tn >= 128; tn -= 16) {
+  // what counts is the number of stages the busiest SM pair runs: whole tile waves, or, when neighbouring pairs
+  // may share a tile along K, an even share of all stages.  Among the widths with the fewest stages the
+  // narrowest with the same tile count wastes least on columns past N.
+  auto stages_of_busiest = [&](int tn) -> long {
     const long tiles = (long)g.m_tiles * div_up(N4, tn);
-    const long waves = (tiles + pairs - 1) / pairs;
-    if (best_waves < 0 || waves < best_waves || (waves == best_waves && div_up(N4, tn) == div_up(N4, best_n))) {
-      best_waves = waves;
+    const long whole = tiles / pairs, rest = tiles % pairs;
+    if (may_share && whole >= 1 && rest != 0)
+      return (whole - 1) * g.k_blocks + ((pairs + rest) * (long)g.k_blocks + pairs - 1) / pairs;
+    return (tiles + pairs - 1) / pairs * g.k_blocks;
+  };
+  int best_n = 256;
+  long best_cost = -1;
+  for (int tn = 256; tn >= 128; tn -= 16) {
+    const long cost = stages_of_busiest(tn);
+    if (best_cost < 0 || cost < best_cost || (cost == best_cost && div_up(N4, tn) == div_up(N4, best_n))) {
+      best_cost = cost;
       best_n = tn;
     }
   }
@@ -717,8 +878,6 @@ PairGeometry pair_geometry(int M, int N, int K, int mode, int sms) {
   if (const char* e = getenv("MLD_PAIR_TN")) g.tile_n = atoi(e);
 #endif
   g.n_tiles = div_up(N4, g.tile_n);
-  const int k_per_stage = i8 ? 128 : 64;
-  g.k_blocks = div_up(g.kp, k_per_stage);
   const int blk = mode == kModeInt4F16 ? 8 : 16;
   g.w_box_bytes = (k_per_stage / 4) * (g.tile_n / 2 / 4) * blk;
   const int w_stage = (g.w_box_bytes + 127) & ~127;
@@ -743,14 +902,29 @@ PairGeometry pair_geometry(int M, int N, int K, int mode, int sms) {
   g.w_stages = w_stages;
   g.smem_bytes = (size_t)stages * (kABytes + kBBytes) + (size_t)w_stages * w_stage + fixed;
   const long tiles = (long)g.m_tiles * g.n_tiles;
-  g.grid = 2 * static_cast<int>(tiles < pairs ? tiles : pairs);
+  // Tiles that do not fill a last wave: the last whole wave and the remainder are cut along K and dealt out
+  // evenly (between one and two tiles' worth of k-blocks per pair); the waves before it go out as whole tiles.
+  g.shares_tiles = may_share && tiles > pairs && tiles % pairs != 0;
+  if (g.shares_tiles) {
+    g.shared_tiles = static_cast<int>(pairs + tiles % pairs);
+    g.units_per_pair = static_cast<int>(((long)g.shared_tiles * g.k_blocks + pairs - 1) / pairs);
+    g.grid = 2 * pairs;
+  } else {
+    g.shared_tiles = 0;
+    g.units_per_pair = 0;
+    g.grid = 2 * static_cast<int>(tiles < pairs ? tiles : pairs);
+  }
   return g;
 }
 
 int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const PairGeometry& g, int M, int N, int K,
                      const void* scale, int scale_mode, int G, int group_slices, float scalar_scale, const void* bias,
                      const float* a_params, const int32_t* w_sum, void* y, int dst_layout, int* error,
-                     cudaStream_t stream, const PeerOutputs* outs) {
+                     cudaStream_t stream, const PeerOutputs* outs, const PairSplit* split) {
+  if (g.shares_tiles && (split == nullptr || split->ws == nullptr || split->flags == nullptr || split->epoch == 0)) {
+    set_last_error_text("this GEMM geometry shares tiles between SM pairs and needs a split workspace");
+    return MLD_INVALID_ARGUMENT;
+  }
   const int N4 = align_n(N, 4);
   const bool i8 = mode == kModeInt8I8 || mode == kModePreparedI8;
   const bool prepared = mode >= kModePreparedF16;
@@ -798,6 +972,13 @@ int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const Pair
   a.y = y;
   a.dst_layout = dst_layout;
   a.error = error;
+  a.shared_tiles = g.shared_tiles;
+  a.units_per_pair = g.units_per_pair;
+  if (g.shares_tiles) {
+    a.split_ws = split->ws;
+    a.split_flags = split->flags;
+    a.epoch = split->epoch;
+  }
   if (outs != nullptr && outs->world > 1 && dst_layout == MLD_LAYOUT_SLICED) a.outs = *outs;
 #ifdef MLD_TRACE
   a.trace = g_pair_trace;
@@ -823,13 +1004,15 @@ int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const Pair
   cfg.blockDim = dim3(kPairThreads, 1, 1);
   cfg.dynamicSmemBytes = g.smem_bytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   MLD_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tw, a));
   count_launch();
   return MLD_OK;

@@ -319,6 +319,8 @@ __global__ void __launch_bounds__(256) dequant_weights_kernel(const uint8_t* __r
                                                              const __half* __restrict__ scale, int scale_mode, int G,
                                                              int group_slices, float scalar_scale, int dst_slices,
                                                              int src_slices, int Kp, void* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int T = 32;
   constexpr int BLK = BITS == 4 ? 8 : 16;
   constexpr int PITCH = T * BLK + 8;  // +8 bytes: lanes that walk down a column hit distinct banks
@@ -415,6 +417,8 @@ __global__ void __launch_bounds__(256) dequant_weights_kernel(const uint8_t* __r
 // (8 bytes each, contiguous in the source) and written with lanes along K (contiguous in the destination).
 __global__ void __launch_bounds__(256) transpose_x_kernel(const __half* __restrict__ x, int layout, int M, int K, int Kp,
                                                           __half* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int S = (K + 3) / 4, Sp = Kp / 4;
   if (layout == MLD_LAYOUT_SLICED) {
     __shared__ uint2 tile[32][33];
@@ -469,6 +473,8 @@ __global__ void __launch_bounds__(256) transpose_x_kernel(const __half* __restri
 __global__ void __launch_bounds__(256) quantize_act_kernel(const __half* __restrict__ x, int layout, int M, int K, int Kp,
                                                            int symmetric, int8_t* __restrict__ xq,
                                                            float* __restrict__ params) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int m = blockIdx.x;
   __shared__ float red[8], red2[8];
   __shared__ int redi[8];
@@ -554,6 +560,8 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const __half* __restr
 // (quantize_and_dequantize.cc:927-936), and that route takes none.
 __global__ void __launch_bounds__(256) act_stats_sliced_kernel(const __half* __restrict__ x, int M, int K,
                                                                float* __restrict__ part) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float smin[8][33], smax[8][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int m = blockIdx.x * 32 + tx;
@@ -594,6 +602,8 @@ __global__ void __launch_bounds__(256) act_quantize_sliced_kernel(const __half* 
                                                                   int symmetric, const float* __restrict__ part,
                                                                   float* __restrict__ params,
                                                                   int8_t* __restrict__ xq) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ uint32_t tile[32][33];
   const int S = (K + 3) / 4, Sp = Kp / 4;
   const int m0 = blockIdx.y * 32, s0 = blockIdx.x * 32;
@@ -710,8 +720,9 @@ int launch_dequant_weights(int bits, bool to_s8, const void* packed, const void*
   dim3 grid(div_up(div_up(Kp, 4), 32), div_up(dst_slices, 32));
   const uint8_t* p = static_cast<const uint8_t*>(packed);
   const __half* s = static_cast<const __half*>(scale);
-#define MLD_DQ(B, S8) \
-  dequant_weights_kernel<B, S8><<<grid, 256, 0, stream>>>(p, s, scale_mode, G, group_slices, scalar_scale, dst_slices, src_slices, Kp, out)
+#define MLD_DQ(B, S8)                                                                                              \
+  MLD_CUDA_CHECK(launch_overlapped(dequant_weights_kernel<B, S8>, grid, dim3(256), 0, stream, p, s, scale_mode, G, \
+                                   group_slices, scalar_scale, dst_slices, src_slices, Kp, out))
   if (bits == 4) {
     if (to_s8) MLD_DQ(4, true); else MLD_DQ(4, false);
   } else {
@@ -725,8 +736,8 @@ int launch_dequant_weights(int bits, bool to_s8, const void* packed, const void*
 int launch_transpose_x(const void* x, int layout, int M, int K, int Kp, void* out, cudaStream_t stream) {
   dim3 grid(div_up(div_up(Kp, 4), 256), M);
   if (layout == MLD_LAYOUT_SLICED) grid = dim3(div_up(div_up(Kp, 4), 32), div_up(M, 32));
-  transpose_x_kernel<<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), layout, M, K, Kp,
-                                               static_cast<__half*>(out));
+  MLD_CUDA_CHECK(launch_overlapped(transpose_x_kernel, grid, dim3(256), 0, stream, static_cast<const __half*>(x), layout,
+                                   M, K, Kp, static_cast<__half*>(out)));
   MLD_LAUNCH_CHECK();
   return MLD_OK;
 }
@@ -737,17 +748,18 @@ int launch_quantize_act(const void* x, int layout, int M, int K, int Kp, bool sy
     // params holds [M][3] parameters followed by the partial extremes [kStatSplits][M][2]
     // (kActParamFloats floats per token in all)
     float* part = params + (size_t)M * 3;
-    act_stats_sliced_kernel<<<dim3(div_up(M, 32), kStatSplits), 256, 0, stream>>>(static_cast<const __half*>(x), M, K,
-                                                                                  part);
+    MLD_CUDA_CHECK(launch_overlapped(act_stats_sliced_kernel, dim3(div_up(M, 32), kStatSplits), dim3(256), 0, stream,
+                                     static_cast<const __half*>(x), M, K, part));
     MLD_LAUNCH_CHECK();
     dim3 grid(div_up(Kp / 4, 32), div_up(M, 32));
-    act_quantize_sliced_kernel<<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), M, K, Kp, symmetric ? 1 : 0,
-                                                         part, params, static_cast<int8_t*>(xq));
+    MLD_CUDA_CHECK(launch_overlapped(act_quantize_sliced_kernel, grid, dim3(256), 0, stream,
+                                     static_cast<const __half*>(x), M, K, Kp, symmetric ? 1 : 0,
+                                     static_cast<const float*>(part), params, static_cast<int8_t*>(xq)));
     MLD_LAUNCH_CHECK();
     return MLD_OK;
   }
-  quantize_act_kernel<<<M, 256, 0, stream>>>(static_cast<const __half*>(x), layout, M, K, Kp, symmetric ? 1 : 0,
-                                             static_cast<int8_t*>(xq), params);
+  MLD_CUDA_CHECK(launch_overlapped(quantize_act_kernel, dim3(M), dim3(256), 0, stream, static_cast<const __half*>(x),
+                                   layout, M, K, Kp, symmetric ? 1 : 0, static_cast<int8_t*>(xq), params));
   MLD_LAUNCH_CHECK();
   return MLD_OK;
 }

@@ -177,15 +177,27 @@ int launch_gemm_umma(bool i8, const void* a_mat, const void* b_mat, const GemmGe
 // ------------------------------------------- prefill GEMM, dequantisation inside (SM pairs)
 struct PairGeometry {
   int kp, tile_n, m_tiles, n_tiles, k_blocks, stages, w_stages, w_box_bytes, grid;
+  int shared_tiles;    // the first so many tiles are cut along K and dealt out evenly over the SM pairs ...
+  int units_per_pair;  // ... so many k-blocks to each; the other tiles go out whole
+  bool shares_tiles;   // shared_tiles > 0: neighbouring pairs meet through a PairSplit workspace
   size_t smem_bytes;
 };
+// Workspace through which two SM pairs that share a tile combine their partial sums.
+struct PairSplit {
+  float* ws;         // pair_split_bytes(sms) bytes
+  uint32_t* flags;   // pair_split_flags(sms) words, zeroed once
+  uint32_t epoch;    // a value no earlier launch on this workspace used (never 0)
+};
+inline size_t pair_split_bytes(int sms) { return (size_t)(sms / 2 > 0 ? sms / 2 : 1) * 2 * 4 * 8 * 8 * 32 * 16; }
+inline size_t pair_split_flags(int sms) { return (size_t)(sms / 2 > 0 ? sms / 2 : 1) * 2 * 4 * 4; }
 // mode: 0 = INT4 weights -> fp16 MMA, 1 = INT8 weights -> fp16 MMA, 2 = INT8 weights x int8 activations (packed
 // weights, transformed in shared memory); 3 / 4 = weights prepared as K-major fp16 / s8 rows [N4][kp] by
 // launch_dequant_weights (then `packed` is that matrix)
-PairGeometry pair_geometry(int M, int N, int K, int mode, int sms);
+// may_share: a PairSplit workspace will be passed to the launch, so tile waves need not be whole
+PairGeometry pair_geometry(int M, int N, int K, int mode, int sms, bool may_share = false);
 int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const PairGeometry& g, int M, int N, int K,
                      const void* scale, int scale_mode, int G, int group_slices, float scalar_scale, const void* bias,
                      const float* a_params, const int32_t* w_sum, void* y, int dst_layout, int* error,
-                     cudaStream_t stream, const PeerOutputs* outs = nullptr);
+                     cudaStream_t stream, const PeerOutputs* outs = nullptr, const PairSplit* split = nullptr);
 
 }  // namespace mld

@@ -64,6 +64,7 @@ def _run_gemm(mld, oracle, x16, packed, scale_dev, N, K, bits, mode, G, bias=Non
     (257, 320, 20, 32, "sliced"),       # a weight row pitch no tensor map can express: served by the prepared route
     (700, 4096, 1200, 64, "sliced"),    # several tiles per SM pair, two scale groups per stage
     (40, 2048, 6000, 32, "row"),        # few tokens: the pair's second CTA holds no rows
+    (2048, 320, 2560, 32, "sliced"),    # 80 tiles on 74 SM pairs: neighbouring pairs share tiles along K
 ])
 def test_int4_prefill_gemm_vs_oracle(mld, oracle, route, cache, M, K, N, block, layout):
     rng = np.random.default_rng(M + K + N)
@@ -101,7 +102,8 @@ def test_int8_weights_float_route(mld, oracle, route, cache, M, K, N):
 
 @pytest.mark.parametrize("rule,route,cache", [("symmetric", "inline", False), ("symmetric", "cached", True),
                                               ("asymmetric", "inline", False), ("asymmetric", "convert", False)])
-@pytest.mark.parametrize("M,K,N", [(64, 128, 32), (256, 512, 128), (130, 1040, 264), (32, 8192, 96), (300, 2048, 520)])
+@pytest.mark.parametrize("M,K,N", [(64, 128, 32), (256, 512, 128), (130, 1040, 264), (32, 8192, 96), (300, 2048, 520),
+                                   (1100, 384, 4608)])   # the last: 90 tiles on 74 SM pairs, tiles shared along K
 def test_w8a8_prefill_vs_oracle(mld, oracle, rule, route, cache, M, K, N):
     rng = np.random.default_rng(M * 3 + K + N)
     w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
