@@ -460,6 +460,19 @@ def side_benchmarks(mld, torch, peaks):
                                   "GBps_median": algo / g[0] / 1e3, "frac_of_hbm_peak_median": algo / g[0] / 1e3 / hbm,
                                   "frac_of_hbm_peak_best": algo / g[1] / 1e3 / hbm}
     plan.close()
+    # the same launches declared independent of one another (independent_io: each reads a constant x and writes
+    # one of four rotating outputs), as the q / k / v or gate / up projections of one input are: consecutive
+    # launches then overlap completely instead of handing over at the activation load
+    plan = mld.FullyConnectedPlan(N, K, 4, scale_mode=mld.SCALE_BLOCK, groups=K // blk, precision=mld.F32F16,
+                                  independent_io=True)
+    ys = [torch.empty(N, dtype=torch.float16, device="cuda") for _ in range(4)]
+    g = time_in_graph(torch, lambda i: plan.run(x, ws[i % sets], ss[i % sets], ys[i % 4], 1), 256)
+    if g is not None:
+        entry["in_cuda_graph_independent_launches"] = {
+            "launches_per_replay": 256, "median_us_per_launch": g[0], "best_us_per_launch": g[1],
+            "GBps_median": algo / g[0] / 1e3, "frac_of_hbm_peak_median": algo / g[0] / 1e3 / hbm,
+            "frac_of_hbm_peak_best": algo / g[1] / 1e3 / hbm}
+    plan.close()
     # CPU restatement of the same GEMV (OpenMP over output slices), one of the sets copied back
     wh, sh = ws[0].cpu().numpy(), np.ascontiguousarray(ss[0].float().cpu().numpy())
     xh = x.float().cpu().numpy()

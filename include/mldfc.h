@@ -44,7 +44,8 @@ typedef enum mld_status {
   MLD_CUDA_ERROR = 3,
   MLD_NCCL_ERROR = 4,
   MLD_TIMEOUT = 5,          /* a bounded device-side wait gave up */
-  MLD_OUT_OF_RANGE = 6      /* size beyond a fixed capacity */
+  MLD_OUT_OF_RANGE = 6,     /* size beyond a fixed capacity */
+  MLD_NOT_FOUND = 7         /* absl::NotFoundError: a weight file is missing */
 } mld_status;
 
 /* common/precision.h:25-36 (CalculationsPrecision). */
@@ -143,6 +144,62 @@ MLD_API int mld_quantize_weights(const float* w, int32_t o, int32_t i,
                                  float* scale, void* stream);
 
 /* ------------------------------------------------------------------------ */
+/* Weight files                                                              */
+/* ------------------------------------------------------------------------ */
+
+/* LlmFileTensorLoader (samples/llm/llm_file_tensor_loader.h:34-84) over the
+ * file set that samples/llm/extract_weights_hf.py writes (:355-440): one raw
+ * little-endian array per checkpoint tensor, `<key>` (float32, int8 [O][I] or
+ * INT4 packed two per byte, low nibble first) and `<key>_quantized_scale`
+ * (float32 [O][I/block], or an int32 group size followed by int8 / int16 values
+ * in units of 1/1024).  The files are read on the host; the rearrangement into
+ * the operator's layouts runs in the kernels of "Weight conversion" above, so
+ * the destinations are device pointers.  Every load is synchronous. */
+typedef struct mld_loader mld_loader;
+
+/* weights_directory is prepended to every tensor name as it is (end it with
+ * its separator), llm_file_tensor_loader.cc:145-148. */
+MLD_API int mld_loader_open(const char* weights_directory, mld_loader** out);
+MLD_API int mld_loader_close(mld_loader* loader);
+/* HasTensor (:499-509): 1 when the file can be opened. */
+MLD_API int mld_loader_has_tensor(mld_loader* loader, const char* name);
+/* GetTensorElementSizeInBits (:511-522): file size * 8 / count, 0 for a
+ * missing file; how the samples tell INT4 from INT8 from float files. */
+MLD_API int mld_loader_element_bits(mld_loader* loader, const char* name,
+                                    int64_t count);
+/* GetQuantizationIGroupSize (:399-452): input channels per scale group,
+ * deduced from the size (and, for the header form, the first word) of
+ * `<base>.weight_quantized_scale`; i when there is no usable scale file. */
+MLD_API int mld_loader_group_size(mld_loader* loader, const char* weights_name,
+                                  int32_t o, int32_t i);
+/* LoadFloat32 (:150-161): count floats into host memory (a short file leaves
+ * zeros at the end); MLD_NOT_FOUND when the file is missing. */
+MLD_API int mld_loader_load_float32(mld_loader* loader, const char* name,
+                                    int64_t count, float* dst);
+/* LoadInt8Weights (:260-302) for bits 8, LoadInt4WeightsFast (:351-397) for
+ * bits 4: the file's [o][i] values ([i][o] with swap_dims) packed into
+ * kOSpatialIOGroupI4O4 at dst (mld_packed_size_bytes bytes on the device), and
+ * weights_sum_i into sum_i (device, sum_len >= o entries, may be NULL). */
+MLD_API int mld_loader_load_weights(mld_loader* loader, const char* name,
+                                    int32_t bits, int32_t o, int32_t i,
+                                    int32_t swap_dims, void* dst,
+                                    int32_t* sum_i, int32_t sum_len,
+                                    void* stream);
+/* LoadScale (:454-467): [o][g] values in either file form -> the operator's
+ * [g][o4] layout on the device (mld_pack_scales). */
+MLD_API int mld_loader_load_scale(mld_loader* loader, const char* name,
+                                  int32_t o, int32_t g, int32_t dst_f16,
+                                  void* dst, void* stream);
+/* LoadZeroPoint (:469-497): the file holds zero_point * scale; the result is
+ * divided by the scale again (0 where the scale is 0), all zero when there is
+ * no such file. */
+MLD_API int mld_loader_load_zero_point(mld_loader* loader,
+                                       const char* zero_point_name,
+                                       const char* scale_name, int32_t o,
+                                       int32_t g, int32_t dst_f16, void* dst,
+                                       void* stream);
+
+/* ------------------------------------------------------------------------ */
 /* FullyConnected operator                                                   */
 /* ------------------------------------------------------------------------ */
 
@@ -208,6 +265,12 @@ typedef struct mld_fc_desc {
   int32_t no_overlap;        /* 1: do not let consecutive launches overlap
                                 (programmatic dependent launch off) */
   int32_t smem_limit_kb;     /* > 0: shared-memory budget of the stage ring */
+  int32_t independent_io;    /* 1: the caller promises that neither src nor dst of a
+                                call is written or read by the launch ahead of it on
+                                the stream (projections of one input, benchmarks over
+                                rotating tensors): consecutive decode launches then
+                                overlap completely instead of handing over at the
+                                activation load; stream order of completion is kept */
 } mld_fc_desc;
 
 typedef struct mld_fc_plan mld_fc_plan;

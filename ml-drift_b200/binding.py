@@ -42,7 +42,7 @@ class FcDesc(C.Structure):
                 ("dst_layout", C.c_int32), ("max_tokens", C.c_int32), ("force_path", C.c_int32),
                 ("device", C.c_int32), ("prefill_act_quant", C.c_int32), ("cache_prepared_weights", C.c_int32),
                 ("epilogue", C.c_int32), ("prefill_route", C.c_int32), ("exact_operands", C.c_int32), ("no_overlap", C.c_int32),
-                ("smem_limit_kb", C.c_int32)]
+                ("smem_limit_kb", C.c_int32), ("independent_io", C.c_int32)]
 
 
 class DecoderDesc(C.Structure):
@@ -169,11 +169,11 @@ class FullyConnectedPlan:
                  scalar_zero_point=0.0, has_zero_point=False, has_bias=False, precision=F32F16,
                  src_layout=LAYOUT_SLICED, dst_layout=LAYOUT_SLICED, max_tokens=1, force_path=PATH_AUTO,
                  device=-1, prefill_act_quant=0, cache_prepared_weights=False, epilogue=0, exact_operands=False,
-                 no_overlap=False, smem_limit_kb=0, prefill_route=0):
+                 no_overlap=False, smem_limit_kb=0, prefill_route=0, independent_io=False):
         self.desc = FcDesc(n, k, weight_bits, scale_mode, groups, scalar_scale, scalar_zero_point,
                            int(has_zero_point), int(has_bias), precision, src_layout, dst_layout,
                            max_tokens, force_path, device, prefill_act_quant, int(cache_prepared_weights), epilogue,
-                           prefill_route, int(exact_operands), int(no_overlap), smem_limit_kb)
+                           prefill_route, int(exact_operands), int(no_overlap), smem_limit_kb, int(independent_io))
         self._h = C.c_void_p()
         _check(lib().mld_fc_plan_create(C.byref(self.desc), C.byref(self._h)), "mld_fc_plan_create")
 
@@ -220,6 +220,69 @@ def embedding_lookup(ids, weights, scale, dst, vocab, dim, bits, scale_mode=SCAL
     d = EmbedDesc(vocab, dim, bits, scale_mode, groups, int(zero_point is not None), int(f16), dst_layout)
     _check(lib().mld_embedding_lookup(C.byref(d), _ptr(ids), _ptr(weights), _ptr(scale), _ptr(zero_point), _ptr(dst),
                                       ids.numel(), _stream(stream)), "mld_embedding_lookup")
+
+
+# ------------------------------------------------------------------ weight files
+NOT_FOUND = 7
+
+
+class FileTensorLoader:
+    """Owns one mld_loader: the LlmFileTensorLoader surface over a directory of converted weight files."""
+
+    def __init__(self, weights_directory: str):
+        self._h = C.c_void_p()
+        _check(lib().mld_loader_open(weights_directory.encode(), C.byref(self._h)), "mld_loader_open")
+
+    def has_tensor(self, name: str) -> bool:
+        return bool(lib().mld_loader_has_tensor(self._h, name.encode()))
+
+    def element_bits(self, name: str, count: int) -> int:
+        return int(lib().mld_loader_element_bits(self._h, name.encode(), C.c_int64(count)))
+
+    def group_size(self, weights_name: str, o: int, i: int) -> int:
+        return int(lib().mld_loader_group_size(self._h, weights_name.encode(), o, i))
+
+    def load_float32(self, name: str, count: int) -> torch.Tensor:
+        out = torch.empty(count, dtype=torch.float32)
+        _check(lib().mld_loader_load_float32(self._h, name.encode(), C.c_int64(count), C.c_void_p(out.data_ptr())),
+               "mld_loader_load_float32")
+        return out
+
+    def load_weights(self, name: str, bits: int, o: int, i: int, swap_dims=False, device="cuda", stream=None):
+        """Returns (packed uint8 device tensor, weights_sum_i int32 device tensor)."""
+        d = PackDesc(o, 1, 1, i, bits, 0, SRC_UINT4_PACKED if bits == 4 else SRC_INT8, 0, 8 if bits == 4 else 128)
+        nbytes = int(lib().mld_packed_size_bytes(C.byref(d)))
+        dst = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        sums = torch.zeros(o, dtype=torch.int32, device=device)
+        _check(lib().mld_loader_load_weights(self._h, name.encode(), bits, o, i, int(swap_dims), _ptr(dst), _ptr(sums), o,
+                                             _stream(stream)), "mld_loader_load_weights")
+        return dst, sums
+
+    def load_scale(self, name: str, o: int, g: int, f16=True, device="cuda", stream=None) -> torch.Tensor:
+        o4 = (o + 3) // 4 * 4
+        dst = torch.empty(g * o4, dtype=torch.float16 if f16 else torch.float32, device=device)
+        _check(lib().mld_loader_load_scale(self._h, name.encode(), o, g, int(f16), _ptr(dst), _stream(stream)),
+               "mld_loader_load_scale")
+        return dst
+
+    def load_zero_point(self, zero_point_name: str, scale_name: str, o: int, g: int, f16=True, device="cuda",
+                        stream=None) -> torch.Tensor:
+        o4 = (o + 3) // 4 * 4
+        dst = torch.empty(g * o4, dtype=torch.float16 if f16 else torch.float32, device=device)
+        _check(lib().mld_loader_load_zero_point(self._h, zero_point_name.encode(), scale_name.encode(), o, g, int(f16),
+                                                _ptr(dst), _stream(stream)), "mld_loader_load_zero_point")
+        return dst
+
+    def close(self):
+        if self._h:
+            lib().mld_loader_close(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
 
 
 # ------------------------------------------------------- operator split over GPUs

@@ -138,6 +138,7 @@ const char* mld_status_string(int status) {
     case MLD_OK: return "OK";
     case MLD_INVALID_ARGUMENT: return "INVALID_ARGUMENT";
     case MLD_UNIMPLEMENTED: return "UNIMPLEMENTED";
+    case MLD_NOT_FOUND: return "NOT_FOUND";
     case MLD_CUDA_ERROR: return "CUDA_ERROR";
     case MLD_NCCL_ERROR: return "NCCL_ERROR";
     case MLD_TIMEOUT: return "TIMEOUT";
@@ -453,8 +454,12 @@ static int run_stream(mld_fc_plan* p, const void* src, const void* weights, cons
   a.dst_layout = d.dst_layout;
   a.epilogue = d.epilogue;
   a.scalar_scale = d.scalar_scale;
-  a.pdl = p->pdl ? 1 : 0;
+  a.pdl = p->pdl ? (d.independent_io != 0 && scatter == nullptr && wait == nullptr ? 2 : 1) : 0;
   a.trace = g_trace_buffer;
+  a.trace_skip_math = 0;
+#ifdef MLD_TRACE
+  a.trace_skip_math = getenv("MLD_GEMV_SKIP_MATH") != nullptr ? 1 : 0;
+#endif
   memset(&a.scatter, 0, sizeof a.scatter);
   memset(&a.wait, 0, sizeof a.wait);
   if (scatter != nullptr) a.scatter = *scatter;

@@ -237,9 +237,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
 
   if (warp == kConsumerWarps) {
     // ------------------------------------------------------------ producer
-    if (lane == 0 && n_st > 0) {
-      prefetch_tmap(&tmap_w);
-      if (a.scale_rows > 0) prefetch_tmap(&tmap_s);
+    if (n_st > 0) {
       const uint64_t pol = policy_evict_first();
       const int total = passes * n_st;
       const uint32_t s_bytes = a.scale_rows > 0 ? static_cast<uint32_t>(a.scale_rows) * WT * 2u : 0u;
@@ -267,10 +265,13 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
       };
       // weights and scales are constants: the first ring-full of them is
       // requested before waiting for the preceding kernel; activations after.
+      // one lane per stage, so that the whole ring is requested at once
       const int head = total < a.stages ? total : a.stages;
-      for (int it = 0; it < head; ++it) issue_weights(it, it);
+      if (lane < head) issue_weights(lane, lane);
+      __syncwarp();
+      if (lane != 0) return;
       if (tr) tr[1] = globaltimer_ns();
-      if (a.pdl) pdl_wait();
+      if (a.pdl == 1) pdl_wait();  // pdl == 2: the caller declared x and y untouched by the launch before
       if (a.wait.world > 1) {
         const unsigned seq = static_cast<unsigned>(*a.wait.step * a.wait.seq_per_step + a.wait.seq_off);
         if (!wait_peer_flags(a.wait.flags, a.wait.world, seq, a.wait.limit_ns)) atomicExch(a.error, kErrPeerWait);
@@ -294,6 +295,9 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
       // Everything this CTA needs has been requested: use the memory system's
       // idle tail (epilogue, the glue kernels that follow) to pull this CTA's
       // share of the next projection's weights into L2.
+      // Launches that did not wait above still complete in stream order: the grid is not done before the
+      // grid ahead of it is.
+      if (a.pdl == 2) pdl_wait();
       if (a.next_w != nullptr) {
         const unsigned long long per = ((a.next_w_bytes / gridDim.x) + 127ull) & ~127ull;
         unsigned long long lo = per * blockIdx.x, hi = lo + per;
@@ -316,6 +320,9 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
   int stage = 0;
   uint32_t phase = 0;
   bool failed = false;
+#ifdef MLD_TRACE
+  long long tr_wait_cycles = 0, tr_busy_cycles = 0;
+#endif
 
   for (int pass = 0; pass < passes && !failed; ++pass) {
     float tot[W][F::NF][NJ];
@@ -327,11 +334,27 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
         for (int j = 0; j < NJ; ++j) tot[b][f][j] = 0.0f;
 
     for (int si = 0; si < n_st; ++si) {
+#ifdef MLD_TRACE
+      const long long tw0 = clock64();
+#endif
       if (!mbar_wait(&full[stage], phase)) {
         atomicExch(a.error, 2);
         failed = true;
         break;
       }
+#ifdef MLD_TRACE
+      const long long tw1 = clock64();
+      tr_wait_cycles += tw1 - tw0;
+      if (a.trace_skip_math) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[stage]);
+        if (++stage == a.stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+        continue;
+      }
+#endif
       if (tr && threadIdx.x == 0 && pass == 0 && si == 0) tr[3] = globaltimer_ns();
       const uint8_t* st = smem + (size_t)stage * a.stage_bytes;
       const uint8_t* xs = st + W * kBoxBytes + a.scale_stage_bytes;
@@ -409,12 +432,21 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[stage]);
+#ifdef MLD_TRACE
+      tr_busy_cycles += clock64() - tw1;
+#endif
       if (++stage == a.stages) {
         stage = 0;
         phase ^= 1;
       }
     }
     if (failed) break;
+#ifdef MLD_TRACE
+    if (tr && threadIdx.x == 0) {
+      tr[6] = static_cast<unsigned long long>(tr_wait_cycles);
+      tr[7] = static_cast<unsigned long long>(tr_busy_cycles);
+    }
+#endif
 
     // ------------------------------------------------ pass epilogue
     if (tr && threadIdx.x == 0) tr[4] = globaltimer_ns();

@@ -92,6 +92,7 @@ struct StripArgs {
   const void* next_w;  // optional: weights of the projection that runs next, pulled into L2 behind this one
   unsigned long long next_w_bytes;
   unsigned long long* trace;  // optional [grid][8] timestamps (ns) for tuning; null in normal use
+  int trace_skip_math;        // tuning builds only: consume the stages without computing
 };
 
 struct StripGeometry {

@@ -89,6 +89,7 @@ Status Status::FromAbi(int abi_status, const char* where) {
   std::string msg = std::string(where) + ": " + mld_status_string(abi_status) + " (" + mld_last_error() + ")";
   if (abi_status == MLD_INVALID_ARGUMENT) return Status(StatusCode::kInvalidArgument, msg);
   if (abi_status == MLD_UNIMPLEMENTED) return Status(StatusCode::kUnimplemented, msg);
+  if (abi_status == MLD_NOT_FOUND) return Status(StatusCode::kNotFound, msg);
   return Status(StatusCode::kInternal, msg);
 }
 
@@ -528,6 +529,107 @@ Status GpuModelBuilder::Run(const std::vector<std::pair<int, const TensorDescrip
     cudaMemcpy(f.second->MutableData().data(), ensure(f.first), td.GetMemorySizeInBytes(), cudaMemcpyDeviceToHost);
   }
   return OkStatus();
+}
+
+// ---------------------------------------------------------------- weight files
+LlmFileTensorLoader::LlmFileTensorLoader(const std::string& weights_directory, const GpuInfo& gpu_info,
+                                         DataType scale_data_type)
+    : gpu_info_(gpu_info), scale_type_(scale_data_type) {
+  mld_loader_open(weights_directory.c_str(), &loader_);
+}
+
+LlmFileTensorLoader::~LlmFileTensorLoader() { mld_loader_close(loader_); }
+
+std::vector<float> LlmFileTensorLoader::LoadFloat32(const std::string& name, int size) {
+  std::vector<float> data(size > 0 ? size : 0);
+  if (mld_loader_load_float32(loader_, name.c_str(), size, data.data()) != MLD_OK) data.clear();
+  return data;
+}
+
+StatusOr<LlmFileTensorLoader::Int8Weights> LlmFileTensorLoader::LoadQuantized(const std::string& tensor_name,
+                                                                               const WeightsDescription& desc,
+                                                                               const OHWI& shape, bool swap_dims,
+                                                                               int bits) {
+  if (desc.layout != WeightsLayout::kOSpatialIOGroupI4O4) return UnimplementedError("Unsupported layout");
+  if (shape.h != 1 || shape.w != 1) return UnimplementedError("spatial weights are not part of this path");
+  mld_pack_desc pd;
+  std::memset(&pd, 0, sizeof pd);
+  pd.o = shape.o;
+  pd.h = pd.w = 1;
+  pd.i = shape.i;
+  pd.bits = bits;
+  const size_t bytes = mld_packed_size_bytes(&pd);
+  DeviceBuffer packed(bytes), sums(static_cast<size_t>(shape.o) * 4);
+  if (!packed.ptr || !sums.ptr) return Status(StatusCode::kInternal, "device allocation failed");
+  const int rc = mld_loader_load_weights(loader_, tensor_name.c_str(), bits, shape.o, shape.i, swap_dims ? 1 : 0,
+                                         packed.ptr, static_cast<int32_t*>(sums.ptr), shape.o, nullptr);
+  if (rc != MLD_OK) return Status::FromAbi(rc, "mld_loader_load_weights");
+  Int8Weights out;
+  out.weights = TensorDescriptor(desc.type, TensorStorageType::kBuffer, Layout::kLinear);
+  out.weights.SetBHWCShape(BHWC(1, 1, 1, static_cast<int>(bytes * 8 / bits)));
+  out.weights.MutableData().resize(bytes);
+  cudaMemcpy(out.weights.MutableData().data(), packed.ptr, bytes, cudaMemcpyDeviceToHost);
+  out.weights_sum_i = TensorDescriptor(DataType::kInt32, TensorStorageType::kBuffer, Layout::kLinear);
+  out.weights_sum_i.SetBHWCShape(BHWC(1, 1, 1, shape.o));
+  out.weights_sum_i.MutableData().resize(static_cast<size_t>(shape.o) * 4);
+  cudaMemcpy(out.weights_sum_i.MutableData().data(), sums.ptr, static_cast<size_t>(shape.o) * 4, cudaMemcpyDeviceToHost);
+  return out;
+}
+
+StatusOr<LlmFileTensorLoader::Int8Weights> LlmFileTensorLoader::LoadInt8Weights(const std::string& tensor_name,
+                                                                                 const WeightsDescription& desc,
+                                                                                 const OHWI& shape, bool swap_dims) {
+  return LoadQuantized(tensor_name, desc, shape, swap_dims, 8);
+}
+
+StatusOr<LlmFileTensorLoader::Int4Weights> LlmFileTensorLoader::LoadInt4Weights(const std::string& tensor_name,
+                                                                                 const WeightsDescription& desc,
+                                                                                 const OHWI& shape, bool swap_dims) {
+  return LoadQuantized(tensor_name, desc, shape, swap_dims, 4);
+}
+
+int LlmFileTensorLoader::GetQuantizationIGroupSize(const std::string& weights_name, const OHWI& weights_shape) const {
+  return mld_loader_group_size(loader_, weights_name.c_str(), weights_shape.o, weights_shape.i);
+}
+
+StatusOr<TensorDescriptor> LlmFileTensorLoader::LoadScale(const std::string& tensor_name, const OHWI& shape) {
+  const bool f16 = scale_type_ == DataType::kFloat16;
+  const int o4 = (shape.o + 3) / 4 * 4, g = shape.h * shape.w * shape.i;
+  const size_t bytes = static_cast<size_t>(g) * o4 * (f16 ? 2 : 4);
+  DeviceBuffer dst(bytes);
+  if (!dst.ptr) return Status(StatusCode::kInternal, "device allocation failed");
+  const int rc = mld_loader_load_scale(loader_, tensor_name.c_str(), shape.o, g, f16 ? 1 : 0, dst.ptr, nullptr);
+  if (rc != MLD_OK) return Status::FromAbi(rc, "mld_loader_load_scale");
+  TensorDescriptor td(scale_type_, TensorStorageType::kBuffer, Layout::kHWC);
+  td.SetBHWCShape(BHWC(1, 1, (shape.o + 3) / 4, 4 * g));  // as ScaleOrZeroPointToTensorDesc lays it out
+  td.MutableData().resize(bytes);
+  cudaMemcpy(td.MutableData().data(), dst.ptr, bytes, cudaMemcpyDeviceToHost);
+  return td;
+}
+
+StatusOr<TensorDescriptor> LlmFileTensorLoader::LoadZeroPoint(const std::string& zero_point_name,
+                                                              const std::string& scale_name, const OHWI& shape) {
+  const bool f16 = scale_type_ == DataType::kFloat16;
+  const int o4 = (shape.o + 3) / 4 * 4, g = shape.h * shape.w * shape.i;
+  const size_t bytes = static_cast<size_t>(g) * o4 * (f16 ? 2 : 4);
+  DeviceBuffer dst(bytes);
+  if (!dst.ptr) return Status(StatusCode::kInternal, "device allocation failed");
+  const int rc = mld_loader_load_zero_point(loader_, zero_point_name.c_str(), scale_name.c_str(), shape.o, g, f16 ? 1 : 0,
+                                            dst.ptr, nullptr);
+  if (rc != MLD_OK) return Status::FromAbi(rc, "mld_loader_load_zero_point");
+  TensorDescriptor td(scale_type_, TensorStorageType::kBuffer, Layout::kHWC);
+  td.SetBHWCShape(BHWC(1, 1, (shape.o + 3) / 4, 4 * g));  // as ScaleOrZeroPointToTensorDesc lays it out
+  td.MutableData().resize(bytes);
+  cudaMemcpy(td.MutableData().data(), dst.ptr, bytes, cudaMemcpyDeviceToHost);
+  return td;
+}
+
+bool LlmFileTensorLoader::HasTensor(const std::string& name) const {
+  return mld_loader_has_tensor(loader_, name.c_str()) != 0;
+}
+
+int LlmFileTensorLoader::GetTensorElementSizeInBits(const std::string& tensor_name, int count) {
+  return mld_loader_element_bits(loader_, tensor_name.c_str(), count);
 }
 
 }  // namespace mld_host

@@ -14,6 +14,7 @@
 //   packers               common/task/weights_conversion.h:35-112
 //   GpuModelBuilder       common/gpu_model_builder.h:189-210 (FC entry points)
 //   execution harness     common/task/testing_util.h:48-143
+//   LlmFileTensorLoader   samples/llm/llm_file_tensor_loader.h:34-84
 #pragma once
 
 #include <cstdint>
@@ -29,7 +30,7 @@ namespace mld_host {
 
 // ------------------------------------------------------------------ status
 // Stand-in for absl::Status / absl::StatusOr (abseil is not a dependency here).
-enum class StatusCode { kOk = 0, kInvalidArgument = 3, kUnimplemented = 12, kInternal = 13 };
+enum class StatusCode { kOk = 0, kInvalidArgument = 3, kNotFound = 5, kUnimplemented = 12, kInternal = 13 };
 class Status {
  public:
   Status() = default;
@@ -46,6 +47,7 @@ class Status {
 inline Status OkStatus() { return Status(); }
 inline Status InvalidArgumentError(std::string m) { return Status(StatusCode::kInvalidArgument, std::move(m)); }
 inline Status UnimplementedError(std::string m) { return Status(StatusCode::kUnimplemented, std::move(m)); }
+inline Status NotFoundError(std::string m) { return Status(StatusCode::kNotFound, std::move(m)); }
 
 template <typename T>
 class StatusOr {
@@ -299,6 +301,43 @@ class GpuModelBuilder {
   CalculationsPrecision precision_;
   std::vector<TensorDescriptor> tensors_;
   std::vector<GpuNode> nodes_;
+};
+
+// ------------------------------------------------------------- weight files
+// LlmFileTensorLoader (samples/llm/llm_file_tensor_loader.h:34-84) over mld_loader_*: reads the converter's
+// files and returns tensors in device layout.  Where the reference hands each descriptor to the tensor-creation
+// callback of its model builder, this returns the descriptor (GpuModelBuilder::AddConstTensor takes it).
+class LlmFileTensorLoader {
+ public:
+  struct Int8Weights {  // samples/llm/llm_tensor_loader.h: weights + weights_sum_i
+    TensorDescriptor weights;
+    TensorDescriptor weights_sum_i;
+  };
+  using Int4Weights = Int8Weights;
+  // scale_data_type: the type scales and zero points are stored in (the builder's activation type)
+  LlmFileTensorLoader(const std::string& weights_directory, const GpuInfo& gpu_info, DataType scale_data_type);
+  ~LlmFileTensorLoader();
+  LlmFileTensorLoader(const LlmFileTensorLoader&) = delete;
+  LlmFileTensorLoader& operator=(const LlmFileTensorLoader&) = delete;
+
+  std::vector<float> LoadFloat32(const std::string& name, int size);  // empty when the file is missing
+  StatusOr<Int8Weights> LoadInt8Weights(const std::string& tensor_name, const WeightsDescription& weights_desc,
+                                        const OHWI& shape, bool swap_dims);
+  StatusOr<Int4Weights> LoadInt4Weights(const std::string& tensor_name, const WeightsDescription& weights_desc,
+                                        const OHWI& shape, bool swap_dims);
+  int GetQuantizationIGroupSize(const std::string& weights_name, const OHWI& weights_shape) const;
+  StatusOr<TensorDescriptor> LoadScale(const std::string& tensor_name, const OHWI& shape);
+  StatusOr<TensorDescriptor> LoadZeroPoint(const std::string& zero_point_name, const std::string& scale_name,
+                                           const OHWI& shape);
+  bool HasTensor(const std::string& name) const;
+  int GetTensorElementSizeInBits(const std::string& tensor_name, int count);
+
+ private:
+  StatusOr<Int8Weights> LoadQuantized(const std::string& tensor_name, const WeightsDescription& weights_desc,
+                                      const OHWI& shape, bool swap_dims, int bits);
+  mld_loader* loader_ = nullptr;
+  GpuInfo gpu_info_;
+  DataType scale_type_;
 };
 
 }  // namespace mld_host

@@ -305,8 +305,88 @@ static void TestBuilderDispatch(CudaExecutionEnvironment& env) {
   }
 }
 
+// A projection built the way the samples' Linear() builds it (samples/llm/qwen3_model_builder.cc:907-945,
+// llm_weights_loader.cc:29-71): bit width from the file size, group size from the scale file, weights and
+// scales from the loader, one FC node; checked against plain arithmetic on the file's own bytes.
+static void TestFileLoader(CudaExecutionEnvironment& env, const std::string& dir) {
+  LlmFileTensorLoader loader(dir, env.GetGpuInfo(), DataType::kFloat16);
+  const std::string name = "model.layers.0.mlp.down_proj.weight", scale_name = name + "_quantized_scale";
+  const OHWI shape(64, 1, 1, 160);
+  EXPECT(loader.HasTensor(name) && loader.HasTensor(scale_name));
+  EXPECT(!loader.HasTensor("model.layers.7.mlp.down_proj.weight"));
+  EXPECT(loader.GetTensorElementSizeInBits(name, 64 * 160) == 4);
+  EXPECT(loader.GetTensorElementSizeInBits("model.norm.weight", 64) == 32);
+  const int group = loader.GetQuantizationIGroupSize(name, shape);
+  EXPECT(group == 32);
+  EXPECT(loader.LoadFloat32("model.norm.weight", 64).size() == 64);
+  EXPECT(loader.LoadFloat32("missing", 4).empty());
+  GpuModelBuilder builder(env.GetGpuInfo(), CalculationsPrecision::F32_F16);
+  GpuModelBuilder::Weights w;
+  w.shape = shape;
+  w.desc = builder.GetFullyConnectedInt4WeightsDesc(shape);
+  w.scale_zp_shape = OHWI(shape.o, 1, 1, shape.i / group);
+  {
+    auto missing = loader.LoadInt4Weights("model.layers.7.mlp.down_proj.weight", w.desc, shape, false);
+    EXPECT(!missing.ok() && missing.status().code() == StatusCode::kNotFound);
+    auto no_scale = loader.LoadScale("model.layers.7.mlp.down_proj.weight_quantized_scale", w.scale_zp_shape);
+    EXPECT(!no_scale.ok() && no_scale.status().code() == StatusCode::kNotFound);
+  }
+  auto i4 = loader.LoadInt4Weights(name, w.desc, shape, false);
+  auto sc = loader.LoadScale(scale_name, w.scale_zp_shape);
+  EXPECT(i4.ok() && sc.ok());
+  if (!i4.ok() || !sc.ok()) return;
+  EXPECT(i4->weights.GetData().size() == 64u * 160u / 2u);
+  EXPECT(i4->weights_sum_i.GetData().size() == 64u * 4u);
+  w.weights = builder.AddConstTensor(i4->weights);
+  w.scale = builder.AddConstTensor(*sc);
+  auto src = builder.AddTensor(BHWC(1, 1, 1, shape.i), DataType::kFloat16);
+  auto dst = builder.FullyConnectedInt4ExternalWeights(src, w, nullptr);
+  EXPECT(dst.ok());
+  if (!dst.ok()) return;
+  std::vector<float> x;
+  for (int k = 0; k < shape.i; ++k) x.push_back(static_cast<float>((k * 7) % 13 - 6) / 8.0f);  // exact in fp16
+  TensorDescriptor feed = MakeSrc(DataType::kFloat16, x, 1), out_td;
+  Status s = builder.Run({{src.id, &feed}}, {{dst->id, &out_td}});
+  EXPECT(s.ok());
+  if (!s.ok()) return;
+  TensorFloat32 y;
+  out_td.DownloadData(&y);
+  // the file's own bytes: nibbles low first, two's complement; float32 scales [o][i / 32]
+  std::vector<uint8_t> raw(64 * 160 / 2);
+  std::vector<float> scales(64 * 5);
+  FILE* f = std::fopen((dir + name).c_str(), "rb");
+  FILE* g = std::fopen((dir + scale_name).c_str(), "rb");
+  EXPECT(f != nullptr && g != nullptr);
+  if (f == nullptr || g == nullptr) return;
+  EXPECT(std::fread(raw.data(), 1, raw.size(), f) == raw.size());
+  EXPECT(std::fread(scales.data(), 4, scales.size(), g) == scales.size());
+  std::fclose(f);
+  std::fclose(g);
+  const int32_t* sums = reinterpret_cast<const int32_t*>(i4->weights_sum_i.GetData().data());
+  double max_err = 0, max_ref = 0;
+  for (int n = 0; n < shape.o; ++n) {
+    double acc = 0;
+    int sum = 0;
+    for (int k = 0; k < shape.i; ++k) {
+      const int e = n * shape.i + k;
+      const int nib = (raw[e / 2] >> (4 * (e & 1))) & 15;
+      const int q = ((nib + 8) & 15) - 8;
+      sum += q;
+      acc += static_cast<double>(x[k]) * q * scales[n * 5 + k / 32];
+    }
+    EXPECT(sums[n] == sum);
+    max_err = std::fmax(max_err, std::fabs(acc - y.data[n]));
+    max_ref = std::fmax(max_ref, std::fabs(acc));
+  }
+  std::printf(" loaded projection: max err %.3g of max %.3g\n", max_err, max_ref);
+  EXPECT(max_err <= 3e-3 * max_ref);  // fp16 storage of scales and outputs
+}
+
 int main(int argc, char** argv) {
   const bool cpu_only = argc > 1 && std::strcmp(argv[1], "--cpu") == 0;
+  std::string fixture;  // --fixture <directory of converted weight files, with its separator>
+  for (int a = 1; a + 1 < argc; ++a)
+    if (std::strcmp(argv[a], "--fixture") == 0) fixture = argv[a + 1];
   std::printf("[host_test] descriptors and dispatch rule\n");
   TestDescriptorsAndDispatchRule();
   std::printf("[host_test] factory errors\n");
@@ -322,6 +402,10 @@ int main(int argc, char** argv) {
     TestKnownAnswers(env);
     std::printf("[host_test] builder dispatch\n");
     TestBuilderDispatch(env);
+    if (!fixture.empty()) {
+      std::printf("[host_test] file loader\n");
+      TestFileLoader(env, fixture);
+    }
   }
   std::printf("[host_test] %s (%d failures)\n", g_failed == 0 ? "PASSED" : "FAILED", g_failed);
   return g_failed == 0 ? 0 : 1;

@@ -15,7 +15,9 @@ import numpy as np
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_quantiser_vectors.py /path/to/ml-drift")
+    ref_root = sys.argv[1]
     path = os.path.join(ref_root, "ml_drift", "samples", "llm", "extract_weights_hf.py")
     spec = importlib.util.spec_from_file_location("extract_weights_hf", path)
     mod = importlib.util.module_from_spec(spec)

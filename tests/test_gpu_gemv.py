@@ -228,6 +228,37 @@ def test_streaming_gemv_is_deterministic_and_reusable(mld, oracle):
     assert _rel(outs[0].float().cpu().numpy()[None], plain) <= 1e-3
 
 
+def test_independent_launches_overlap_and_finish_in_stream_order(mld, oracle):
+    """independent_io: the launches do not wait for one another at the activation load.  Their results equal
+    the ordinary plan's bit for bit, and a kernel queued behind them on the stream sees all of them."""
+    rng = np.random.default_rng(15)
+    K, N = 2048, 4096
+    sets = []
+    for i in range(6):
+        q, s, packed = _quantised_case(oracle, rng, 4, K, N, 32)
+        sets.append((_dev(packed), _dev(oracle.scale_layout(s, True).view(np.float16))))
+    x = _dev(rng.standard_normal(K).astype(np.float16))
+    ref_plan = mld.FullyConnectedPlan(N, K, 4, scale_mode=mld.SCALE_BLOCK, groups=K // 32, precision=mld.F32F16)
+    plan = mld.FullyConnectedPlan(N, K, 4, scale_mode=mld.SCALE_BLOCK, groups=K // 32, precision=mld.F32F16,
+                                  independent_io=True)
+    want = [torch.zeros(N, dtype=torch.float16, device="cuda") for _ in sets]
+    for (w, sc), y in zip(sets, want):
+        ref_plan.run(x, w, sc, y, 1)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        got = [torch.zeros(N, dtype=torch.float16, device="cuda") for _ in sets]
+        for (w, sc), y in zip(sets, got):
+            plan.run(x, w, sc, y, 1)
+        total = torch.stack(got).float().sum(0)        # queued behind the six launches, no synchronisation between
+        torch.cuda.synchronize()
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+        assert torch.equal(total, torch.stack(want).float().sum(0))
+    assert plan.device_status() == 0
+    plan.close()
+    ref_plan.close()
+
+
 def test_row_major_single_token(mld, oracle):
     rng = np.random.default_rng(6)
     K, N = 1024, 512

@@ -28,6 +28,7 @@ def test_host_mirror_device_checks():
     exe = os.path.join(ROOT, "ml-drift_b200", "build", "host_test")
     if not os.path.exists(exe):
         exe = _build()
-    out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    fixture = os.path.join(ROOT, "tests", "golden", "loader_fixture", "int4_block32") + os.sep
+    out = subprocess.run([exe, "--fixture", fixture], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout + out.stderr
-    assert "PASSED" in out.stdout
+    assert "PASSED" in out.stdout and "file loader" in out.stdout
