@@ -265,11 +265,17 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
       };
       // weights and scales are constants: the first ring-full of them is
       // requested before waiting for the preceding kernel; activations after.
-      // one lane per stage, so that the whole ring is requested at once
+      // Launches that overlap completely request the whole ring at once, one lane per stage.  A launch that
+      // hands over at the activation load requests it stage by stage: measured, its burst only gets in the way
+      // of the launch ahead of it, which is still streaming.
       const int head = total < a.stages ? total : a.stages;
-      if (lane < head) issue_weights(lane, lane);
-      __syncwarp();
+      if (a.pdl == 2) {
+        if (lane < head) issue_weights(lane, lane);
+        __syncwarp();
+      }
       if (lane != 0) return;
+      if (a.pdl != 2)
+        for (int it = 0; it < head; ++it) issue_weights(it, it);
       if (tr) tr[1] = globaltimer_ns();
       if (a.pdl == 1) pdl_wait();  // pdl == 2: the caller declared x and y untouched by the launch before
       if (a.wait.world > 1) {
