@@ -134,13 +134,15 @@ MLD_API int mld_weights_sum_i(const int8_t* src, int32_t o, int32_t hwi,
 MLD_API int mld_pack_scales(const float* src, int32_t o, int32_t g,
                             int32_t dst_f16, void* dst, void* stream);
 
-/* quantize_tensor_int8_sym / quantize_tensor_int4_sym with
- * optimize_scale=False (samples/llm/extract_weights_hf.py:137-229):
- * w [o][i] fp32 -> q [o][i] int8 and scale [o][g] fp32; bits 8 is
- * per-channel (block ignored), bits 4 uses blocks of `block` input channels
- * (0 = per-channel). */
+/* quantize_tensor_int8_sym / quantize_tensor_int4_sym
+ * (samples/llm/extract_weights_hf.py:137-229): w [o][i] fp32 -> q [o][i] int8
+ * and scale [o][g] fp32; bits 8 is per-channel (block ignored), bits 4 uses
+ * blocks of `block` input channels (0 = per-channel).  optimize_scale must be
+ * 0 (scale = absmax / 127 or / 7); 1 asks for the converter's grid search over
+ * seven candidate scales (:78-134), which is not built: MLD_UNIMPLEMENTED. */
 MLD_API int mld_quantize_weights(const float* w, int32_t o, int32_t i,
-                                 int32_t bits, int32_t block, int8_t* q,
+                                 int32_t bits, int32_t block,
+                                 int32_t optimize_scale, int8_t* q,
                                  float* scale, void* stream);
 
 /* ------------------------------------------------------------------------ */
@@ -215,7 +217,8 @@ enum mld_prefill_route {
 typedef struct mld_fc_desc {
   int32_t n;                 /* weights.shape.o */
   int32_t k;                 /* weights.shape.i */
-  int32_t weight_bits;       /* 4 or 8 */
+  int32_t weight_bits;       /* 4 or 8 (2, the reference's kUint2 weights:
+                                MLD_UNIMPLEMENTED) */
   int32_t scale_mode;        /* mld_scale_mode */
   int32_t groups;            /* scale_zp_shape.i (1 unless block-wise) */
   float scalar_scale;        /* ExternalWeights::scalar_scale */
@@ -253,11 +256,22 @@ typedef struct mld_fc_desc {
   int32_t prefill_route;     /* prefill GEMM only, mld_prefill_route: 0 = the
                                 builder's conversion-cost rule
                                 (gpu_model_builder.cc:1132-1173: convert the
-                                weights in a pass of their own when
-                                100 * 2.5 / (2 * tokens) * 32 <= 20, i.e. from
-                                200 tokens up, and dequantise inside the GEMM
-                                below that), 1 = always inside the GEMM, 2 =
-                                always the separate pass */
+                                weights in a pass of their own when that costs
+                                little beside the product, dequantise inside
+                                the GEMM otherwise; with the costs measured
+                                for these kernels the pass pays above 512
+                                tokens, with the reference's constants above
+                                200), 1 = always inside the GEMM, 2 = always
+                                the separate pass */
+  /* Features of the reference operator that this library does not serve: a
+   * non-zero value makes mld_fc_plan_create return MLD_UNIMPLEMENTED and name
+   * the feature in mld_last_error(). */
+  int32_t runtime_channel_bounds; /* ConvRuntimeCheckDesc: src / dst channel
+                                counts read from a tensor at run time
+                                (common/kernels/fully_connected.cc:410-470) */
+  int32_t has_batch_ids;     /* per-token weight selection of the mixture-of-
+                                experts builder
+                                (common/gpu_model_builder_moe_util.cc:200-270) */
   /* Tuning of the streaming decode kernel; 0 everywhere = the defaults. */
   int32_t exact_operands;    /* 1: dequantise to exact fp16 integers before the MMA
                                 instead of feeding the raw nibbles / bytes as fp16

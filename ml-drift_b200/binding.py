@@ -41,7 +41,8 @@ class FcDesc(C.Structure):
                 ("has_bias", C.c_int32), ("precision", C.c_int32), ("src_layout", C.c_int32),
                 ("dst_layout", C.c_int32), ("max_tokens", C.c_int32), ("force_path", C.c_int32),
                 ("device", C.c_int32), ("prefill_act_quant", C.c_int32), ("cache_prepared_weights", C.c_int32),
-                ("epilogue", C.c_int32), ("prefill_route", C.c_int32), ("exact_operands", C.c_int32), ("no_overlap", C.c_int32),
+                ("epilogue", C.c_int32), ("prefill_route", C.c_int32), ("runtime_channel_bounds", C.c_int32),
+                ("has_batch_ids", C.c_int32), ("exact_operands", C.c_int32), ("no_overlap", C.c_int32),
                 ("smem_limit_kb", C.c_int32), ("independent_io", C.c_int32)]
 
 
@@ -147,12 +148,12 @@ def pack_scales(scale: torch.Tensor, f16: bool, stream=None):
     return dst
 
 
-def quantize_weights(w: torch.Tensor, bits: int, block: int = 0, stream=None):
+def quantize_weights(w: torch.Tensor, bits: int, block: int = 0, optimize_scale: bool = False, stream=None):
     o, i = w.shape
     g = i // block if (bits == 4 and block > 0) else 1
     q = torch.empty((o, i), dtype=torch.int8, device=w.device)
     s = torch.empty((o, g), dtype=torch.float32, device=w.device)
-    _check(lib().mld_quantize_weights(_ptr(w), o, i, bits, block, _ptr(q), _ptr(s), _stream(stream)),
+    _check(lib().mld_quantize_weights(_ptr(w), o, i, bits, block, int(optimize_scale), _ptr(q), _ptr(s), _stream(stream)),
            "mld_quantize_weights")
     return q, s
 
@@ -169,11 +170,13 @@ class FullyConnectedPlan:
                  scalar_zero_point=0.0, has_zero_point=False, has_bias=False, precision=F32F16,
                  src_layout=LAYOUT_SLICED, dst_layout=LAYOUT_SLICED, max_tokens=1, force_path=PATH_AUTO,
                  device=-1, prefill_act_quant=0, cache_prepared_weights=False, epilogue=0, exact_operands=False,
-                 no_overlap=False, smem_limit_kb=0, prefill_route=0, independent_io=False):
+                 no_overlap=False, smem_limit_kb=0, prefill_route=0, independent_io=False, runtime_channel_bounds=False,
+                 has_batch_ids=False):
         self.desc = FcDesc(n, k, weight_bits, scale_mode, groups, scalar_scale, scalar_zero_point,
                            int(has_zero_point), int(has_bias), precision, src_layout, dst_layout,
                            max_tokens, force_path, device, prefill_act_quant, int(cache_prepared_weights), epilogue,
-                           prefill_route, int(exact_operands), int(no_overlap), smem_limit_kb, int(independent_io))
+                           prefill_route, int(runtime_channel_bounds), int(has_batch_ids), int(exact_operands),
+                           int(no_overlap), smem_limit_kb, int(independent_io))
         self._h = C.c_void_p()
         _check(lib().mld_fc_plan_create(C.byref(self.desc), C.byref(self._h)), "mld_fc_plan_create")
 

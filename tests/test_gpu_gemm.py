@@ -1,8 +1,8 @@
 """Prefill dequant-GEMM (tcgen05) through the C ABI vs the CPU oracle.
 
 Every case runs on each route: "inline" (the GEMM reads the packed weights and dequantises them in shared
-memory; what the cost rule picks below 200 tokens), "convert" (a conversion pass writes a K-major copy and
-a GEMM with both operands loaded by TMA follows; the rule's pick from 200 tokens up) and "cached" (the
+memory; what the cost rule picks up to 512 tokens), "convert" (a conversion pass writes a K-major copy and
+a GEMM with both operands loaded by TMA follows; the rule's pick above 512 tokens) and "cached" (the
 same with the copy kept between calls).  All apply the same arithmetic to every weight.
 Float route: tolerance 1e-3 of max |ref| against the restated WeightsConverter + fp32-accumulate GEMM
 (fp16 operands, exact products).  Int8-activation route: the int32 accumulators are exact, so outputs
@@ -193,8 +193,8 @@ def test_prefill_dispatch_threshold_and_cache(mld, oracle):
 
 
 def test_conversion_cost_rule_picks_the_route(mld, oracle):
-    # below 200 tokens the weights are dequantised inside the GEMM (transpose + GEMM = 2 launches); from
-    # 200 tokens up a conversion pass runs first (3 launches); both give the oracle's answer
+    # up to 512 tokens the weights are dequantised inside the GEMM (transpose + GEMM = 2 launches); above that
+    # a conversion pass runs first (3 launches); both give the oracle's answer
     rng = np.random.default_rng(33)
     K, N = 512, 256
     w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
@@ -202,9 +202,9 @@ def test_conversion_cost_rule_picks_the_route(mld, oracle):
     packed = oracle.rearrange_int8_as_uint4(q)
     sgn = oracle.scale_layout(s, True)
     plan = mld.FullyConnectedPlan(N, K, 4, scale_mode=mld.SCALE_BLOCK, groups=K // 32, precision=mld.F32F16,
-                                  max_tokens=256)
+                                  max_tokens=600)
     pd, sd = _dev(packed), _dev(sgn.view(np.float16))
-    for M, launches in ((199, 2), (200, 3)):
+    for M, launches in ((512, 2), (513, 3)):
         x16 = rng.standard_normal((M, K)).astype(np.float16)
         xd = _dev(oracle.to_sliced(x16.astype(np.float32)).astype(np.float16))
         y = torch.zeros(N * M, dtype=torch.float16, device="cuda")

@@ -288,6 +288,15 @@ def test_errors(mld):
     with pytest.raises(mld.MldError) as e:
         mld.FullyConnectedPlan(16, 16, 5)
     assert e.value.status == mld.INVALID_ARGUMENT
+    # features of the reference operator that are not built are refused by name
+    for kwargs, word in ((dict(weight_bits=2), "INT2"), (dict(weight_bits=4, runtime_channel_bounds=True), "channel bounds"),
+                         (dict(weight_bits=4, has_batch_ids=True), "batch ids")):
+        with pytest.raises(mld.MldError) as e:
+            mld.FullyConnectedPlan(16, 16, **kwargs)
+        assert e.value.status == mld.UNIMPLEMENTED and word in str(e.value)
+    with pytest.raises(mld.MldError) as e:
+        mld.quantize_weights(torch.zeros((4, 32), device="cuda"), 4, 32, optimize_scale=True)
+    assert e.value.status == mld.UNIMPLEMENTED and "optimize_scale" in str(e.value)
     plan = mld.FullyConnectedPlan(16, 16, 4, max_tokens=2)
     x = torch.zeros(64, dtype=torch.float16, device="cuda")
     with pytest.raises(mld.MldError):

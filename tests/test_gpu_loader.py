@@ -138,3 +138,24 @@ def test_projection_from_loaded_files(mld, oracle, loader_ref):
     ref = oracle.fc_plain_reference(q, s16, x.astype(np.float32))
     got = y.float().cpu().numpy()[None]
     assert np.max(np.abs(got - ref)) <= 1e-3 * np.max(np.abs(ref))
+
+
+def test_tiny_files_of_the_reference_loader_test(mld, oracle, loader_ref, tmp_path):
+    """The int8 (5 x 2) and int4 (8 x 1, the word 0x12345678) files of
+    samples/llm/llm_file_tensor_loader_test.cc:96-112: both load, and the packed bytes are the CPU packer's."""
+    d = str(tmp_path) + os.sep
+    np.arange(1, 11, dtype=np.int8).tofile(d + "model.layers.9.mlp.gate_proj.weight")
+    np.array([0x12345678], np.int32).tofile(d + "model.layers.9.mlp.gate_proj.weight_int4")
+    ld = mld.FileTensorLoader(d)
+    packed, sums = ld.load_weights("model.layers.9.mlp.gate_proj.weight", 8, 5, 2)
+    q = np.arange(1, 11, dtype=np.int8).reshape(5, 2)
+    assert np.array_equal(packed.cpu().numpy(), oracle.rearrange_int8_as_uint8(q))
+    assert np.array_equal(sums.cpu().numpy(), q.astype(np.int32).sum(1))
+    packed4, sums4 = ld.load_weights("model.layers.9.mlp.gate_proj.weight_int4", 4, 8, 1)
+    raw = np.fromfile(d + "model.layers.9.mlp.gate_proj.weight_int4", dtype=np.uint8)
+    want, want_sums = oracle.rearrange_uint4_packed(raw, (8, 1, 1, 1))
+    assert np.array_equal(packed4.cpu().numpy(), want) and np.array_equal(sums4.cpu().numpy(), want_sums)
+    v = loader_ref.int4_file_as_int8(d + "model.layers.9.mlp.gate_proj.weight_int4", 8)
+    assert list(v) == [-8, 7, 6, 5, 4, 3, 2, 1]          # nibbles of 0x12345678, low first, two's complement
+    assert np.array_equal(want_sums, v.astype(np.int32))
+    ld.close()

@@ -118,3 +118,32 @@ def test_group_header_scale_files(mld, loader_ref, tmp_path):
         assert want == 32
         assert loader_ref.is_grouped(d + name + "_quantized_scale", o * (i // 32))
         ld.close()
+
+
+def test_group_size_answers_of_the_reference_loader_test(mld, loader_ref, tmp_path):
+    """The two cases of samples/llm/llm_file_tensor_loader_test.cc:196-264, with their caching: the answer
+    survives the removal of the scale file."""
+    d = str(tmp_path) + os.sep
+    ld = mld.FileTensorLoader(d)
+    # ten float32 values for OHWI(5, 1, 1, 8): two scales per output -> groups of 4 inputs
+    f = d + "model.layers.0.mlp.gate_proj.weight_quantized_scale"
+    np.ones(10, np.float32).tofile(f)
+    assert loader_ref.group_size(d, "model.layers.0.mlp.gate_proj.weight", 5, 8) == 4
+    assert ld.group_size("model.layers.0.mlp.gate_proj.weight", 5, 8) == 4
+    os.remove(f)
+    assert ld.group_size("model.layers.0.mlp.gate_proj.weight", 5, 8) == 4
+    # header 16, then eight int8 values, for OHWI(4, 1, 1, 32): 12 bytes = 3 float32 values, not a multiple of
+    # the 4 outputs, so the header decides
+    f = d + "model.layers.1.mlp.gate_proj.weight_quantized_scale"
+    with open(f, "wb") as fh:
+        np.int32(16).tofile(fh)
+        np.ones(8, np.int8).tofile(fh)
+    assert loader_ref.group_size(d, "model.layers.1.mlp.gate_proj.weight", 4, 32) == 16
+    assert ld.group_size("model.layers.1.mlp.gate_proj.weight", 4, 32) == 16
+    os.remove(f)
+    assert ld.group_size("model.layers.1.mlp.gate_proj.weight", 4, 32) == 16
+    # and the float read of the same test (:80-95, 148-154)
+    np.arange(1, 11, dtype=np.float32).tofile(d + "model.layers.9.mlp.gate_proj.weight_quantized_scale")
+    got = ld.load_float32("model.layers.9.mlp.gate_proj.weight_quantized_scale", 10).numpy()
+    assert np.array_equal(got, np.arange(1, 11, dtype=np.float32))
+    ld.close()
