@@ -2,8 +2,8 @@
 // kOSpatialIOGroupI4O4 buffer layout, scale layout.  All integer/byte work is
 // bit-exact with the CPU rearrangers of ml-drift
 // (common/task/weights_conversion.cc); these kernels are HBM-bound, so they
-// read rows coalesced, transpose through shared memory and write whole 4x4
-// blocks with vector stores.
+// read rows coalesced, transpose in registers (or, for ragged shapes, through
+// shared memory) and write whole 4x4 blocks with vector stores.
 #include "common.cuh"
 
 namespace mld {
@@ -162,6 +162,91 @@ __global__ void __launch_bounds__(256) pack_from_u4_kernel(PackArgs a) {
   store_tile<4>(tile, a, hw, s0, d0);
 }
 
+// The common case without shared memory: int8 source, one output group (the FullyConnected choice), input
+// channels a multiple of 16, 16-byte aligned rows.  A warp takes 16 output rows x 128 input channels.  Per
+// step it reads four rows, eight lanes to a row and 16 bytes to a lane; the four lanes that hold the same 16
+// input channels of the four rows exchange words so that each ends up with the four rows of ONE group of four
+// input channels, i.e. one 4x4 block, which it transposes byte-wise in registers.  After four steps a lane
+// holds four blocks that are neighbours in the destination (same input slice, four consecutive output
+// slices) and writes them as one 64-byte (32-byte for 4 bits) run.
+template <int BITS>
+__global__ void __launch_bounds__(256) pack_rows_kernel(PackArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hw = blockIdx.z;
+  const int r = lane >> 3, c = lane & 7;                 // row of the step's four, 16-byte chunk of the 128 inputs
+  const int i0 = blockIdx.x * 128 + c * 16;              // first input channel of this lane's chunk
+  const int o0 = (blockIdx.y * 8 + warp) * 16;           // first of the warp's 16 output rows
+  if (o0 >= a.dst_slices * 4) return;
+  const int8_t* src = reinterpret_cast<const int8_t*>(a.src);
+  const uint32_t padw = (a.pad & 0xFFu) * 0x01010101u;
+  uint32_t blk[4][4];                                     // [step = output slice][word k = input channel of the block]
+#pragma unroll
+  for (int st = 0; st < 4; ++st) {
+    const int o = o0 + st * 4 + r;
+    uint4 v = make_uint4(padw, padw, padw, padw);
+    int32_t rowsum = 0;
+    if (o < a.O && i0 < a.I) {
+      v = *reinterpret_cast<const uint4*>(src + ((int64_t)o * a.HW + hw) * a.I + i0);
+      rowsum = __dp4a(static_cast<int>(v.x), 0x01010101, 0);
+      rowsum = __dp4a(static_cast<int>(v.y), 0x01010101, rowsum);
+      rowsum = __dp4a(static_cast<int>(v.z), 0x01010101, rowsum);
+      rowsum = __dp4a(static_cast<int>(v.w), 0x01010101, rowsum);
+      // q + shift, byte-wise: +128 is a flip of the top bit; +8 on values in [-8, 7] likewise, kept to 4 bits
+      const uint32_t flip = BITS == 8 ? 0x80808080u : 0x08080808u, keep = BITS == 8 ? 0xFFFFFFFFu : 0x0F0F0F0Fu;
+      v.x = (v.x ^ flip) & keep;
+      v.y = (v.y ^ flip) & keep;
+      v.z = (v.z ^ flip) & keep;
+      v.w = (v.w ^ flip) & keep;
+    }
+    if (a.sum_i != nullptr) {
+      rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 1);
+      rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 2);
+      rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 4);
+      if (c == 0 && o < a.O && o < a.sum_len && rowsum != 0) atomicAdd(a.sum_i + o, rowsum);
+    }
+    // lane (r, c) collects word r of the rows 0..3 held by lanes (0..3, c): row n's word comes from lane 8n + c
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t rows[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int offer = (r + j) & 3;                       // as a source: serve destination row (r + j) & 3
+      const uint32_t mine = offer == 0 ? w[0] : offer == 1 ? w[1] : offer == 2 ? w[2] : w[3];
+      const int from_row = (r - j) & 3;                    // as a destination: read source row (r - j) & 3
+      const uint32_t got = __shfl_sync(0xffffffffu, mine, from_row * 8 + c);
+      if (from_row == 0) rows[0] = got;
+      else if (from_row == 1) rows[1] = got;
+      else if (from_row == 2) rows[2] = got;
+      else rows[3] = got;
+    }
+    // rows[n] = bytes (k = 0..3) of output n; the block wants word k = bytes (n = 0..3)
+    const uint32_t t0 = __byte_perm(rows[0], rows[1], 0x5140), t1 = __byte_perm(rows[2], rows[3], 0x5140);
+    const uint32_t t2 = __byte_perm(rows[0], rows[1], 0x7362), t3 = __byte_perm(rows[2], rows[3], 0x7362);
+    blk[st][0] = __byte_perm(t0, t1, 0x5410);
+    blk[st][1] = __byte_perm(t0, t1, 0x7632);
+    blk[st][2] = __byte_perm(t2, t3, 0x5410);
+    blk[st][3] = __byte_perm(t2, t3, 0x7632);
+  }
+  const int s = (i0 >> 2) + r;                             // this lane's input slice
+  if (s >= a.src_slices) return;
+  const int ds0 = o0 >> 2;
+  const int64_t block_index = ((int64_t)hw * a.src_slices + s) * a.group + ds0;
+  if (BITS == 8) {
+    uint4* dst = reinterpret_cast<uint4*>(a.dst + block_index * 16);
+#pragma unroll
+    for (int st = 0; st < 4; ++st)
+      if (ds0 + st < a.total_ds) dst[st] = make_uint4(blk[st][0], blk[st][1], blk[st][2], blk[st][3]);
+  } else {
+    uint2* dst = reinterpret_cast<uint2*>(a.dst + block_index * 8);
+#pragma unroll
+    for (int st = 0; st < 4; ++st) {
+      // bytes v0 v1 v2 v3 of a word (each < 16) -> v0 | v1 << 4, v2 | v3 << 4
+      const uint32_t y0 = blk[st][0] | (blk[st][0] >> 4), y1 = blk[st][1] | (blk[st][1] >> 4);
+      const uint32_t y2 = blk[st][2] | (blk[st][2] >> 4), y3 = blk[st][3] | (blk[st][3] >> 4);
+      if (ds0 + st < a.total_ds) dst[st] = make_uint2(__byte_perm(y0, y1, 0x6420), __byte_perm(y2, y3, 0x6420));
+    }
+  }
+}
+
 __global__ void sum_i_kernel(const int8_t* src, int O, int64_t hwi, int32_t* sum_i) {
   const int o = blockIdx.x;
   if (o >= O) return;
@@ -217,6 +302,74 @@ __global__ void __launch_bounds__(128) quantize_kernel(const float* w, int O, in
   }
 }
 
+// The same arithmetic with 32-byte loads: the tensor is a flat sequence of blocks of 8 * LPB values (rows are
+// whole numbers of blocks), LPB lanes to a block, eight consecutive values to a lane.
+template <int LPB>
+__global__ void __launch_bounds__(256) quantize_blocks_kernel(const float* __restrict__ w, int64_t chunks, float qmax,
+                                                              float qlo, float qhi, int8_t* __restrict__ q,
+                                                              float* __restrict__ scale) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t rounds = (chunks + stride - 1) / stride;  // whole warps stay together for the shuffles
+  int64_t ch = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (int64_t it = 0; it < rounds; ++it, ch += stride) {
+    const bool has = ch < chunks;
+    float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f), b = a;
+    if (has) {
+      a = *reinterpret_cast<const float4*>(w + ch * 8);
+      b = *reinterpret_cast<const float4*>(w + ch * 8 + 4);
+    }
+    float bound = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
+                        fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
+#pragma unroll
+    for (int off = 1; off < LPB; off <<= 1) bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, off));
+    float sc = __fdiv_rn(bound, qmax);
+    if (sc == 0.0f) sc = 1.0f;
+    if (has) {
+      auto one = [&](float x) -> uint32_t {
+        const float v = fminf(fmaxf(rintf(__fdiv_rn(x, sc)), qlo), qhi);
+        return static_cast<uint32_t>(static_cast<int>(v)) & 0xFFu;
+      };
+      uint2 out;
+      out.x = one(a.x) | (one(a.y) << 8) | (one(a.z) << 16) | (one(a.w) << 24);
+      out.y = one(b.x) | (one(b.y) << 8) | (one(b.z) << 16) | (one(b.w) << 24);
+      *reinterpret_cast<uint2*>(q + ch * 8) = out;
+      if ((ch & (LPB - 1)) == 0) scale[ch / LPB] = sc;
+    }
+  }
+}
+
+// One CTA per row for long blocks (per-channel quantisation): the row is read twice, the second time from
+// L2 / L1, 16 bytes per lane.
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restrict__ w, int I, float qmax, float qlo,
+                                                            float qhi, int8_t* __restrict__ q, float* __restrict__ scale) {
+  __shared__ float red[8];
+  const float* row = w + (int64_t)blockIdx.x * I;
+  float bound = 0.0f;
+  for (int i = threadIdx.x * 4; i < I; i += 1024) {
+    const float4 v = *reinterpret_cast<const float4*>(row + i);
+    bound = fmaxf(bound, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, off));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = bound;
+  __syncthreads();
+  bound = red[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) bound = fmaxf(bound, red[k]);
+  float sc = __fdiv_rn(bound, qmax);
+  if (sc == 0.0f) sc = 1.0f;
+  int8_t* qr = q + (int64_t)blockIdx.x * I;
+  for (int i = threadIdx.x * 4; i < I; i += 1024) {
+    const float4 v = *reinterpret_cast<const float4*>(row + i);
+    auto one = [&](float x) -> uint32_t {
+      const float t = fminf(fmaxf(rintf(__fdiv_rn(x, sc)), qlo), qhi);
+      return static_cast<uint32_t>(static_cast<int>(t)) & 0xFFu;
+    };
+    *reinterpret_cast<uint32_t*>(qr + i) = one(v.x) | (one(v.y) << 8) | (one(v.z) << 16) | (one(v.w) << 24);
+  }
+  if (threadIdx.x == 0) scale[blockIdx.x] = sc;
+}
+
 }  // namespace
 
 int pack_weights_impl(const mld_pack_desc* d, const void* src, void* dst, int32_t* sum_i, int32_t sum_len,
@@ -242,7 +395,15 @@ int pack_weights_impl(const mld_pack_desc* d, const void* src, void* dst, int32_
   }
   dim3 grid(div_up(a.src_slices, kTileSlices), div_up(a.total_ds, kTileSlices), a.HW);
   if (grid.x == 0 || grid.y == 0 || grid.z == 0) return MLD_OK;
-  if (d->source == MLD_SRC_INT8) {
+  const bool rows_fit = d->source == MLD_SRC_INT8 && a.I % 16 == 0 && a.group == a.dst_slices &&
+                        (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+  if (rows_fit) {
+    dim3 rgrid(div_up(a.I, 128), div_up(a.dst_slices * 4, 128), a.HW);
+    if (d->bits == 8)
+      pack_rows_kernel<8><<<rgrid, 256, 0, stream>>>(a);
+    else
+      pack_rows_kernel<4><<<rgrid, 256, 0, stream>>>(a);
+  } else if (d->source == MLD_SRC_INT8) {
     if (d->bits == 8)
       pack_from_int8_kernel<8><<<grid, 256, 0, stream>>>(a);
     else
@@ -278,8 +439,27 @@ int quantize_weights_impl(const float* w, int32_t o, int32_t i, int32_t bits, in
   const float qmax = bits == 8 ? 127.0f : 7.0f;
   const float qlo = bits == 8 ? -128.0f : -8.0f;
   const float qhi = bits == 8 ? 127.0f : 7.0f;
-  dim3 grid(o, G >= 64 ? 4 : 1);
-  quantize_kernel<<<grid, 128, 0, stream>>>(w, o, i, block, G, qmax, qlo, qhi, q, scale);
+  const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0;
+  const int lpb = block / 8;
+  if (aligned && block % 8 == 0 && lpb >= 1 && lpb <= 32 && (lpb & (lpb - 1)) == 0) {
+    const int64_t chunks = (int64_t)o * i / 8;
+    int64_t blocks = (chunks + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    const unsigned gb = static_cast<unsigned>(blocks);
+    switch (lpb) {
+      case 1: quantize_blocks_kernel<1><<<gb, 256, 0, stream>>>(w, chunks, qmax, qlo, qhi, q, scale); break;
+      case 2: quantize_blocks_kernel<2><<<gb, 256, 0, stream>>>(w, chunks, qmax, qlo, qhi, q, scale); break;
+      case 4: quantize_blocks_kernel<4><<<gb, 256, 0, stream>>>(w, chunks, qmax, qlo, qhi, q, scale); break;
+      case 8: quantize_blocks_kernel<8><<<gb, 256, 0, stream>>>(w, chunks, qmax, qlo, qhi, q, scale); break;
+      case 16: quantize_blocks_kernel<16><<<gb, 256, 0, stream>>>(w, chunks, qmax, qlo, qhi, q, scale); break;
+      default: quantize_blocks_kernel<32><<<gb, 256, 0, stream>>>(w, chunks, qmax, qlo, qhi, q, scale); break;
+    }
+  } else if (aligned && G == 1 && i % 4 == 0) {
+    quantize_rows_kernel<<<o, 256, 0, stream>>>(w, i, qmax, qlo, qhi, q, scale);
+  } else {
+    dim3 grid(o, G >= 64 ? 4 : 1);
+    quantize_kernel<<<grid, 128, 0, stream>>>(w, o, i, block, G, qmax, qlo, qhi, q, scale);
+  }
   MLD_LAUNCH_CHECK();
   return MLD_OK;
 }

@@ -19,7 +19,9 @@ def _dev(a):
 
 
 SHAPES = [(4, 1, 1, 4), (3, 1, 1, 4), (4, 1, 1, 2), (533, 1, 1, 171), (534, 1, 1, 171), (7, 1, 1, 6),
-          (256, 1, 1, 512), (16, 2, 1, 8), (130, 3, 1, 36), (2048, 1, 1, 2048)]
+          (256, 1, 1, 512), (16, 2, 1, 8), (130, 3, 1, 36), (2048, 1, 1, 2048),
+          # input channels a multiple of 16: the register-transpose kernel; ragged outputs, several tiles, H > 1
+          (48, 1, 1, 64), (37, 1, 1, 16), (130, 1, 1, 400), (18, 2, 1, 144), (300, 1, 1, 1024)]
 
 
 @pytest.mark.parametrize("shape", SHAPES)
@@ -87,7 +89,7 @@ def test_pack_scales(mld, oracle, O, G, f16):
         assert np.array_equal(got, ref)
 
 
-@pytest.mark.parametrize("O,I", [(8, 64), (37, 96), (256, 2048)])
+@pytest.mark.parametrize("O,I", [(8, 64), (37, 96), (256, 2048), (5, 36), (9, 4096), (3, 10), (64, 1000)])
 def test_quantiser_bit_exact(mld, oracle, O, I):
     rng = np.random.default_rng(O * I)
     w = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
@@ -95,7 +97,9 @@ def test_quantiser_bit_exact(mld, oracle, O, I):
     q, s = mld.quantize_weights(_dev(w), 8)
     qr, sr = oracle.quantize_int8_sym(w)
     assert np.array_equal(q.cpu().numpy(), qr) and np.array_equal(s.cpu().numpy().reshape(-1), sr)
-    for block in (32, 0):
+    for block in (32, 0, 8, 64, 128, 12):
+        if block and I % block:
+            continue
         q, s = mld.quantize_weights(_dev(w), 4, block)
         qr, sr = oracle.quantize_int4_sym(w, block)
         assert np.array_equal(q.cpu().numpy(), qr)
