@@ -300,6 +300,18 @@ MLD_API int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out);
 MLD_API int mld_fc_plan_destroy(mld_fc_plan* plan);
 /* Bytes of device workspace the plan holds. */
 MLD_API size_t mld_fc_plan_workspace_bytes(const mld_fc_plan* plan);
+/* Which kernels served the plan's most recent mld_fc_run (mld_fc_route;
+ * MLD_ROUTE_NONE before the first run): what the builder's node names tell a
+ * reader of the reference's graph (fc1x1_*, fc_prefill_*). */
+enum mld_fc_route {
+  MLD_ROUTE_NONE = 0,
+  MLD_ROUTE_DECODE_STREAMING = 1,   /* the decode GEMV over TMA-staged weights */
+  MLD_ROUTE_DECODE_GENERAL = 2,     /* the general decode kernel */
+  MLD_ROUTE_PREFILL_INLINE = 3,     /* GEMM that dequantises inside */
+  MLD_ROUTE_PREFILL_CONVERTED = 4,  /* conversion pass, then GEMM */
+  MLD_ROUTE_PREFILL_CACHED = 5      /* GEMM on the copy kept from an earlier call */
+};
+MLD_API int mld_fc_plan_last_route(const mld_fc_plan* plan);
 /* Synchronous read of the plan's device-side status: *code = 0, or the code of
  * a bounded device-side wait that gave up during an earlier mld_fc_run (then
  * cleared); the function then returns MLD_TIMEOUT.  The kernels never spin

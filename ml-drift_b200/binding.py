@@ -16,6 +16,8 @@ SCALE_SCALAR, SCALE_PER_CHANNEL, SCALE_BLOCK = 0, 1, 2
 LAYOUT_SLICED, LAYOUT_ROW_MAJOR = 0, 1
 SRC_INT8, SRC_UINT4_PACKED = 0, 1
 PATH_AUTO, PATH_GEMV, PATH_GEMM = 0, 1, 2
+(ROUTE_NONE, ROUTE_DECODE_STREAMING, ROUTE_DECODE_GENERAL, ROUTE_PREFILL_INLINE, ROUTE_PREFILL_CONVERTED,
+ ROUTE_PREFILL_CACHED) = range(6)
 DECODER_AUTO, DECODER_OP_CHAIN, DECODER_SINGLE_KERNEL = 0, 1, 2
 HANDOVER_TAGGED, HANDOVER_BARRIERS = 0, 1
 EPILOGUE_NONE, EPILOGUE_SWIGLU_PAIRS = 0, 1
@@ -184,6 +186,10 @@ class FullyConnectedPlan:
         """sum_i: device int32 tensor [n] (kept alive here)."""
         self._w_sum = sum_i
         _check(lib().mld_fc_plan_set_weights_sum(self._h, _ptr(sum_i)), "mld_fc_plan_set_weights_sum")
+
+    def last_route(self) -> int:
+        """ROUTE_* of the most recent run."""
+        return int(lib().mld_fc_plan_last_route(self._h))
 
     def workspace_bytes(self) -> int:
         return int(lib().mld_fc_plan_workspace_bytes(self._h))

@@ -106,6 +106,7 @@ struct mld_fc_plan {
   void* w_kmajor;        // dequantised fp16 / re-biased s8 weights, [N4][kp]
   void* x_kmajor;        // activations, [max_tokens][kp]
   PairSplit split;       // where SM pairs that share a tile of the prefill GEMM combine their partial sums
+  int last_route;        // mld_fc_route of the most recent run
   float* a_params;       // per-token {inv_scale, offset, sum}
   const void* prepared_w;
   const void* prepared_s;
@@ -275,6 +276,7 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   p->ws_bytes = 0;
   p->w_kmajor = p->x_kmajor = nullptr;
   p->split = PairSplit{nullptr, nullptr, 0};
+  p->last_route = MLD_ROUTE_NONE;
   p->a_params = nullptr;
   p->prepared_w = p->prepared_s = nullptr;
   p->w_sum = nullptr;
@@ -358,6 +360,7 @@ int mld_fc_plan_destroy(mld_fc_plan* plan) {
 }
 
 size_t mld_fc_plan_workspace_bytes(const mld_fc_plan* plan) { return plan ? plan->ws_bytes : 0; }
+int mld_fc_plan_last_route(const mld_fc_plan* plan) { return plan ? plan->last_route : MLD_ROUTE_NONE; }
 
 int mld_fc_plan_device_status(mld_fc_plan* plan, int32_t* code) {
   MLD_REQUIRE(plan != nullptr && code != nullptr, "null argument");
@@ -518,6 +521,7 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
   const bool convert = d.cache_prepared_weights != 0 || !p->pair_ok || d.prefill_route == MLD_PREFILL_ROUTE_CONVERT ||
                        (d.prefill_route == MLD_PREFILL_ROUTE_AUTO && convert_pays(tokens));
   if (!convert) {
+    p->last_route = MLD_ROUTE_PREFILL_INLINE;
     const int mode = i8 ? 2 : (d.weight_bits == 4 ? 0 : 1);
     const PairGeometry pg = pair_geometry(tokens, d.n, d.k, mode, p->sms, true);
     if (++p->split.epoch == 0) p->split.epoch = 1;
@@ -535,15 +539,22 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
 
   const GemmGeometry g = gemm_geometry(tokens, d.n, d.k, i8, p->sms);
   const bool reuse = d.cache_prepared_weights && p->prepared_w == weights && p->prepared_s == scale;
+  bool x_done = false;
+  p->last_route = reuse ? MLD_ROUTE_PREFILL_CACHED : MLD_ROUTE_PREFILL_CONVERTED;
   if (!reuse) {
+    // float route, sliced activations: their transposition rides along in the conversion launch
+    const bool ride = !i8 && d.src_layout == MLD_LAYOUT_SLICED;
     rc = launch_dequant_weights(d.weight_bits, i8, weights, scale, d.scale_mode,
                                 d.scale_mode == MLD_SCALE_BLOCK ? d.groups : 1, p->group_slices, d.scalar_scale, d.n,
-                                d.k, g.kp, p->w_kmajor, stream);
+                                d.k, g.kp, p->w_kmajor, stream, ride ? src : nullptr, tokens, p->x_kmajor);
     if (rc != MLD_OK) return rc;
     p->prepared_w = weights;
     p->prepared_s = scale;
+    x_done = ride;
   }
-  if (i8)
+  if (x_done) {
+    rc = MLD_OK;
+  } else if (i8)
     rc = launch_quantize_act(src, d.src_layout, tokens, d.k, g.kp, d.prefill_act_quant == 1, p->x_kmajor, p->a_params,
                              stream);
   else
@@ -615,6 +626,7 @@ int mld::fc_run_internal(mld_fc_plan* plan, const void* src, const void* weights
       set_last_error_text("quantised-activation prefill needs fp16 tensors and no zero points");
       return MLD_UNIMPLEMENTED;
     }
+    plan->last_route = MLD_ROUTE_DECODE_GENERAL;
     return run_generic(plan, src, weights, scale, zp, b, dst, tokens, stream);
   }
   if (d.epilogue != MLD_EPILOGUE_NONE && !(path == 1 && plan->stream_ok && tokens <= 16)) {
@@ -624,12 +636,15 @@ int mld::fc_run_internal(mld_fc_plan* plan, const void* src, const void* weights
   const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
                        (scale == nullptr || (reinterpret_cast<uintptr_t>(scale) & 15) == 0);
   const bool layout_ok = d.src_layout == MLD_LAYOUT_SLICED || tokens == 1;
-  if (plan->stream_ok && tokens <= 16 && aligned && layout_ok)
+  if (plan->stream_ok && tokens <= 16 && aligned && layout_ok) {
+    plan->last_route = MLD_ROUTE_DECODE_STREAMING;
     return run_stream(plan, src, weights, scale, b, dst, tokens, stream, scatter, wait);
+  }
   if (d.epilogue != MLD_EPILOGUE_NONE) {
     set_last_error_text("the fused SiLU*mul write needs 16-byte aligned fp16 tensors in the sliced layout");
     return MLD_UNIMPLEMENTED;
   }
+  plan->last_route = MLD_ROUTE_DECODE_GENERAL;
   return run_generic(plan, src, weights, scale, zp, b, dst, tokens, stream);
 }
 

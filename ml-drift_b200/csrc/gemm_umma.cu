@@ -314,13 +314,31 @@ __device__ __forceinline__ uint32_t dq_pair8(uint32_t bytes2, __half2 s2, __half
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+__device__ __forceinline__ void transpose_sliced_tile(const __half* __restrict__ x, int M, int K, int Kp,
+                                                      __half* __restrict__ out, int tile_s, int tile_m);
+
+// The activations of the same call can ride along: rows of blocks past `weight_rows` of the grid transpose
+// 32 x 32 tiles of the sliced activation tensor instead (x_src null: none), which saves a launch and hides the
+// small transposition behind the conversion.
+struct RideAlong {
+  const __half* x_src;
+  __half* x_out;
+  int M, K;
+  int weight_rows;  // gridDim.y of the conversion proper
+};
+
 template <int BITS, bool TO_S8>
 __global__ void __launch_bounds__(256) dequant_weights_kernel(const uint8_t* __restrict__ packed,
                                                              const __half* __restrict__ scale, int scale_mode, int G,
                                                              int group_slices, float scalar_scale, int dst_slices,
-                                                             int src_slices, int Kp, void* __restrict__ out) {
+                                                             int src_slices, int Kp, void* __restrict__ out,
+                                                             RideAlong ride) {
   pdl_launch_dependents();
   pdl_wait();
+  if (ride.x_src != nullptr && static_cast<int>(blockIdx.y) >= ride.weight_rows) {
+    transpose_sliced_tile(ride.x_src, ride.M, ride.K, Kp, ride.x_out, blockIdx.x, blockIdx.y - ride.weight_rows);
+    return;
+  }
   constexpr int T = 32;
   constexpr int BLK = BITS == 4 ? 8 : 16;
   constexpr int PITCH = T * BLK + 8;  // +8 bytes: lanes that walk down a column hit distinct banks
@@ -415,37 +433,43 @@ __global__ void __launch_bounds__(256) dequant_weights_kernel(const uint8_t* __r
 // Activations: sliced [K/4][M][4] (or row-major [M][K]) fp16 -> row-major [M][Kp] fp16.
 // Sliced source: a 32-token x 32-slice tile goes through shared memory, read with lanes along the tokens
 // (8 bytes each, contiguous in the source) and written with lanes along K (contiguous in the destination).
+__device__ __forceinline__ void transpose_sliced_tile(const __half* __restrict__ x, int M, int K, int Kp,
+                                                      __half* __restrict__ out, int tile_s, int tile_m) {
+  __shared__ uint2 tile[32][33];
+  const int S = (K + 3) / 4, Sp = Kp / 4;
+  const int m0 = tile_m * 32, s0 = tile_s * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 8 rows of the tile per pass
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int sl = s0 + ty + 8 * r, m = m0 + tx;
+    uint2 v = make_uint2(0u, 0u);
+    if (sl < S && m < M) v = *reinterpret_cast<const uint2*>(x + ((size_t)sl * M + m) * 4);
+    tile[ty + 8 * r][tx] = v;  // [slice][token]
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int m = m0 + ty + 8 * r, sl = s0 + tx;
+    if (m < M && sl < Sp) {
+      uint2 v = tile[tx][ty + 8 * r];
+      // a ragged K: the channels past K inside the last slice must read as zero
+      if (sl * 4 + 3 >= K) {
+        __half* h = reinterpret_cast<__half*>(&v);
+        for (int i = 0; i < 4; ++i)
+          if (sl * 4 + i >= K) h[i] = __float2half(0.0f);
+      }
+      *reinterpret_cast<uint2*>(out + (size_t)m * Kp + sl * 4) = v;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) transpose_x_kernel(const __half* __restrict__ x, int layout, int M, int K, int Kp,
                                                           __half* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
-  const int S = (K + 3) / 4, Sp = Kp / 4;
+  const int Sp = Kp / 4;
   if (layout == MLD_LAYOUT_SLICED) {
-    __shared__ uint2 tile[32][33];
-    const int m0 = blockIdx.y * 32, s0 = blockIdx.x * 32;
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 8 rows of the tile per pass
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int sl = s0 + ty + 8 * r, m = m0 + tx;
-      uint2 v = make_uint2(0u, 0u);
-      if (sl < S && m < M) v = *reinterpret_cast<const uint2*>(x + ((size_t)sl * M + m) * 4);
-      tile[ty + 8 * r][tx] = v;  // [slice][token]
-    }
-    __syncthreads();
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int m = m0 + ty + 8 * r, sl = s0 + tx;
-      if (m < M && sl < Sp) {
-        uint2 v = tile[tx][ty + 8 * r];
-        // a ragged K: the channels past K inside the last slice must read as zero
-        if (sl * 4 + 3 >= K) {
-          __half* h = reinterpret_cast<__half*>(&v);
-          for (int i = 0; i < 4; ++i)
-            if (sl * 4 + i >= K) h[i] = __float2half(0.0f);
-        }
-        *reinterpret_cast<uint2*>(out + (size_t)m * Kp + sl * 4) = v;
-      }
-    }
+    transpose_sliced_tile(x, M, K, Kp, out, blockIdx.x, blockIdx.y);
     return;
   }
   const int ks = blockIdx.x * 32 * 8 + threadIdx.x;  // one token row per blockIdx.y, 256 slices per block
@@ -715,14 +739,22 @@ GemmGeometry gemm_geometry(int M, int N, int K, bool i8, int sms) {
 }
 
 int launch_dequant_weights(int bits, bool to_s8, const void* packed, const void* scale, int scale_mode, int G,
-                           int group_slices, float scalar_scale, int N, int K, int Kp, void* out, cudaStream_t stream) {
+                           int group_slices, float scalar_scale, int N, int K, int Kp, void* out, cudaStream_t stream,
+                           const void* x_sliced, int M, void* x_kmajor) {
   const int dst_slices = div_up(N, 4), src_slices = div_up(K, 4);
   dim3 grid(div_up(div_up(Kp, 4), 32), div_up(dst_slices, 32));
+  RideAlong ride;
+  ride.x_src = static_cast<const __half*>(x_sliced);
+  ride.x_out = static_cast<__half*>(x_kmajor);
+  ride.M = M;
+  ride.K = K;
+  ride.weight_rows = static_cast<int>(grid.y);
+  if (x_sliced != nullptr) grid.y += div_up(M, 32);
   const uint8_t* p = static_cast<const uint8_t*>(packed);
   const __half* s = static_cast<const __half*>(scale);
 #define MLD_DQ(B, S8)                                                                                              \
   MLD_CUDA_CHECK(launch_overlapped(dequant_weights_kernel<B, S8>, grid, dim3(256), 0, stream, p, s, scale_mode, G, \
-                                   group_slices, scalar_scale, dst_slices, src_slices, Kp, out))
+                                   group_slices, scalar_scale, dst_slices, src_slices, Kp, out, ride))
   if (bits == 4) {
     if (to_s8) MLD_DQ(4, true); else MLD_DQ(4, false);
   } else {

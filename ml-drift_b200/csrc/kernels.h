@@ -162,8 +162,10 @@ struct GemmGeometry {
   int grid;
 };
 GemmGeometry gemm_geometry(int M, int N, int K, bool i8, int sms);
+// x_sliced != null: the same launch also brings M tokens of sliced fp16 activations into K-major order (x_kmajor)
 int launch_dequant_weights(int bits, bool to_s8, const void* packed, const void* scale, int scale_mode, int G,
-                           int group_slices, float scalar_scale, int N, int K, int Kp, void* out, cudaStream_t stream);
+                           int group_slices, float scalar_scale, int N, int K, int Kp, void* out, cudaStream_t stream,
+                           const void* x_sliced = nullptr, int M = 0, void* x_kmajor = nullptr);
 int launch_transpose_x(const void* x, int layout, int M, int K, int Kp, void* out, cudaStream_t stream);
 // Per-token workspace of launch_quantize_act: {inv_scale, offset, sum} followed by the partial extremes of
 // kStatSplits ranges of the input channels.

@@ -185,7 +185,7 @@ def test_prefill_dispatch_threshold_and_cache(mld, oracle):
     plan.run(xd, pd, sd, y2, M)
     c2 = mld.kernel_launch_count()
     torch.cuda.synchronize()
-    assert c1 - c0 == 3 and c2 - c1 == 2        # dequant + transpose + gemm, then transpose + gemm
+    assert c1 - c0 == 2 and c2 - c1 == 2        # conversion (+ transpose in the same launch) + gemm, then transpose + gemm
     assert torch.equal(y1, y2)
     ref = oracle.f16_bits_to_f32(oracle.prefill_gemm_int4(x16.view(np.uint16), packed, sgn, N))
     got = oracle.from_sliced(y1.float().cpu().numpy().reshape(N // 4, M, 4), N)
@@ -193,8 +193,8 @@ def test_prefill_dispatch_threshold_and_cache(mld, oracle):
 
 
 def test_conversion_cost_rule_picks_the_route(mld, oracle):
-    # up to 512 tokens the weights are dequantised inside the GEMM (transpose + GEMM = 2 launches); above that
-    # a conversion pass runs first (3 launches); both give the oracle's answer
+    # up to 512 tokens the weights are dequantised inside the GEMM; above that a conversion pass runs first (the
+    # activations' transposition rides along in its launch); both give the oracle's answer
     rng = np.random.default_rng(33)
     K, N = 512, 256
     w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
@@ -204,13 +204,13 @@ def test_conversion_cost_rule_picks_the_route(mld, oracle):
     plan = mld.FullyConnectedPlan(N, K, 4, scale_mode=mld.SCALE_BLOCK, groups=K // 32, precision=mld.F32F16,
                                   max_tokens=600)
     pd, sd = _dev(packed), _dev(sgn.view(np.float16))
-    for M, launches in ((512, 2), (513, 3)):
+    for M, route in ((512, mld.ROUTE_PREFILL_INLINE), (513, mld.ROUTE_PREFILL_CONVERTED)):
         x16 = rng.standard_normal((M, K)).astype(np.float16)
         xd = _dev(oracle.to_sliced(x16.astype(np.float32)).astype(np.float16))
         y = torch.zeros(N * M, dtype=torch.float16, device="cuda")
         c0 = mld.kernel_launch_count()
         plan.run(xd, pd, sd, y, M)
-        assert mld.kernel_launch_count() - c0 == launches
+        assert mld.kernel_launch_count() - c0 == 2 and plan.last_route() == route
         torch.cuda.synchronize()
         ref = oracle.f16_bits_to_f32(oracle.prefill_gemm_int4(x16.view(np.uint16), packed, sgn, N))
         got = oracle.from_sliced(y.float().cpu().numpy().reshape(N // 4, M, 4), N)
