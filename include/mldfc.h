@@ -211,7 +211,11 @@ MLD_API int mld_loader_load_zero_point(mld_loader* loader,
 enum mld_prefill_route {
   MLD_PREFILL_ROUTE_AUTO = 0,
   MLD_PREFILL_ROUTE_INLINE = 1,
-  MLD_PREFILL_ROUTE_CONVERT = 2
+  MLD_PREFILL_ROUTE_CONVERT = 2,
+  MLD_PREFILL_ROUTE_INLINE_SMEM = 3  /* inside the GEMM, through shared memory
+                                        instead of tensor memory (the form the
+                                        int8-activation route uses; kept
+                                        selectable for comparison) */
 };
 
 typedef struct mld_fc_desc {

@@ -13,8 +13,8 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libmldfc.so")
 
 SOURCES = ["api.cu", "pack_kernels.cu", "gemv_generic.cu", "gemv_stream.cu", "decode_step.cu", "decode_mega.cu",
-           "gemm_umma.cu", "gemm_pair.cu", "shard_group.cu", "embedding.cu", "loader.cu"]
-HEADERS = ["common.cuh", "kernels.h", "nccl_lazy.h", os.path.join(ROOT, "include", "mldfc.h")]
+           "gemm_umma.cu", "gemm_pair.cu", "gemm_wtmem.cu", "shard_group.cu", "embedding.cu", "loader.cu"]
+HEADERS = ["common.cuh", "kernels.h", "nccl_lazy.h", "pair_common.cuh", os.path.join(ROOT, "include", "mldfc.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -317,7 +317,7 @@ int mld_fc_plan_create(const mld_fc_desc* d, mld_fc_plan** out) {
   // An operator that may run as the prefill GEMM gets its operand workspace now, so that mld_fc_run never
   // allocates: the K-major copy of the weights, the K-major (optionally quantised) activations and the
   // per-token quantisation parameters.
-  MLD_REQUIRE(d->prefill_route >= MLD_PREFILL_ROUTE_AUTO && d->prefill_route <= MLD_PREFILL_ROUTE_CONVERT,
+  MLD_REQUIRE(d->prefill_route >= MLD_PREFILL_ROUTE_AUTO && d->prefill_route <= MLD_PREFILL_ROUTE_INLINE_SMEM,
               "prefill_route out of range");
   const bool may_gemm = d->force_path == 2 || (d->force_path == 0 && !mld_fc_is_gemv_recommended(d->precision, d->max_tokens));
   if (may_gemm && d->precision != MLD_PRECISION_F32 && !d->has_zero_point) {
@@ -519,7 +519,19 @@ static int run_gemm(mld_fc_plan* p, const void* src, const void* weights, const 
   }
   int rc;
   const bool convert = d.cache_prepared_weights != 0 || !p->pair_ok || d.prefill_route == MLD_PREFILL_ROUTE_CONVERT ||
-                       (d.prefill_route == MLD_PREFILL_ROUTE_AUTO && convert_pays(tokens));
+                       (d.prefill_route == MLD_PREFILL_ROUTE_AUTO && convert_pays(tokens));  // (routes 1 and 3: inside)
+  if (!convert && !i8 && d.prefill_route != MLD_PREFILL_ROUTE_INLINE_SMEM) {
+    // float route: the dequantised weights go to tensor memory
+    p->last_route = MLD_ROUTE_PREFILL_INLINE;
+    const int mode = d.weight_bits == 4 ? 0 : 1;
+    const WtGeometry wg = wtmem_geometry(tokens, d.n, d.k, mode, p->sms, true);
+    if (++p->split.epoch == 0) p->split.epoch = 1;
+    rc = launch_transpose_x(src, d.src_layout, tokens, d.k, wg.kp, p->x_kmajor, stream);
+    if (rc != MLD_OK) return rc;
+    return launch_gemm_wtmem(mode, p->x_kmajor, weights, wg, tokens, d.n, d.k, scale, d.scale_mode,
+                             d.scale_mode == MLD_SCALE_BLOCK ? d.groups : 1, p->group_slices, d.scalar_scale, bias, dst,
+                             d.dst_layout, err, stream, outs, &p->split);
+  }
   if (!convert) {
     p->last_route = MLD_ROUTE_PREFILL_INLINE;
     const int mode = i8 ? 2 : (d.weight_bits == 4 ? 0 : 1);

@@ -1527,6 +1527,11 @@ __device__ void run_attention(Ctx& c, const MegaLayer* ly) {
     }
     seq_lo = seq_hi;
   }
+  if (atracing) {  // thread 0's time waiting for tiles and the CTA's number of items
+    unsigned long long* tr = a.trace + ((size_t)blockIdx.x * a.n_layers * kOpsPerLayer + c.op_index) * kTraceSlots;
+    tr[4] = static_cast<unsigned long long>(awaited);
+    tr[5] = static_cast<unsigned long long>(i1 - i0);
+  }
   c.attn_runs += runs.R;
   c.ring_base += 2 * (i1 - i0);
 }

@@ -203,4 +203,18 @@ int launch_gemm_pair(int mode, const void* a_mat, const void* packed, const Pair
                      const float* a_params, const int32_t* w_sum, void* y, int dst_layout, int* error,
                      cudaStream_t stream, const PeerOutputs* outs = nullptr, const PairSplit* split = nullptr);
 
+// ------------------------------------------- prefill GEMM, dequantised weights in tensor memory (SM pairs)
+struct WtGeometry {
+  int kp, tile_tok, tok_tiles, n_tiles, k_blocks, w_stages, grid;
+  int shared_tiles, units_per_pair;
+  bool shares_tiles;
+  size_t smem_bytes;
+};
+// mode: 0 = INT4 weights, 1 = INT8 weights, both dequantised to fp16 inside the kernel (float activations)
+WtGeometry wtmem_geometry(int M, int N, int K, int mode, int sms, bool may_share = false);
+int launch_gemm_wtmem(int mode, const void* x_kmajor, const void* packed, const WtGeometry& g, int M, int N, int K,
+                      const void* scale, int scale_mode, int G, int group_slices, float scalar_scale, const void* bias,
+                      void* y, int dst_layout, int* error, cudaStream_t stream, const PeerOutputs* outs = nullptr,
+                      const PairSplit* split = nullptr);
+
 }  // namespace mld

@@ -1,7 +1,7 @@
 """Prefill dequant-GEMM (tcgen05) through the C ABI vs the CPU oracle.
 
 Every case runs on each route: "inline" (the GEMM reads the packed weights and dequantises them in shared
-memory; what the cost rule picks up to 512 tokens), "convert" (a conversion pass writes a K-major copy and
+tensor memory - or, "inline_smem", in shared memory; what the cost rule picks up to 512 tokens), "convert" (a conversion pass writes a K-major copy and
 a GEMM with both operands loaded by TMA follows; the rule's pick above 512 tokens) and "cached" (the
 same with the copy kept between calls).  All apply the same arithmetic to every weight.
 Float route: tolerance 1e-3 of max |ref| against the restated WeightsConverter + fp32-accumulate GEMM
@@ -28,8 +28,8 @@ def _rel(a, b):
     return float(np.max(np.abs(a - b)) / max(np.max(np.abs(b)), 1e-30))
 
 
-ROUTES = [("inline", False), ("convert", False), ("cached", True)]
-ROUTE_CODE = {"inline": 1, "convert": 2, "cached": 0, "auto": 0}
+ROUTES = [("inline", False), ("inline_smem", False), ("convert", False), ("cached", True)]
+ROUTE_CODE = {"inline": 1, "convert": 2, "cached": 0, "auto": 0, "inline_smem": 3}
 
 
 def _run_gemm(mld, oracle, x16, packed, scale_dev, N, K, bits, mode, G, bias=None, layout="sliced", act_quant=0,
