@@ -56,6 +56,15 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 // D[tmem_d] (+)= A[tmem_a] B[desc_b]^T over the pair; A: 16 halves per lane in 8 columns of both CTAs' tensor memory.
 __device__ __forceinline__ void umma_pair_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
                                              uint32_t accumulate) {
@@ -278,14 +287,12 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       __half bias_h = __float2half_rn(0.0f);
       if (a.bias != nullptr && has_n) bias_h = static_cast<const __half*>(a.bias)[n];
       const int q = lane & 3;  // place among the four channels of the output slice n >> 2
-      for (int c0 = 0; c0 < wa.tile_tok; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(c0), r);
-        tmem_ld_wait();
+      // Sixteen token columns at a time, the next sixteen already on their way from tensor memory.
+      auto piece = [&](uint32_t (&r)[16], int c0) {
         if (takes_over) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint4 o = __ldcg(&slot_rows[((c0 >> 5) * 8 + j) * 32]);
+          for (int j = 0; j < 4; ++j) {
+            const uint4 o = __ldcg(&slot_rows[((c0 >> 5) * 8 + ((c0 >> 4) & 1) * 4 + j) * 32]);
             r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + __uint_as_float(o.x));
             r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + __uint_as_float(o.y));
             r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + __uint_as_float(o.z));
@@ -293,21 +300,21 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           }
         }
         // token pairs as packed halves: h2[i] = tokens c0 + 2i, c0 + 2i + 1 of channel n
-        uint32_t h2[16];
+        uint32_t h2[8];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < 8; ++i) {
           __half2 v = __floats2half2_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
           if (a.bias != nullptr) v = __hadd2(v, __half2half2(bias_h));
           h2[i] = *reinterpret_cast<const uint32_t*>(&v);
         }
 #ifdef MLD_TRACE
-        if (wa.trace_flags & 2) continue;
+        if (wa.trace_flags & 2) return;
 #endif
         if (a.dst_layout == MLD_LAYOUT_SLICED) {
           // Eight tokens at a time: the four lanes of a slice exchange token pairs so that lane q holds tokens
           // 2q, 2q + 1 (of the eight) of all four channels, 16 contiguous bytes of [slice][token][4 channels].
 #pragma unroll
-          for (int grp = 0; grp < 4; ++grp) {
+          for (int grp = 0; grp < 2; ++grp) {
             // 4 x 4 transpose over the slice's four lanes in two butterfly steps (lanes 2 apart, then 1 apart):
             // lane q starts with its channel's pairs p0..p3 and ends with pair q of channels 0..3
             uint32_t x0 = h2[4 * grp], x1 = h2[4 * grp + 1], x2 = h2[4 * grp + 2], x3 = h2[4 * grp + 3];
@@ -335,13 +342,12 @@ __global__ void __launch_bounds__(kPairThreads, 1)
                 x3 = r1;
               }
             }
-            const uint32_t ch[4] = {x0, x1, x2, x3};  // pair q of channels 0..3
             const int m = m_first + c0 + 8 * grp + 2 * q;  // first of this lane's two tokens
             uint4 pk;
-            pk.x = __byte_perm(ch[0], ch[1], 0x5410);  // token m: channels 0, 1
-            pk.y = __byte_perm(ch[2], ch[3], 0x5410);  //          channels 2, 3
-            pk.z = __byte_perm(ch[0], ch[1], 0x7632);  // token m + 1
-            pk.w = __byte_perm(ch[2], ch[3], 0x7632);
+            pk.x = __byte_perm(x0, x1, 0x5410);  // token m: channels 0, 1
+            pk.y = __byte_perm(x2, x3, 0x5410);  //          channels 2, 3
+            pk.z = __byte_perm(x0, x1, 0x7632);  // token m + 1
+            pk.w = __byte_perm(x2, x3, 0x7632);
 #ifdef MLD_TRACE
             if (wa.trace_flags & 1) continue;
 #endif
@@ -362,7 +368,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           }
         } else if (n < a.N) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < 8; ++i) {
             const int m = m_first + c0 + 2 * i;
             if (c0 + 2 * i < wa.tile_tok && m < a.M)
               static_cast<__half*>(a.y)[(size_t)m * a.N + n] = __ushort_as_half(static_cast<unsigned short>(h2[i] & 0xFFFFu));
@@ -370,6 +376,19 @@ __global__ void __launch_bounds__(kPairThreads, 1)
               static_cast<__half*>(a.y)[(size_t)(m + 1) * a.N + n] = __ushort_as_half(static_cast<unsigned short>(h2[i] >> 16));
           }
         }
+      };
+      const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+      uint32_t ra[16], rb[16];
+      tmem_ld16(lane_base, ra);
+      tmem_ld_wait();
+      for (int c0 = 0; c0 < wa.tile_tok; c0 += 32) {
+        const bool second = c0 + 16 < wa.tile_tok;  // (tile_tok is a multiple of 16)
+        if (second) tmem_ld16(lane_base + static_cast<uint32_t>(c0 + 16), rb);
+        piece(ra, c0);
+        tmem_ld_wait();
+        if (c0 + 32 < wa.tile_tok) tmem_ld16(lane_base + static_cast<uint32_t>(c0 + 32), ra);
+        if (second) piece(rb, c0 + 16);
+        tmem_ld_wait();
       }
       tc_before();
       __syncwarp();
