@@ -28,8 +28,9 @@
 //   warps 2..5   epilogue: a thread reads its output channel's accumulators (one TMEM lane, a column per token),
 //                adds the bias, and four neighbouring lanes exchange values so that each holds the four channels
 //                of one output slice for two tokens, a 16-byte piece of the sliced output layout
-// Tensor memory: columns 0..255 accumulators (one buffer: the epilogue of a tile is not overlapped, which costs
-// about a tenth of a tile), columns 256..511 the weight ring (8 stages x 32 columns).
+// Tensor memory: columns 0..255 accumulators (one buffer: reading a tile's accumulators is not overlapped with
+// the next tile's MMAs, so the transform warps, idle meanwhile, share the reading with the epilogue warps),
+// columns 256..511 the weight ring (8 stages x 32 columns).
 // The split of the work over the pairs (tiles of the last wave shared along K) is gemm_pair_kernel's.
 // Every wait is bounded.
 #include <cuda_fp16.h>
@@ -47,6 +48,7 @@ constexpr int kWtRows = 128;          // output channels per CTA
 constexpr int kWtTokBytes = 128 * kKBytes;  // up to 128 token rows per CTA and stage
 constexpr uint32_t kWtACol = 256;     // first TMEM column of the weight ring
 constexpr int kErrWtBase = 50;
+constexpr int kDrainParts = 5;        // warps that read one lane quarter's accumulators: one epilogue + four transform
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
@@ -131,7 +133,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       mbar_init(&xf_done[s], kTransformWarps);
     }
     mbar_init(tmem_full, 1);
-    mbar_init(tmem_empty, 2 * 4);
+    mbar_init(tmem_empty, 2 * 4 * kDrainParts);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -149,6 +151,147 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   // tile -> (token tile, channel tile): the token tiles of one channel tile follow each other
   auto tile_tok0 = [&](int tile) { return (tile % a.m_tiles) * wa.tile_tok; };
   auto tile_n0 = [&](int tile) { return (tile / a.m_tiles) * 2 * kWtRows; };
+
+  // Accumulators -> outputs, the share `part` of kDrainParts of the warps that can address this lane quarter
+  // (one epilogue warp and the quarter's four transform warps, which have nothing to transform while the only
+  // accumulator buffer is being read): pieces of 16 token columns, part, part + kDrainParts, ...  A tile shared
+  // with a neighbouring pair (see gemm_pair_kernel): the pair that holds the tile's last k-blocks leaves its raw
+  // accumulators in the workspace slot of the pair before it, which adds them to its own and writes the outputs.
+  auto drain = [&](const Segment& sg, int part) -> bool {
+    const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+    const bool hands_over = sg.kb0 > 0, takes_over = sg.kb1 < a.k_blocks;
+    const int slot = hands_over ? pair - 1 : pair;
+    uint4* const slot_rows =
+        reinterpret_cast<uint4*>(a.split_ws) + ((size_t)(slot * 2 + static_cast<int>(rank)) * 4 + quad) * (8 * 8 * 32) + lane;
+    uint32_t* const slot_flag = a.split_flags + ((slot * 2 + static_cast<int>(rank)) * 4 + quad) * 8 + part;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const int n_pieces = wa.tile_tok >> 4;
+    if (hands_over) {
+      for (int pc = part; pc < n_pieces; pc += kDrainParts) {
+        uint32_t r[16];
+        tmem_ld16(lane_base + static_cast<uint32_t>(16 * pc), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) slot_rows[(pc * 4 + j) * 32] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+      }
+      __threadfence();
+      tc_before();
+      __syncwarp();
+      if (lane == 0) {
+        st_release_gpu(slot_flag, a.epoch);
+        arrive_remote(tmem_empty_lead);
+      }
+      return true;
+    }
+    if (takes_over) {
+      uint32_t seen = 0;
+      if (lane == 0) {
+        const unsigned long long t0 = globaltimer_ns();
+        while ((seen = ld_acquire_gpu(slot_flag)) != a.epoch && globaltimer_ns() - t0 <= kWaitLimitNs) __nanosleep(64);
+      }
+      seen = __shfl_sync(0xffffffffu, seen, 0);
+      if (seen != a.epoch) {
+        atomicExch(a.error, kErrWtBase + 8);
+        return false;
+      }
+    }
+    const int n = (sg.tile / a.m_tiles) * 2 * kWtRows + static_cast<int>(rank) * kWtRows + quad * 32 + lane;  // output channel
+    const int m_first = (sg.tile % a.m_tiles) * wa.tile_tok;
+    const bool has_n = n < a.N4;
+    __half bias_h = __float2half_rn(0.0f);
+    if (a.bias != nullptr && has_n) bias_h = static_cast<const __half*>(a.bias)[n];
+    const int q = lane & 3;  // place among the four channels of the output slice n >> 2
+    for (int pc = part; pc < n_pieces; pc += kDrainParts) {
+      const int c0 = 16 * pc;
+      uint32_t r[16];
+      tmem_ld16(lane_base + static_cast<uint32_t>(c0), r);
+      tmem_ld_wait();
+      if (takes_over) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 o = __ldcg(&slot_rows[(pc * 4 + j) * 32]);
+          r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + __uint_as_float(o.x));
+          r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + __uint_as_float(o.y));
+          r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + __uint_as_float(o.z));
+          r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + __uint_as_float(o.w));
+        }
+      }
+      // token pairs as packed halves: h2[i] = tokens c0 + 2i, c0 + 2i + 1 of channel n
+      uint32_t h2[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        __half2 v = __floats2half2_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        if (a.bias != nullptr) v = __hadd2(v, __half2half2(bias_h));
+        h2[i] = *reinterpret_cast<const uint32_t*>(&v);
+      }
+      if (a.dst_layout == MLD_LAYOUT_SLICED) {
+        // Eight tokens at a time: the four lanes of a slice exchange token pairs so that lane q holds tokens
+        // 2q, 2q + 1 (of the eight) of all four channels, 16 contiguous bytes of [slice][token][4 channels].
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+          // 4 x 4 transpose over the slice's four lanes in two butterfly steps (lanes 2 apart, then 1 apart):
+          // lane q starts with its channel's pairs p0..p3 and ends with pair q of channels 0..3
+          uint32_t x0 = h2[4 * grp], x1 = h2[4 * grp + 1], x2 = h2[4 * grp + 2], x3 = h2[4 * grp + 3];
+          {
+            const bool up = (q & 2) != 0;
+            const uint32_t s0 = up ? x0 : x2, s1 = up ? x1 : x3;  // what the lane 2 away needs
+            const uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 2), r1 = __shfl_xor_sync(0xffffffffu, s1, 2);
+            if (up) {
+              x0 = r0;
+              x1 = r1;
+            } else {
+              x2 = r0;
+              x3 = r1;
+            }
+          }
+          {
+            const bool up = (q & 1) != 0;
+            const uint32_t s0 = up ? x0 : x1, s1 = up ? x2 : x3;  // what the lane 1 away needs
+            const uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 1), r1 = __shfl_xor_sync(0xffffffffu, s1, 1);
+            if (up) {
+              x0 = r0;
+              x2 = r1;
+            } else {
+              x1 = r0;
+              x3 = r1;
+            }
+          }
+          const int m = m_first + c0 + 8 * grp + 2 * q;  // first of this lane's two tokens
+          uint4 pk;
+          pk.x = __byte_perm(x0, x1, 0x5410);  // token m: channels 0, 1
+          pk.y = __byte_perm(x2, x3, 0x5410);  //          channels 2, 3
+          pk.z = __byte_perm(x0, x1, 0x7632);  // token m + 1
+          pk.w = __byte_perm(x2, x3, 0x7632);
+          if (has_n && m < a.M) {
+            const size_t at = ((size_t)(n >> 2) * a.M + m) * 4;  // in halves
+            const bool both = m + 1 < a.M && ((at * 2) & 15) == 0;
+            const int world = a.outs.world > 1 ? a.outs.world : 1;
+            for (int pr = 0; pr < world; ++pr) {
+              __half* base = static_cast<__half*>(a.outs.world > 1 ? a.outs.y[pr] : a.y) + at;
+              if (both) {
+                *reinterpret_cast<uint4*>(base) = pk;
+              } else {
+                *reinterpret_cast<uint2*>(base) = make_uint2(pk.x, pk.y);
+                if (m + 1 < a.M) *reinterpret_cast<uint2*>(base + 4) = make_uint2(pk.z, pk.w);
+              }
+            }
+          }
+        }
+      } else if (n < a.N) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = m_first + c0 + 2 * i;
+          if (m < a.M) static_cast<__half*>(a.y)[(size_t)m * a.N + n] = __ushort_as_half(static_cast<unsigned short>(h2[i] & 0xFFFFu));
+          if (m + 1 < a.M)
+            static_cast<__half*>(a.y)[(size_t)(m + 1) * a.N + n] = __ushort_as_half(static_cast<unsigned short>(h2[i] >> 16));
+        }
+      }
+    }
+    tc_before();
+    __syncwarp();
+    if (lane == 0) arrive_remote(tmem_empty_lead);
+    return true;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------ producer of the activation tiles
@@ -229,174 +372,18 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     }
   } else if (warp < 6) {
     // --------------------------------------------------------------------- epilogue
-    const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
     uint32_t acc_phase = 0;
-    bool ok = true;
     WorkList work = work0;
     Segment sg;
-    [[maybe_unused]] long long tr_full = 0;
-    [[maybe_unused]] const long long tr_start = MLD_PAIR_CLOCK();
-    while (ok && work.next(sg)) {
-      [[maybe_unused]] const long long tf0 = MLD_PAIR_CLOCK();
+    while (work.next(sg)) {
       if (!mbar_wait(tmem_full, acc_phase)) {
         atomicExch(a.error, kErrWtBase + 4);
         break;
       }
       acc_phase ^= 1;
       tc_after();
-      tr_full += MLD_PAIR_CLOCK() - tf0;
-      // (tiles shared with a neighbour: see gemm_pair_kernel)
-      const bool hands_over = sg.kb0 > 0, takes_over = sg.kb1 < a.k_blocks;
-      const int slot = hands_over ? pair - 1 : pair;
-      uint4* const slot_rows =
-          reinterpret_cast<uint4*>(a.split_ws) + ((size_t)(slot * 2 + static_cast<int>(rank)) * 4 + quad) * (8 * 8 * 32) + lane;
-      uint32_t* const slot_flag = a.split_flags + ((slot * 2 + static_cast<int>(rank)) * 4 + quad) * 4;
-      if (hands_over) {
-        for (int c0 = 0; c0 < wa.tile_tok; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(c0), r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            slot_rows[((c0 >> 5) * 8 + j) * 32] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        }
-        __threadfence();
-        tc_before();
-        __syncwarp();
-        if (lane == 0) {
-          st_release_gpu(slot_flag, a.epoch);
-          arrive_remote(tmem_empty_lead);
-        }
-        continue;
-      }
-      if (takes_over) {
-        uint32_t seen = 0;
-        if (lane == 0) {
-          const unsigned long long t0 = globaltimer_ns();
-          while ((seen = ld_acquire_gpu(slot_flag)) != a.epoch && globaltimer_ns() - t0 <= kWaitLimitNs) __nanosleep(64);
-        }
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        if (seen != a.epoch) {
-          atomicExch(a.error, kErrWtBase + 8);
-          break;
-        }
-      }
-      const int n = tile_n0(sg.tile) + static_cast<int>(rank) * kWtRows + quad * 32 + lane;  // this lane's output channel
-      const int m_first = tile_tok0(sg.tile);
-      const bool has_n = n < a.N4;
-      __half bias_h = __float2half_rn(0.0f);
-      if (a.bias != nullptr && has_n) bias_h = static_cast<const __half*>(a.bias)[n];
-      const int q = lane & 3;  // place among the four channels of the output slice n >> 2
-      // Sixteen token columns at a time, the next sixteen already on their way from tensor memory.
-      auto piece = [&](uint32_t (&r)[16], int c0) {
-        if (takes_over) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint4 o = __ldcg(&slot_rows[((c0 >> 5) * 8 + ((c0 >> 4) & 1) * 4 + j) * 32]);
-            r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + __uint_as_float(o.x));
-            r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + __uint_as_float(o.y));
-            r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + __uint_as_float(o.z));
-            r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + __uint_as_float(o.w));
-          }
-        }
-        // token pairs as packed halves: h2[i] = tokens c0 + 2i, c0 + 2i + 1 of channel n
-        uint32_t h2[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          __half2 v = __floats2half2_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-          if (a.bias != nullptr) v = __hadd2(v, __half2half2(bias_h));
-          h2[i] = *reinterpret_cast<const uint32_t*>(&v);
-        }
-#ifdef MLD_TRACE
-        if (wa.trace_flags & 2) return;
-#endif
-        if (a.dst_layout == MLD_LAYOUT_SLICED) {
-          // Eight tokens at a time: the four lanes of a slice exchange token pairs so that lane q holds tokens
-          // 2q, 2q + 1 (of the eight) of all four channels, 16 contiguous bytes of [slice][token][4 channels].
-#pragma unroll
-          for (int grp = 0; grp < 2; ++grp) {
-            // 4 x 4 transpose over the slice's four lanes in two butterfly steps (lanes 2 apart, then 1 apart):
-            // lane q starts with its channel's pairs p0..p3 and ends with pair q of channels 0..3
-            uint32_t x0 = h2[4 * grp], x1 = h2[4 * grp + 1], x2 = h2[4 * grp + 2], x3 = h2[4 * grp + 3];
-            {
-              const bool up = (q & 2) != 0;
-              const uint32_t s0 = up ? x0 : x2, s1 = up ? x1 : x3;  // what the lane 2 away needs
-              const uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 2), r1 = __shfl_xor_sync(0xffffffffu, s1, 2);
-              if (up) {
-                x0 = r0;
-                x1 = r1;
-              } else {
-                x2 = r0;
-                x3 = r1;
-              }
-            }
-            {
-              const bool up = (q & 1) != 0;
-              const uint32_t s0 = up ? x0 : x1, s1 = up ? x2 : x3;  // what the lane 1 away needs
-              const uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 1), r1 = __shfl_xor_sync(0xffffffffu, s1, 1);
-              if (up) {
-                x0 = r0;
-                x2 = r1;
-              } else {
-                x1 = r0;
-                x3 = r1;
-              }
-            }
-            const int m = m_first + c0 + 8 * grp + 2 * q;  // first of this lane's two tokens
-            uint4 pk;
-            pk.x = __byte_perm(x0, x1, 0x5410);  // token m: channels 0, 1
-            pk.y = __byte_perm(x2, x3, 0x5410);  //          channels 2, 3
-            pk.z = __byte_perm(x0, x1, 0x7632);  // token m + 1
-            pk.w = __byte_perm(x2, x3, 0x7632);
-#ifdef MLD_TRACE
-            if (wa.trace_flags & 1) continue;
-#endif
-            if (has_n && c0 + 8 * grp + 2 * q < wa.tile_tok && m < a.M) {
-              const size_t at = ((size_t)(n >> 2) * a.M + m) * 4;  // in halves
-              const bool both = m + 1 < a.M && ((at * 2) & 15) == 0;
-              const int world = a.outs.world > 1 ? a.outs.world : 1;
-              for (int pr = 0; pr < world; ++pr) {
-                __half* base = static_cast<__half*>(a.outs.world > 1 ? a.outs.y[pr] : a.y) + at;
-                if (both) {
-                  *reinterpret_cast<uint4*>(base) = pk;
-                } else {
-                  *reinterpret_cast<uint2*>(base) = make_uint2(pk.x, pk.y);
-                  if (m + 1 < a.M) *reinterpret_cast<uint2*>(base + 4) = make_uint2(pk.z, pk.w);
-                }
-              }
-            }
-          }
-        } else if (n < a.N) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int m = m_first + c0 + 2 * i;
-            if (c0 + 2 * i < wa.tile_tok && m < a.M)
-              static_cast<__half*>(a.y)[(size_t)m * a.N + n] = __ushort_as_half(static_cast<unsigned short>(h2[i] & 0xFFFFu));
-            if (c0 + 2 * i + 1 < wa.tile_tok && m + 1 < a.M)
-              static_cast<__half*>(a.y)[(size_t)(m + 1) * a.N + n] = __ushort_as_half(static_cast<unsigned short>(h2[i] >> 16));
-          }
-        }
-      };
-      const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-      uint32_t ra[16], rb[16];
-      tmem_ld16(lane_base, ra);
-      tmem_ld_wait();
-      for (int c0 = 0; c0 < wa.tile_tok; c0 += 32) {
-        const bool second = c0 + 16 < wa.tile_tok;  // (tile_tok is a multiple of 16)
-        if (second) tmem_ld16(lane_base + static_cast<uint32_t>(c0 + 16), rb);
-        piece(ra, c0);
-        tmem_ld_wait();
-        if (c0 + 32 < wa.tile_tok) tmem_ld16(lane_base + static_cast<uint32_t>(c0 + 32), ra);
-        if (second) piece(rb, c0 + 16);
-        tmem_ld_wait();
-      }
-      tc_before();
-      __syncwarp();
-      if (lane == 0) arrive_remote(tmem_empty_lead);
+      if (!drain(sg, 0)) break;
     }
-#ifdef MLD_TRACE
-    if (wa.trace != nullptr && warp == 2 && lane == 0) wa.trace[blockIdx.x * 8 + 1] = MLD_PAIR_CLOCK() - tr_start - tr_full;
-#endif
     if (a.outs.world > 1) __threadfence_system();  // the peer stores are performed before the kernel ends
   } else if (warp == 24) {
     // ------------------------------------------------- producer of the packed weight boxes
@@ -469,6 +456,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     };
     bool ok = true;
     int xf_iter = 0;
+    uint32_t acc_phase = 0;
     WorkList work = work0;
     Segment sg;
     [[maybe_unused]] long long tr_wait = 0, tr_work = 0, tr_st = 0;
@@ -553,6 +541,17 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         advance(kb + 1 < sg.kb1 ? 2 : 1);
       }
       xf_iter += sg.kb1 - sg.kb0;
+      if (!ok) break;
+      // This segment's accumulators: the transform warps share the reading with the epilogue warp of their
+      // quarter.  (Measured: reading them only when the ring is full and the next stage blocked, so that the next
+      // tile's first stages are transformed beforehand, costs more in polling than the refill costs here.)
+      if (!mbar_wait(tmem_full, acc_phase)) {
+        atomicExch(a.error, kErrWtBase + 9);
+        break;
+      }
+      acc_phase ^= 1;
+      tc_after();
+      if (!drain(sg, 1 + group * 2 + half)) break;
     }
 #ifdef MLD_TRACE
     if (wa.trace != nullptr && warp == 6 && lane == 0) {

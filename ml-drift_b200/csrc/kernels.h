@@ -192,7 +192,7 @@ struct PairSplit {
   uint32_t epoch;    // a value no earlier launch on this workspace used (never 0)
 };
 inline size_t pair_split_bytes(int sms) { return (size_t)(sms / 2 > 0 ? sms / 2 : 1) * 2 * 4 * 8 * 8 * 32 * 16; }
-inline size_t pair_split_flags(int sms) { return (size_t)(sms / 2 > 0 ? sms / 2 : 1) * 2 * 4 * 4; }
+inline size_t pair_split_flags(int sms) { return (size_t)(sms / 2 > 0 ? sms / 2 : 1) * 2 * 4 * 8; }
 // mode: 0 = INT4 weights -> fp16 MMA, 1 = INT8 weights -> fp16 MMA, 2 = INT8 weights x int8 activations (packed
 // weights, transformed in shared memory); 3 / 4 = weights prepared as K-major fp16 / s8 rows [N4][kp] by
 // launch_dequant_weights (then `packed` is that matrix)
