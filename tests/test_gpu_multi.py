@@ -236,7 +236,7 @@ def _sharded_fc_worker(rank, world, port, out_dir):
     dist.broadcast(nccl_id, 0)
     results = []
     cases = [("int4_prefill", 4, 300, 1024, 520, 0), ("w8a8_asym", 8, 300, 1024, 520, 2), ("w8a8_sym", 8, 130, 2048, 264, 1),
-             ("int4_decode", 4, 1, 1024, 520, 0)]
+             ("int4_decode", 4, 1, 1024, 520, 0), ("int4_prefill_converted", 4, 600, 512, 264, 0)]
     group = mld.ShardGroup(rank, world, 2 * 1024 * 1024, nccl_id=nccl_id.numpy().tobytes())
     mine = torch.frombuffer(bytearray(group.ipc_export()), dtype=torch.uint8).clone()
     table = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
