@@ -164,23 +164,37 @@ def run_reference(args):
 
 # ------------------------------------------------------------------- GPU arm
 class ClockSampler:
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi in loop mode beside the run (read-only queries, 20 ms apart).  It is started before the warm-up so
+    that it is already sampling when the timed region begins; `mark()` brackets the timed region, and only the
+    samples whose time stamps fall inside it count (all samples of the run when the region was too short to
+    catch one, which `window` then says)."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index = index
         self.proc = None
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
+    def mark(self):
+        import datetime
+        now = datetime.datetime.now()
+        if self.t0 is None:
+            self.t0 = now
+        else:
+            self.t1 = now
+
     def stop(self):
+        import datetime
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -189,21 +203,28 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        rows = []
         for ln in out.splitlines():
             f = [c.strip() for c in ln.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
+                when = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+                rows.append((when, float(f[1]), float(f[2]), f[5:9]))
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+        inside = [r for r in rows if self.t0 is not None and self.t1 is not None and self.t0 <= r[0] <= self.t1]
+        window = "timed region"
+        if not inside:
+            inside, window = rows, "whole run (no sample fell inside the timed region)"
+        reasons = set()
+        for r in inside:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
+        sm, mx = [r[1] for r in inside], [r[2] for r in inside]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "window": window, "reasons": sorted(reasons)}
 
 
 def build_model(mld, torch, rank, world, n_layers, dev, shard_layout=0):
@@ -799,17 +820,19 @@ def run_ours(args):
             dec.step(x, y, pos)
 
     with torch.cuda.stream(stream):
+        sampler = ClockSampler(local)
+        sampler.start()
         for _ in range(max(args.warmup, 3)):
             step_once()
         barrier()
-        sampler = ClockSampler(local)
-        sampler.start()
+        sampler.mark()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):
             step_once()
         e1.record(stream)
         barrier()
+        sampler.mark()
         ms = e0.elapsed_time(e1)
         # end to end through the host-buffer entry point
         xh = x.cpu().pin_memory()
