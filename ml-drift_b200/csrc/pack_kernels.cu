@@ -247,6 +247,80 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(PackArgs a) {
   }
 }
 
+// The same for the dense nibble source (two's-complement nibbles, two input channels per byte, the form the
+// converter's INT4 files have), input channels a multiple of 32 and output channels a multiple of 4: a lane reads
+// 32 input channels (16 bytes) of one output row, the four lanes that hold the same channels of four rows exchange
+// words, and each transposes the 4 x 4 nibbles of two input slices in registers (bytes first, then nibbles).
+__global__ void __launch_bounds__(256) pack_rows_u4_kernel(PackArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hw = blockIdx.z;
+  const int r = lane >> 3, c = lane & 7;
+  const int i0 = blockIdx.x * 256 + c * 32;              // first input channel of this lane's 16 bytes
+  const int o0 = (blockIdx.y * 8 + warp) * 16;           // first of the warp's 16 output rows
+  if (o0 >= a.O) return;
+  uint2 blk_a[4], blk_b[4];                              // [output slice of the four]: input slices i0/4 + 2r, + 2r + 1
+#pragma unroll
+  for (int st = 0; st < 4; ++st) {
+    const int o = o0 + st * 4 + r;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    int32_t rowsum = 0;
+    if (o < a.O && i0 < a.I) {
+      v = *reinterpret_cast<const uint4*>(a.src + ((((int64_t)o * a.HW + hw) * a.I + i0) >> 1));
+      // destination nibble = source nibble ^ 8 (two's complement -> offset by 8); its value is nibble - 8
+      v.x ^= 0x88888888u;
+      v.y ^= 0x88888888u;
+      v.z ^= 0x88888888u;
+      v.w ^= 0x88888888u;
+      const uint32_t m = 0x0F0F0F0Fu;
+      rowsum = __dp4a(static_cast<int>((v.x & m) + ((v.x >> 4) & m)), 0x01010101, -64 * 4);
+      rowsum = __dp4a(static_cast<int>((v.y & m) + ((v.y >> 4) & m)), 0x01010101, rowsum);
+      rowsum = __dp4a(static_cast<int>((v.z & m) + ((v.z >> 4) & m)), 0x01010101, rowsum);
+      rowsum = __dp4a(static_cast<int>((v.w & m) + ((v.w >> 4) & m)), 0x01010101, rowsum);
+    }
+    if (a.sum_i != nullptr) {
+      rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 1);
+      rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 2);
+      rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 4);
+      if (c == 0 && o < a.O && o < a.sum_len && rowsum != 0) atomicAdd(a.sum_i + o, rowsum);
+    }
+    // lane (r, c) collects word r (input channels i0 + 8 r .. + 7) of the rows held by lanes (0..3, c)
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t rows[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int offer = (r + j) & 3;
+      const uint32_t mine = offer == 0 ? w[0] : offer == 1 ? w[1] : offer == 2 ? w[2] : w[3];
+      const int from_row = (r - j) & 3;
+      const uint32_t got = __shfl_sync(0xffffffffu, mine, from_row * 8 + c);
+      if (from_row == 0) rows[0] = got;
+      else if (from_row == 1) rows[1] = got;
+      else if (from_row == 2) rows[2] = got;
+      else rows[3] = got;
+    }
+    // rows[n]: low half = nibbles k0..k3 of output n in the first slice, high half = the second slice.
+    // bytes first: b0 = (k0 k1) of outputs 0, 2; b1 = of outputs 1, 3; b2, b3 = (k2 k3) likewise
+    const uint32_t b0 = __byte_perm(rows[0], rows[2], 0x6240), b2 = __byte_perm(rows[0], rows[2], 0x7351);
+    const uint32_t b1 = __byte_perm(rows[1], rows[3], 0x6240), b3 = __byte_perm(rows[1], rows[3], 0x7351);
+    // then nibbles: c_k = outputs 0..3 of input channel k (both slices at once)
+    const uint32_t m = 0x0F0F0F0Fu;
+    const uint32_t c0 = (b0 & m) | ((b1 & m) << 4), c1 = ((b0 >> 4) & m) | (b1 & ~m);
+    const uint32_t c2 = (b2 & m) | ((b3 & m) << 4), c3 = ((b2 >> 4) & m) | (b3 & ~m);
+    blk_a[st] = make_uint2(__byte_perm(c0, c1, 0x5410), __byte_perm(c2, c3, 0x5410));
+    blk_b[st] = make_uint2(__byte_perm(c0, c1, 0x7632), __byte_perm(c2, c3, 0x7632));
+  }
+  const int s = (i0 >> 2) + 2 * r;                       // this lane's first input slice
+  const int ds0 = o0 >> 2;
+  const int n_ds = min(4, a.dst_slices - ds0);           // (output channels are a multiple of 4 here)
+  if (s < a.src_slices) {
+    uint2* dst = reinterpret_cast<uint2*>(a.dst + (((int64_t)hw * a.src_slices + s) * a.group + ds0) * 8);
+    for (int st = 0; st < n_ds; ++st) dst[st] = blk_a[st];
+  }
+  if (s + 1 < a.src_slices) {
+    uint2* dst = reinterpret_cast<uint2*>(a.dst + (((int64_t)hw * a.src_slices + s + 1) * a.group + ds0) * 8);
+    for (int st = 0; st < n_ds; ++st) dst[st] = blk_b[st];
+  }
+}
+
 __global__ void sum_i_kernel(const int8_t* src, int O, int64_t hwi, int32_t* sum_i) {
   const int o = blockIdx.x;
   if (o >= O) return;
@@ -403,6 +477,11 @@ int pack_weights_impl(const mld_pack_desc* d, const void* src, void* dst, int32_
       pack_rows_kernel<8><<<rgrid, 256, 0, stream>>>(a);
     else
       pack_rows_kernel<4><<<rgrid, 256, 0, stream>>>(a);
+  } else if (d->source == MLD_SRC_UINT4_PACKED && a.I % 32 == 0 && a.O % 4 == 0 && !a.swap_dims &&
+             a.group == a.dst_slices && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+    dim3 rgrid(div_up(a.I, 256), div_up(a.O, 128), a.HW);
+    pack_rows_u4_kernel<<<rgrid, 256, 0, stream>>>(a);
   } else if (d->source == MLD_SRC_INT8) {
     if (d->bits == 8)
       pack_from_int8_kernel<8><<<grid, 256, 0, stream>>>(a);

@@ -21,7 +21,9 @@ def _dev(a):
 SHAPES = [(4, 1, 1, 4), (3, 1, 1, 4), (4, 1, 1, 2), (533, 1, 1, 171), (534, 1, 1, 171), (7, 1, 1, 6),
           (256, 1, 1, 512), (16, 2, 1, 8), (130, 3, 1, 36), (2048, 1, 1, 2048),
           # input channels a multiple of 16: the register-transpose kernel; ragged outputs, several tiles, H > 1
-          (48, 1, 1, 64), (37, 1, 1, 16), (130, 1, 1, 400), (18, 2, 1, 144), (300, 1, 1, 1024)]
+          (48, 1, 1, 64), (37, 1, 1, 16), (130, 1, 1, 400), (18, 2, 1, 144), (300, 1, 1, 1024),
+          # nibble sources with input channels a multiple of 32 and whole output slices: their own transpose kernel
+          (20, 2, 1, 96), (132, 1, 1, 288), (16, 1, 1, 32), (516, 1, 1, 544)]
 
 
 @pytest.mark.parametrize("shape", SHAPES)
