@@ -43,6 +43,11 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t x, uint32_t mask, uint32_t orv) {
   uint32_t r;
   asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(x), "r"(mask), "r"(orv));  // (x & mask) | orv
@@ -181,7 +186,14 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 
 // W: weight boxes per stage (strip width up to W * 128 bytes per pass).
 // MONE: single-token launch (only token column 0 is kept).
-template <int BITS, int W, bool SUBNORMAL, bool MONE>
+// DIGITS (4-bit weights, one token, a one-token activation vector): integer MMAs instead.  The whole
+// activation vector is fetched once, and every warp turns the units of 32 inputs it will meet (one per
+// stage) into 16-bit fixed point with a power-of-two scale of their own, x ~ s (256 hi + lo), before the
+// first stage.  One m16n8k32 u8 x s8 MMA per 16 outputs then multiplies the nibbles, as bytes that hold
+// two outputs each, by the two digits (columns 0 and 1): 8 MMAs per stage and warp where the fp16 form
+// needs 18, and two byte permutes per MMA instead of shifts and masks.  Everything is exact in int32;
+// the error is that of the fixed point, at most 2^-16 of the unit's largest input per input.
+template <int BITS, int W, bool SUBNORMAL, bool MONE, bool DIGITS = false>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
     fc_strip_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
                     StripArgs a) {
@@ -195,6 +207,11 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
   uint64_t* full = reinterpret_cast<uint64_t*>(peer + ((WT * a.red_m + 1) & ~1));
   uint64_t* empty = full + a.stages;
   uint64_t* peer_bar = empty + a.stages;
+  // DIGITS: the activation vector of this CTA's K range, digitised in place ([unit][hi: 8 words][lo: 8 words],
+  // word j = the four inputs of k-slice j), then per unit {bits of the digit scale, 8 x the sum of its integers}
+  uint64_t* xbar = peer_bar + 1;
+  uint8_t* xdig = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(xbar + 1) + 15) & ~uintptr_t(15));
+  uint2* xmeta = reinterpret_cast<uint2*>(xdig + (size_t)a.rows_per_split * 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kr = a.ksplit > 1 ? static_cast<int>(cluster_ctarank()) : 0;
@@ -224,6 +241,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
         mbar_init(&empty[s], kConsumerWarps);
       }
       mbar_init(peer_bar, kConsumerWarps * 32);
+      if constexpr (DIGITS) mbar_init(xbar, 1);
       fence_barrier_init();
     }
     __syncwarp();
@@ -247,7 +265,8 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
         const int row0 = r_lo + si * kStageRows;
         const int rows = min(kStageRows, r_hi - row0);
         const int chunk0 = cs + pass * W * 8;
-        mbar_arrive_expect_tx(&full[stage], W * kBoxBytes + s_bytes + static_cast<uint32_t>(rows) * a.M_total * 8u);
+        mbar_arrive_expect_tx(&full[stage],
+                              W * kBoxBytes + s_bytes + (DIGITS ? 0u : static_cast<uint32_t>(rows) * a.M_total * 8u));
 #pragma unroll
         for (int b = 0; b < W; ++b)
           tma_load_2d_hint(st + b * kBoxBytes, &tmap_w, &full[stage], (chunk0 + b * 8) * 16, row0, pol);
@@ -255,6 +274,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
           tma_load_2d(st + W * kBoxBytes, &tmap_s, &full[stage], chunk0 * F::NPL, row0 / a.group_slices);
       };
       auto issue_x = [&](int item, int stage) {
+        if constexpr (DIGITS) return;  // the whole vector is fetched once, below
         const int si = item % n_st;
         uint8_t* st = smem + (size_t)stage * a.stage_bytes;
         const int row0 = r_lo + si * kStageRows;
@@ -283,6 +303,11 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
         if (!wait_peer_flags(a.wait.flags, a.wait.world, seq, a.wait.limit_ns)) atomicExch(a.error, kErrPeerWait);
       }
       if (tr) tr[2] = globaltimer_ns();
+      if constexpr (DIGITS) {
+        const uint32_t xbytes = static_cast<uint32_t>(r_hi - r_lo) * 8u;
+        mbar_arrive_expect_tx(xbar, xbytes);
+        bulk_load_1d(xdig, static_cast<const uint8_t*>(a.x) + (size_t)r_lo * 8, xbytes, xbar);
+      }
       for (int it = 0; it < head; ++it) issue_x(it, it);
       int stage = head == a.stages ? 0 : head;
       uint32_t phase = head == a.stages ? 1 : 0;
@@ -321,7 +346,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
   const int g = lane >> 2, t = lane & 3;
   constexpr uint32_t kOnesA = BITS == 4 ? 0x00080008u : 0x00800080u;  // subnormal 8 / 128
   constexpr float kOdd = BITS == 4 ? 0.0625f : 1.0f;                  // high nibbles are carried x16
-  constexpr float kOutScale = SUBNORMAL ? 16777216.0f : 1.0f;
+  constexpr float kOutScale = (SUBNORMAL && !DIGITS) ? 16777216.0f : 1.0f;
   const int rbase = warp * 8;
   int stage = 0;
   uint32_t phase = 0;
@@ -329,6 +354,72 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
 #ifdef MLD_TRACE
   long long tr_wait_cycles = 0, tr_busy_cycles = 0;
 #endif
+
+  if constexpr (DIGITS) {
+    if (n_st > 0) {
+      if (!mbar_wait(xbar, 0)) {
+        atomicExch(a.error, 2);
+        failed = true;
+      }
+      // this warp's unit of stage si is unit si * 8 + warp of the CTA's K range; lane = 4 * (stage of the round) + chunk,
+      // a chunk being eight inputs (k-slices 2q and 2q + 1 of the unit)
+      for (int si0 = 0; si0 < n_st && !failed; si0 += 8) {
+        const int si = si0 + (lane >> 2), q = lane & 3;
+        const bool have = si < n_st;
+        const int u = si * 8 + warp;
+        const int row = r_lo + u * 8 + 2 * q;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (have && row < r_hi) {
+          v = *reinterpret_cast<const uint4*>(xdig + (size_t)u * 64 + q * 16);
+          if (row + 1 >= r_hi) v.z = v.w = 0u;
+        }
+        __syncwarp();  // the unit's four lanes have read before any of them rewrites it
+        float xf[8];
+        {
+          const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+          const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+          const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&v.z));
+          const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
+          xf[0] = f0.x; xf[1] = f0.y; xf[2] = f1.x; xf[3] = f1.y;
+          xf[4] = f2.x; xf[5] = f2.y; xf[6] = f3.x; xf[7] = f3.y;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(xf[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        // the smallest power of two s with amax / s <= 32512 (a float with an empty mantissa); 1 / s is exact
+        uint32_t sbits = (__float_as_uint(amax * (1.0f / 32512.0f)) + 0x007FFFFFu) & 0x7F800000u;
+        if (sbits < (16u << 23)) sbits = 16u << 23;
+        const float inv = __uint_as_float((254u << 23) - sbits);
+        // z = round(x / s) + 128 in the low 16 bits of the sum's mantissa: byte 1 = high digit, byte 0 ^ 0x80 = low digit
+        uint32_t z[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) z[i] = __float_as_uint(fmaf(xf[i], inv, 12583040.0f));
+        uint32_t hiw[2], low[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t h01 = prmt(z[4 * e], z[4 * e + 1], 0x0051u), h23 = prmt(z[4 * e + 2], z[4 * e + 3], 0x0051u);
+          const uint32_t l01 = prmt(z[4 * e], z[4 * e + 1], 0x0040u), l23 = prmt(z[4 * e + 2], z[4 * e + 3], 0x0040u);
+          hiw[e] = prmt(h01, h23, 0x5410u);
+          low[e] = prmt(l01, l23, 0x5410u) ^ 0x80808080u;
+        }
+        int isum = __dp4a(static_cast<int>(hiw[0]), 0x01010101, 0);
+        isum = __dp4a(static_cast<int>(hiw[1]), 0x01010101, isum) * 256;
+        isum = __dp4a(static_cast<int>(low[0]), 0x01010101, isum);
+        isum = __dp4a(static_cast<int>(low[1]), 0x01010101, isum);
+        isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+        isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+        if (have) {
+          uint32_t* ud = reinterpret_cast<uint32_t*>(xdig + (size_t)u * 64);
+          *reinterpret_cast<uint2*>(ud + 2 * q) = make_uint2(hiw[0], hiw[1]);
+          *reinterpret_cast<uint2*>(ud + 8 + 2 * q) = make_uint2(low[0], low[1]);
+          if (q == 0) xmeta[u] = make_uint2(sbits, static_cast<uint32_t>(8 * isum));  // the nibbles carry the weights + 8
+        }
+      }
+      __syncwarp();
+    }
+  }
 
   for (int pass = 0; pass < passes && !failed; ++pass) {
     float tot[W][F::NF][NJ];
@@ -365,44 +456,42 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
       const uint8_t* st = smem + (size_t)stage * a.stage_bytes;
       const uint8_t* xs = st + W * kBoxBytes + a.scale_stage_bytes;
       const int row0 = r_lo + si * kStageRows;
-      // activation fragments of this warp's eight rows (two steps)
-      uint32_t bx[2][2];
-#pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        const int r = rbase + 2 * t + p;
-        bx[p][0] = bx[p][1] = 0u;
-        if (row0 + r < r_hi && g < a.M) {
-          const uint2 xv = *reinterpret_cast<const uint2*>(xs + ((size_t)r * a.M_total + a.tok0 + g) * 8);
-          bx[p][0] = xv.x;
-          bx[p][1] = xv.y;
+      if constexpr (DIGITS) {
+        static_assert(!DIGITS || (BITS == 4 && MONE), "the digit form is for 4-bit weights and one token");
+        // this warp's unit: k-slice rows rbase + t and rbase + 4 + t are what lane t feeds the MMA's K with
+        const int ra = rbase + t, rb = rbase + 4 + t;
+        const int u = si * 8 + warp;
+        const uint32_t* ud = reinterpret_cast<const uint32_t*>(xdig + (size_t)u * 64);
+        // column g of B comes from lanes g: column 0 the high digits, column 1 the low ones, nothing else
+        uint32_t b0 = 0u, b1 = 0u;
+        if (g < 2) {
+          b0 = ud[8 * g + t];
+          b1 = ud[8 * g + 4 + t];
         }
-      }
-      float ones[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      if constexpr (SUBNORMAL) {
-        const uint32_t oa[4] = {kOnesA, kOnesA, kOnesA, kOnesA};
-        mma_f16(ones, oa, bx[0][0], bx[0][1]);
-        mma_f16(ones, oa, bx[1][0], bx[1][1]);
-      }
-      const int gidx = a.gs_shift >= 0 ? (rbase >> a.gs_shift) : 0;
+        const uint2 meta = xmeta[u];
+        const float sx = __uint_as_float(meta.x);
+        const int off = static_cast<int>(meta.y);
+        const int gidx = a.gs_shift >= 0 ? (rbase >> a.gs_shift) : 0;
 #pragma unroll
-      for (int b = 0; b < W; ++b) {
-        float grp[F::NF][4];
+        for (int b = 0; b < W; ++b) {
+          const uint4 qa = *reinterpret_cast<const uint4*>(st + b * kBoxBytes + ra * 128 + ((g ^ (ra & 7)) << 4));
+          const uint4 qb = *reinterpret_cast<const uint4*>(st + b * kBoxBytes + rb * 128 + ((g ^ (rb & 7)) << 4));
+          int acc[4][4];
 #pragma unroll
-        for (int f = 0; f < F::NF; ++f) grp[f][0] = grp[f][1] = grp[f][2] = grp[f][3] = 0.0f;
-#pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          const int r = rbase + 2 * t + p;
-          const uint4 q = *reinterpret_cast<const uint4*>(st + b * kBoxBytes + r * 128 + ((g ^ (r & 7)) << 4));
-          uint32_t av[F::NF][4];
-          unpack<BITS, SUBNORMAL>(q, av);
-#pragma unroll
-          for (int f = 0; f < F::NF; ++f) mma_f16(grp[f], av[f], bx[p][0], bx[p][1]);
-        }
-        // scales of this lane's outputs for the group these eight rows are in
-        float sc[F::NPL];
-        if (a.scale_rows > 0) {
-          const __half* sp = reinterpret_cast<const __half*>(st + W * kBoxBytes) + gidx * WT + b * F::BOX_N + F::NPL * g;
-          if constexpr (BITS == 4) {
+          for (int f = 0; f < 4; ++f) {
+            // outputs 2f (low nibbles) and 2f + 1 (high nibbles) of this lane's eight: byte j of a block word is
+            // input j / 2, output pair j % 2, so the four inputs of a pair are bytes 0, 2 (or 1, 3) of the two words
+            const uint32_t sel = (f & 1) ? 0x7531u : 0x6420u;
+            const uint32_t wa = f < 2 ? prmt(qa.x, qa.y, sel) : prmt(qa.z, qa.w, sel);
+            const uint32_t wb = f < 2 ? prmt(qb.x, qb.y, sel) : prmt(qb.z, qb.w, sel);
+            // rows g take the whole byte (even output + 16 x odd output), rows g + 8 the odd output x 16
+            const uint32_t af[4] = {wa, wa & 0xF0F0F0F0u, wb, wb & 0xF0F0F0F0u};
+            acc[f][0] = acc[f][1] = acc[f][2] = acc[f][3] = 0;
+            mma_u8s8(acc[f], af, b0, b1);
+          }
+          float sc[8];
+          if (a.scale_rows > 0) {
+            const __half* sp = reinterpret_cast<const __half*>(st + W * kBoxBytes) + gidx * WT + b * F::BOX_N + F::NPL * g;
             const uint4 sv = *reinterpret_cast<const uint4*>(sp);
             const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
             const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
@@ -411,30 +500,90 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
             sc[0] = f0.x; sc[1] = f0.y; sc[2] = f1.x; sc[3] = f1.y;
             sc[4] = f2.x; sc[5] = f2.y; sc[6] = f3.x; sc[7] = f3.y;
           } else {
-            const uint2 sv = *reinterpret_cast<const uint2*>(sp);
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
-            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
-            sc[0] = f0.x; sc[1] = f0.y; sc[2] = f1.x; sc[3] = f1.y;
-          }
-        } else {
 #pragma unroll
-          for (int i = 0; i < F::NPL; ++i) sc[i] = a.scalar_scale;
+            for (int i = 0; i < 8; ++i) sc[i] = a.scalar_scale;
+          }
+          // lanes t == 0 hold columns 0 and 1: {row g high, row g low, row g + 8 high, row g + 8 low}
+#pragma unroll
+          for (int f = 0; f < 4; ++f) {
+            const int even = (acc[f][0] - acc[f][2]) * 256 + (acc[f][1] - acc[f][3]) - off;
+            const int odd = ((acc[f][2] * 256 + acc[f][3]) >> 4) - off;
+            tot[b][f][0] = fmaf(sc[2 * f] * sx, static_cast<float>(even), tot[b][f][0]);
+            tot[b][f][1] = fmaf(sc[2 * f + 1] * sx, static_cast<float>(odd), tot[b][f][1]);
+          }
         }
-        // row g of MMA f is output 2f, row g+8 is output 2f+1
+      } else {
+        // activation fragments of this warp's eight rows (two steps)
+        uint32_t bx[2][2];
 #pragma unroll
-        for (int f = 0; f < F::NF; ++f)
-#pragma unroll
-          for (int jj = 0; jj < NJ; ++jj) {
-            const int j = MONE ? 2 * jj : jj;  // MONE keeps (row g, token 2t) and (row g+8, token 2t)
-            const bool odd = (j & 2) != 0;
-            float v = grp[f][j];
-            if constexpr (SUBNORMAL) {
-              v = odd ? fmaf(v, kOdd, -ones[j & 1]) : (v - ones[j & 1]);
-            } else {
-              if (odd) v *= kOdd;
-            }
-            tot[b][f][jj] = fmaf(sc[2 * f + (odd ? 1 : 0)], v, tot[b][f][jj]);
+        for (int p = 0; p < 2; ++p) {
+          const int r = rbase + 2 * t + p;
+          bx[p][0] = bx[p][1] = 0u;
+          if (row0 + r < r_hi && g < a.M) {
+            const uint2 xv = *reinterpret_cast<const uint2*>(xs + ((size_t)r * a.M_total + a.tok0 + g) * 8);
+            bx[p][0] = xv.x;
+            bx[p][1] = xv.y;
           }
+        }
+        float ones[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if constexpr (SUBNORMAL) {
+          const uint32_t oa[4] = {kOnesA, kOnesA, kOnesA, kOnesA};
+          mma_f16(ones, oa, bx[0][0], bx[0][1]);
+          mma_f16(ones, oa, bx[1][0], bx[1][1]);
+        }
+        const int gidx = a.gs_shift >= 0 ? (rbase >> a.gs_shift) : 0;
+#pragma unroll
+        for (int b = 0; b < W; ++b) {
+          float grp[F::NF][4];
+#pragma unroll
+          for (int f = 0; f < F::NF; ++f) grp[f][0] = grp[f][1] = grp[f][2] = grp[f][3] = 0.0f;
+#pragma unroll
+          for (int p = 0; p < 2; ++p) {
+            const int r = rbase + 2 * t + p;
+            const uint4 q = *reinterpret_cast<const uint4*>(st + b * kBoxBytes + r * 128 + ((g ^ (r & 7)) << 4));
+            uint32_t av[F::NF][4];
+            unpack<BITS, SUBNORMAL>(q, av);
+#pragma unroll
+            for (int f = 0; f < F::NF; ++f) mma_f16(grp[f], av[f], bx[p][0], bx[p][1]);
+          }
+          // scales of this lane's outputs for the group these eight rows are in
+          float sc[F::NPL];
+          if (a.scale_rows > 0) {
+            const __half* sp = reinterpret_cast<const __half*>(st + W * kBoxBytes) + gidx * WT + b * F::BOX_N + F::NPL * g;
+            if constexpr (BITS == 4) {
+              const uint4 sv = *reinterpret_cast<const uint4*>(sp);
+              const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
+              const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
+              const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&sv.z));
+              const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&sv.w));
+              sc[0] = f0.x; sc[1] = f0.y; sc[2] = f1.x; sc[3] = f1.y;
+              sc[4] = f2.x; sc[5] = f2.y; sc[6] = f3.x; sc[7] = f3.y;
+            } else {
+              const uint2 sv = *reinterpret_cast<const uint2*>(sp);
+              const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
+              const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
+              sc[0] = f0.x; sc[1] = f0.y; sc[2] = f1.x; sc[3] = f1.y;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < F::NPL; ++i) sc[i] = a.scalar_scale;
+          }
+          // row g of MMA f is output 2f, row g+8 is output 2f+1
+#pragma unroll
+          for (int f = 0; f < F::NF; ++f)
+#pragma unroll
+            for (int jj = 0; jj < NJ; ++jj) {
+              const int j = MONE ? 2 * jj : jj;  // MONE keeps (row g, token 2t) and (row g+8, token 2t)
+              const bool odd = (j & 2) != 0;
+              float v = grp[f][j];
+              if constexpr (SUBNORMAL) {
+                v = odd ? fmaf(v, kOdd, -ones[j & 1]) : (v - ones[j & 1]);
+              } else {
+                if (odd) v *= kOdd;
+              }
+              tot[b][f][jj] = fmaf(sc[2 * f + (odd ? 1 : 0)], v, tot[b][f][jj]);
+            }
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[stage]);
@@ -569,10 +718,10 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
   }
 }
 
-template <int BITS, int W, bool SUBNORMAL, bool MONE>
+template <int BITS, int W, bool SUBNORMAL, bool MONE, bool DIGITS = false>
 int launch_strip_t(const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a, const StripGeometry& gm,
                    cudaStream_t stream) {
-  auto kern = fc_strip_kernel<BITS, W, SUBNORMAL, MONE>;
+  auto kern = fc_strip_kernel<BITS, W, SUBNORMAL, MONE, DIGITS>;
   static bool configured[kMaxDevices];  // per instantiation and device
   int dev;
   if (needs_configure(configured, &dev)) {
@@ -609,6 +758,9 @@ template <int BITS, int W>
 int launch_strip_w(bool subnormal, bool mone, const CUtensorMap& tw, const CUtensorMap& ts, const StripArgs& a,
                    const StripGeometry& gm, cudaStream_t stream) {
   if (subnormal) {
+    if constexpr (BITS == 4) {
+      if (mone && a.M_total == 1 && gm.xdig_bytes > 0) return launch_strip_t<BITS, W, true, true, true>(tw, ts, a, gm, stream);
+    }
     if (mone) return launch_strip_t<BITS, W, true, true>(tw, ts, a, gm, stream);
     return launch_strip_t<BITS, W, true, false>(tw, ts, a, gm, stream);
   }
@@ -667,7 +819,10 @@ StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slic
   const int x_bytes = align_n(kStageRows * m_total * 8, 128);
   gm.stage_bytes = align_n(gm.w * kBoxBytes + gm.scale_stage_bytes + x_bytes, 1024);
   gm.red_m = m_total < 8 ? m_total : 8;
-  const int fixed = (kConsumerWarps + 1) * wt * gm.red_m * 4 + 8 + (2 * 16 + 1) * 8 + 1024 + 64;
+  // 4-bit weights: room for a one-token activation vector of this CTA's K range as digits (8 bytes per k-slice,
+  // 8 per unit of eight k-slices, a barrier)
+  gm.xdig_bytes = bits == 4 ? gm.rows_per_split * 9 + 48 : 0;
+  const int fixed = (kConsumerWarps + 1) * wt * gm.red_m * 4 + 8 + (2 * 16 + 1) * 8 + gm.xdig_bytes + 1024 + 64;
   gm.stage_rows = kStageRows;
   // With programmatic dependent launch two consecutive GEMVs share an SM while
   // one drains and the next prefetches, so each takes at most half of it.

@@ -100,6 +100,7 @@ struct StripGeometry {
   int rows_per_split;
   int scale_rows, group_slices, gs_shift;
   int scale_stage_bytes, stage_bytes, stages, red_m, stage_rows;
+  int xdig_bytes;  // shared memory kept for the digitised activation vector (4-bit weights), else 0
   size_t smem_bytes;
 };
 StripGeometry strip_geometry(int bits, int N, int K, int m_total, int group_slices, int scale_mode, int sms,
