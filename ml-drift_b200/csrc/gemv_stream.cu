@@ -361,8 +361,8 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
         atomicExch(a.error, 2);
         failed = true;
       }
-      // this warp's unit of stage si is unit si * 8 + warp of the CTA's K range; lane = 4 * (stage of the round) + chunk,
-      // a chunk being eight inputs (k-slices 2q and 2q + 1 of the unit)
+      // this warp digitises unit si * 8 + warp of every stage si; lane = 4 * (stage of the round) + chunk, a chunk
+      // being eight inputs (k-slices 2q and 2q + 1 of the unit)
       for (int si0 = 0; si0 < n_st && !failed; si0 += 8) {
         const int si = si0 + (lane >> 2), q = lane & 3;
         const bool have = si < n_st;
@@ -417,8 +417,8 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
           if (q == 0) xmeta[u] = make_uint2(sbits, static_cast<uint32_t>(8 * isum));  // the nibbles carry the weights + 8
         }
       }
-      __syncwarp();
     }
+    MLD_CONSUMER_BARRIER();  // a warp multiplies by units other warps digitised
   }
 
   for (int pass = 0; pass < passes && !failed; ++pass) {
@@ -458,40 +458,49 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
       const int row0 = r_lo + si * kStageRows;
       if constexpr (DIGITS) {
         static_assert(!DIGITS || (BITS == 4 && MONE), "the digit form is for 4-bit weights and one token");
-        // this warp's unit: k-slice rows rbase + t and rbase + 4 + t are what lane t feeds the MMA's K with
-        const int ra = rbase + t, rb = rbase + 4 + t;
-        const int u = si * 8 + warp;
-        const uint32_t* ud = reinterpret_cast<const uint32_t*>(xdig + (size_t)u * 64);
-        // column g of B comes from lanes g: column 0 the high digits, column 1 the low ones, nothing else
-        uint32_t b0 = 0u, b1 = 0u;
-        if (g < 2) {
-          b0 = ud[8 * g + t];
-          b1 = ud[8 * g + 4 + t];
-        }
-        const uint2 meta = xmeta[u];
-        const float sx = __uint_as_float(meta.x);
-        const int off = static_cast<int>(meta.y);
-        const int gidx = a.gs_shift >= 0 ? (rbase >> a.gs_shift) : 0;
-#pragma unroll
-        for (int b = 0; b < W; ++b) {
-          const uint4 qa = *reinterpret_cast<const uint4*>(st + b * kBoxBytes + ra * 128 + ((g ^ (ra & 7)) << 4));
-          const uint4 qb = *reinterpret_cast<const uint4*>(st + b * kBoxBytes + rb * 128 + ((g ^ (rb & 7)) << 4));
+        // A stage is 2 W tasks: (half of its 64 k-slice rows = four units) x (box of 64 outputs).  The four
+        // units of a task share accumulators: B column 2 j holds the high and 2 j + 1 the low digits of unit j
+        // (lanes g supply column g, zero for the other units), so after the units' MMAs lane t holds both
+        // digit sums of unit t and finishes that unit.  With fewer tasks than warps, groups of warps take
+        // the stages in turn; every warp still waits for and releases every stage.
+        constexpr int T = W == 3 ? 8 : 2 * W;
+        constexpr int GC = kConsumerWarps / T;
+        const int task = warp % T, tb = task >> 1, hq = task & 1;
+        if (tb < W && si % GC == warp / T) {
+          const int ubase = si * 8 + hq * 4;  // the task's first unit within the CTA's K range
+          const uint32_t* ud = reinterpret_cast<const uint32_t*>(xdig + (size_t)(ubase + (g >> 1)) * 64) + 8 * (g & 1);
+          const uint32_t bm0 = ud[t], bm1 = ud[4 + t];
           int acc[4][4];
 #pragma unroll
-          for (int f = 0; f < 4; ++f) {
-            // outputs 2f (low nibbles) and 2f + 1 (high nibbles) of this lane's eight: byte j of a block word is
-            // input j / 2, output pair j % 2, so the four inputs of a pair are bytes 0, 2 (or 1, 3) of the two words
-            const uint32_t sel = (f & 1) ? 0x7531u : 0x6420u;
-            const uint32_t wa = f < 2 ? prmt(qa.x, qa.y, sel) : prmt(qa.z, qa.w, sel);
-            const uint32_t wb = f < 2 ? prmt(qb.x, qb.y, sel) : prmt(qb.z, qb.w, sel);
-            // rows g take the whole byte (even output + 16 x odd output), rows g + 8 the odd output x 16
-            const uint32_t af[4] = {wa, wa & 0xF0F0F0F0u, wb, wb & 0xF0F0F0F0u};
-            acc[f][0] = acc[f][1] = acc[f][2] = acc[f][3] = 0;
-            mma_u8s8(acc[f], af, b0, b1);
+          for (int f = 0; f < 4; ++f) acc[f][0] = acc[f][1] = acc[f][2] = acc[f][3] = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            // k-slice rows ra and ra + 4 of unit j are what lane t feeds the MMA's K with
+            const int ra = 32 * hq + 8 * j + t, rb = ra + 4;
+            const uint4 qa = *reinterpret_cast<const uint4*>(st + tb * kBoxBytes + ra * 128 + ((g ^ (ra & 7)) << 4));
+            const uint4 qb = *reinterpret_cast<const uint4*>(st + tb * kBoxBytes + rb * 128 + ((g ^ (rb & 7)) << 4));
+            const bool mine = (g >> 1) == j;
+            const uint32_t b0 = mine ? bm0 : 0u, b1 = mine ? bm1 : 0u;
+#pragma unroll
+            for (int f = 0; f < 4; ++f) {
+              // outputs 2f (low nibbles) and 2f + 1 (high nibbles) of this lane's eight: byte i of a block word is
+              // input i / 2, output pair i % 2, so the four inputs of a pair are bytes 0, 2 (or 1, 3) of the two words
+              const uint32_t sel = (f & 1) ? 0x7531u : 0x6420u;
+              const uint32_t wa = f < 2 ? prmt(qa.x, qa.y, sel) : prmt(qa.z, qa.w, sel);
+              const uint32_t wb = f < 2 ? prmt(qb.x, qb.y, sel) : prmt(qb.z, qb.w, sel);
+              // rows g take the whole byte (even output + 16 x odd output), rows g + 8 the odd output x 16
+              const uint32_t af[4] = {wa, wa & 0xF0F0F0F0u, wb, wb & 0xF0F0F0F0u};
+              mma_u8s8(acc[f], af, b0, b1);
+            }
           }
+          // lane t finishes unit t: its digit scale and offset, the weight scales of its group
+          const uint2 meta = xmeta[ubase + t];
+          const float sx = __uint_as_float(meta.x);
+          const int off = static_cast<int>(meta.y);
           float sc[8];
           if (a.scale_rows > 0) {
-            const __half* sp = reinterpret_cast<const __half*>(st + W * kBoxBytes) + gidx * WT + b * F::BOX_N + F::NPL * g;
+            const int gidx = a.gs_shift >= 0 ? ((32 * hq + 8 * t) >> a.gs_shift) : 0;
+            const __half* sp = reinterpret_cast<const __half*>(st + W * kBoxBytes) + gidx * WT + tb * F::BOX_N + F::NPL * g;
             const uint4 sv = *reinterpret_cast<const uint4*>(sp);
             const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
             const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
@@ -503,13 +512,13 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
 #pragma unroll
             for (int i = 0; i < 8; ++i) sc[i] = a.scalar_scale;
           }
-          // lanes t == 0 hold columns 0 and 1: {row g high, row g low, row g + 8 high, row g + 8 low}
+          // acc: {row g high digit, row g low, row g + 8 high, row g + 8 low} of unit t
 #pragma unroll
           for (int f = 0; f < 4; ++f) {
             const int even = (acc[f][0] - acc[f][2]) * 256 + (acc[f][1] - acc[f][3]) - off;
             const int odd = ((acc[f][2] * 256 + acc[f][3]) >> 4) - off;
-            tot[b][f][0] = fmaf(sc[2 * f] * sx, static_cast<float>(even), tot[b][f][0]);
-            tot[b][f][1] = fmaf(sc[2 * f + 1] * sx, static_cast<float>(odd), tot[b][f][1]);
+            tot[0][f][0] = fmaf(sc[2 * f] * sx, static_cast<float>(even), tot[0][f][0]);
+            tot[0][f][1] = fmaf(sc[2 * f + 1] * sx, static_cast<float>(odd), tot[0][f][1]);
           }
         }
       } else {
@@ -605,17 +614,37 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
 
     // ------------------------------------------------ pass epilogue
     if (tr && threadIdx.x == 0) tr[4] = globaltimer_ns();
+    if constexpr (DIGITS) {
+      // tot[0] is this warp's box (tb) summed over the units the lane finished: add the four lanes t up; the
+      // warp contributes nothing to the other boxes
+      constexpr int T = W == 3 ? 8 : 2 * W;
+      const int tb = (warp % T) >> 1;
 #pragma unroll
-    for (int b = 0; b < W; ++b)
+      for (int f = 0; f < 4; ++f)
 #pragma unroll
-      for (int f = 0; f < F::NF; ++f)
+        for (int jj = 0; jj < 2; ++jj) {
+          float v = tot[0][f][jj];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          if (t == 0) {
 #pragma unroll
-        for (int jj = 0; jj < NJ; ++jj) {
-          const int j = MONE ? 2 * jj : jj;
-          const int n_local = b * F::BOX_N + F::NPL * g + 2 * f + ((j >> 1) & 1);
-          const int tok = 2 * t + (j & 1);
-          if (tok < a.M) red[(warp * WT + n_local) * a.red_m + tok] = tot[b][f][jj];
+            for (int b = 0; b < W; ++b)
+              red[(warp * WT + b * F::BOX_N + F::NPL * g + 2 * f + jj) * a.red_m] = b == tb ? v : 0.0f;
+          }
         }
+    } else {
+#pragma unroll
+      for (int b = 0; b < W; ++b)
+#pragma unroll
+        for (int f = 0; f < F::NF; ++f)
+#pragma unroll
+          for (int jj = 0; jj < NJ; ++jj) {
+            const int j = MONE ? 2 * jj : jj;
+            const int n_local = b * F::BOX_N + F::NPL * g + 2 * f + ((j >> 1) & 1);
+            const int tok = 2 * t + (j & 1);
+            if (tok < a.M) red[(warp * WT + n_local) * a.red_m + tok] = tot[b][f][jj];
+          }
+    }
     MLD_CONSUMER_BARRIER();
     const int chunk0 = cs + pass * W * 8;
     const int n0 = chunk0 * F::NPL;               // first output of this pass

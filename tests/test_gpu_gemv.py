@@ -259,6 +259,35 @@ def test_independent_launches_overlap_and_finish_in_stream_order(mld, oracle):
     ref_plan.close()
 
 
+@pytest.mark.parametrize("K,N,block", [(2048, 1024, 32), (40, 64, 0), (200, 328, 0), (4096, 512, 64), (1032, 1160, 0),
+                                       (11008, 256, 128)])
+@pytest.mark.parametrize("outliers", [False, True])
+def test_one_token_int4_digit_route(mld, oracle, K, N, block, outliers):
+    """4-bit weights with one token take integer MMAs on the activations as 16-bit fixed point, one
+    power-of-two scale per 32 inputs: K tails inside a unit and inside a stage, several scale groupings,
+    channels at 300 sigma, all against the plain dequantised product and against the fp16 route."""
+    rng = np.random.default_rng(K * 3 + N + block)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    if block:
+        q, s = oracle.quantize_int4_sym(w, block)
+        mode, G = mld.SCALE_BLOCK, K // block
+    else:
+        q, s = oracle.quantize_int4_sym(w, 0)
+        mode, G = mld.SCALE_PER_CHANNEL, 1
+    packed = oracle.rearrange_int8_as_uint4(q)
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    if outliers:
+        x[0, rng.choice(K, 3, replace=False)] *= 300.0
+    x = x.astype(np.float16).astype(np.float32)
+    s16 = oracle.f16_bits_to_f32(oracle.f32_to_f16_bits(s))
+    plain = oracle.fc_plain_reference(q, s16, x)
+    y = _run(mld, oracle, "F32F16", 4, x, packed, N, K, scale=s, mode=mode, G=G)
+    exact = _run(mld, oracle, "F32F16", 4, x, packed, N, K, scale=s, mode=mode, G=G, exact_operands=True)
+    assert _rel(exact, plain) <= 1e-3
+    assert _rel(y, plain) <= 1e-3
+    assert _rel(y, exact) <= 1e-3
+
+
 def test_row_major_single_token(mld, oracle):
     rng = np.random.default_rng(6)
     K, N = 1024, 512
