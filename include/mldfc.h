@@ -277,9 +277,12 @@ typedef struct mld_fc_desc {
                                 experts builder
                                 (common/gpu_model_builder_moe_util.cc:200-270) */
   /* Tuning of the streaming decode kernel; 0 everywhere = the defaults. */
-  int32_t exact_operands;    /* 1: dequantise to exact fp16 integers before the MMA
-                                instead of feeding the raw nibbles / bytes as fp16
-                                subnormals (same results up to fp32 summation order) */
+  int32_t exact_operands;    /* 1: dequantise to exact fp16 integers before the MMA.
+                                0: 4-bit weights with one token multiply the nibbles
+                                by the activations as 16-bit fixed point (one power-
+                                of-two scale per 32 inputs) in integer MMAs; the other
+                                cases feed the raw nibbles / bytes as fp16 subnormals
+                                (same results up to fp32 summation order) */
   int32_t no_overlap;        /* 1: do not let consecutive launches overlap
                                 (programmatic dependent launch off) */
   int32_t smem_limit_kb;     /* > 0: shared-memory budget of the stage ring */
