@@ -75,6 +75,7 @@ constexpr int kAttnSlots = 2;                // head runs likewise
 constexpr int kAttDump = kHeadDim + 4;       // 128 outputs, then max and sum (padded: rows stay 16-byte aligned)
 constexpr int kDumpFloats = 2 * kCW * kStripN > kAttnSlots * kCW * kAttDump ? 2 * kCW * kStripN : kAttnSlots * kCW * kAttDump;
 constexpr int kWarpScratch = 3 * kHeadDim;   // attention: rotated q, new k, new v (floats) per warp
+constexpr int kMaxParts = 8;                 // CTAs that share a head at most: the merging part reads all partials in one round
 constexpr int kTraceSlots = 12;              // per (CTA, op): 4 timestamps, warp 0's clocks, all-warps-done, last load issued
 enum { kQkv = 0, kAttn = 1, kO = 2, kGu = 3, kDown = 4, kOpsPerLayer = 5 };
 
@@ -328,6 +329,7 @@ struct AttnSplit {
   int nt, I, G, heads, P;
   __device__ __forceinline__ AttnSplit(int heads_, int nt_, int G_) : nt(nt_), I(heads_ * nt_), G(G_), heads(heads_) {
     P = G >= heads ? G / heads : 0;
+    if (P > kMaxParts) P = kMaxParts;
   }
   __device__ __forceinline__ void range(int cta, int& i0, int& i1) const {
     if (P > 0) {
