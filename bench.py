@@ -532,12 +532,16 @@ def side_benchmarks(mld, torch, peaks):
     e1.record()
     torch.cuda.synchronize()
     us1 = e0.elapsed_time(e1) * 1e3 / 100
+    g1 = time_in_graph(torch, lambda i: plan.run(dx, dw, dsc, dy, 1, bias=db), 256)
     plan.close()
+    gpu1 = {"us_per_launch": us1, "GBps": algo1 / us1 / 1e3, "timed_with": "100 launches from the host, CUDA events",
+            "note": "4 MB of weights stay in L2 between launches: not an HBM figure"}
+    if g1 is not None:
+        gpu1["in_cuda_graph"] = {"launches_per_replay": 256, "median_us_per_launch": g1[0], "best_us_per_launch": g1[1]}
     out["fc_gemv_int8_f32"] = {"workload": "INT8 per-channel GEMV N=2048 K=2048, fp32 activations + bias, seed 0",
                                "algorithmic_bytes": algo1,
                                "cpu": {"us": t_cpu * 1e6, "GBps": algo1 / t_cpu / 1e9, "cores": cores, "kind": "port"},
-                               "gpu": {"us_per_launch": us1, "GBps": algo1 / us1 / 1e3,
-                                       "note": "4 MB of weights stay in L2 between launches: not an HBM figure"}}
+                               "gpu": gpu1}
 
     # ---- weight conversion: quantise + pack a 16384 x 2048 matrix (GPU kernels) next to the CPU restatement
     # (quantiser on all cores; the rearrangement is the reference's single-threaded loop order)
