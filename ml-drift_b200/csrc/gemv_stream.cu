@@ -14,6 +14,8 @@
 //    completing on one mbarrier per stage;
 //  * eight consumer warps dequantise in registers and feed m16n8k16 tensor-core
 //    MMAs (weights as the 16-row operand, tokens as columns), fp32 accumulate;
+//    4-bit weights with a single token go through integer MMAs on 16-bit
+//    fixed-point activations instead (the DIGITS form below);
 //  * with programmatic dependent launch the next GEMV starts streaming its
 //    weights while this one drains; only the activation loads wait for the
 //    predecessor.
@@ -187,12 +189,13 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 // W: weight boxes per stage (strip width up to W * 128 bytes per pass).
 // MONE: single-token launch (only token column 0 is kept).
 // DIGITS (4-bit weights, one token, a one-token activation vector): integer MMAs instead.  The whole
-// activation vector is fetched once, and every warp turns the units of 32 inputs it will meet (one per
-// stage) into 16-bit fixed point with a power-of-two scale of their own, x ~ s (256 hi + lo), before the
-// first stage.  One m16n8k32 u8 x s8 MMA per 16 outputs then multiplies the nibbles, as bytes that hold
-// two outputs each, by the two digits (columns 0 and 1): 8 MMAs per stage and warp where the fp16 form
-// needs 18, and two byte permutes per MMA instead of shifts and masks.  Everything is exact in int32;
-// the error is that of the fixed point, at most 2^-16 of the unit's largest input per input.
+// activation vector is fetched once, and before the first stage is consumed the warps turn every unit
+// of 32 inputs into 16-bit fixed point with a power-of-two scale of its own, x ~ s (256 hi + lo).  One
+// m16n8k32 u8 x s8 MMA per 16 outputs and unit then multiplies the nibbles, as the bytes of the reference
+// layout that hold two outputs each, by the unit's two digits; four units share accumulators (their
+// digits sit in different B columns), so a stage costs 64 MMAs where the fp16 form needs 144, with two
+// byte permutes per MMA instead of shifts and masks.  Everything is exact in int32; the error is that
+// of the fixed point, at most 2^-16 of the unit's largest input per input.
 template <int BITS, int W, bool SUBNORMAL, bool MONE, bool DIGITS = false>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
     fc_strip_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
