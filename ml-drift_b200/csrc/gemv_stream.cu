@@ -395,6 +395,12 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
         uint32_t sbits = (__float_as_uint(amax * (1.0f / 32512.0f)) + 0x007FFFFFu) & 0x7F800000u;
         if (sbits < (16u << 23)) sbits = 16u << 23;
         const float inv = __uint_as_float((254u << 23) - sbits);
+        // an infinity or NaN among the unit's inputs (an all-ones fp16 exponent) has no digits: the unit's scale
+        // becomes NaN, and with it every output, as the reference arithmetic would make most of them
+        const auto non_finite = [](uint32_t w) { return (w & 0x7C00u) == 0x7C00u || (w & 0x7C000000u) == 0x7C000000u; };
+        unsigned bad = (non_finite(v.x) || non_finite(v.y) || non_finite(v.z) || non_finite(v.w)) ? 1u : 0u;
+        bad |= __shfl_xor_sync(0xffffffffu, bad, 1);
+        bad |= __shfl_xor_sync(0xffffffffu, bad, 2);
         // z = round(x / s) + 128 in the low 16 bits of the sum's mantissa: byte 1 = high digit, byte 0 ^ 0x80 = low digit
         uint32_t z[8];
 #pragma unroll
@@ -417,7 +423,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, W <= 2 ? 2 : 1)
           uint32_t* ud = reinterpret_cast<uint32_t*>(xdig + (size_t)u * 64);
           *reinterpret_cast<uint2*>(ud + 2 * q) = make_uint2(hiw[0], hiw[1]);
           *reinterpret_cast<uint2*>(ud + 8 + 2 * q) = make_uint2(low[0], low[1]);
-          if (q == 0) xmeta[u] = make_uint2(sbits, static_cast<uint32_t>(8 * isum));  // the nibbles carry the weights + 8
+          if (q == 0) xmeta[u] = make_uint2(bad ? 0x7FC00000u : sbits, static_cast<uint32_t>(8 * isum));  // (nibbles = weights + 8)
         }
       }
     }

@@ -286,6 +286,10 @@ def test_one_token_int4_digit_route(mld, oracle, K, N, block, outliers):
     assert _rel(exact, plain) <= 1e-3
     assert _rel(y, plain) <= 1e-3
     assert _rel(y, exact) <= 1e-3
+    if outliers:  # an infinity among the inputs must not come out as finite numbers
+        x[0, K // 2] = np.inf
+        y = _run(mld, oracle, "F32F16", 4, x, packed, N, K, scale=s, mode=mode, G=G)
+        assert not np.isfinite(y).any()
 
 
 def test_row_major_single_token(mld, oracle):
